@@ -1,0 +1,103 @@
+/*
+ * strata_masonry_b200 -- C ABI of the B200 (sm_100a) dense GEMM path.
+ *
+ * The reference project (strata-masonry) exposes this path only as two executables,
+ * kernel_sm100a_dense_gemm_bf16 and kernel_sm100a_dense_gemm_nvfp4, each a single .cu
+ * with its own main().  This header declares the library those drivers sit on here;
+ * each entry point names the reference code it stands in for.
+ *
+ * Conventions: every function returns SMB_OK (0) or a negative smb_status; nothing
+ * calls exit() or throws across this boundary; smb_last_error() returns a thread-local
+ * message for the last failure.  Device entry points are stream-ordered and never
+ * synchronise; the caller owns all operand buffers.  `stream` is a cudaStream_t passed
+ * as void* (NULL = the default stream).  A missing GPU is an error, never a silent CPU
+ * path.
+ */
+#ifndef STRATA_MASONRY_B200_H_
+#define STRATA_MASONRY_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum smb_status {
+  SMB_OK = 0,
+  SMB_ERR_INVALID = -1,      /* bad shape, null pointer, misaligned pointer or stride */
+  SMB_ERR_UNSUPPORTED = -2,  /* valid request that this build cannot serve */
+  SMB_ERR_CUDA = -3,         /* a CUDA runtime / driver call failed */
+  SMB_ERR_DEVICE = -4,       /* a kernel reported a non-zero status word */
+  SMB_ERR_IO = -5,           /* file could not be written */
+  SMB_ERR_NOMEM = -6
+} smb_status;
+
+/* Library version, major * 1000 + minor. */
+int smb_version(void);
+
+/* Message describing the last error on the calling thread ("" if none). */
+const char* smb_last_error(void);
+
+/* ------------------------------------------------------------------------------------
+ * Input generators.  Bit-identical to the reference drivers' host fills; `index0` lets a
+ * caller generate a slab of a larger logical tensor (N-sharding) with the global indices.
+ * ---------------------------------------------------------------------------------- */
+
+/* BF16 fills 1..4 of the reference driver (fill_random_bf16, dense_gemm_bf16.cu:268-279;
+ * verifier fill(), dense_gemm_bf16_cpu_verifier.py:32-44), plus fills 5..7: a Gaussian
+ * stand-in (sum of twelve 16-bit uniform fields of a counter hash, mean 0, variance 1)
+ * scaled by 0.1, 0.05 and 1.0.  Element (r, c) of the [rows, cols] output takes the value
+ * of flat index  index0 + r * index_row_stride + c * index_col_stride  (32-bit wrap-around
+ * as in the reference): A[M,K] uses strides (K, 1) and seed 1; BT[N,K], the transpose of the
+ * reference's B[K,N], uses strides (1, N) and seed 2.
+ * `out` is device memory, row-major, `ld` elements between rows. */
+int smb_fill_bf16_device(uint16_t* out, int64_t rows, int64_t cols, int64_t ld, uint64_t index0,
+                         uint64_t index_row_stride, uint64_t index_col_stride, int fill,
+                         uint32_t seed, void* stream);
+/* Same on the host (single thread; for tests and small shapes). */
+int smb_fill_bf16_host(uint16_t* out, int64_t rows, int64_t cols, int64_t ld, uint64_t index0,
+                       uint64_t index_row_stride, uint64_t index_col_stride, int fill,
+                       uint32_t seed);
+
+/* ------------------------------------------------------------------------------------
+ * Dense BF16 GEMM:  D[M,N] = bf16_rne( sum_k A[M,K] * BT[N,K] ), FP32 accumulate.
+ * Stands in for dense_gemm_bf16_k0_impl + run_one_impl
+ * (src/kernels/gemm/sm100a/dense_gemm_bf16.cu:86-234, :281-445).
+ * A is row-major [M,K] (lda elements between rows), BT row-major [N,K] (ldb), D row-major
+ * [M,N] (ldd).  Any M, N >= 1; K >= 8 and K % 8 == 0 (rows of A and BT must start on
+ * 16-byte boundaries: lda % 8 == 0, ldb % 8 == 0, base pointers 16-byte aligned).
+ * ---------------------------------------------------------------------------------- */
+typedef struct smb_bf16_plan smb_bf16_plan;
+
+/* Encode tensor maps and pick the tile configuration for one (A, BT, D) buffer set on the
+ * current device.  `flags`: 0, or SMB_FLAG_* below. */
+int smb_bf16_plan_create(smb_bf16_plan** plan, const void* a, const void* bt, void* d, int M, int N,
+                         int K, int64_t lda, int64_t ldb, int64_t ldd, unsigned flags);
+/* Launch the GEMM on `stream`.  Returns after enqueueing. */
+int smb_bf16_plan_run(smb_bf16_plan* plan, void* stream);
+/* Synchronise `stream` and translate the kernels' status word: SMB_OK, or SMB_ERR_DEVICE with
+ * the role that gave up in smb_last_error(). */
+int smb_bf16_plan_check(smb_bf16_plan* plan, void* stream);
+int smb_bf16_plan_destroy(smb_bf16_plan* plan);
+/* Tuning knobs (tests and sweeps): raster group height in tiles, cap on clusters. */
+int smb_bf16_plan_tune(smb_bf16_plan* plan, int group_m, int max_clusters);
+
+/* One-shot convenience: plan + run + check + destroy on device pointers. */
+int smb_dense_gemm_bf16(const void* a, const void* bt, void* d, int M, int N, int K, void* stream);
+
+/* Host-buffer entry point, what a caller without device memory of its own uses:
+ * allocates, copies A and BT to the device, runs, copies D back.  The reference driver does
+ * these steps inline (dense_gemm_bf16.cu:293-307, :401-404). */
+int smb_dense_gemm_bf16_host(const uint16_t* a, const uint16_t* bt, uint16_t* d, int M, int N, int K);
+
+#define SMB_FLAG_NONE 0u
+#define SMB_FLAG_FORCE_PLAIN_STORE 1u /* use the non-TMA epilogue even when D is aligned */
+#define SMB_FLAG_TILE_N_128 2u        /* force 256 x 128 tiles */
+#define SMB_FLAG_TILE_N_64 4u         /* force 256 x 64 tiles */
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* STRATA_MASONRY_B200_H_ */

@@ -1,0 +1,83 @@
+"""ctypes prototypes for every symbol declared in include/strata_masonry_b200.h.
+
+``lib()`` loads the shared library built by build.py (and fails loudly if it is missing:
+there is no fallback implementation).  ``DECLARED`` lists (name, restype, argtypes) for each
+exported function; the CPU test suite checks that the library exports all of them.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "lib" / "libstrata_masonry_b200.so"
+
+SMB_OK = 0
+SMB_ERR_INVALID = -1
+SMB_ERR_UNSUPPORTED = -2
+SMB_ERR_CUDA = -3
+SMB_ERR_DEVICE = -4
+SMB_ERR_IO = -5
+SMB_ERR_NOMEM = -6
+
+FLAG_NONE = 0
+FLAG_FORCE_PLAIN_STORE = 1
+FLAG_TILE_N_128 = 2
+FLAG_TILE_N_64 = 4
+
+_vp = C.c_void_p
+_i = C.c_int
+_i64 = C.c_int64
+_u64 = C.c_uint64
+_u32 = C.c_uint32
+
+DECLARED = [
+    ("smb_version", _i, []),
+    ("smb_last_error", C.c_char_p, []),
+    ("smb_fill_bf16_device", _i, [_vp, _i64, _i64, _i64, _u64, _u64, _u64, _i, _u32, _vp]),
+    ("smb_fill_bf16_host", _i, [_vp, _i64, _i64, _i64, _u64, _u64, _u64, _i, _u32]),
+    ("smb_bf16_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, C.c_uint]),
+    ("smb_bf16_plan_run", _i, [_vp, _vp]),
+    ("smb_bf16_plan_check", _i, [_vp, _vp]),
+    ("smb_bf16_plan_destroy", _i, [_vp]),
+    ("smb_bf16_plan_tune", _i, [_vp, _i, _i]),
+    ("smb_dense_gemm_bf16", _i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    ("smb_dense_gemm_bf16_host", _i, [_vp, _vp, _vp, _i, _i, _i]),
+]
+
+
+class SmbError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"strata_masonry_b200 error {code}: {message}")
+        self.code = code
+        self.message = message
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Load the library once and attach prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python strata-masonry_b200/build.py` "
+            "(there is no CPU fallback for this path)")
+    handle = C.CDLL(str(LIB_PATH))
+    for name, restype, argtypes in DECLARED:
+        fn = getattr(handle, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = handle
+    return handle
+
+
+def last_error() -> str:
+    return lib().smb_last_error().decode("utf-8", "replace")
+
+
+def check(code: int) -> None:
+    if code != SMB_OK:
+        raise SmbError(code, last_error())

@@ -1,0 +1,180 @@
+// C-ABI of the BF16 GEMM: plans (tensor maps + tile choice), launch, status check, and the
+// host-buffer convenience path.  Host-side counterpart of run_one_impl in the reference
+// (src/kernels/gemm/sm100a/dense_gemm_bf16.cu:281-445).
+#include <new>
+
+#include "gemm_common.cuh"
+
+namespace smb {
+const char* last_error_message();
+void clear_error();
+const char* device_status_name(int code);
+}  // namespace smb
+
+using namespace smb;
+
+struct smb_bf16_plan {
+  Bf16Launch launch;
+  int* status_dev;
+};
+
+extern "C" int smb_version(void) { return 1000; }
+
+extern "C" const char* smb_last_error(void) { return last_error_message(); }
+
+namespace smb {
+const char* device_status_name(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case 101: return "load role timed out waiting for a free ring slot";
+    case 102: return "MMA role timed out waiting for a filled ring slot";
+    case 103: return "MMA role timed out waiting for a drained accumulator";
+    case 104: return "epilogue role timed out waiting for an accumulator";
+    case 105: return "a role timed out waiting for the tile scheduler";
+    case 106: return "split-K fix-up timed out";
+    case 107: return "bounded-wait probe ran out of budget";
+    default: return "unknown device status";
+  }
+}
+}  // namespace smb
+
+extern "C" int smb_bf16_plan_create(smb_bf16_plan** out, const void* a, const void* bt, void* d,
+                                    int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd,
+                                    unsigned flags) {
+  if (out == nullptr) return set_error(SMB_ERR_INVALID, "plan: null output handle");
+  *out = nullptr;
+  if (a == nullptr || bt == nullptr || d == nullptr)
+    return set_error(SMB_ERR_INVALID, "plan: null operand pointer");
+  if (M <= 0 || N <= 0 || K <= 0)
+    return set_error(SMB_ERR_INVALID, "plan: dimensions must be positive (M=%d N=%d K=%d)", M, N, K);
+  if (K % 8 != 0)
+    return set_error(SMB_ERR_UNSUPPORTED, "plan: K=%d must be a multiple of 8 (16-byte operand rows)", K);
+  if (lda < K || ldb < K || ldd < N)
+    return set_error(SMB_ERR_INVALID, "plan: leading dimension smaller than the row length");
+  if (lda % 8 != 0 || ldb % 8 != 0)
+    return set_error(SMB_ERR_INVALID, "plan: lda and ldb must be multiples of 8 elements");
+  if (reinterpret_cast<uintptr_t>(d) % 2 != 0)
+    return set_error(SMB_ERR_INVALID, "plan: D is not 2-byte aligned");
+
+  smb_bf16_plan* p = new (std::nothrow) smb_bf16_plan();
+  if (p == nullptr) return set_error(SMB_ERR_NOMEM, "plan: out of host memory");
+  Bf16Launch& L = p->launch;
+  L.M = M;
+  L.N = N;
+  L.K = K;
+  L.tile_n = bf16_tile_n(N);
+  if (flags & SMB_FLAG_TILE_N_128) L.tile_n = 128;
+  if (flags & SMB_FLAG_TILE_N_64) L.tile_n = 64;
+  L.group_m = 0;
+  L.max_clusters = 0;
+  L.d = d;
+  L.ldd = static_cast<int>(ldd);
+  L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
+                !(flags & SMB_FLAG_FORCE_PLAIN_STORE);
+  p->status_dev = nullptr;
+
+  int rc = encode_tmap_2d(&L.tmap_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda * 2, 128, 64, true);
+  if (rc == SMB_OK)
+    rc = encode_tmap_2d(&L.tmap_b, bt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb * 2,
+                        L.tile_n / 2, 64, true);
+  if (rc == SMB_OK) {
+    if (L.tma_store) {
+      rc = encode_tmap_2d(&L.tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldd * 2, 32, 64, true);
+    } else {
+      L.tmap_d = L.tmap_a;  // never dereferenced by the plain-store kernel
+    }
+  }
+  if (rc == SMB_OK) {
+    cudaError_t e = cudaMalloc(&p->status_dev, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(p->status_dev, 0, sizeof(int));
+    if (e != cudaSuccess) rc = set_cuda_error(e, "plan: status word allocation");
+  }
+  if (rc != SMB_OK) {
+    if (p->status_dev) cudaFree(p->status_dev);
+    delete p;
+    return rc;
+  }
+  L.status = p->status_dev;
+  *out = p;
+  return SMB_OK;
+}
+
+extern "C" int smb_bf16_plan_tune(smb_bf16_plan* plan, int group_m, int max_clusters) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "plan: null handle");
+  if (group_m < 0 || max_clusters < 0) return set_error(SMB_ERR_INVALID, "plan: negative tuning value");
+  plan->launch.group_m = group_m;
+  plan->launch.max_clusters = max_clusters;
+  return SMB_OK;
+}
+
+extern "C" int smb_bf16_plan_run(smb_bf16_plan* plan, void* stream) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "plan: null handle");
+  return bf16_launch(plan->launch, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int smb_bf16_plan_check(smb_bf16_plan* plan, void* stream) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "plan: null handle");
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return set_cuda_error(e, "plan check: stream synchronize");
+  int status = 0;
+  e = cudaMemcpy(&status, plan->status_dev, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return set_cuda_error(e, "plan check: status read");
+  if (status != 0) {
+    cudaMemset(plan->status_dev, 0, sizeof(int));
+    return set_error(SMB_ERR_DEVICE, "bf16 GEMM kernel reported status %d: %s", status,
+                     device_status_name(status));
+  }
+  return SMB_OK;
+}
+
+extern "C" int smb_bf16_plan_destroy(smb_bf16_plan* plan) {
+  if (plan == nullptr) return SMB_OK;
+  if (plan->status_dev) cudaFree(plan->status_dev);
+  delete plan;
+  return SMB_OK;
+}
+
+extern "C" int smb_dense_gemm_bf16(const void* a, const void* bt, void* d, int M, int N, int K,
+                                   void* stream) {
+  smb_bf16_plan* plan = nullptr;
+  int rc = smb_bf16_plan_create(&plan, a, bt, d, M, N, K, K, K, N, SMB_FLAG_NONE);
+  if (rc != SMB_OK) return rc;
+  rc = smb_bf16_plan_run(plan, stream);
+  if (rc == SMB_OK) rc = smb_bf16_plan_check(plan, stream);
+  smb_bf16_plan_destroy(plan);
+  return rc;
+}
+
+extern "C" int smb_dense_gemm_bf16_host(const uint16_t* a, const uint16_t* bt, uint16_t* d, int M,
+                                        int N, int K) {
+  if (a == nullptr || bt == nullptr || d == nullptr)
+    return set_error(SMB_ERR_INVALID, "host GEMM: null operand pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return set_error(SMB_ERR_INVALID, "host GEMM: bad dimensions");
+  const size_t a_bytes = static_cast<size_t>(M) * K * 2;
+  const size_t b_bytes = static_cast<size_t>(N) * K * 2;
+  // Pad rows of D to 8 elements so that the TMA-store epilogue is always usable.
+  const int64_t ldd = (static_cast<int64_t>(N) + 7) / 8 * 8;
+  const size_t d_bytes = static_cast<size_t>(M) * ldd * 2;
+  void *da = nullptr, *db = nullptr, *dd = nullptr;
+  int rc = SMB_OK;
+  cudaError_t e = cudaMalloc(&da, a_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&db, b_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&dd, d_bytes);
+  if (e == cudaSuccess) e = cudaMemcpy(da, a, a_bytes, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(db, bt, b_bytes, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) rc = set_cuda_error(e, "host GEMM: allocation or upload");
+  smb_bf16_plan* plan = nullptr;
+  if (rc == SMB_OK) rc = smb_bf16_plan_create(&plan, da, db, dd, M, N, K, K, K, ldd, SMB_FLAG_NONE);
+  if (rc == SMB_OK) rc = smb_bf16_plan_run(plan, nullptr);
+  if (rc == SMB_OK) rc = smb_bf16_plan_check(plan, nullptr);
+  if (rc == SMB_OK) {
+    e = cudaMemcpy2D(d, static_cast<size_t>(N) * 2, dd, static_cast<size_t>(ldd) * 2,
+                     static_cast<size_t>(N) * 2, M, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) rc = set_cuda_error(e, "host GEMM: download");
+  }
+  smb_bf16_plan_destroy(plan);
+  cudaFree(da);
+  cudaFree(db);
+  cudaFree(dd);
+  return rc;
+}

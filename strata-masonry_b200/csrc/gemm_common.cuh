@@ -1,0 +1,60 @@
+// Shared between the kernels' translation units and the C-ABI layer: error plumbing,
+// launch descriptors, the tile raster, tensor-map encoding.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/strata_masonry_b200.h"
+
+namespace smb {
+
+// --------------------------------------------------------------------------- errors
+// Record a message for smb_last_error() (thread-local) and return `code`.
+int set_error(int code, const char* fmt, ...);
+int set_cuda_error(cudaError_t e, const char* what);
+
+// --------------------------------------------------------------------------- raster
+// Map a flat tile index onto (tile_m, tile_n).  Tiles are walked in groups of `group_m`
+// tile rows; inside a group the M index runs fastest.  With ~74 clusters working on
+// consecutive indices, one wave touches about group_m A panels and 74 / group_m B panels
+// at the same K position, so both operands are shared through L2.  (The reference gets
+// the same effect from its blocked raster, dense_gemm_nvfp4.cu:358-434.)
+__host__ __device__ inline void tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& tm,
+                                            int& tn) {
+  const int per_group = group_m * tiles_n;
+  const int g = t / per_group;
+  const int first_m = g * group_m;
+  const int rows = (tiles_m - first_m) < group_m ? (tiles_m - first_m) : group_m;
+  const int r = t - g * per_group;
+  tm = first_m + r % rows;
+  tn = r / rows;
+}
+
+// --------------------------------------------------------------------------- tensor maps
+// 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements, `ld_bytes` between rows,
+// copied in boxes of [box_rows, box_cols].  `swizzle128`: 128-byte shared-memory swizzle
+// (box_cols * elem_bytes must then be 128).  Out-of-range elements read as zero.
+// Counterpart of make_tma_2d_tiled (reference src/primitives/23_tma_tensormap.cuh:43-64).
+int encode_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes,
+                   uint64_t rows, uint64_t cols, uint64_t ld_bytes, uint32_t box_rows,
+                   uint32_t box_cols, bool swizzle128);
+
+// --------------------------------------------------------------------------- bf16 launch
+struct Bf16Launch {
+  CUtensorMap tmap_a, tmap_b, tmap_d;
+  int M, N, K;
+  int tile_n;        // 64, 128 or 256
+  bool tma_store;    // false: D rows are not 16-byte aligned, use plain stores
+  int group_m;       // raster group height (0 = default)
+  int max_clusters;  // 0 = as many as fit
+  void* d;
+  int ldd;
+  int* status;       // device status word, may be null
+};
+int bf16_tile_n(int N);
+int bf16_launch(const Bf16Launch& L, cudaStream_t stream);
+
+}  // namespace smb

@@ -1,0 +1,87 @@
+// Error plumbing and tensor-map encoding shared by every entry point.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "gemm_common.cuh"
+
+namespace smb {
+
+namespace {
+thread_local char g_error[512] = {0};
+}
+
+const char* last_error_message() { return g_error; }
+void clear_error() { g_error[0] = 0; }
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int set_cuda_error(cudaError_t e, const char* what) {
+  snprintf(g_error, sizeof(g_error), "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+  return SMB_ERR_CUDA;
+}
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so that the library links against the
+// CUDA runtime only and still loads on a machine without a driver.
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn != nullptr) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || sym == nullptr) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  return fn;
+}
+
+}  // namespace
+
+int encode_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes,
+                   uint64_t rows, uint64_t cols, uint64_t ld_bytes, uint32_t box_rows,
+                   uint32_t box_cols, bool swizzle128) {
+  if (base == nullptr) return set_error(SMB_ERR_INVALID, "tensor map: null base pointer");
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0)
+    return set_error(SMB_ERR_INVALID, "tensor map: base pointer %p is not 16-byte aligned", base);
+  if (ld_bytes % 16 != 0)
+    return set_error(SMB_ERR_INVALID, "tensor map: row pitch %llu bytes is not a multiple of 16",
+                     static_cast<unsigned long long>(ld_bytes));
+  if (box_rows == 0 || box_rows > 256 || box_cols == 0 || box_cols > 256)
+    return set_error(SMB_ERR_INVALID, "tensor map: box %u x %u out of range", box_rows, box_cols);
+  if ((static_cast<uint64_t>(box_cols) * elem_bytes) % 16 != 0)
+    return set_error(SMB_ERR_INVALID, "tensor map: box row of %u bytes is not a multiple of 16",
+                     box_cols * elem_bytes);
+  if (swizzle128 && box_cols * elem_bytes != 128)
+    return set_error(SMB_ERR_INVALID, "tensor map: 128-byte swizzle needs 128-byte box rows");
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr)
+    return set_error(SMB_ERR_CUDA, "cuTensorMapEncodeTiled is not available (no CUDA driver?)");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {ld_bytes};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(SMB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return SMB_OK;
+}
+
+}  // namespace smb
