@@ -80,8 +80,17 @@ int smb_bf16_plan_run(smb_bf16_plan* plan, void* stream);
  * the role that gave up in smb_last_error(). */
 int smb_bf16_plan_check(smb_bf16_plan* plan, void* stream);
 int smb_bf16_plan_destroy(smb_bf16_plan* plan);
-/* Tuning knobs (tests and sweeps): raster group height in tiles, cap on clusters. */
+/* Tuning knobs (tests and sweeps): raster group height in tiles (0 = default), cap on
+ * clusters (0 = all that fit). */
 int smb_bf16_plan_tune(smb_bf16_plan* plan, int group_m, int max_clusters);
+
+/* Role timers (the reference's counterpart is its WARP_PROF region markers, of which only a
+ * no-op stub ships: src/primitives/_warp_prof_noop.cuh).  `counters` is device memory of
+ * 8 int64 per CTA (2 CTAs per cluster, at most 2 * SM count CTAs), or NULL to switch the
+ * timers off.  Per CTA: [0] load role cycles waiting for a free slot, [1] load role total,
+ * [2] MMA role waiting for data, [3] MMA role waiting for an accumulator, [4] MMA role
+ * total, [5] epilogue waiting for an accumulator, [6] epilogue total, [7] tiles done. */
+int smb_bf16_plan_set_profile(smb_bf16_plan* plan, long long* counters);
 
 /* One-shot convenience: plan + run + check + destroy on device pointers. */
 int smb_dense_gemm_bf16(const void* a, const void* bt, void* d, int M, int N, int K, void* stream);
@@ -95,6 +104,8 @@ int smb_dense_gemm_bf16_host(const uint16_t* a, const uint16_t* bt, uint16_t* d,
 #define SMB_FLAG_FORCE_PLAIN_STORE 1u /* use the non-TMA epilogue even when D is aligned */
 #define SMB_FLAG_TILE_N_128 2u        /* force 256 x 128 tiles */
 #define SMB_FLAG_TILE_N_64 4u         /* force 256 x 64 tiles */
+#define SMB_FLAG_TILE_N_256 8u        /* force 256 x 256 tiles, two accumulator banks */
+#define SMB_FLAG_TILE_N_512 16u       /* force 256 x 512 tiles, one accumulator set */
 
 #ifdef __cplusplus
 }

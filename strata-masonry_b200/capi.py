@@ -24,6 +24,8 @@ FLAG_NONE = 0
 FLAG_FORCE_PLAIN_STORE = 1
 FLAG_TILE_N_128 = 2
 FLAG_TILE_N_64 = 4
+FLAG_TILE_N_256 = 8
+FLAG_TILE_N_512 = 16
 
 _vp = C.c_void_p
 _i = C.c_int
@@ -41,6 +43,7 @@ DECLARED = [
     ("smb_bf16_plan_check", _i, [_vp, _vp]),
     ("smb_bf16_plan_destroy", _i, [_vp]),
     ("smb_bf16_plan_tune", _i, [_vp, _i, _i]),
+    ("smb_bf16_plan_set_profile", _i, [_vp, _vp]),
     ("smb_dense_gemm_bf16", _i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     ("smb_dense_gemm_bf16_host", _i, [_vp, _vp, _vp, _i, _i, _i]),
 ]

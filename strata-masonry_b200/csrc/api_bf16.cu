@@ -62,11 +62,14 @@ extern "C" int smb_bf16_plan_create(smb_bf16_plan** out, const void* a, const vo
   L.M = M;
   L.N = N;
   L.K = K;
-  L.tile_n = bf16_tile_n(N);
-  if (flags & SMB_FLAG_TILE_N_128) L.tile_n = 128;
-  if (flags & SMB_FLAG_TILE_N_64) L.tile_n = 64;
+  bf16_pick_tile(M, N, K, &L.tile_n, &L.sub_blocks);
+  if (flags & SMB_FLAG_TILE_N_512) { L.tile_n = 256; L.sub_blocks = 2; }
+  if (flags & SMB_FLAG_TILE_N_256) { L.tile_n = 256; L.sub_blocks = 1; }
+  if (flags & SMB_FLAG_TILE_N_128) { L.tile_n = 128; L.sub_blocks = 1; }
+  if (flags & SMB_FLAG_TILE_N_64) { L.tile_n = 64; L.sub_blocks = 1; }
   L.group_m = 0;
   L.max_clusters = 0;
+  L.prof = nullptr;
   L.d = d;
   L.ldd = static_cast<int>(ldd);
   L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
@@ -104,6 +107,12 @@ extern "C" int smb_bf16_plan_tune(smb_bf16_plan* plan, int group_m, int max_clus
   if (group_m < 0 || max_clusters < 0) return set_error(SMB_ERR_INVALID, "plan: negative tuning value");
   plan->launch.group_m = group_m;
   plan->launch.max_clusters = max_clusters;
+  return SMB_OK;
+}
+
+extern "C" int smb_bf16_plan_set_profile(smb_bf16_plan* plan, long long* counters) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "plan: null handle");
+  plan->launch.prof = counters;
   return SMB_OK;
 }
 

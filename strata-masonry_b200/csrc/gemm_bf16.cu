@@ -4,19 +4,25 @@
 // (src/kernels/gemm/sm100a/dense_gemm_bf16.cu:86-234) and of the warp-role bodies it
 // composes (blocks/88 load, blocks/90 MMA, blocks/93 epilogue, blocks/97 scheduler).
 // Differences by design: M, N and K are run-time values with edge predication (the
-// reference takes K as a template value and rejects ragged shapes), the ring is 6 deep,
-// the epilogue stages through 128-byte-swizzled shared memory with one TMA store chain
-// per warp (no CTA-wide barrier), every wait is bounded, and tiles are walked in a
-// grouped raster so that the clusters of one wave share A and B panels in L2.
+// reference takes K as a template value and rejects ragged shapes); the epilogue stages
+// through 128-byte-swizzled shared memory with one TMA store chain per warp (no CTA-wide
+// barrier); every wait is bounded; tiles are walked in a grouped raster so that the
+// clusters of one wave share A and B panels in L2; and for long K a 256 x 512 tile is
+// used, because on B200 the L2 sector rate, not the tensor pipe, limits a 256 x 256 tile
+// fed without multicast loads.
 //
-// One cluster = 2 CTAs = one 256 x TN output tile (TN = 256, 128 or 64):
-//   CTA r loads A rows [m0 + 128 r, +128) and BT rows [n0 + TN/2 r, +TN/2) per 64-wide K
-//   block; the leader CTA (rank 0) issues tcgen05.mma.cta_group::2 with M = 256, N = TN,
-//   K = 16; CTA r ends up with rows [m0 + 128 r, +128) x TN fp32 in its tensor memory.
-// Warp roles per CTA (192 threads): warp 0 TMA producer, warp 1 MMA issue + TMEM owner,
-// warps 2-5 epilogue (warp w owns TMEM lanes 32 (w % 4) .. +31).
-// Tensor memory: two accumulator banks of TN columns (512 columns allocated), so the
-// epilogue of tile i overlaps the main loop of tile i + 1.
+// One cluster = 2 CTAs = one output tile of 256 x (NB * TN), TN in {256, 128, 64}, NB in {1, 2}:
+//   CTA r loads A rows [m0 + 128 r, +128) and, per N sub-block h, BT rows
+//   [n0 + h TN + TN/2 r, +TN/2) for each 64-wide K block; the leader CTA (rank 0) issues
+//   tcgen05.mma.cta_group::2 with M = 256, N = TN, K = 16; CTA r ends up with rows
+//   [m0 + 128 r, +128) of the tile as fp32 in its tensor memory.
+// Tensor memory (512 columns) holds two accumulator slots of up to 256 columns:
+//   NB = 1: the slots are two banks, the epilogue of tile i overlaps the main loop of i + 1;
+//   NB = 2: the slots are the two N halves of one tile; the MMA role restarts half h of the
+//           next tile as soon as the epilogue has drained half h.
+// Warp roles per CTA (320 threads): warp 0 TMA producer, warp 1 MMA issue + TMEM owner,
+// warps 2-9 epilogue (warp w reads TMEM lanes 32 (w % 4) .. +31; warps 2-5 take the first
+// half of a slot's columns / slot 0, warps 6-9 the second half / slot 1).
 #include "gemm_common.cuh"
 #include "ptx.cuh"
 
@@ -26,24 +32,34 @@ namespace bf16k {
 
 constexpr int kBlockM = 128;          // rows of A per CTA
 constexpr int kBlockK = 64;           // K elements per stage (= 128 bytes per row)
-constexpr int kStages = 6;
-constexpr int kThreads = 192;
-constexpr int kEpiWarps = 4;
+constexpr int kThreads = 320;
+constexpr int kEpiWarps = 8;
 constexpr int kStoreCols = 64;        // columns per TMA store box (= 128 bytes per row)
 constexpr int kStoreBufBytes = 32 * kStoreCols * 2;   // one warp's 32 x 64 bf16 box
-constexpr int kStoreBufsPerWarp = 2;
 constexpr int kABytes = kBlockM * kBlockK * 2;        // 16 KiB
 constexpr int kTmemCols = 512;
+constexpr int kRingBudget = 192 * 1024;
 
-template <int TN>
-struct Smem {
-  static constexpr int kBBytes = (TN / 2) * kBlockK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;
+template <int TN, int NB>
+struct Cfg {
+  static_assert(TN == 64 || TN == 128 || TN == 256, "tile width");
+  static_assert(NB == 1 || (NB == 2 && TN == 256), "two sub-blocks only at full width");
+  static constexpr int kBBytes = (TN / 2) * kBlockK * 2;         // one sub-block, one CTA
+  static constexpr int kStageBytes = kABytes + NB * kBBytes;
+  static constexpr int kStages = kRingBudget / kStageBytes;      // 6, 8, 9 or 4
   static constexpr int kRingBytes = kStages * kStageBytes;
-  static constexpr int kStoreBytes = kEpiWarps * kStoreBufsPerWarp * kStoreBufBytes;
+  static constexpr int kStoreBytes = kEpiWarps * kStoreBufBytes;
   static constexpr int kBarrierBytes = 1024;
   // + 1024 so that the kernel can round the dynamic base up to a 1024-byte boundary.
   static constexpr int kTotal = 1024 + kRingBytes + kStoreBytes + kBarrierBytes;
+  static constexpr int kTileN = TN * NB;
+  // Columns of one accumulator slot are split between the two epilogue warp groups when
+  // there are at least 128 of them (each group then stores whole 64-column boxes).
+  static constexpr int kGroupsPerSlot = (NB == 2) ? 1 : (TN >= 128 ? 2 : 1);
+  static constexpr int kColsPerWarp = TN / kGroupsPerSlot;
+  static constexpr int kSlotReaders = 2 * 4 * kGroupsPerSlot;    // arrivals per drained slot
+  static_assert(kTotal <= 232448, "shared memory budget");
+  static_assert(kStages >= 2 && kStages <= 16, "ring depth");
 };
 
 struct Params {
@@ -53,26 +69,31 @@ struct Params {
   int ldd;            // elements between rows of D (used by the plain-store epilogue)
   uint16_t* d_ptr;    // D base (used by the plain-store epilogue)
   int* status;
+  long long* prof;    // optional: 8 cycle counters per CTA (see kProf* below), or null
 };
 
-template <int TN, bool kTmaStore>
+// Per-CTA role timers (cycles), written when Params::prof is set.
+enum { kProfLoadWait = 0, kProfLoadTotal, kProfMmaWaitFull, kProfMmaWaitAcc, kProfMmaTotal,
+       kProfEpiWait, kProfEpiTotal, kProfTiles, kProfCount };
+
+template <int TN, int NB, bool kTmaStore>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_d, const Params p) {
-  using S = Smem<TN>;
+  using C = Cfg<TN, NB>;
+  constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t ring_base = smem_base;
-  const uint32_t store_base = ring_base + S::kRingBytes;
-  const uint32_t bar_base = store_base + S::kStoreBytes;
+  const uint32_t store_base = ring_base + C::kRingBytes;
+  const uint32_t bar_base = store_base + C::kStoreBytes;
   // Barrier block: full[kStages], empty[kStages], acc_full[2], acc_empty[2], tmem slot.
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * kStages + 4);
-  const uint32_t abort_flag = tmem_slot + 8;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -84,14 +105,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar(s), 2);    // one arrive.expect_tx per CTA of the pair
+      mbar_init(full_bar(s), 1);    // the leader's arrive.expect_tx covers both CTAs' bytes
       mbar_init(empty_bar(s), 1);   // one tcgen05.commit
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full_bar(b), 1);                 // one tcgen05.commit
-      mbar_init(acc_empty_bar(b), 2 * kEpiWarps);    // every epilogue warp of both CTAs
+      mbar_init(acc_empty_bar(b), C::kSlotReaders);  // every epilogue warp that reads the slot
     }
-    asm volatile("st.shared.b32 [%0], %1;" ::"r"(abort_flag), "r"(0) : "memory");
     fence_mbar_init_cluster();
   }
   if (warp == 0 && lane == 0) {
@@ -117,29 +137,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      const bool prof = p.prof != nullptr;
+      long long waited = 0;
+      const long long t_begin = prof ? clock64() : 0;
       for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
-        const int row_b = tn * TN + static_cast<int>(rank) * (TN / 2);
+        const int row_b = tn * C::kTileN + static_cast<int>(rank) * (TN / 2);
         for (int kb = 0; kb < num_kb; ++kb) {
+          const long long w0 = prof ? clock64() : 0;
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
             report_status(p.status, kDevTimeoutProducer);
             ok = false;
             break;
           }
+          if (prof) waited += clock64() - w0;
           const uint32_t bar = leader_full0 + 8u * s;
-          const uint32_t dst_a = ring_base + s * S::kStageBytes;
-          const uint32_t dst_b = dst_a + kABytes;
-          mbar_arrive_expect_tx_cluster(bar, S::kStageBytes);
+          const uint32_t dst_a = ring_base + s * C::kStageBytes;
+          // Only the leader arms its barrier (for both CTAs' bytes); the peer's copies credit the
+          // same barrier and may land before or after the arming, which mbarrier tolerates.
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * C::kStageBytes);
           tma_load_2d_pair(dst_a, &tmap_a, bar, kb * kBlockK, row_a);
-          tma_load_2d_pair(dst_b, &tmap_b, bar, kb * kBlockK, row_b);
+#pragma unroll
+          for (int h = 0; h < NB; ++h) {
+            tma_load_2d_pair(dst_a + kABytes + h * C::kBBytes, &tmap_b, bar, kb * kBlockK,
+                             row_b + h * TN);
+          }
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
       }
       if (!ok) {
         // Give copies already in flight time to land before this CTA's shared memory goes away.
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+      if (prof) {
+        p.prof[blockIdx.x * kProfCount + kProfLoadWait] = waited;
+        p.prof[blockIdx.x * kProfCount + kProfLoadTotal] = clock64() - t_begin;
       }
     }
   } else if (warp == 1) {
@@ -150,129 +184,171 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t ph = 0;
       int local = 0;
       bool ok = true;
+      const bool prof = p.prof != nullptr;
+      long long wait_full = 0, wait_acc = 0;
+      const long long t_begin = prof ? clock64() : 0;
       for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++local) {
-        const int bank = local & 1;
-        const uint32_t use_parity = static_cast<uint32_t>(local >> 1) & 1u;
-        if (!mbar_wait(acc_empty_bar(bank), use_parity ^ 1u)) {
-          report_status(p.status, kDevTimeoutMmaAcc);
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(bank * TN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        // NB = 1: slot = bank (local & 1), used every second tile.  NB = 2: slots 0 and 1 are the
+        // two halves of every tile.
+        const int bank = (NB == 1) ? (local & 1) : 0;
+        const uint32_t use_parity =
+            static_cast<uint32_t>((NB == 1) ? (local >> 1) : local) & 1u;
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          const long long w0 = prof ? clock64() : 0;
           if (!mbar_wait(full_bar(s), ph)) {
             report_status(p.status, kDevTimeoutMmaFull);
             ok = false;
             break;
           }
+          if (prof) wait_full += clock64() - w0;
           tc_fence_after_sync();
-          const uint32_t a_addr = ring_base + s * S::kStageBytes;
+          const uint32_t a_addr = ring_base + s * C::kStageBytes;
           const uint64_t desc_a = make_smem_desc(a_addr, 1024, 16, kSwizzle128B);
-          const uint64_t desc_b = make_smem_desc(a_addr + kABytes, 1024, 16, kSwizzle128B);
 #pragma unroll
-          for (int k = 0; k < kBlockK / 16; ++k) {
-            // 16 bf16 = 32 bytes further along K inside the 128-byte swizzle row.
-            mma_bf16_ss<2>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc,
-                           (kb > 0 || k > 0) ? 1u : 0u);
+          for (int h = 0; h < NB; ++h) {
+            const int slot = (NB == 1) ? bank : h;
+            if (kb == 0) {
+              // The epilogue must have drained this slot (previous user) before it is overwritten.
+              const long long a0 = prof ? clock64() : 0;
+              if (!mbar_wait(acc_empty_bar(slot), use_parity ^ 1u)) {
+                report_status(p.status, kDevTimeoutMmaAcc);
+                ok = false;
+                break;
+              }
+              if (prof) wait_acc += clock64() - a0;
+              tc_fence_after_sync();
+            }
+            const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(slot * TN);
+            const uint64_t desc_b =
+                make_smem_desc(a_addr + kABytes + h * C::kBBytes, 1024, 16, kSwizzle128B);
+#pragma unroll
+            for (int k = 0; k < kBlockK / 16; ++k) {
+              // 16 bf16 = 32 bytes further along K inside the 128-byte swizzle row.
+              mma_bf16_ss<2>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc,
+                             (kb > 0 || k > 0) ? 1u : 0u);
+            }
           }
+          if (!ok) break;
           mma_commit_pair(empty_bar(s), 0x3);
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
         if (ok) mma_commit_pair(acc_full_bar(bank), 0x3);
       }
+      if (prof) {
+        p.prof[blockIdx.x * kProfCount + kProfMmaWaitFull] = wait_full;
+        p.prof[blockIdx.x * kProfCount + kProfMmaWaitAcc] = wait_acc;
+        p.prof[blockIdx.x * kProfCount + kProfMmaTotal] = clock64() - t_begin;
+        p.prof[blockIdx.x * kProfCount + kProfTiles] = local;
+      }
     }
   } else {
-    // ------------------------------------------------------------- epilogue (4 warps)
-    const int quarter = warp & 3;     // TMEM lane quarter this warp may read
-    const int epi = warp - 2;         // staging-buffer owner index
-    const uint32_t leader_acc_empty0 = mapa_u32(acc_empty_bar(0), 0);
-    const uint32_t my_bufs = store_base + epi * kStoreBufsPerWarp * kStoreBufBytes;
-    int local = 0;
-    int buf = 0;
-    bool ok = true;
-    for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++local) {
-      int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
-      const int bank = local & 1;
-      const uint32_t use_parity = static_cast<uint32_t>(local >> 1) & 1u;
-      if (!mbar_wait(acc_full_bar(bank), use_parity)) {
-        if (lane == 0) report_status(p.status, kDevTimeoutEpilogue);
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      const int row0 = tm * 256 + static_cast<int>(rank) * kBlockM + quarter * 32;
-      const int col0 = tn * TN;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                             static_cast<uint32_t>(bank * TN);
-#pragma unroll 1
-      for (int c = 0; c < TN / kStoreCols; ++c) {
-        uint32_t v0[32], v1[32];
-        tmem_ld_32x32b_x32(taddr + c * kStoreCols, v0);
-        tmem_ld_32x32b_x32(taddr + c * kStoreCols + 32, v1);
-        tmem_ld_wait();
-        if (c == TN / kStoreCols - 1) {
-          // Accumulator fully read: hand the bank back to the MMA role.
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8u * bank);
+    // ------------------------------------------------------------- epilogue (8 warps)
+    const int quarter = warp & 3;           // TMEM lane quarter this warp may read
+    const int group = (warp - 2) >> 2;      // 0: warps 2-5, 1: warps 6-9
+    const bool active = (NB == 2) || (group < C::kGroupsPerSlot);
+    if (active) {
+      const uint32_t leader_acc_empty0 = mapa_u32(acc_empty_bar(0), 0);
+      const uint32_t sbuf = store_base + (warp - 2) * kStoreBufBytes;
+      int local = 0;
+      bool ok = true;
+      const bool prof = p.prof != nullptr && warp == 2 && lane == 0;
+      long long waited = 0;
+      const long long t_begin = prof ? clock64() : 0;
+      for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++local) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+        const int bank = (NB == 1) ? (local & 1) : 0;
+        const int slot = (NB == 1) ? bank : group;
+        const uint32_t use_parity =
+            static_cast<uint32_t>((NB == 1) ? (local >> 1) : local) & 1u;
+        const long long w0 = prof ? clock64() : 0;
+        if (!mbar_wait(acc_full_bar(bank), use_parity)) {
+          if (lane == 0) report_status(p.status, kDevTimeoutEpilogue);
+          ok = false;
+          break;
         }
-        uint32_t packed[32];
+        if (prof) waited += clock64() - w0;
+        tc_fence_after_sync();
+        const int row0 = tm * 256 + static_cast<int>(rank) * kBlockM + quarter * 32;
+        // First column (in the tile and in tensor memory) this warp is responsible for.
+        const int tile_col = (NB == 1) ? group * C::kColsPerWarp : group * TN;
+        const int col0 = tn * C::kTileN + tile_col;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                               static_cast<uint32_t>((NB == 1) ? bank * TN + tile_col : tile_col);
+        constexpr int kChunks = C::kColsPerWarp / kStoreCols;
+        // Phase 1: pull this warp's whole share of the slot out of tensor memory, rounding to
+        // bf16 on the way (2 columns per register), and hand the slot back to the MMA role
+        // before any store is issued.  With 256 x 512 tiles the main loop of the next tile
+        // cannot start until this has happened, so nothing slow may sit in front of it.
+        uint32_t packed[C::kColsPerWarp / 2];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          packed[i] = pack_bf16x2(v0[2 * i], v0[2 * i + 1]);
-          packed[16 + i] = pack_bf16x2(v1[2 * i], v1[2 * i + 1]);
+        for (int g = 0; g < C::kColsPerWarp / 32; ++g) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + g * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) packed[g * 16 + i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
         }
-        const uint32_t sbuf = my_bufs + buf * kStoreBufBytes;
-        // The TMA store that last read this buffer must have finished reading it.
-        if (kTmaStore) {
-          if (lane == 0) bulk_wait_group_read<kStoreBufsPerWarp - 1>();
-        }
+        tc_fence_before_sync();
         __syncwarp();
-        // Row `lane` of the 32 x 64 box; 16-byte chunk j goes to chunk (j ^ (lane & 7)):
-        // the 128-byte swizzle the store tensor map expects, and conflict-free.
+        if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8u * slot);
+        // Phase 2: stage 32 x 64 boxes through shared memory and store them.
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t dst = sbuf + lane * 128 + ((j ^ (lane & 7)) << 4);
-          st_shared_v4(dst, packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-        }
-        if (kTmaStore) {
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (row0 < p.M && col0 + c * kStoreCols < p.N) {
-              tma_store_2d(&tmap_d, sbuf, col0 + c * kStoreCols, row0);
-            }
-            bulk_commit_group();
-          }
-        } else {
-          // Row stride of D is not a multiple of 16 bytes: no TMA store possible.  Read the
-          // staged box back so that consecutive lanes write consecutive columns of one row.
-          __syncwarp();
-          for (int r = 0; r < 32; ++r) {
-            const int grow = row0 + r;
-            if (grow >= p.M) break;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int cc = h * 32 + lane;               // column inside the box
-              const int gcol = col0 + c * kStoreCols + cc;
-              const uint32_t src = sbuf + r * 128 + ((((cc >> 3) ^ (r & 7)) << 4) | ((cc & 7) << 1));
-              uint16_t val;
-              asm volatile("ld.shared.u16 %0, [%1];" : "=h"(val) : "r"(src) : "memory");
-              if (gcol < p.N) p.d_ptr[static_cast<size_t>(grow) * p.ldd + gcol] = val;
-            }
+        for (int c = 0; c < kChunks; ++c) {
+          // The TMA store that last read the staging buffer must have finished reading it.
+          if (kTmaStore) {
+            if (lane == 0) bulk_wait_group_read<0>();
           }
           __syncwarp();
+          // Row `lane` of the 32 x 64 box; 16-byte chunk j goes to chunk (j ^ (lane & 7)):
+          // the 128-byte swizzle the store tensor map expects.
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t dst = sbuf + lane * 128 + ((j ^ (lane & 7)) << 4);
+            st_shared_v4(dst, packed[c * 32 + 4 * j], packed[c * 32 + 4 * j + 1],
+                         packed[c * 32 + 4 * j + 2], packed[c * 32 + 4 * j + 3]);
+          }
+          if (kTmaStore) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (row0 < p.M && col0 + c * kStoreCols < p.N) {
+                tma_store_2d(&tmap_d, sbuf, col0 + c * kStoreCols, row0);
+              }
+              bulk_commit_group();
+            }
+          } else {
+            // Row stride of D is not a multiple of 16 bytes: no TMA store possible.  Read the
+            // staged box back so that consecutive lanes write consecutive columns of one row.
+            __syncwarp();
+            for (int r = 0; r < 32; ++r) {
+              const int grow = row0 + r;
+              if (grow >= p.M) break;
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int cc = h * 32 + lane;               // column inside the box
+                const int gcol = col0 + c * kStoreCols + cc;
+                const uint32_t src =
+                    sbuf + r * 128 + ((((cc >> 3) ^ (r & 7)) << 4) | ((cc & 7) << 1));
+                uint16_t val;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(val) : "r"(src) : "memory");
+                if (gcol < p.N) p.d_ptr[static_cast<size_t>(grow) * p.ldd + gcol] = val;
+              }
+            }
+            __syncwarp();
+          }
         }
-        buf ^= 1;
+      }
+      if (kTmaStore) {
+        if (lane == 0) bulk_wait_group<0>();
+      }
+      if (prof) {
+        p.prof[blockIdx.x * kProfCount + kProfEpiWait] = waited;
+        p.prof[blockIdx.x * kProfCount + kProfEpiTotal] = clock64() - t_begin;
       }
     }
-    if (kTmaStore) {
-      if (lane == 0) bulk_wait_group<0>();
-    }
-    __syncwarp();
   }
+  __syncwarp();
 
   tc_fence_before_sync();
   __syncthreads();
@@ -290,22 +366,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // -----------------------------------------------------------------------------------
 namespace {
 
-template <int TN, bool kTmaStore>
+template <int TN, int NB, bool kTmaStore>
 int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
-  using S = bf16k::Smem<TN>;
-  auto kernel = bf16k::gemm_bf16_kernel<TN, kTmaStore>;
+  using C = bf16k::Cfg<TN, NB>;
+  auto kernel = bf16k::gemm_bf16_kernel<TN, NB, kTmaStore>;
   static thread_local int configured_device = -1;
   static thread_local int max_clusters = 0;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return set_error(SMB_ERR_CUDA, "cudaGetDevice failed");
   if (configured_device != dev) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         S::kTotal);
+                                         C::kTotal);
     if (e != cudaSuccess) return set_cuda_error(e, "cudaFuncSetAttribute(bf16 smem)");
     cudaLaunchConfig_t probe = {};
     probe.gridDim = dim3(2, 1, 1);
     probe.blockDim = dim3(bf16k::kThreads, 1, 1);
-    probe.dynamicSmemBytes = S::kTotal;
+    probe.dynamicSmemBytes = C::kTotal;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2;
@@ -325,39 +401,54 @@ int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
   p.N = L.N;
   p.K = L.K;
   p.tiles_m = (L.M + 255) / 256;
-  p.tiles_n = (L.N + TN - 1) / TN;
-  p.group_m = L.group_m > 0 ? L.group_m : 8;
+  p.tiles_n = (L.N + C::kTileN - 1) / C::kTileN;
+  // Default raster group: about sqrt(clusters * tile_n / tile_m) tile rows, so that one wave
+  // touches as few distinct operand rows as possible.
+  p.group_m = L.group_m > 0 ? L.group_m : (NB == 2 ? 16 : 8);
   p.ldd = L.ldd;
   p.d_ptr = static_cast<uint16_t*>(L.d);
   p.status = L.status;
+  p.prof = L.prof;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (L.max_clusters > 0 && clusters > L.max_clusters) clusters = L.max_clusters;
-  kernel<<<dim3(2 * clusters, 1, 1), dim3(bf16k::kThreads, 1, 1), S::kTotal, stream>>>(
+  kernel<<<dim3(2 * clusters, 1, 1), dim3(bf16k::kThreads, 1, 1), C::kTotal, stream>>>(
       L.tmap_a, L.tmap_b, L.tmap_d, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error(e, "bf16 GEMM launch");
   return SMB_OK;
 }
 
+template <int TN, int NB>
+int launch_bf16_store(const Bf16Launch& L, cudaStream_t stream) {
+  return L.tma_store ? launch_bf16<TN, NB, true>(L, stream) : launch_bf16<TN, NB, false>(L, stream);
+}
+
 }  // namespace
 
-int bf16_tile_n(int N) {
-  if (N > 128) return 256;
-  if (N > 64) return 128;
-  return 64;
+void bf16_pick_tile(int M, int N, int K, int* tile_n, int* sub_blocks) {
+  (void)M;
+  *sub_blocks = 1;
+  if (N > 128) {
+    *tile_n = 256;
+    // 256 x 512 tiles cut the L2 sector traffic per flop by a quarter but give up the
+    // overlap of epilogue and main loop: worth it once the K loop is long.
+    if (N > 256 && K >= 2048) *sub_blocks = 2;
+  } else if (N > 64) {
+    *tile_n = 128;
+  } else {
+    *tile_n = 64;
+  }
 }
 
 int bf16_launch(const Bf16Launch& L, cudaStream_t stream) {
+  if (L.sub_blocks == 2 && L.tile_n == 256) return launch_bf16_store<256, 2>(L, stream);
+  if (L.sub_blocks != 1) return set_error(SMB_ERR_INVALID, "bf16: two sub-blocks need 256-wide tiles");
   switch (L.tile_n) {
-    case 256:
-      return L.tma_store ? launch_bf16<256, true>(L, stream) : launch_bf16<256, false>(L, stream);
-    case 128:
-      return L.tma_store ? launch_bf16<128, true>(L, stream) : launch_bf16<128, false>(L, stream);
-    case 64:
-      return L.tma_store ? launch_bf16<64, true>(L, stream) : launch_bf16<64, false>(L, stream);
-    default:
-      return set_error(SMB_ERR_INVALID, "bf16 tile width must be 64, 128 or 256");
+    case 256: return launch_bf16_store<256, 1>(L, stream);
+    case 128: return launch_bf16_store<128, 1>(L, stream);
+    case 64: return launch_bf16_store<64, 1>(L, stream);
+    default: return set_error(SMB_ERR_INVALID, "bf16 tile width must be 64, 128 or 256");
   }
 }
 

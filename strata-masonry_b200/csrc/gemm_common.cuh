@@ -46,15 +46,17 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype
 struct Bf16Launch {
   CUtensorMap tmap_a, tmap_b, tmap_d;
   int M, N, K;
-  int tile_n;        // 64, 128 or 256
+  int tile_n;        // width of one N sub-block: 64, 128 or 256
+  int sub_blocks;    // N sub-blocks per tile: 1, or 2 (256 x 512 tiles, tile_n = 256 only)
   bool tma_store;    // false: D rows are not 16-byte aligned, use plain stores
   int group_m;       // raster group height (0 = default)
   int max_clusters;  // 0 = as many as fit
   void* d;
   int ldd;
   int* status;       // device status word, may be null
+  long long* prof;   // device buffer of 8 counters per CTA (role timers), or null
 };
-int bf16_tile_n(int N);
+void bf16_pick_tile(int M, int N, int K, int* tile_n, int* sub_blocks);
 int bf16_launch(const Bf16Launch& L, cudaStream_t stream);
 
 }  // namespace smb
