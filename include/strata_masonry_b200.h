@@ -60,6 +60,47 @@ int smb_fill_bf16_host(uint16_t* out, int64_t rows, int64_t cols, int64_t ld, ui
                        uint64_t index_row_stride, uint64_t index_col_stride, int fill,
                        uint32_t seed);
 
+/* E2M1 operands with one UE8M0 scale per 32 K (the reference's "NVFP4" format).
+ * `data` receives rows x K/2 bytes (two codes per byte, even k in the low nibble, `ld_bytes`
+ * between rows, 16-byte aligned); `sf_packed` (optional) receives the scales in the packed
+ * layout the kernels read, smb_sf_packed_bytes(rows, K/32) bytes; `sf_rowmajor` (optional)
+ * receives them as plain [rows, K/32] bytes (exponent + 127).  `row0` is the global index of
+ * the first row (N-sharding); `which` is 0 for A (seed 0x9E3779B9, scale rule of SFA) and 1
+ * for B (seed 0x7F4A7C15, SFB).  Fills 1..4 are the reference's direct code/scale fills
+ * (k1_e2m1_nibble / k1_generic_sf_exp, nvfp4/dense_gemm_nvfp4.cu:2279-2290, :2394-2398,
+ * :2436-2437; verifier data_values / scale_values, dense_gemm_nvfp4_cpu_verifier.py:46-77).
+ * Fills 5 and 6 have no reference counterpart: Gaussian FP32 source values (6: rounded to
+ * bf16 first) pushed through the quantiser below. */
+int smb_fill_fp4_device(uint8_t* data, int64_t ld_bytes, uint8_t* sf_packed, uint8_t* sf_rowmajor,
+                        int64_t rows, int64_t K, uint64_t row0, int fill, int which, void* stream);
+int smb_fill_fp4_host(uint8_t* data, int64_t ld_bytes, uint8_t* sf_packed, uint8_t* sf_rowmajor,
+                      int64_t rows, int64_t K, uint64_t row0, int fill, int which);
+
+/* FP32 -> E2M1 + UE8M0 quantiser, per row and per 32 consecutive k: scale exponent = the
+ * smallest e with 6 * 2^e >= max|v| (0 for an all-zero block, clamped to [-126, 127]), each
+ * value times 2^-e rounded to the nearest E2M1 code with ties to the even code.  No reference
+ * counterpart (the reference generates codes directly); outputs as for the fills. */
+int smb_quantize_mx_device(const float* src, int64_t ld_src, uint8_t* data, int64_t ld_bytes,
+                           uint8_t* sf_packed, uint8_t* sf_rowmajor, int64_t rows, int64_t K,
+                           void* stream);
+int smb_quantize_mx_host(const float* src, int64_t ld_src, uint8_t* data, int64_t ld_bytes,
+                         uint8_t* sf_packed, uint8_t* sf_rowmajor, int64_t rows, int64_t K);
+
+/* Packed scale layout (sf_pack, nvfp4/dense_gemm_nvfp4.cu:2418-2435): bands of 128 rows, each
+ * band (K/32 + 3) / 4 chunks of 512 bytes, byte (r, j) of a band at
+ * (j / 4) * 512 + (r % 32) * 16 + (r / 32) * 4 + j % 4.  Padding holds 127 (scale 1). */
+size_t smb_sf_packed_bytes(int64_t rows, int64_t kblocks);
+int smb_sf_pack_host(const uint8_t* sf_rowmajor, int64_t rows, int64_t kblocks, uint8_t* packed);
+
+/* Bit-pattern helpers, exported so that host-side known-answer tests can pin them the way the
+ * reference's tests/8_tcgen05_mma_idesc_test.cu and tests/42_smem_desc_blackwell_test.cu do. */
+uint64_t smb_debug_smem_desc(uint32_t smem_addr, uint32_t sbo_bytes, uint32_t lbo_bytes,
+                             uint32_t swizzle_mode);
+uint32_t smb_debug_idesc_bf16(int mma_m, int mma_n);
+uint32_t smb_debug_idesc_mxf4(int mma_m, int mma_n, uint32_t sf_id_a, uint32_t sf_id_b, int ue8m0);
+void smb_debug_tile_coords(int t, int tiles_m, int tiles_n, int group_m, int* tm, int* tn);
+uint64_t smb_debug_sf_offset(uint32_t row, uint32_t kblock, uint32_t kblocks);
+
 /* ------------------------------------------------------------------------------------
  * Dense BF16 GEMM:  D[M,N] = bf16_rne( sum_k A[M,K] * BT[N,K] ), FP32 accumulate.
  * Stands in for dense_gemm_bf16_k0_impl + run_one_impl

@@ -38,6 +38,17 @@ DECLARED = [
     ("smb_last_error", C.c_char_p, []),
     ("smb_fill_bf16_device", _i, [_vp, _i64, _i64, _i64, _u64, _u64, _u64, _i, _u32, _vp]),
     ("smb_fill_bf16_host", _i, [_vp, _i64, _i64, _i64, _u64, _u64, _u64, _i, _u32]),
+    ("smb_fill_fp4_device", _i, [_vp, _i64, _vp, _vp, _i64, _i64, _u64, _i, _i, _vp]),
+    ("smb_fill_fp4_host", _i, [_vp, _i64, _vp, _vp, _i64, _i64, _u64, _i, _i]),
+    ("smb_quantize_mx_device", _i, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _vp]),
+    ("smb_quantize_mx_host", _i, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64]),
+    ("smb_sf_packed_bytes", C.c_size_t, [_i64, _i64]),
+    ("smb_sf_pack_host", _i, [_vp, _i64, _i64, _vp]),
+    ("smb_debug_smem_desc", _u64, [_u32, _u32, _u32, _u32]),
+    ("smb_debug_idesc_bf16", _u32, [_i, _i]),
+    ("smb_debug_idesc_mxf4", _u32, [_i, _i, _u32, _u32, _i]),
+    ("smb_debug_tile_coords", None, [_i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
+    ("smb_debug_sf_offset", _u64, [_u32, _u32, _u32]),
     ("smb_bf16_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, C.c_uint]),
     ("smb_bf16_plan_run", _i, [_vp, _vp]),
     ("smb_bf16_plan_check", _i, [_vp, _vp]),

@@ -1,0 +1,145 @@
+"""Python face of the C ABI for the two GEMMs.
+
+Host-array helpers (`*_host`) take and return NumPy arrays and go through the library's
+host-buffer entry points (upload, run, download).  Plan classes wrap device pointers (any
+object with ``data_ptr()``, e.g. a torch CUDA tensor, or a raw integer address) and are what
+timing loops use.  Nothing in here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+
+
+def _ptr(x) -> int:
+    if x is None:
+        return 0
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return int(x.data_ptr())
+    if isinstance(x, np.ndarray):
+        return int(x.ctypes.data)
+    raise TypeError(f"cannot take the address of {type(x)!r}")
+
+
+def _stream_ptr(stream) -> int:
+    if stream is None:
+        return 0
+    if isinstance(stream, int):
+        return stream
+    return int(stream.cuda_stream)
+
+
+# ------------------------------------------------------------------------------- BF16
+def dense_gemm_bf16_host(a_bits: np.ndarray, bt_bits: np.ndarray) -> np.ndarray:
+    """D = bf16(A . BT^T) for host arrays of bf16 bit patterns: A [M,K], BT [N,K] -> D [M,N]."""
+    a = np.ascontiguousarray(a_bits, dtype=np.uint16)
+    bt = np.ascontiguousarray(bt_bits, dtype=np.uint16)
+    if a.ndim != 2 or bt.ndim != 2 or a.shape[1] != bt.shape[1]:
+        raise ValueError("A must be [M,K] and BT [N,K]")
+    m, k = a.shape
+    n = bt.shape[0]
+    d = np.empty((m, n), dtype=np.uint16)
+    capi.check(capi.lib().smb_dense_gemm_bf16_host(a.ctypes.data, bt.ctypes.data, d.ctypes.data, m, n, k))
+    return d
+
+
+class Bf16Plan:
+    """Tensor maps + tile choice for one (A, BT, D) device buffer set."""
+
+    def __init__(self, a, bt, d, m: int, n: int, k: int, lda: int | None = None,
+                 ldb: int | None = None, ldd: int | None = None, flags: int = 0):
+        self._lib = capi.lib()
+        self._h = C.c_void_p()
+        self.shape = (m, n, k)
+        self._keep = (a, bt, d)
+        capi.check(self._lib.smb_bf16_plan_create(
+            C.byref(self._h), _ptr(a), _ptr(bt), _ptr(d), m, n, k,
+            k if lda is None else lda, k if ldb is None else ldb, n if ldd is None else ldd, flags))
+
+    def tune(self, group_m: int = 0, max_clusters: int = 0) -> None:
+        capi.check(self._lib.smb_bf16_plan_tune(self._h, group_m, max_clusters))
+
+    def set_profile(self, counters) -> None:
+        capi.check(self._lib.smb_bf16_plan_set_profile(self._h, _ptr(counters)))
+
+    def run(self, stream=None) -> None:
+        capi.check(self._lib.smb_bf16_plan_run(self._h, _stream_ptr(stream)))
+
+    def check(self, stream=None) -> None:
+        capi.check(self._lib.smb_bf16_plan_check(self._h, _stream_ptr(stream)))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.smb_bf16_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ------------------------------------------------------------------------------- fills
+def fill_bf16_device(out, rows: int, cols: int, fill: int, seed: int, index0: int = 0,
+                     row_stride: int | None = None, col_stride: int = 1, ld: int | None = None,
+                     stream=None) -> None:
+    capi.check(capi.lib().smb_fill_bf16_device(
+        _ptr(out), rows, cols, cols if ld is None else ld, index0,
+        cols if row_stride is None else row_stride, col_stride, fill, seed, _stream_ptr(stream)))
+
+
+def fill_bf16_host(rows: int, cols: int, fill: int, seed: int, index0: int = 0,
+                   row_stride: int | None = None, col_stride: int = 1) -> np.ndarray:
+    out = np.empty((rows, cols), dtype=np.uint16)
+    capi.check(capi.lib().smb_fill_bf16_host(
+        out.ctypes.data, rows, cols, cols, index0, cols if row_stride is None else row_stride,
+        col_stride, fill, seed))
+    return out
+
+
+def bf16_operands_device(a, bt, m: int, n: int, k: int, fill: int, n0: int = 0,
+                         n_total: int | None = None, stream=None) -> None:
+    """Fill A [m,k] and BT [n,k] on the device as the reference driver would on the host
+    (A index m*K+k seed 1; B index k*N+n seed 2, stored transposed)."""
+    n_total = n if n_total is None else n_total
+    fill_bf16_device(a, m, k, fill, 1, 0, k, 1, stream=stream)
+    fill_bf16_device(bt, n, k, fill, 2, n0, 1, n_total, stream=stream)
+
+
+def fill_fp4_host(rows: int, k: int, fill: int, which: int, row0: int = 0):
+    """Returns (data [rows, k/2] u8, packed scales u8, row-major scales [rows, k/32] u8)."""
+    lib = capi.lib()
+    data = np.empty((rows, k // 2), dtype=np.uint8)
+    sf_rm = np.empty((rows, k // 32), dtype=np.uint8)
+    sf_packed = np.empty(lib.smb_sf_packed_bytes(rows, k // 32), dtype=np.uint8)
+    capi.check(lib.smb_fill_fp4_host(data.ctypes.data, k // 2, sf_packed.ctypes.data,
+                                     sf_rm.ctypes.data, rows, k, row0, fill, which))
+    return data, sf_packed, sf_rm
+
+
+def quantize_mx_host(src: np.ndarray):
+    """FP32 [rows, K] -> (data [rows, K/2] u8, packed scales, row-major scales)."""
+    lib = capi.lib()
+    src = np.ascontiguousarray(src, dtype=np.float32)
+    rows, k = src.shape
+    data = np.empty((rows, k // 2), dtype=np.uint8)
+    sf_rm = np.empty((rows, k // 32), dtype=np.uint8)
+    sf_packed = np.empty(lib.smb_sf_packed_bytes(rows, k // 32), dtype=np.uint8)
+    capi.check(lib.smb_quantize_mx_host(src.ctypes.data, k, data.ctypes.data, k // 2,
+                                        sf_packed.ctypes.data, sf_rm.ctypes.data, rows, k))
+    return data, sf_packed, sf_rm
+
+
+def sf_pack_host(sf_rowmajor: np.ndarray) -> np.ndarray:
+    lib = capi.lib()
+    sf = np.ascontiguousarray(sf_rowmajor, dtype=np.uint8)
+    rows, kb = sf.shape
+    out = np.empty(lib.smb_sf_packed_bytes(rows, kb), dtype=np.uint8)
+    capi.check(lib.smb_sf_pack_host(sf.ctypes.data, rows, kb, out.ctypes.data))
+    return out

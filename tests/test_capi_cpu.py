@@ -1,0 +1,169 @@
+"""CPU-side checks of the C ABI: the library loads, exports what the header declares, its
+host-side generators agree with the oracle bit for bit, its descriptor bit patterns match the
+known answers, and argument errors come back as status codes.  No kernel is launched here."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol(smb):
+    lib = smb.capi.lib()
+    header = (ROOT / "include" / "strata_masonry_b200.h").read_text()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(smb_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations parsed"
+    bound = {name for name, _, _ in smb.capi.DECLARED}
+    assert declared == bound, (declared - bound, bound - declared)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.smb_version() >= 1000
+
+
+def test_product_never_reaches_into_the_oracle():
+    # The oracle is test infrastructure: nothing under the package may import, include or open it.
+    for p in (ROOT / "strata-masonry_b200").rglob("*"):
+        if p.suffix == ".py":
+            for line in p.read_text().splitlines():
+                assert not re.match(r"\s*(from|import)\s+\S*oracle", line), (p, line)
+                assert "oracle/" not in line and "oracle.py" not in line, (p, line)
+        elif p.suffix in (".cu", ".cuh", ".cpp", ".h"):
+            for line in p.read_text().splitlines():
+                if line.lstrip().startswith("#include"):
+                    assert "oracle" not in line, (p, line)
+
+
+@pytest.mark.parametrize("fill", [1, 2, 3, 4, 5, 6, 7])
+def test_bf16_host_fill_matches_oracle(smb, oracle, fill):
+    m, k, n = 37, 72, 29
+    a = smb.gemm.fill_bf16_host(m, k, fill, 1, 0, k, 1)
+    bt = smb.gemm.fill_bf16_host(n, k, fill, 2, 0, 1, n)
+    wa, wbt = oracle.bf16_operands(m, n, k, fill)
+    np.testing.assert_array_equal(a, wa)
+    np.testing.assert_array_equal(bt, wbt)
+    # A slab of a wider BT (N-sharding) uses the global column index.
+    slab = smb.gemm.fill_bf16_host(8, k, fill, 2, 13, 1, 64)
+    _, wslab = oracle.bf16_operands(1, 8, k, fill, n0=13, n_total=64)
+    np.testing.assert_array_equal(slab, wslab)
+
+
+@pytest.mark.parametrize("fill", [1, 2, 3, 4])
+def test_bf16_host_fill_matches_reference_vectors(smb, oracle, golden, fill):
+    idx = golden["fill_indices"]
+    for seed in (1, 2):
+        want = oracle.f32_to_bf16(golden[f"bf16_fill_m{fill}_s{seed}"])
+        got = np.empty(idx.size, dtype=np.uint16)
+        lib = smb.capi.lib()
+        for i, v in enumerate(idx[:: max(1, idx.size // 512)]):
+            one = np.empty(1, dtype=np.uint16)
+            assert lib.smb_fill_bf16_host(one.ctypes.data, 1, 1, 1, int(v) & 0xFFFFFFFFFFFFFFFF, 0, 0, fill, seed) == 0
+            assert one[0] == want[i * max(1, idx.size // 512)]
+
+
+def test_bf16_fill_wraps_at_32_bits(smb, oracle):
+    # Index arithmetic wraps modulo 2^32 as in the reference driver.
+    big = (1 << 32) + 12345
+    a = smb.gemm.fill_bf16_host(1, 8, 2, 1, big, 8, 1)
+    b = smb.gemm.fill_bf16_host(1, 8, 2, 1, 12345, 8, 1)
+    np.testing.assert_array_equal(a, b)
+
+
+@pytest.mark.parametrize("fill", [1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("which", [0, 1])
+def test_fp4_host_fill_matches_oracle(smb, oracle, fill, which):
+    rows, k, row0 = 150, 320, 7
+    data, sf_packed, sf_rm = smb.gemm.fill_fp4_host(rows, k, fill, which, row0)
+    codes, sf = oracle.fp4_operand(rows, k, fill, which, row0)
+    np.testing.assert_array_equal(data, oracle.pack_codes(codes))
+    np.testing.assert_array_equal(sf_rm, sf)
+    np.testing.assert_array_equal(sf_packed, oracle.sf_pack(sf))
+
+
+def test_quantizer_matches_oracle(smb, oracle):
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((70, 256)).astype(np.float32)
+    x[0, :32] = 0.0                       # all-zero block
+    x[1, :32] = 6.0                       # exactly the top code
+    x[2, :32] = np.float32(6.0000005)     # just above: next exponent
+    x[3, :8] = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0]   # ties at scale 1
+    x[3, 8:32] = 0.0
+    x[4, :32] = 1e-41                     # subnormal block
+    x[5, :32] *= 1e30
+    data, sf_packed, sf_rm = smb.gemm.quantize_mx_host(x)
+    codes, sf = oracle.quantize_mx(x)
+    np.testing.assert_array_equal(sf_rm, sf)
+    np.testing.assert_array_equal(data, oracle.pack_codes(codes))
+    np.testing.assert_array_equal(sf_packed, oracle.sf_pack(sf))
+    assert sf_rm.min() >= 1 and sf_rm.max() <= 254
+
+
+def test_sf_pack_matches_oracle(smb, oracle):
+    sf = (np.arange(300 * 10) * 7 % 251).astype(np.uint8).reshape(300, 10)
+    np.testing.assert_array_equal(smb.gemm.sf_pack_host(sf), oracle.sf_pack(sf))
+    lib = smb.capi.lib()
+    assert lib.smb_sf_packed_bytes(300, 10) == oracle.sf_packed_size(300, 10)
+    assert lib.smb_debug_sf_offset(95, 7, 10) == (7 // 4) * 512 + (95 % 32) * 16 + (95 // 32) * 4 + 3
+
+
+def test_descriptor_known_answers(smb):
+    lib = smb.capi.lib()
+    # Shared-memory descriptor: addr 0x4000, SBO 256, LBO 128, 128-byte swizzle (the case pinned
+    # by the reference's tests/42_smem_desc_blackwell_test.cu).
+    want = (0x4000 >> 4) | ((128 >> 4) << 16) | ((256 >> 4) << 32) | (1 << 46) | (2 << 61)
+    assert lib.smb_debug_smem_desc(0x4000, 256, 128, 2) == want
+    assert (lib.smb_debug_smem_desc(0x4000, 256, 128, 0) >> 61) == 0
+    # The operand descriptors the kernels build: SBO 1024, LBO 16.
+    d = lib.smb_debug_smem_desc(0x8400, 1024, 16, 2)
+    assert d & 0x3FFF == 0x840 and (d >> 16) & 0x3FFF == 1 and (d >> 32) & 0x3FFF == 64
+    # kind::f16 instruction descriptor (layout pinned by tests/8_tcgen05_mma_idesc_test.cu):
+    # D = F32 at bit 4, A/B = BF16 at bits 7/10, N >> 3 at 17, M >> 4 at 24.
+    assert lib.smb_debug_idesc_bf16(128, 64) == (1 << 4) | (1 << 7) | (1 << 10) | (8 << 17) | (8 << 24)
+    assert lib.smb_debug_idesc_bf16(256, 256) == (1 << 4) | (1 << 7) | (1 << 10) | (32 << 17) | (16 << 24)
+    # kind::mxf4nvf4: E2M1 at bits 7/10, N >> 3 at 17, UE8M0 at 23, M >> 7 at 27, scale ids at 4/29.
+    base = (1 << 7) | (1 << 10) | (16 << 17) | (1 << 23) | (2 << 27)
+    assert lib.smb_debug_idesc_mxf4(256, 128, 0, 0, 1) == base
+    assert lib.smb_debug_idesc_mxf4(256, 128, 2, 2, 1) == base | (2 << 4) | (2 << 29)
+    assert lib.smb_debug_idesc_mxf4(128, 128, 0, 0, 0) == (1 << 7) | (1 << 10) | (16 << 17) | (1 << 27)
+
+
+def test_tile_raster_matches_oracle(smb, oracle):
+    lib = smb.capi.lib()
+    tm, tn = C.c_int(), C.c_int()
+    for tiles_m, tiles_n, gm in [(32, 16, 16), (5, 7, 8), (17, 3, 4), (128, 14, 16)]:
+        for t in range(tiles_m * tiles_n):
+            lib.smb_debug_tile_coords(t, tiles_m, tiles_n, gm, C.byref(tm), C.byref(tn))
+            assert (tm.value, tn.value) == oracle.tile_coords(t, tiles_m, tiles_n, gm)
+
+
+def test_argument_errors_are_status_codes(smb):
+    lib = smb.capi.lib()
+    capi = smb.capi
+    plan = C.c_void_p()
+    buf = np.zeros(64, dtype=np.uint16)
+    p = buf.ctypes.data
+    assert lib.smb_bf16_plan_create(C.byref(plan), None, p, p, 256, 128, 64, 64, 64, 128, 0) == capi.SMB_ERR_INVALID
+    assert "null" in capi.last_error()
+    assert lib.smb_bf16_plan_create(C.byref(plan), p, p, p, 0, 128, 64, 64, 64, 128, 0) == capi.SMB_ERR_INVALID
+    assert lib.smb_bf16_plan_create(C.byref(plan), p, p, p, 256, 128, 60, 64, 64, 128, 0) == capi.SMB_ERR_UNSUPPORTED
+    assert lib.smb_bf16_plan_create(C.byref(plan), p, p, p, 256, 128, 64, 32, 64, 128, 0) == capi.SMB_ERR_INVALID
+    assert lib.smb_bf16_plan_run(None, None) == capi.SMB_ERR_INVALID
+    assert lib.smb_bf16_plan_destroy(None) == capi.SMB_OK
+    assert lib.smb_fill_bf16_host(p, 2, 2, 2, 0, 2, 1, 9, 1) == capi.SMB_ERR_INVALID
+    assert lib.smb_fill_bf16_host(None, 2, 2, 2, 0, 2, 1, 1, 1) == capi.SMB_ERR_INVALID
+    assert lib.smb_fill_fp4_host(p, 16, None, None, 1, 48, 0, 2, 0) == capi.SMB_ERR_INVALID   # K % 32
+    assert lib.smb_fill_fp4_host(p, 16, None, None, 1, 32, 0, 9, 0) == capi.SMB_ERR_INVALID   # fill id
+    assert lib.smb_dense_gemm_bf16_host(None, p, p, 1, 1, 8) == capi.SMB_ERR_INVALID
+    with pytest.raises(capi.SmbError):
+        capi.check(capi.SMB_ERR_INVALID)
+
+
+def test_missing_library_is_loud(smb, tmp_path, monkeypatch):
+    capi = smb.capi
+    monkeypatch.setattr(capi, "_lib", None)
+    monkeypatch.setattr(capi, "LIB_PATH", tmp_path / "absent.so")
+    with pytest.raises(ImportError, match="no CPU fallback"):
+        capi.lib()
