@@ -141,12 +141,41 @@ int smb_dense_gemm_bf16(const void* a, const void* bt, void* d, int M, int N, in
  * these steps inline (dense_gemm_bf16.cu:293-307, :401-404). */
 int smb_dense_gemm_bf16_host(const uint16_t* a, const uint16_t* bt, uint16_t* d, int M, int N, int K);
 
+/* ------------------------------------------------------------------------------------
+ * Dense block-scaled FP4 GEMM ("NVFP4" in the reference):
+ *   D[M,N] = bf16_rne( sum_k (A[m,k] SFA[m,k/32]) (B[n,k] SFB[n,k/32]) ), FP32 accumulate.
+ * Stands in for dense_gemm_nvfp4_k1_impl + run_one_k1
+ * (src/kernels/gemm/sm100a/nvfp4/dense_gemm_nvfp4.cu:1705-2250, :2353-2700).
+ * A: [M, K/2] bytes (two E2M1 codes per byte, even k low), B: [N, K/2] bytes, row pitches in
+ * bytes (multiples of 16); SFA / SFB: UE8M0 bytes in the packed layout of
+ * smb_sf_packed_bytes(); D: bf16 row-major.  Any M, N >= 1; K a multiple of 32.
+ * ---------------------------------------------------------------------------------- */
+typedef struct smb_fp4_plan smb_fp4_plan;
+int smb_fp4_plan_create(smb_fp4_plan** plan, const void* a, const void* sfa, const void* b,
+                        const void* sfb, void* d, int M, int N, int K, int64_t lda_bytes,
+                        int64_t ldb_bytes, int64_t ldd, unsigned flags);
+int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream);
+int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream);
+int smb_fp4_plan_destroy(smb_fp4_plan* plan);
+int smb_fp4_plan_tune(smb_fp4_plan* plan, int group_m, int max_clusters);
+/* Role timers, same layout as smb_bf16_plan_set_profile. */
+int smb_fp4_plan_set_profile(smb_fp4_plan* plan, long long* counters);
+
+/* One-shot on device pointers (packed scales). */
+int smb_dense_gemm_nvfp4(const void* a, const void* sfa, const void* b, const void* sfb, void* d,
+                         int M, int N, int K, void* stream);
+/* Host buffers; the scales are given in their logical form, [rows, K/32] bytes row-major, and
+ * are packed here (sf_pack in the reference driver, nvfp4/dense_gemm_nvfp4.cu:2418-2435). */
+int smb_dense_gemm_nvfp4_host(const uint8_t* a, const uint8_t* sfa_rowmajor, const uint8_t* b,
+                              const uint8_t* sfb_rowmajor, uint16_t* d, int M, int N, int K);
+
 #define SMB_FLAG_NONE 0u
 #define SMB_FLAG_FORCE_PLAIN_STORE 1u /* use the non-TMA epilogue even when D is aligned */
 #define SMB_FLAG_TILE_N_128 2u        /* force 256 x 128 tiles */
 #define SMB_FLAG_TILE_N_64 4u         /* force 256 x 64 tiles */
 #define SMB_FLAG_TILE_N_256 8u        /* force 256 x 256 tiles, two accumulator banks */
 #define SMB_FLAG_TILE_N_512 16u       /* force 256 x 512 tiles, one accumulator set */
+#define SMB_FLAG_TILE_N_384 32u       /* FP4 only: force 256 x 384 tiles */
 
 #ifdef __cplusplus
 }

@@ -29,7 +29,8 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
           "--expt-relaxed-constexpr"]
 
-LIB_SOURCES = ["runtime.cu", "fills.cu", "gemm_bf16.cu", "api_bf16.cu"]
+LIB_SOURCES = ["runtime.cu", "fills.cu", "gemm_bf16.cu", "api_bf16.cu", "gemm_nvfp4.cu",
+               "api_nvfp4.cu"]
 DRIVERS = {}
 
 

@@ -1,0 +1,192 @@
+// C-ABI of the block-scaled FP4 GEMM: plans, launch, status check, host-buffer path.
+// Host-side counterpart of run_one_k1 in the reference
+// (src/kernels/gemm/sm100a/nvfp4/dense_gemm_nvfp4.cu:2353-2700).
+#include <new>
+#include <vector>
+
+#include "formats.cuh"
+#include "gemm_common.cuh"
+
+namespace smb {
+const char* device_status_name(int code);
+}
+
+using namespace smb;
+
+struct smb_fp4_plan {
+  Fp4Launch launch;
+  int* status_dev;
+};
+
+extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void* sfa, const void* b,
+                                   const void* sfb, void* d, int M, int N, int K, int64_t lda_bytes,
+                                   int64_t ldb_bytes, int64_t ldd, unsigned flags) {
+  if (out == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null output handle");
+  *out = nullptr;
+  if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || d == nullptr)
+    return set_error(SMB_ERR_INVALID, "fp4 plan: null operand pointer");
+  if (M <= 0 || N <= 0 || K <= 0)
+    return set_error(SMB_ERR_INVALID, "fp4 plan: dimensions must be positive (M=%d N=%d K=%d)", M, N, K);
+  if (K % 32 != 0)
+    return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: K=%d must be a multiple of 32 (one scale per 32 K)", K);
+  if (lda_bytes < K / 2 || ldb_bytes < K / 2 || ldd < N)
+    return set_error(SMB_ERR_INVALID, "fp4 plan: leading dimension smaller than the row length");
+  if (lda_bytes % 16 != 0 || ldb_bytes % 16 != 0)
+    return set_error(SMB_ERR_INVALID, "fp4 plan: operand row pitches must be multiples of 16 bytes");
+
+  smb_fp4_plan* p = new (std::nothrow) smb_fp4_plan();
+  if (p == nullptr) return set_error(SMB_ERR_NOMEM, "fp4 plan: out of host memory");
+  Fp4Launch& L = p->launch;
+  L.M = M;
+  L.N = N;
+  L.K = K;
+  fp4_pick_tile(M, N, K, &L.w0, &L.w1);
+  if (flags & SMB_FLAG_TILE_N_128) { L.w0 = 128; L.w1 = 0; }
+  if (flags & SMB_FLAG_TILE_N_256) { L.w0 = 256; L.w1 = 0; }
+  if (flags & SMB_FLAG_TILE_N_384) { L.w0 = 256; L.w1 = 128; }
+  L.group_m = 0;
+  L.max_clusters = 0;
+  L.prof = nullptr;
+  L.d = d;
+  L.ldd = static_cast<int>(ldd);
+  L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
+                !(flags & SMB_FLAG_FORCE_PLAIN_STORE);
+  p->status_dev = nullptr;
+
+  const uint64_t kchunks = (static_cast<uint64_t>(K) / 32 + 3) / 4;
+  const uint64_t bands_a = (static_cast<uint64_t>(M) + 127) / 128;
+  const uint64_t bands_b = (static_cast<uint64_t>(N) + 127) / 128;
+  const int tile_n = L.w0 + L.w1;
+  int rc = encode_tmap_2d(&L.tmap_a, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, lda_bytes, 128, 128, true);
+  if (rc == SMB_OK)
+    rc = encode_tmap_2d(&L.tmap_b0, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, ldb_bytes, L.w0 / 2, 128, true);
+  if (rc == SMB_OK) {
+    if (L.w1 > 0)
+      rc = encode_tmap_2d(&L.tmap_b1, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, ldb_bytes, L.w1 / 2, 128, true);
+    else
+      L.tmap_b1 = L.tmap_b0;
+  }
+  if (rc == SMB_OK)
+    rc = encode_tmap_2d(&L.tmap_sfa, sfa, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_a, kchunks * 64,
+                        kchunks * 512, 1, 128, false);
+  if (rc == SMB_OK)
+    rc = encode_tmap_2d(&L.tmap_sfb, sfb, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_b, kchunks * 64,
+                        kchunks * 512, tile_n / 128, 128, false);
+  if (rc == SMB_OK) {
+    if (L.tma_store)
+      rc = encode_tmap_2d(&L.tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldd * 2, 32, 64, true);
+    else
+      L.tmap_d = L.tmap_a;
+  }
+  if (rc == SMB_OK) {
+    cudaError_t e = cudaMalloc(&p->status_dev, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(p->status_dev, 0, sizeof(int));
+    if (e != cudaSuccess) rc = set_cuda_error(e, "fp4 plan: status word allocation");
+  }
+  if (rc != SMB_OK) {
+    if (p->status_dev) cudaFree(p->status_dev);
+    delete p;
+    return rc;
+  }
+  L.status = p->status_dev;
+  *out = p;
+  return SMB_OK;
+}
+
+extern "C" int smb_fp4_plan_tune(smb_fp4_plan* plan, int group_m, int max_clusters) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
+  if (group_m < 0 || max_clusters < 0) return set_error(SMB_ERR_INVALID, "fp4 plan: negative tuning value");
+  plan->launch.group_m = group_m;
+  plan->launch.max_clusters = max_clusters;
+  return SMB_OK;
+}
+
+extern "C" int smb_fp4_plan_set_profile(smb_fp4_plan* plan, long long* counters) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
+  plan->launch.prof = counters;
+  return SMB_OK;
+}
+
+extern "C" int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
+  return fp4_launch(plan->launch, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return set_cuda_error(e, "fp4 plan check: stream synchronize");
+  int status = 0;
+  e = cudaMemcpy(&status, plan->status_dev, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return set_cuda_error(e, "fp4 plan check: status read");
+  if (status != 0) {
+    cudaMemset(plan->status_dev, 0, sizeof(int));
+    return set_error(SMB_ERR_DEVICE, "nvfp4 GEMM kernel reported status %d: %s", status,
+                     device_status_name(status));
+  }
+  return SMB_OK;
+}
+
+extern "C" int smb_fp4_plan_destroy(smb_fp4_plan* plan) {
+  if (plan == nullptr) return SMB_OK;
+  if (plan->status_dev) cudaFree(plan->status_dev);
+  delete plan;
+  return SMB_OK;
+}
+
+extern "C" int smb_dense_gemm_nvfp4(const void* a, const void* sfa, const void* b, const void* sfb,
+                                    void* d, int M, int N, int K, void* stream) {
+  smb_fp4_plan* plan = nullptr;
+  int rc = smb_fp4_plan_create(&plan, a, sfa, b, sfb, d, M, N, K, K / 2, K / 2, N, SMB_FLAG_NONE);
+  if (rc != SMB_OK) return rc;
+  rc = smb_fp4_plan_run(plan, stream);
+  if (rc == SMB_OK) rc = smb_fp4_plan_check(plan, stream);
+  smb_fp4_plan_destroy(plan);
+  return rc;
+}
+
+extern "C" int smb_dense_gemm_nvfp4_host(const uint8_t* a, const uint8_t* sfa_rowmajor,
+                                         const uint8_t* b, const uint8_t* sfb_rowmajor, uint16_t* d,
+                                         int M, int N, int K) {
+  if (a == nullptr || b == nullptr || sfa_rowmajor == nullptr || sfb_rowmajor == nullptr || d == nullptr)
+    return set_error(SMB_ERR_INVALID, "host fp4 GEMM: null operand pointer");
+  if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0)
+    return set_error(SMB_ERR_INVALID, "host fp4 GEMM: bad dimensions (K must be a multiple of 32)");
+  const int64_t kblocks = K / 32;
+  std::vector<uint8_t> pa(smb_sf_packed_bytes(M, kblocks)), pb(smb_sf_packed_bytes(N, kblocks));
+  int rc = smb_sf_pack_host(sfa_rowmajor, M, kblocks, pa.data());
+  if (rc == SMB_OK) rc = smb_sf_pack_host(sfb_rowmajor, N, kblocks, pb.data());
+  if (rc != SMB_OK) return rc;
+  const size_t a_bytes = static_cast<size_t>(M) * K / 2;
+  const size_t b_bytes = static_cast<size_t>(N) * K / 2;
+  const int64_t ldd = (static_cast<int64_t>(N) + 7) / 8 * 8;
+  const size_t d_bytes = static_cast<size_t>(M) * ldd * 2;
+  void *da = nullptr, *db = nullptr, *dsa = nullptr, *dsb = nullptr, *dd = nullptr;
+  cudaError_t e = cudaMalloc(&da, a_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&db, b_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&dsa, pa.size());
+  if (e == cudaSuccess) e = cudaMalloc(&dsb, pb.size());
+  if (e == cudaSuccess) e = cudaMalloc(&dd, d_bytes);
+  if (e == cudaSuccess) e = cudaMemcpy(da, a, a_bytes, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(db, b, b_bytes, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(dsa, pa.data(), pa.size(), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(dsb, pb.data(), pb.size(), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) rc = set_cuda_error(e, "host fp4 GEMM: allocation or upload");
+  smb_fp4_plan* plan = nullptr;
+  if (rc == SMB_OK)
+    rc = smb_fp4_plan_create(&plan, da, dsa, db, dsb, dd, M, N, K, K / 2, K / 2, ldd, SMB_FLAG_NONE);
+  if (rc == SMB_OK) rc = smb_fp4_plan_run(plan, nullptr);
+  if (rc == SMB_OK) rc = smb_fp4_plan_check(plan, nullptr);
+  if (rc == SMB_OK) {
+    e = cudaMemcpy2D(d, static_cast<size_t>(N) * 2, dd, static_cast<size_t>(ldd) * 2,
+                     static_cast<size_t>(N) * 2, M, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) rc = set_cuda_error(e, "host fp4 GEMM: download");
+  }
+  smb_fp4_plan_destroy(plan);
+  cudaFree(da);
+  cudaFree(db);
+  cudaFree(dsa);
+  cudaFree(dsb);
+  cudaFree(dd);
+  return rc;
+}

@@ -1,0 +1,98 @@
+// Accumulator read-back shared by the GEMM kernels: tensor memory -> registers (rounded to
+// bf16) -> 128-byte-swizzled shared memory -> TMA store, one independent chain per warp.
+// Counterpart of the reference's epilogue blocks (blocks/93_epi_warp_blackwell.cuh:192-321 and
+// the per-warp store chains of nvfp4/dense_gemm_nvfp4.cu:1343-1424), without CTA-wide barriers.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace smb {
+
+constexpr int kStoreCols = 64;                        // columns per store box (128 bytes of bf16)
+constexpr int kStoreBufBytes = 32 * kStoreCols * 2;   // one warp's 32 x 64 bf16 staging box
+
+struct StoreTarget {
+  const CUtensorMap* tmap_d;   // D as [M, N] bf16, box 32 x 64, 128-byte swizzle (TMA path)
+  uint16_t* d_ptr;             // D base and pitch (plain-store path)
+  int ldd;
+  int M, N;
+};
+
+// One warp drains kCols fp32 columns of its 32 TMEM lanes starting at `taddr`, then writes them
+// to D rows [row0, row0 + 32), columns [col0, col0 + kCols).
+//   Phase 1: everything is pulled into registers (two bf16 per register) and `release_bar` (a
+//   cluster-mapped mbarrier address) gets one arrival: the accumulator columns are free again
+//   before any store is issued.
+//   Phase 2: 64-column boxes go through the warp's staging buffer `sbuf` (1024-byte aligned).
+// kTmaStore = false is the path for a D whose rows are not 16-byte aligned.
+template <int kCols, bool kTmaStore>
+__device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, const StoreTarget& out,
+                                                int row0, int col0, uint32_t release_bar, int lane) {
+  static_assert(kCols % kStoreCols == 0, "whole store boxes only");
+  uint32_t packed[kCols / 2];
+#pragma unroll
+  for (int g = 0; g < kCols / 32; ++g) {
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + g * 32, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 16; ++i) packed[g * 16 + i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+  }
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) mbar_arrive_cluster(release_bar);
+
+#pragma unroll
+  for (int c = 0; c < kCols / kStoreCols; ++c) {
+    // The TMA store that last read the staging buffer must have finished reading it.
+    if (kTmaStore) {
+      if (lane == 0) bulk_wait_group_read<0>();
+    }
+    __syncwarp();
+    // Row `lane` of the box; 16-byte chunk j goes to chunk (j ^ (lane & 7)): the 128-byte
+    // swizzle the store tensor map expects.
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t dst = sbuf + lane * 128 + ((j ^ (lane & 7)) << 4);
+      st_shared_v4(dst, packed[c * 32 + 4 * j], packed[c * 32 + 4 * j + 1],
+                   packed[c * 32 + 4 * j + 2], packed[c * 32 + 4 * j + 3]);
+    }
+    const int gcol0 = col0 + c * kStoreCols;
+    if (kTmaStore) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (row0 < out.M && gcol0 < out.N) tma_store_2d(out.tmap_d, sbuf, gcol0, row0);
+        bulk_commit_group();
+      }
+    } else {
+      // Read the staged box back so that consecutive lanes write consecutive columns of a row.
+      __syncwarp();
+      for (int r = 0; r < 32; ++r) {
+        const int grow = row0 + r;
+        if (grow >= out.M) break;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int cc = h * 32 + lane;
+          const int gcol = gcol0 + cc;
+          const uint32_t src = sbuf + r * 128 + ((((cc >> 3) ^ (r & 7)) << 4) | ((cc & 7) << 1));
+          uint16_t val;
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(val) : "r"(src) : "memory");
+          if (gcol < out.N) out.d_ptr[static_cast<size_t>(grow) * out.ldd + gcol] = val;
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// Call once per warp after its last tile: outstanding stores must finish before the CTA exits.
+template <bool kTmaStore>
+__device__ __forceinline__ void drain_store_groups(int lane) {
+  if (kTmaStore) {
+    if (lane == 0) bulk_wait_group<0>();
+  }
+  __syncwarp();
+}
+
+}  // namespace smb

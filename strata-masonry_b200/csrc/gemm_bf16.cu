@@ -23,6 +23,7 @@
 // Warp roles per CTA (320 threads): warp 0 TMA producer, warp 1 MMA issue + TMEM owner,
 // warps 2-9 epilogue (warp w reads TMEM lanes 32 (w % 4) .. +31; warps 2-5 take the first
 // half of a slot's columns / slot 0, warps 6-9 the second half / slot 1).
+#include "epilogue.cuh"
 #include "gemm_common.cuh"
 #include "ptx.cuh"
 
@@ -34,8 +35,6 @@ constexpr int kBlockM = 128;          // rows of A per CTA
 constexpr int kBlockK = 64;           // K elements per stage (= 128 bytes per row)
 constexpr int kThreads = 320;
 constexpr int kEpiWarps = 8;
-constexpr int kStoreCols = 64;        // columns per TMA store box (= 128 bytes per row)
-constexpr int kStoreBufBytes = 32 * kStoreCols * 2;   // one warp's 32 x 64 bf16 box
 constexpr int kABytes = kBlockM * kBlockK * 2;        // 16 KiB
 constexpr int kTmemCols = 512;
 constexpr int kRingBudget = 192 * 1024;
@@ -249,6 +248,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (active) {
       const uint32_t leader_acc_empty0 = mapa_u32(acc_empty_bar(0), 0);
       const uint32_t sbuf = store_base + (warp - 2) * kStoreBufBytes;
+      StoreTarget out;
+      out.tmap_d = &tmap_d;
+      out.d_ptr = p.d_ptr;
+      out.ldd = p.ldd;
+      out.M = p.M;
+      out.N = p.N;
       int local = 0;
       bool ok = true;
       const bool prof = p.prof != nullptr && warp == 2 && lane == 0;
@@ -275,73 +280,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int col0 = tn * C::kTileN + tile_col;
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                static_cast<uint32_t>((NB == 1) ? bank * TN + tile_col : tile_col);
-        constexpr int kChunks = C::kColsPerWarp / kStoreCols;
-        // Phase 1: pull this warp's whole share of the slot out of tensor memory, rounding to
-        // bf16 on the way (2 columns per register), and hand the slot back to the MMA role
-        // before any store is issued.  With 256 x 512 tiles the main loop of the next tile
-        // cannot start until this has happened, so nothing slow may sit in front of it.
-        uint32_t packed[C::kColsPerWarp / 2];
-#pragma unroll
-        for (int g = 0; g < C::kColsPerWarp / 32; ++g) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(taddr + g * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) packed[g * 16 + i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
-        }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8u * slot);
-        // Phase 2: stage 32 x 64 boxes through shared memory and store them.
-#pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-          // The TMA store that last read the staging buffer must have finished reading it.
-          if (kTmaStore) {
-            if (lane == 0) bulk_wait_group_read<0>();
-          }
-          __syncwarp();
-          // Row `lane` of the 32 x 64 box; 16-byte chunk j goes to chunk (j ^ (lane & 7)):
-          // the 128-byte swizzle the store tensor map expects.
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t dst = sbuf + lane * 128 + ((j ^ (lane & 7)) << 4);
-            st_shared_v4(dst, packed[c * 32 + 4 * j], packed[c * 32 + 4 * j + 1],
-                         packed[c * 32 + 4 * j + 2], packed[c * 32 + 4 * j + 3]);
-          }
-          if (kTmaStore) {
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              if (row0 < p.M && col0 + c * kStoreCols < p.N) {
-                tma_store_2d(&tmap_d, sbuf, col0 + c * kStoreCols, row0);
-              }
-              bulk_commit_group();
-            }
-          } else {
-            // Row stride of D is not a multiple of 16 bytes: no TMA store possible.  Read the
-            // staged box back so that consecutive lanes write consecutive columns of one row.
-            __syncwarp();
-            for (int r = 0; r < 32; ++r) {
-              const int grow = row0 + r;
-              if (grow >= p.M) break;
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const int cc = h * 32 + lane;               // column inside the box
-                const int gcol = col0 + c * kStoreCols + cc;
-                const uint32_t src =
-                    sbuf + r * 128 + ((((cc >> 3) ^ (r & 7)) << 4) | ((cc & 7) << 1));
-                uint16_t val;
-                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(val) : "r"(src) : "memory");
-                if (gcol < p.N) p.d_ptr[static_cast<size_t>(grow) * p.ldd + gcol] = val;
-              }
-            }
-            __syncwarp();
-          }
-        }
+        // Pull this warp's share of the slot out of tensor memory, hand the slot back to the MMA
+        // role, then store.  With 256 x 512 tiles the main loop of the next tile cannot start
+        // until the slot is handed back, so no store sits in front of that.
+        drain_and_store<C::kColsPerWarp, kTmaStore>(taddr, sbuf, out, row0, col0,
+                                                     leader_acc_empty0 + 8u * slot, lane);
       }
-      if (kTmaStore) {
-        if (lane == 0) bulk_wait_group<0>();
-      }
+      drain_store_groups<kTmaStore>(lane);
       if (prof) {
         p.prof[blockIdx.x * kProfCount + kProfEpiWait] = waited;
         p.prof[blockIdx.x * kProfCount + kProfEpiTotal] = clock64() - t_begin;

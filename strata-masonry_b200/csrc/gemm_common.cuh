@@ -59,4 +59,20 @@ struct Bf16Launch {
 void bf16_pick_tile(int M, int N, int K, int* tile_n, int* sub_blocks);
 int bf16_launch(const Bf16Launch& L, cudaStream_t stream);
 
+// --------------------------------------------------------------------------- nvfp4 launch
+struct Fp4Launch {
+  CUtensorMap tmap_a, tmap_b0, tmap_b1, tmap_sfa, tmap_sfb, tmap_d;
+  int M, N, K;
+  int w0, w1;        // widths of the tile's N sub-blocks (w1 = 0: one sub-block)
+  bool tma_store;
+  int group_m;
+  int max_clusters;
+  void* d;
+  int ldd;
+  int* status;
+  long long* prof;
+};
+void fp4_pick_tile(int M, int N, int K, int* w0, int* w1);
+int fp4_launch(const Fp4Launch& L, cudaStream_t stream);
+
 }  // namespace smb

@@ -1,0 +1,474 @@
+// Dense block-scaled FP4 GEMM for sm_100a:
+//   D[M,N] = bf16( sum_k (A[m,k] * SFA[m,k/32]) * (B[n,k] * SFB[n,k/32]) ),  FP32 accumulate,
+// A and B are E2M1 codes, two per byte (even k in the low nibble), SFA/SFB are UE8M0 bytes in
+// the packed layout of smb_sf_packed_bytes().
+//
+// From-scratch counterpart of the reference kernel dense_gemm_nvfp4_k1_impl
+// (src/kernels/gemm/sm100a/nvfp4/dense_gemm_nvfp4.cu:1705-2250) and of its local load / MMA /
+// epilogue bodies (:448-852, :970-1333, :1343-1674).  Same numerics (kind::mxf4nvf4,
+// scale_vec::2X, UE8M0) and the same scale path (TMA -> shared memory -> tcgen05.cp -> tensor
+// memory, two K=64 instructions sharing one 4-byte scale cell through the scale-id field).
+// Differences by design: run-time M, N, K with edge predication; no multicast loads (each CTA
+// fetches its own copy of the B scales); tile widths up to 384 columns with a single
+// accumulator set, because at FP4 rates the L2 sector rate bounds narrower tiles; bounded waits.
+//
+// One cluster = 2 CTAs = one 256 x (W0 + W1) output tile, built from one or two N sub-blocks of
+// width 128 or 256.  Per 256-wide K block (= 128 bytes per row) CTA r loads
+//   A rows [m0 + 128 r, +128)                             16 KiB
+//   for sub-block h: B rows [n_h + W_h/2 r, +W_h/2)       W_h/2 x 128 B
+//   SFA for its own 128 rows                              1 KiB  (two 512-byte cells, K 0-127 / 128-255)
+//   SFB for ALL columns of the tile                       (W0 + W1)/128 KiB  (every CTA multiplies
+//                                                         its 128 rows with every column)
+// Tensor memory: accumulators first (two banks of 128 columns when the tile is 128 wide, else one
+// set of W0 + W1 columns), then a ring of scale slots, one per pipeline stage:
+//   [SFA cell 0 (4 cols) | SFA cell 1 | SFB sub-block 0: cell 0 (W0/32 cols) | cell 1 | SFB sub-block 1 ...]
+#include "epilogue.cuh"
+#include "gemm_common.cuh"
+#include "ptx.cuh"
+
+namespace smb {
+
+namespace fp4k {
+
+constexpr int kBlockM = 128;          // rows of A per CTA
+constexpr int kBlockKBytes = 128;     // bytes of K per row per stage (= 256 E2M1 values)
+constexpr int kBlockK = 256;
+constexpr int kThreads = 352;
+constexpr int kEpiWarps = 8;
+constexpr int kABytes = kBlockM * kBlockKBytes;   // 16 KiB
+constexpr int kSfCellBytes = 512;     // 128 rows x 4 scale bytes (K = 128)
+constexpr int kTmemCols = 512;
+constexpr int kRingBudget = 192 * 1024;
+
+template <int W0, int W1>
+struct Cfg {
+  static_assert(W0 == 128 || W0 == 256, "first sub-block width");
+  static_assert(W1 == 0 || W1 == 128 || W1 == 256, "second sub-block width");
+  static constexpr int kSubs = (W1 == 0) ? 1 : 2;
+  static constexpr int kTileN = W0 + W1;
+  static constexpr bool kTwoBanks = (kTileN == 128);              // epilogue overlaps next main loop
+  static constexpr int kB0Bytes = (W0 / 2) * kBlockKBytes;
+  static constexpr int kB1Bytes = (W1 / 2) * kBlockKBytes;
+  static constexpr int kSfaBytes = 2 * kSfCellBytes;              // this CTA's 128 rows, K = 256
+  static constexpr int kSfbBytes = (kTileN / 128) * 2 * kSfCellBytes;
+  static constexpr int kStageBytes = kABytes + kB0Bytes + kB1Bytes + kSfaBytes + kSfbBytes;
+  static constexpr int kOffB0 = kABytes;
+  static constexpr int kOffB1 = kOffB0 + kB0Bytes;
+  static constexpr int kOffSfa = kOffB1 + kB1Bytes;
+  static constexpr int kOffSfb = kOffSfa + kSfaBytes;
+  // Tensor memory map.
+  static constexpr int kAccCols = kTwoBanks ? 256 : kTileN;
+  static constexpr int kSfaCols = 8;                               // 2 cells x 4 columns
+  static constexpr int kSfbCols = (kTileN / 128) * 8;
+  static constexpr int kSlotCols = kSfaCols + kSfbCols;
+  static constexpr int kMaxSlots = (kTmemCols - kAccCols) / kSlotCols;
+  static constexpr int kStagesBySmem = kRingBudget / kStageBytes;
+  static constexpr int kStages = kStagesBySmem < kMaxSlots ? kStagesBySmem : kMaxSlots;
+  static constexpr int kRingBytes = kStages * kStageBytes;
+  static constexpr int kStoreBytes = kEpiWarps * kStoreBufBytes;
+  static constexpr int kTotal = 1024 + kRingBytes + kStoreBytes + 1024;
+  static constexpr int kColsPerWarp = kTileN / 2;                  // two epilogue warp groups
+  static_assert(kStageBytes % 1024 == 0, "stage bases must stay 1024-byte aligned");
+  static_assert(kColsPerWarp % kStoreCols == 0, "epilogue split");
+  static_assert(kAccCols + kStages * kSlotCols <= kTmemCols, "tensor memory budget");
+  static_assert(kTotal <= 232448, "shared memory budget");
+  static_assert(kStages >= 2, "ring depth");
+};
+
+struct Params {
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int group_m;
+  int ldd;
+  uint16_t* d_ptr;
+  int* status;
+  long long* prof;
+};
+
+enum { kProfLoadWait = 0, kProfLoadTotal, kProfMmaWaitFull, kProfMmaWaitAcc, kProfMmaTotal,
+       kProfEpiWait, kProfEpiTotal, kProfTiles, kProfCount };
+
+template <int W0, int W1, bool kTmaStore>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                  const __grid_constant__ CUtensorMap tmap_b0,
+                  const __grid_constant__ CUtensorMap tmap_b1,
+                  const __grid_constant__ CUtensorMap tmap_sfa,
+                  const __grid_constant__ CUtensorMap tmap_sfb,
+                  const __grid_constant__ CUtensorMap tmap_d, const Params p) {
+  using C = Cfg<W0, W1>;
+  constexpr int kStages = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t ring_base = smem_base;
+  const uint32_t store_base = ring_base + C::kRingBytes;
+  const uint32_t bar_base = store_base + C::kStoreBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * kStages + 4);
+  auto sf_ready_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 6 + s); };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster = static_cast<int>(cluster_id_x());
+  const int n_clusters = static_cast<int>(num_clusters_x());
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(sf_ready_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 2 * kEpiWarps);   // all epilogue warps of both CTAs
+    }
+    fence_mbar_init_cluster();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b0);
+    if (C::kSubs == 2) tma_prefetch_desc(&tmap_b1);
+    tma_prefetch_desc(&tmap_sfa);
+    tma_prefetch_desc(&tmap_sfb);
+    if (kTmaStore) tma_prefetch_desc(&tmap_d);
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(tmem_slot, kTmemCols);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      const uint32_t leader_full0 = mapa_u32(full_bar(0), 0);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      const bool prof = p.prof != nullptr;
+      long long waited = 0;
+      const long long t_begin = prof ? clock64() : 0;
+      for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+        const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
+        const int col0 = tn * C::kTileN;
+        const int band_a = tm * 2 + static_cast<int>(rank);     // 128-row band of SFA
+        const int band_b = col0 / 128;                          // first 128-row band of SFB
+        const bool has_sub1 = (C::kSubs == 2) && (col0 + W0 < p.N);   // else: right edge of D
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const long long w0 = prof ? clock64() : 0;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
+            report_status(p.status, kDevTimeoutProducer);
+            ok = false;
+            break;
+          }
+          if (prof) waited += clock64() - w0;
+          const uint32_t bar = leader_full0 + 8u * s;
+          const uint32_t dst = ring_base + s * C::kStageBytes;
+          if (rank == 0) {
+            mbar_arrive_expect_tx(full_bar(s), 2 * (C::kStageBytes - (has_sub1 ? 0 : C::kB1Bytes)));
+          }
+          tma_load_2d_pair(dst, &tmap_a, bar, kb * kBlockKBytes, row_a);
+          tma_load_2d_pair(dst + C::kOffB0, &tmap_b0, bar, kb * kBlockKBytes,
+                           col0 + static_cast<int>(rank) * (W0 / 2));
+          if (C::kSubs == 2 && has_sub1) {
+            tma_load_2d_pair(dst + C::kOffB1, &tmap_b1, bar, kb * kBlockKBytes,
+                             col0 + W0 + static_cast<int>(rank) * (W1 / 2));
+          }
+          // Scales: the packed buffer is viewed as [bands, K/128 * 64] 64-bit words; one stage
+          // covers 128 words (two 512-byte cells) of each band.
+          tma_load_2d_pair(dst + C::kOffSfa, &tmap_sfa, bar, kb * 128, band_a);
+          tma_load_2d_pair(dst + C::kOffSfb, &tmap_sfb, bar, kb * 128, band_b);
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+      if (prof) {
+        p.prof[blockIdx.x * kProfCount + kProfLoadWait] = waited;
+        p.prof[blockIdx.x * kProfCount + kProfLoadTotal] = clock64() - t_begin;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issue (leader CTA only)
+    if (rank == 0 && lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      int local = 0;
+      bool ok = true;
+      const bool prof = p.prof != nullptr;
+      long long wait_full = 0, wait_acc = 0;
+      const long long t_begin = prof ? clock64() : 0;
+      for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++local) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+        const bool has_sub1 = (C::kSubs == 2) && (tn * C::kTileN + W0 < p.N);
+        const int bank = C::kTwoBanks ? (local & 1) : 0;
+        const uint32_t use_parity =
+            static_cast<uint32_t>(C::kTwoBanks ? (local >> 1) : local) & 1u;
+        const long long a0 = prof ? clock64() : 0;
+        if (!mbar_wait(acc_empty_bar(bank), use_parity ^ 1u)) {
+          report_status(p.status, kDevTimeoutMmaAcc);
+          ok = false;
+          break;
+        }
+        if (prof) wait_acc += clock64() - a0;
+        tc_fence_after_sync();
+        const uint32_t acc_base = tmem_base + static_cast<uint32_t>(bank * 128);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          // The scale warp waited for this stage's data and copied its scales into tensor memory;
+          // its commit on sf_ready therefore also says that A and B have landed.
+          const long long w0 = prof ? clock64() : 0;
+          if (!mbar_wait(sf_ready_bar(s), ph)) {
+            report_status(p.status, kDevTimeoutMmaFull);
+            ok = false;
+            break;
+          }
+          if (prof) wait_full += clock64() - w0;
+          tc_fence_after_sync();
+          const uint32_t stage = ring_base + s * C::kStageBytes;
+          const uint32_t sf_t = tmem_base + static_cast<uint32_t>(C::kAccCols + s * C::kSlotCols);
+          const uint64_t desc_a = make_smem_desc(stage, 1024, 16, kSwizzle128B);
+#pragma unroll
+          for (int ki = 0; ki < 4; ++ki) {
+            // K = 64 per instruction = 32 bytes along the swizzled row.  Atoms 2c and 2c + 1 share
+            // scale cell c: the first reads bytes 0-1 of each cell (scale id 0), the second bytes
+            // 2-3 (scale id 2).
+            const uint32_t sf_id = (ki & 1) ? 2u : 0u;
+            const uint32_t cell = static_cast<uint32_t>(ki >> 1);
+            uint32_t sfb_col = C::kSfaCols;
+            uint32_t acc_col = 0;
+#pragma unroll
+            for (int h = 0; h < C::kSubs; ++h) {
+              const int width = (h == 0) ? W0 : W1;
+              const int bands = width / 128;
+              if (h == 0 || has_sub1) {
+                const uint64_t desc_b = make_smem_desc(stage + (h == 0 ? C::kOffB0 : C::kOffB1),
+                                                       1024, 16, kSwizzle128B);
+                const uint32_t idesc = make_idesc_mxf4(256, width, sf_id, sf_id, true);
+                mma_mxf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc,
+                               sf_t + 4u * cell,
+                               sf_t + sfb_col + cell * static_cast<uint32_t>(bands * 4),
+                               (kb > 0 || ki > 0) ? 1u : 0u);
+              }
+              sfb_col += static_cast<uint32_t>(bands * 8);
+              acc_col += static_cast<uint32_t>(width);
+            }
+          }
+          mma_commit_pair(empty_bar(s), 0x3);
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+        if (ok) mma_commit_pair(acc_full_bar(bank), 0x3);
+      }
+      if (prof) {
+        p.prof[blockIdx.x * kProfCount + kProfMmaWaitFull] = wait_full;
+        p.prof[blockIdx.x * kProfCount + kProfMmaWaitAcc] = wait_acc;
+        p.prof[blockIdx.x * kProfCount + kProfMmaTotal] = clock64() - t_begin;
+        p.prof[blockIdx.x * kProfCount + kProfTiles] = local;
+      }
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------- scale copies (leader CTA only)
+    // Scale cells go shared memory -> tensor memory with tcgen05.cp: one copy moves 32 lines of 16
+    // bytes (= 128 rows x 4 scale bytes) into 4 columns, replicated into all four lane quarters.
+    // SFB in shared memory is [band][cell][512 B]; in tensor memory, per sub-block,
+    // [cell][band][4 columns], so that one instruction of width W reads W/32 adjacent columns.
+    // The copies are issued from this warp, not from the MMA thread: issued in line with the MMAs
+    // they cost the tensor pipe about 50 cycles each (measured: 256 x 256 tiles went from 3.6 to
+    // 5.1 PFLOP/s when they moved here), from a second warp they overlap the MMAs.
+    if (rank == 0 && lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(s), ph)) {
+            report_status(p.status, kDevTimeoutMmaFull);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t stage = ring_base + s * C::kStageBytes;
+          const uint32_t sf_t = tmem_base + static_cast<uint32_t>(C::kAccCols + s * C::kSlotCols);
+          const uint64_t sfa_desc = make_smem_desc(stage + C::kOffSfa, 128, 16, kSwizzleNone);
+          const uint64_t sfb_desc = make_smem_desc(stage + C::kOffSfb, 128, 16, kSwizzleNone);
+#pragma unroll
+          for (int cell = 0; cell < 2; ++cell) {
+            tmem_cp_32x128b_warpx4<2>(sf_t + 4u * cell, sfa_desc + cell * (kSfCellBytes / 16));
+          }
+          int band0 = 0;
+          uint32_t col = C::kSfaCols;
+#pragma unroll
+          for (int h = 0; h < C::kSubs; ++h) {
+            const int bands = (h == 0 ? W0 : W1) / 128;
+#pragma unroll
+            for (int cell = 0; cell < 2; ++cell) {
+#pragma unroll
+              for (int b = 0; b < bands; ++b) {
+                tmem_cp_32x128b_warpx4<2>(sf_t + col + static_cast<uint32_t>((cell * bands + b) * 4),
+                                          sfb_desc + ((band0 + b) * 2 + cell) * (kSfCellBytes / 16));
+              }
+            }
+            band0 += bands;
+            col += static_cast<uint32_t>(bands * 8);
+          }
+          mma_commit_pair(sf_ready_bar(s), 0x1);
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue (8 warps)
+    const int quarter = warp & 3;
+    const int group = (warp - 2) >> 2;
+    const uint32_t leader_acc_empty0 = mapa_u32(acc_empty_bar(0), 0);
+    const uint32_t sbuf = store_base + (warp - 2) * kStoreBufBytes;
+    StoreTarget out;
+    out.tmap_d = &tmap_d;
+    out.d_ptr = p.d_ptr;
+    out.ldd = p.ldd;
+    out.M = p.M;
+    out.N = p.N;
+    int local = 0;
+    bool ok = true;
+    const bool prof = p.prof != nullptr && warp == 2 && lane == 0;
+    long long waited = 0;
+    const long long t_begin = prof ? clock64() : 0;
+    for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++local) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      const int bank = C::kTwoBanks ? (local & 1) : 0;
+      const uint32_t use_parity = static_cast<uint32_t>(C::kTwoBanks ? (local >> 1) : local) & 1u;
+      const long long w0 = prof ? clock64() : 0;
+      if (!mbar_wait(acc_full_bar(bank), use_parity)) {
+        if (lane == 0) report_status(p.status, kDevTimeoutEpilogue);
+        ok = false;
+        break;
+      }
+      if (prof) waited += clock64() - w0;
+      tc_fence_after_sync();
+      const int row0 = tm * 256 + static_cast<int>(rank) * kBlockM + quarter * 32;
+      const int tile_col = group * C::kColsPerWarp;
+      const int col0 = tn * C::kTileN + tile_col;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(bank * 128 + tile_col);
+      drain_and_store<C::kColsPerWarp, kTmaStore>(taddr, sbuf, out, row0, col0,
+                                                   leader_acc_empty0 + 8u * bank, lane);
+    }
+    drain_store_groups<kTmaStore>(lane);
+    if (prof) {
+      p.prof[blockIdx.x * kProfCount + kProfEpiWait] = waited;
+      p.prof[blockIdx.x * kProfCount + kProfEpiTotal] = clock64() - t_begin;
+    }
+  }
+  __syncwarp();
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<2>(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace fp4k
+
+// -----------------------------------------------------------------------------------
+// Host side
+// -----------------------------------------------------------------------------------
+namespace {
+
+template <int W0, int W1, bool kTmaStore>
+int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
+  using C = fp4k::Cfg<W0, W1>;
+  auto kernel = fp4k::gemm_nvfp4_kernel<W0, W1, kTmaStore>;
+  static thread_local int configured_device = -1;
+  static thread_local int max_clusters = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return set_error(SMB_ERR_CUDA, "cudaGetDevice failed");
+  if (configured_device != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::kTotal);
+    if (e != cudaSuccess) return set_cuda_error(e, "cudaFuncSetAttribute(nvfp4 smem)");
+    cudaLaunchConfig_t probe = {};
+    probe.gridDim = dim3(2, 1, 1);
+    probe.blockDim = dim3(fp4k::kThreads, 1, 1);
+    probe.dynamicSmemBytes = C::kTotal;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    probe.attrs = &attr;
+    probe.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kernel, &probe);
+    if (e != cudaSuccess) return set_cuda_error(e, "cudaOccupancyMaxActiveClusters(nvfp4)");
+    if (n <= 0) return set_error(SMB_ERR_CUDA, "no 2-CTA cluster of the nvfp4 kernel fits on this device");
+    max_clusters = n;
+    configured_device = dev;
+  }
+  fp4k::Params p;
+  p.M = L.M;
+  p.N = L.N;
+  p.K = L.K;
+  p.tiles_m = (L.M + 255) / 256;
+  p.tiles_n = (L.N + C::kTileN - 1) / C::kTileN;
+  p.group_m = L.group_m > 0 ? L.group_m : (C::kTileN >= 384 ? 12 : 8);
+  p.ldd = L.ldd;
+  p.d_ptr = static_cast<uint16_t*>(L.d);
+  p.status = L.status;
+  p.prof = L.prof;
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
+  if (L.max_clusters > 0 && clusters > L.max_clusters) clusters = L.max_clusters;
+  kernel<<<dim3(2 * clusters, 1, 1), dim3(fp4k::kThreads, 1, 1), C::kTotal, stream>>>(
+      L.tmap_a, L.tmap_b0, L.tmap_b1, L.tmap_sfa, L.tmap_sfb, L.tmap_d, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_cuda_error(e, "nvfp4 GEMM launch");
+  return SMB_OK;
+}
+
+template <int W0, int W1>
+int launch_fp4_store(const Fp4Launch& L, cudaStream_t stream) {
+  return L.tma_store ? launch_fp4<W0, W1, true>(L, stream) : launch_fp4<W0, W1, false>(L, stream);
+}
+
+}  // namespace
+
+void fp4_pick_tile(int M, int N, int K, int* w0, int* w1) {
+  (void)M;
+  if (N <= 128) {
+    *w0 = 128;
+    *w1 = 0;
+  } else if (N <= 256 || K < 2048) {
+    *w0 = 256;
+    *w1 = 0;
+  } else {
+    *w0 = 256;
+    *w1 = 128;
+  }
+}
+
+int fp4_launch(const Fp4Launch& L, cudaStream_t stream) {
+  if (L.w0 == 128 && L.w1 == 0) return launch_fp4_store<128, 0>(L, stream);
+  if (L.w0 == 256 && L.w1 == 0) return launch_fp4_store<256, 0>(L, stream);
+  if (L.w0 == 256 && L.w1 == 128) return launch_fp4_store<256, 128>(L, stream);
+  return set_error(SMB_ERR_INVALID, "nvfp4: unsupported tile %d + %d", L.w0, L.w1);
+}
+
+}  // namespace smb

@@ -143,3 +143,72 @@ def sf_pack_host(sf_rowmajor: np.ndarray) -> np.ndarray:
     out = np.empty(lib.smb_sf_packed_bytes(rows, kb), dtype=np.uint8)
     capi.check(lib.smb_sf_pack_host(sf.ctypes.data, rows, kb, out.ctypes.data))
     return out
+
+
+# ------------------------------------------------------------------------------- block-scaled FP4
+def dense_gemm_nvfp4_host(a_packed: np.ndarray, a_sf: np.ndarray, b_packed: np.ndarray,
+                          b_sf: np.ndarray) -> np.ndarray:
+    """Host arrays: A [M,K/2] u8, SFA [M,K/32] u8 (row-major), B [N,K/2] u8, SFB [N,K/32] u8
+    -> D [M,N] bf16 bit patterns."""
+    a = np.ascontiguousarray(a_packed, dtype=np.uint8)
+    b = np.ascontiguousarray(b_packed, dtype=np.uint8)
+    sa = np.ascontiguousarray(a_sf, dtype=np.uint8)
+    sb = np.ascontiguousarray(b_sf, dtype=np.uint8)
+    m, kh = a.shape
+    n = b.shape[0]
+    k = kh * 2
+    if b.shape[1] != kh or sa.shape != (m, k // 32) or sb.shape != (n, k // 32):
+        raise ValueError("operand shapes do not agree")
+    d = np.empty((m, n), dtype=np.uint16)
+    capi.check(capi.lib().smb_dense_gemm_nvfp4_host(a.ctypes.data, sa.ctypes.data, b.ctypes.data,
+                                                    sb.ctypes.data, d.ctypes.data, m, n, k))
+    return d
+
+
+class Fp4Plan:
+    """Tensor maps + tile choice for one (A, SFA, B, SFB, D) device buffer set (packed scales)."""
+
+    def __init__(self, a, sfa, b, sfb, d, m: int, n: int, k: int, lda_bytes: int | None = None,
+                 ldb_bytes: int | None = None, ldd: int | None = None, flags: int = 0):
+        self._lib = capi.lib()
+        self._h = C.c_void_p()
+        self.shape = (m, n, k)
+        self._keep = (a, sfa, b, sfb, d)
+        capi.check(self._lib.smb_fp4_plan_create(
+            C.byref(self._h), _ptr(a), _ptr(sfa), _ptr(b), _ptr(sfb), _ptr(d), m, n, k,
+            k // 2 if lda_bytes is None else lda_bytes, k // 2 if ldb_bytes is None else ldb_bytes,
+            n if ldd is None else ldd, flags))
+
+    def tune(self, group_m: int = 0, max_clusters: int = 0) -> None:
+        capi.check(self._lib.smb_fp4_plan_tune(self._h, group_m, max_clusters))
+
+    def set_profile(self, counters) -> None:
+        capi.check(self._lib.smb_fp4_plan_set_profile(self._h, _ptr(counters)))
+
+    def run(self, stream=None) -> None:
+        capi.check(self._lib.smb_fp4_plan_run(self._h, _stream_ptr(stream)))
+
+    def check(self, stream=None) -> None:
+        capi.check(self._lib.smb_fp4_plan_check(self._h, _stream_ptr(stream)))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.smb_fp4_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def fill_fp4_device(data, sf_packed, sf_rowmajor, rows: int, k: int, fill: int, which: int,
+                    row0: int = 0, ld_bytes: int | None = None, stream=None) -> None:
+    capi.check(capi.lib().smb_fill_fp4_device(
+        _ptr(data), k // 2 if ld_bytes is None else ld_bytes, _ptr(sf_packed), _ptr(sf_rowmajor),
+        rows, k, row0, fill, which, _stream_ptr(stream)))
+
+
+def sf_packed_bytes(rows: int, k: int) -> int:
+    return int(capi.lib().smb_sf_packed_bytes(rows, k // 32))
