@@ -1,0 +1,349 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle and the
+golden vectors produced by the reference's own verifier code.
+
+Tolerances (stated where used):
+  * north-star bound  |C - C64| <= 2^-7 |C64| + 2^-10 sqrt(K) rms(C64)  against an fp64 reference;
+  * the reference verifiers' bounds: BF16 max(0.05, 0.05 |ref|), NVFP4 max(16, 0.008 |ref|)
+    against the reference CPU path's fp32 result;
+  * exact equality where the arithmetic is exact (constant fills, generators, quantiser).
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _bits(t):
+    """bf16 CUDA tensor -> uint16 numpy."""
+    torch = _torch()
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _run_bf16(smb, m, n, k, fill, flags=0, ldd=None, group_m=0, max_clusters=0):
+    torch = _torch()
+    dev = torch.device("cuda:0")
+    a = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
+    bt = torch.empty(n, k, device=dev, dtype=torch.bfloat16)
+    ldd = n if ldd is None else ldd
+    d = torch.full((m, ldd), float("nan"), device=dev, dtype=torch.bfloat16)
+    smb.gemm.bf16_operands_device(a, bt, m, n, k, fill)
+    plan = smb.gemm.Bf16Plan(a, bt, d, m, n, k, ldd=ldd, flags=flags)
+    plan.tune(group_m, max_clusters)
+    plan.run()
+    plan.check()
+    plan.close()
+    return a, bt, d
+
+
+def _check_bf16_full(oracle, a, bt, d, n, k):
+    torch = _torch()
+    ref = a.double() @ bt.double().t()
+    got = d[:, :n].double()
+    rms = float(ref.pow(2).mean().sqrt())
+    bound = 2.0 ** -7 * ref.abs() + 2.0 ** -10 * (k ** 0.5) * rms
+    bad = ~torch.isfinite(got) | ((got - ref).abs() > bound)
+    assert int(bad.sum()) == 0, f"{int(bad.sum())} elements outside the north-star bound"
+
+
+# ------------------------------------------------------------------------------- generators
+@pytest.mark.parametrize("fill", [1, 2, 3, 4, 5, 6, 7])
+def test_device_bf16_fill_is_bit_identical_to_oracle(smb, oracle, cuda_device, fill):
+    torch = _torch()
+    m, k, n = 130, 264, 77
+    a = torch.empty(m, k, device=cuda_device, dtype=torch.bfloat16)
+    bt = torch.empty(n, k, device=cuda_device, dtype=torch.bfloat16)
+    smb.gemm.bf16_operands_device(a, bt, m, n, k, fill)
+    wa, wbt = oracle.bf16_operands(m, n, k, fill)
+    np.testing.assert_array_equal(_bits(a), wa)
+    np.testing.assert_array_equal(_bits(bt), wbt)
+    # N-shard slab with global indices.
+    slab = torch.empty(16, k, device=cuda_device, dtype=torch.bfloat16)
+    smb.gemm.bf16_operands_device(a, slab, m, 16, k, fill, n0=40, n_total=n)
+    np.testing.assert_array_equal(_bits(slab), wbt[40:56])
+
+
+@pytest.mark.parametrize("fill", [1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("which", [0, 1])
+def test_device_fp4_fill_is_bit_identical_to_oracle(smb, oracle, cuda_device, fill, which):
+    torch = _torch()
+    rows, k, row0 = 200, 384, 11
+    data = torch.empty(rows, k // 2, device=cuda_device, dtype=torch.uint8)
+    sfp = torch.empty(smb.gemm.sf_packed_bytes(rows, k), device=cuda_device, dtype=torch.uint8)
+    sfr = torch.empty(rows, k // 32, device=cuda_device, dtype=torch.uint8)
+    smb.gemm.fill_fp4_device(data, sfp, sfr, rows, k, fill, which, row0)
+    codes, sf = oracle.fp4_operand(rows, k, fill, which, row0)
+    np.testing.assert_array_equal(data.cpu().numpy(), oracle.pack_codes(codes))
+    np.testing.assert_array_equal(sfr.cpu().numpy(), sf)
+    np.testing.assert_array_equal(sfp.cpu().numpy(), oracle.sf_pack(sf))
+
+
+def test_device_quantizer_is_bit_identical_to_oracle(smb, oracle, cuda_device):
+    torch = _torch()
+    rng = np.random.default_rng(21)
+    x = (rng.standard_normal((96, 512)) * np.exp2(rng.integers(-8, 8, (96, 1)))).astype(np.float32)
+    x[0, :32] = 0
+    x[1, :8] = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0]
+    x[1, 8:32] = 0
+    xs = torch.from_numpy(x).to(cuda_device)
+    data = torch.empty(96, 256, device=cuda_device, dtype=torch.uint8)
+    sfp = torch.empty(smb.gemm.sf_packed_bytes(96, 512), device=cuda_device, dtype=torch.uint8)
+    sfr = torch.empty(96, 16, device=cuda_device, dtype=torch.uint8)
+    smb.capi.check(smb.capi.lib().smb_quantize_mx_device(
+        xs.data_ptr(), 512, data.data_ptr(), 256, sfp.data_ptr(), sfr.data_ptr(), 96, 512, None))
+    torch.cuda.synchronize()
+    codes, sf = oracle.quantize_mx(x)
+    np.testing.assert_array_equal(sfr.cpu().numpy(), sf)
+    np.testing.assert_array_equal(data.cpu().numpy(), oracle.pack_codes(codes))
+    # "Dequantised operands match bit-exactly": decode both and compare.
+    np.testing.assert_array_equal(
+        oracle.dequantize(oracle.unpack_codes(data.cpu().numpy()), sfr.cpu().numpy()).view(np.uint32),
+        oracle.dequantize(codes, sf).view(np.uint32))
+
+
+# ------------------------------------------------------------------------------- BF16 GEMM
+@pytest.mark.parametrize("fill", [1, 2, 3, 4])
+def test_bf16_smoke_against_reference_golden(smb, oracle, golden, cuda_device, fill):
+    """The reference's smoke case (--shape=256,64,128): output vs the reference CPU path."""
+    m, k, n = 256, 64, 128
+    a, bt, d = _run_bf16(smb, m, n, k, fill)
+    got = _bits(d)
+    want = golden[f"bf16_smoke_out_m{fill}"]
+    # Verifier tolerance on every element (it samples 64; here all 32768).
+    ok, bad = oracle.check_verifier_bf16(got, oracle.bf16_to_f32(want))
+    assert ok, bad
+    # And bit-level: fp32 accumulation order may move a result by one bf16 ulp at most.
+    diff = np.abs(got.astype(np.int32) - want.astype(np.int32))
+    assert diff.max() <= 1 and (diff == 0).mean() > 0.99
+    if fill == 3:
+        assert np.all(oracle.bf16_to_f32(got) == 64.0)
+
+
+def test_bf16_smoke_through_host_entry_point(smb, oracle, cuda_device):
+    a_bits, bt_bits = oracle.bf16_operands(256, 128, 64, 1)
+    d = smb.gemm.dense_gemm_bf16_host(a_bits, bt_bits)
+    ref = oracle.gemm_f64(oracle.bf16_to_f32(a_bits), oracle.bf16_to_f32(bt_bits))
+    ok, ratio, bad = oracle.check_north_star(d, ref, 64)
+    assert ok, (ratio, bad)
+
+
+@pytest.mark.parametrize("shape", [
+    (256, 64, 128),      # BASELINE config 1 read as M=256, N=64, K=128
+    (256, 256, 64),
+    (512, 512, 512),
+    (300, 200, 72),      # ragged everywhere
+    (1, 8, 8),           # minimum
+    (257, 513, 136),
+    (1024, 2048, 4096),
+    (2048, 2624, 2048),  # N tail inside a 512-wide tile
+])
+@pytest.mark.parametrize("fill", [2, 5])
+def test_bf16_shapes_against_fp64(smb, oracle, cuda_device, shape, fill):
+    m, n, k = shape
+    a, bt, d = _run_bf16(smb, m, n, k, fill)
+    _check_bf16_full(oracle, a, bt, d, n, k)
+
+
+@pytest.mark.parametrize("flags_name", ["FLAG_TILE_N_64", "FLAG_TILE_N_128", "FLAG_TILE_N_256",
+                                        "FLAG_TILE_N_512", "FLAG_FORCE_PLAIN_STORE"])
+def test_bf16_every_tile_configuration(smb, oracle, cuda_device, flags_name):
+    flags = getattr(smb.capi, flags_name)
+    m, n, k = 768, 1088, 2112
+    a, bt, d = _run_bf16(smb, m, n, k, 5, flags=flags)
+    _check_bf16_full(oracle, a, bt, d, n, k)
+
+
+def test_bf16_ragged_edge_case(smb, oracle, cuda_device):
+    """BASELINE config 5's ragged case: M=4095, N=12289, K=4160.  D's row pitch (24578 B) is not a
+    multiple of 16, so this runs the plain-store epilogue; rows of A/B are 16-byte aligned."""
+    torch = _torch()
+    m, n, k = 4095, 12289, 4160
+    a, bt, d = _run_bf16(smb, m, n, k, 6)
+    rows, cols = oracle.sample_coordinates(m, n, 4096)
+    # Sampled fp64 check on the GPU operands plus full tiles on every edge.
+    ra = torch.from_numpy(rows).to(cuda_device)
+    ca = torch.from_numpy(cols).to(cuda_device)
+    ref = (a[ra].double() * bt[ca].double()).sum(1)
+    full = a[-300:].double() @ bt.double().t()
+    rms = float(full.pow(2).mean().sqrt())
+    got = d[ra, ca].double()
+    bound = 2.0 ** -7 * ref.abs() + 2.0 ** -10 * (k ** 0.5) * rms
+    assert int(((got - ref).abs() > bound).sum()) == 0
+    got_full = d[-300:].double()
+    bound = 2.0 ** -7 * full.abs() + 2.0 ** -10 * (k ** 0.5) * rms
+    assert int(((got_full - full).abs() > bound).sum()) == 0
+    right = a.double() @ bt[-130:].double().t()
+    bound = 2.0 ** -7 * right.abs() + 2.0 ** -10 * (k ** 0.5) * rms
+    assert int(((d[:, -130:].double() - right).abs() > bound).sum()) == 0
+
+
+def test_bf16_padded_output_rows_are_not_touched(smb, oracle, cuda_device):
+    """Canary columns beyond N (ldd > N) must keep their contents: no out-of-range store."""
+    torch = _torch()
+    m, n, k, ldd = 300, 200, 128, 264
+    a, bt, d = _run_bf16(smb, m, n, k, 2, ldd=ldd)
+    assert bool(torch.isnan(d[:, n:]).all())
+    _check_bf16_full(oracle, a, bt, d, n, k)
+
+
+def test_bf16_8192_cubed_properties(smb, oracle, cuda_device):
+    """BASELINE config 2 at full size: sampled fp64 check, constant-fill exactness (every element
+    written once and only once), independence from the tile walk order."""
+    torch = _torch()
+    m = n = k = 8192
+    a, bt, d = _run_bf16(smb, m, n, k, 5)
+    rows, cols = oracle.sample_coordinates(m, n, 8192)
+    ra = torch.from_numpy(rows).to(cuda_device)
+    ca = torch.from_numpy(cols).to(cuda_device)
+    ref = (a[ra].double() * bt[ca].double()).sum(1)
+    # rms of the full product estimated from a 512 x 8192 slab in fp64.
+    rms = float((a[:512].double() @ bt.double().t()).pow(2).mean().sqrt())
+    bound = 2.0 ** -7 * ref.abs() + 2.0 ** -10 * (k ** 0.5) * rms
+    assert int(((d[ra, ca].double() - ref).abs() > bound).sum()) == 0
+    # Same product under another raster and another cluster count: bit-identical.
+    _, _, d2 = _run_bf16(smb, m, n, k, 5, group_m=5, max_clusters=37)
+    assert torch.equal(d.view(torch.int16), d2.view(torch.int16))
+    _, _, d3 = _run_bf16(smb, m, n, k, 3)
+    assert bool((d3 == 8192.0).all())
+
+
+def test_bf16_argument_errors_on_device(smb, cuda_device):
+    torch = _torch()
+    t = torch.zeros(1024, device=cuda_device, dtype=torch.bfloat16)
+    with pytest.raises(smb.capi.SmbError) as e:
+        smb.gemm.Bf16Plan(t, t, t, 16, 16, 20)        # K % 8
+    assert e.value.code == smb.capi.SMB_ERR_UNSUPPORTED
+    with pytest.raises(smb.capi.SmbError) as e:
+        smb.gemm.Bf16Plan(t[1:], t, t, 16, 16, 16)    # misaligned A
+    assert e.value.code == smb.capi.SMB_ERR_INVALID
+
+
+# ------------------------------------------------------------------------------- NVFP4 GEMM
+LUT = [0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6]
+
+
+def _fp4_operand(smb, rows, k, fill, which, row0=0):
+    torch = _torch()
+    dev = torch.device("cuda:0")
+    data = torch.empty(rows, k // 2, device=dev, dtype=torch.uint8)
+    sfp = torch.empty(smb.gemm.sf_packed_bytes(rows, k), device=dev, dtype=torch.uint8)
+    sfr = torch.empty(rows, k // 32, device=dev, dtype=torch.uint8)
+    smb.gemm.fill_fp4_device(data, sfp, sfr, rows, k, fill, which, row0)
+    return data, sfp, sfr
+
+
+def _dequant(data, sfr):
+    torch = _torch()
+    lut = torch.tensor(LUT, device=data.device, dtype=torch.float64)
+    lo = lut[(data & 15).long()]
+    hi = lut[(data >> 4).long()]
+    v = torch.stack([lo, hi], dim=-1).reshape(data.shape[0], -1)
+    return v * torch.exp2(sfr.double() - 127).repeat_interleave(32, dim=1)
+
+
+def _run_fp4(smb, m, n, k, fill, flags=0, fill_a=None):
+    torch = _torch()
+    a, sfa, sfar = _fp4_operand(smb, m, k, fill if fill_a is None else fill_a, 0)
+    b, sfb, sfbr = _fp4_operand(smb, n, k, fill, 1)
+    d = torch.full((m, n), float("nan"), device=a.device, dtype=torch.bfloat16)
+    plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k, flags=flags)
+    plan.run()
+    plan.check()
+    plan.close()
+    return (a, sfar), (b, sfbr), d
+
+
+def _check_fp4_full(A, B, d, k):
+    torch = _torch()
+    ref = _dequant(*A) @ _dequant(*B).t()
+    rms = float(ref.pow(2).mean().sqrt())
+    bound = 2.0 ** -7 * ref.abs() + 2.0 ** -10 * (k ** 0.5) * rms
+    got = d.double()
+    bad = ~torch.isfinite(got) | ((got - ref).abs() > bound)
+    assert int(bad.sum()) == 0, f"{int(bad.sum())} elements outside the north-star bound"
+
+
+@pytest.mark.parametrize("fill", [1, 2, 3, 4])
+def test_fp4_smoke_against_reference_golden(smb, oracle, golden, cuda_device, fill):
+    """The reference's smoke case (--shape=256,256,128): output vs the reference CPU path."""
+    A, B, d = _run_fp4(smb, 256, 128, 256, fill)
+    got = _bits(d)
+    want = golden[f"fp4_smoke_out_m{fill}"]
+    ok, bad = oracle.check_verifier_nvfp4(got, oracle.bf16_to_f32(want))
+    assert ok, bad
+    diff = np.abs(got.astype(np.int32) - want.astype(np.int32))
+    assert diff.max() <= 1
+    if fill in (1, 3):
+        # Powers of two throughout: exact, any layout slip in the scale path shows here.
+        np.testing.assert_array_equal(got, want)
+
+
+def test_fp4_smoke_through_host_entry_point(smb, oracle, cuda_device):
+    a_codes, a_sf = oracle.fp4_operand(256, 256, 2, 0)
+    b_codes, b_sf = oracle.fp4_operand(128, 256, 2, 1)
+    d = smb.gemm.dense_gemm_nvfp4_host(oracle.pack_codes(a_codes), a_sf, oracle.pack_codes(b_codes), b_sf)
+    ref = oracle.gemm_f64(oracle.dequantize(a_codes, a_sf), oracle.dequantize(b_codes, b_sf))
+    ok, ratio, bad = oracle.check_north_star(d, ref, 256)
+    assert ok, (ratio, bad)
+    ref32 = oracle.bf16_to_f32(oracle.gemm_nvfp4_reference(a_codes, a_sf, b_codes, b_sf))
+    ok, bad = oracle.check_verifier_nvfp4(d, ref32)
+    assert ok, bad
+
+
+@pytest.mark.parametrize("shape", [
+    (256, 128, 256), (512, 256, 1024), (512, 768, 1024), (512, 640, 1024), (300, 200, 96),
+    (1, 1, 32), (1000, 1000, 1056), (1024, 1024, 2048), (2048, 2048, 8192),
+])
+@pytest.mark.parametrize("fill", [2, 5])
+def test_fp4_shapes_against_fp64(smb, cuda_device, shape, fill):
+    m, n, k = shape
+    A, B, d = _run_fp4(smb, m, n, k, fill)
+    _check_fp4_full(A, B, d, k)
+
+
+@pytest.mark.parametrize("flags_name", ["FLAG_TILE_N_128", "FLAG_TILE_N_256", "FLAG_TILE_N_384",
+                                        "FLAG_FORCE_PLAIN_STORE"])
+@pytest.mark.parametrize("fill", [3, 4, 5])
+def test_fp4_every_tile_configuration(smb, cuda_device, flags_name, fill):
+    flags = getattr(smb.capi, flags_name)
+    m, n, k = 768, 1088, 2112 - 2112 % 32
+    A, B, d = _run_fp4(smb, m, n, k, fill, flags=flags)
+    _check_fp4_full(A, B, d, k)
+
+
+def test_fp4_flagship_samples_against_reference_golden(smb, oracle, golden, cuda_device):
+    """The reference verifier's `flagship` case (30720 x 4096 x 8192, fill 2): its own sampled
+    reference values, its own tolerance."""
+    torch = _torch()
+    m, k, n = (int(x) for x in golden["fp4_flagship_shape"])
+    A, B, d = _run_fp4(smb, m, n, k, 2)
+    rows, cols = golden["fp4_flagship_rows"], golden["fp4_flagship_cols"]
+    got = d[torch.from_numpy(rows).to(d.device), torch.from_numpy(cols).to(d.device)]
+    ok, bad = oracle.check_verifier_nvfp4(_bits(got), golden["fp4_flagship_ref_m2"])
+    assert ok, bad
+
+
+def test_fp4_8192_cubed_properties(smb, oracle, cuda_device):
+    """BASELINE config 3 at full size (quantised Gaussian operands): sampled fp64 check and the
+    closed form of the constant fill."""
+    torch = _torch()
+    m = n = k = 8192
+    A, B, d = _run_fp4(smb, m, n, k, 5)
+    rows, cols = oracle.sample_coordinates(m, n, 4096)
+    ra = torch.from_numpy(rows).to(d.device)
+    ca = torch.from_numpy(cols).to(d.device)
+    da = _dequant(A[0][ra], A[1][ra])
+    db = _dequant(B[0][ca], B[1][ca])
+    ref = (da * db).sum(1)
+    rms = float((_dequant(A[0][:256], A[1][:256]) @ _dequant(*B).t()).pow(2).mean().sqrt())
+    bound = 2.0 ** -7 * ref.abs() + 2.0 ** -10 * (k ** 0.5) * rms
+    assert int(((d[ra, ca].double() - ref).abs() > bound).sum()) == 0
+    _, _, d3 = _run_fp4(smb, m, n, k, 3)
+    mm = torch.arange(m, device=d.device).view(-1, 1)
+    nn = torch.arange(n, device=d.device).view(1, -1)
+    exact = (k * torch.exp2((mm % 5) - 2.0) * torch.exp2((nn % 3) - 1.0)).to(torch.bfloat16)
+    assert torch.equal(d3, exact)
