@@ -1,0 +1,420 @@
+#!/usr/bin/env python
+"""Headline benchmark of the dense GEMM path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one batch of synthetic input: one GEMM of the
+named workload (default: BF16 8192^3, operands N(0,1)*0.1 stand-in, FP32 accumulate, BF16 out).
+With N > 1 (launched under torch.distributed.run, one rank per GPU) the N dimension is sharded
+column-parallel: rank r computes D[:, r*N/g : (r+1)*N/g] with no communication in the kernel;
+the optional all-gather of D is timed separately and reported under "allgather".
+
+Rank 0 prints ONE JSON line.  `value` is whole-job TFLOP/s with operands resident in HBM
+(device-timed, max over ranks); `e2e` is the same metric through the host-buffer entry point of
+the C ABI with the host<->device copies inside the timed region; `roofline` relates the kernel
+to the measured tensor peak; `cpu_baseline` is the reference's NumPy CPU path timed on this
+host's cores on a bounded sample.
+
+`--impl reference` times that NumPy CPU path alone (the reference has no other CPU
+implementation of this path), on the same metric and config.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (kind, M, N, K, fill, description)
+    "bf16_8192": ("bf16", 8192, 8192, 8192, 5, "dense BF16 GEMM M=N=K=8192, operands N(0,1)*0.1 stand-in"),
+    "nvfp4_8192": ("nvfp4", 8192, 8192, 8192, 5, "dense NVFP4 GEMM M=N=K=8192, quantised N(0,1) stand-in"),
+    "bf16_large": ("bf16", 32768, 57344, 8192, 6, "dense BF16 GEMM 32768x57344x8192, operands N(0,1)*0.05 stand-in"),
+    "bf16_smoke": ("bf16", 256, 128, 64, 2, "reference smoke shape 256x128x64, fill 2"),
+}
+
+# DRAM bytes per launch of the BF16 8192^3 kernel from the committed ncu capture
+# (profiles/bf16_gemm_8192.md: dram__bytes_read.sum + dram__bytes_write.sum).
+NCU_TRAFFIC_BYTES = {"bf16_8192": None, "nvfp4_8192": None}
+
+THROTTLE_BITS = {
+    0x4: "sw_power_cap",
+    0x8: "hw_slowdown",
+    0x20: "sw_thermal_slowdown",
+    0x40: "hw_thermal_slowdown",
+    0x80: "hw_power_brake_slowdown",
+}
+
+
+def _load_oracle():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("smb_oracle", ROOT / "oracle" / "oracle.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    def __init__(self, uuid: str | None, index: int, period_s: float = 0.01):
+        self.period = period_s
+        self.samples: list[tuple[int, int, float]] = []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            h = None
+            if uuid:
+                try:
+                    h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if isinstance(uuid, str) else uuid)
+                except Exception:
+                    h = None
+            if h is None:
+                h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self._h = h
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._h = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                mhz = int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                reasons = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                try:
+                    watts = nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0
+                except Exception:
+                    watts = float("nan")
+                self.samples.append((mhz, reasons, watts))
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self._h is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+
+    def summary(self):
+        if not self.samples:
+            return None
+        mhz = sorted(s[0] for s in self.samples)
+        bits = 0
+        for s in self.samples:
+            bits |= s[1]
+        reasons = [name for bit, name in THROTTLE_BITS.items() if bits & bit]
+        watts = [s[2] for s in self.samples if s[2] == s[2]]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(mhz), "power_w_max": round(max(watts), 1) if watts else None}
+
+
+def _peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()), "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def cpu_gemm_rate(oracle, a_bits, bt_bits, budget_s: float):
+    """Time the reference's CPU path (bf16 -> fp32, fp32 matmul, round to bf16) on as large a
+    square sub-block as fits the time budget.  Returns (TFLOP/s, description, seconds)."""
+    k = a_bits.shape[1]
+    probe = min(512, a_bits.shape[0], bt_bits.shape[0])
+    t0 = time.perf_counter()
+    oracle.gemm_bf16_reference(a_bits[:probe], bt_bits[:probe])
+    dt = max(time.perf_counter() - t0, 1e-4)
+    rate = 2.0 * probe * probe * k / dt
+    side = int((budget_s * rate / (2.0 * k)) ** 0.5)
+    side = max(256, min(side // 256 * 256, a_bits.shape[0], bt_bits.shape[0]))
+    best = None
+    for _ in range(2):
+        t0 = time.perf_counter()
+        oracle.gemm_bf16_reference(a_bits[:side], bt_bits[:side])
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return 2.0 * side * side * k / best / 1e12, f"{side}x{side}x{k} sub-block of the workload, best of 2", best
+
+
+def run_reference(args):
+    """The reference arm: the reference's NumPy CPU GEMM on this host's cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    kind, m, n, k, fill, desc = WORKLOADS[args.workload]
+    oracle = _load_oracle()
+    cores = os.cpu_count() or 1
+    steps, warmup = args.steps, args.warmup
+    # Bounded sample: the whole run must end within a few minutes.
+    per_step_budget = max(0.05, min(2.0, 120.0 / max(1, steps + warmup)))
+    rows = min(m, 4096)
+    cols = min(n, 4096)
+    if kind == "bf16":
+        a_bits, bt_bits = oracle.bf16_operands(min(rows, 1024), min(cols, 1024), k, 2 if fill > 4 else fill)
+        # Tile the small generated block up to the sample size: the timing does not depend on values.
+        a_bits = np.tile(a_bits, (max(1, rows // a_bits.shape[0]), 1))
+        bt_bits = np.tile(bt_bits, (max(1, cols // bt_bits.shape[0]), 1))
+        run = lambda side: oracle.gemm_bf16_reference(a_bits[:side], bt_bits[:side])
+    else:
+        ac, asf = oracle.fp4_operand(min(rows, 512), k, 2, 0)
+        bc, bsf = oracle.fp4_operand(min(cols, 512), k, 2, 1)
+        reps = max(1, rows // ac.shape[0])
+        ac, asf = np.tile(ac, (reps, 1)), np.tile(asf, (reps, 1))
+        bc, bsf = np.tile(bc, (reps, 1)), np.tile(bsf, (reps, 1))
+        run = lambda side: oracle.gemm_nvfp4_reference(ac[:side], asf[:side], bc[:side], bsf[:side])
+    limit = min(a_bits.shape[0], bt_bits.shape[0]) if kind == "bf16" else min(ac.shape[0], bc.shape[0])
+    probe = min(256, limit)
+    t0 = time.perf_counter()
+    run(probe)
+    rate = 2.0 * probe * probe * k / max(time.perf_counter() - t0, 1e-4)
+    side = int((per_step_budget * rate / (2.0 * k)) ** 0.5)
+    side = max(128, min(side // 128 * 128, limit))
+    for _ in range(warmup):
+        run(side)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run(side)
+    dt = time.perf_counter() - t0
+    flops = 2.0 * side * side * k * steps
+    value = flops / dt / 1e12
+    line = {
+        "impl": "reference", "metric": "GEMM TFLOPS", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt / steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16" if kind == "bf16" else "e2m1", "data": "synthetic",
+        "config": {"workload": args.workload, "description": desc, "shape_mnk": [m, n, k],
+                   "step": f"reference NumPy CPU path on a {side}x{side}x{k} sub-block"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": f"{side}x{side}x{k} sub-block per step, {steps} steps"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="bf16_8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--allgather", action="store_true", help="also time the all-gather of D (N > 1)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=8)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import __graft_entry__ as entry
+
+    smb = entry.load_package()
+    smb.capi.lib()   # fails loudly if the CUDA library is missing: there is no CPU fallback
+    oracle = None
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+    g = world
+
+    kind, m, n, k, fill, desc = WORKLOADS[args.workload]
+    if n % g != 0 or (n // g) % 8 != 0:
+        raise SystemExit(f"N={n} cannot be sharded {g} ways with 16-byte-aligned rows")
+    n_local = n // g
+    n0 = rank * n_local
+    stream = torch.cuda.current_stream()
+
+    # ---------------------------------------------------------------- operands, resident in HBM
+    if kind == "bf16":
+        a = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
+        bt = torch.empty(n_local, k, device=dev, dtype=torch.bfloat16)
+        d = torch.empty(m, n_local, device=dev, dtype=torch.bfloat16)
+        smb.gemm.bf16_operands_device(a, bt, m, n_local, k, fill, n0=n0, n_total=n, stream=stream)
+        plan = smb.gemm.Bf16Plan(a, bt, d, m, n_local, k)
+        resident_bytes = a.numel() * 2 + bt.numel() * 2 + d.numel() * 2
+        dtype = "bf16"
+    else:
+        a = torch.empty(m, k // 2, device=dev, dtype=torch.uint8)
+        sfa = torch.empty(smb.gemm.sf_packed_bytes(m, k), device=dev, dtype=torch.uint8)
+        bt = torch.empty(n_local, k // 2, device=dev, dtype=torch.uint8)
+        sfb = torch.empty(smb.gemm.sf_packed_bytes(n_local, k), device=dev, dtype=torch.uint8)
+        d = torch.empty(m, n_local, device=dev, dtype=torch.bfloat16)
+        smb.gemm.fill_fp4_device(a, sfa, None, m, k, fill, 0, 0, stream=stream)
+        smb.gemm.fill_fp4_device(bt, sfb, None, n_local, k, fill, 1, n0, stream=stream)
+        plan = smb.gemm.Fp4Plan(a, sfa, bt, sfb, d, m, n_local, k)
+        resident_bytes = a.numel() + bt.numel() + sfa.numel() + sfb.numel() + d.numel() * 2
+        dtype = "e2m1"
+    torch.cuda.synchronize()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------------------------------------------------------- device-timed region
+    for _ in range(args.warmup):
+        plan.run(stream)
+    plan.check(stream)
+    uuid = None
+    try:
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(dev).uuid)
+    except Exception:
+        uuid = None
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(uuid, local_rank) as sampler:
+        e0.record(stream)
+        for _ in range(args.steps):
+            plan.run(stream)
+        e1.record(stream)
+        barrier()
+    plan.check(stream)
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_local = e0.elapsed_time(e1)
+    ms_step = ms_total / args.steps
+    flops_step = 2.0 * m * n * k
+    value = flops_step / (ms_step * 1e-3) / 1e12
+    clocks = sampler.summary()
+
+    # ---------------------------------------------------------------- roofline of the kernel
+    peaks, peak_kind = _peaks()
+    launch_ms = ms_local / args.steps
+    achieved = 2.0 * m * n_local * k / (launch_ms * 1e-3) / 1e12
+    timed_s = ms_total * 1e-3
+    if kind == "bf16":
+        peak = peaks["bf16_tflops"] if timed_s < 2.0 else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+        peak_note = f"{peak_kind} cuBLAS bf16 {'burst' if timed_s < 2.0 else 'sustained'} TFLOP/s"
+    else:
+        # No FP4 entry in the measured peaks: four times the measured dense bf16 rate (the ratio
+        # of the nominal dense FP4 and BF16 figures, 9 and 2.25 PFLOP/s).
+        base = peaks["bf16_tflops"] if timed_s < 2.0 else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+        peak = 4.0 * base
+        peak_note = f"4 x {peak_kind} cuBLAS bf16 TFLOP/s (no measured FP4 figure)"
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                "peak_source": peak_note,
+                "nominal_frac": achieved / (2250.0 if kind == "bf16" else 9000.0)}
+
+    # ---------------------------------------------------------------- optional all-gather of D
+    allgather = None
+    if dist is not None and args.allgather:
+        gathered = torch.empty(g, m, n_local, device=dev, dtype=torch.bfloat16)
+        for _ in range(2):
+            dist.all_gather_into_tensor(gathered, d)
+        barrier()
+        g0 = torch.cuda.Event(enable_timing=True)
+        g1 = torch.cuda.Event(enable_timing=True)
+        g0.record()
+        reps = 5
+        for _ in range(reps):
+            dist.all_gather_into_tensor(gathered, d)
+        g1.record()
+        barrier()
+        ag_ms = max_over_ranks(g0.elapsed_time(g1)) / reps
+        recv = (g - 1) * m * n_local * 2
+        allgather = {"ms": ag_ms, "recv_gb_per_s_per_gpu": recv / (ag_ms * 1e-3) / 1e9,
+                     "layout": "rank-major [g, M, N/g]"}
+        del gathered
+
+    # ---------------------------------------------------------------- end to end, host buffers
+    e2e = None
+    if kind == "bf16":
+        a_host = torch.empty(m, k, dtype=torch.int16).pin_memory()
+        bt_host = torch.empty(n_local, k, dtype=torch.int16).pin_memory()
+        d_host = torch.empty(m, n_local, dtype=torch.int16).pin_memory()
+        a_host.copy_(a.view(torch.int16))
+        bt_host.copy_(bt.view(torch.int16))
+        ctx = smb.gemm.Bf16HostContext(m, n_local, k)
+        for _ in range(2):
+            ctx.run(a_host, bt_host, d_host)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            ctx.run(a_host, bt_host, d_host)
+        barrier()
+        e2e_s = max_over_ranks(time.perf_counter() - t0) / args.e2e_steps
+        same = bool(torch.equal(d_host, d.view(torch.int16).cpu()))
+        e2e = {"value": flops_step / e2e_s / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(a_host.numel() * 2 + bt_host.numel() * 2),
+               "d2h_bytes_per_step": int(d_host.numel() * 2), "ms_per_step": e2e_s * 1e3,
+               "steps": args.e2e_steps, "matches_device_path": same,
+               "api": "smb_bf16_host_ctx_run (pinned host buffers, per-GPU shard)"}
+        ctx.close()
+
+    # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1)
+    cpu_baseline = None
+    if rank == 0 and g == 1 and not args.no_cpu_baseline and kind == "bf16":
+        oracle = _load_oracle()
+        rows = min(m, 4096)
+        a_np = a_host[:rows].numpy().view(np.uint16)
+        bt_np = bt_host[:min(n_local, 4096)].numpy().view(np.uint16)
+        rate, sample, secs = cpu_gemm_rate(oracle, a_np, bt_np, budget_s=8.0)
+        cpu_baseline = {"value": rate, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                        "sample": sample + f" ({secs:.2f} s)",
+                        "what": "reference NumPy CPU path: bf16 operands -> fp32, a @ b, round to bf16"}
+
+    plan.close()
+    if rank == 0:
+        line = {
+            "metric": "GEMM TFLOPS", "value": value, "unit": "TFLOP/s", "n_gpus": g,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": dtype, "data": "synthetic",
+            "config": {"workload": args.workload, "description": desc, "shape_mnk": [m, n, k],
+                       "sharding": f"N column-parallel over {g} GPU(s), {n_local} columns each",
+                       "l2": f"operands + output resident per GPU = {resident_bytes / 1e6:.0f} MB > 126 MB L2 (no flush)",
+                       "per_gpu_tflops": value / g},
+            "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "gpu_launches": args.steps, "allgather": allgather,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

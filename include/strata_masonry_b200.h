@@ -141,6 +141,14 @@ int smb_dense_gemm_bf16(const void* a, const void* bt, void* d, int M, int N, in
  * these steps inline (dense_gemm_bf16.cu:293-307, :401-404). */
 int smb_dense_gemm_bf16_host(const uint16_t* a, const uint16_t* bt, uint16_t* d, int M, int N, int K);
 
+/* The same with the device buffers, plan and stream kept between calls: create once for a
+ * shape, then every run uploads A and BT, launches, downloads D and synchronises.  Pass pinned
+ * host memory for full copy bandwidth. */
+typedef struct smb_bf16_host_ctx smb_bf16_host_ctx;
+int smb_bf16_host_ctx_create(smb_bf16_host_ctx** ctx, int M, int N, int K);
+int smb_bf16_host_ctx_run(smb_bf16_host_ctx* ctx, const uint16_t* a, const uint16_t* bt, uint16_t* d);
+int smb_bf16_host_ctx_destroy(smb_bf16_host_ctx* ctx);
+
 /* ------------------------------------------------------------------------------------
  * Dense block-scaled FP4 GEMM ("NVFP4" in the reference):
  *   D[M,N] = bf16_rne( sum_k (A[m,k] SFA[m,k/32]) (B[n,k] SFB[n,k/32]) ), FP32 accumulate.

@@ -58,6 +58,9 @@ DECLARED = [
     ("smb_bf16_plan_set_profile", _i, [_vp, _vp]),
     ("smb_dense_gemm_bf16", _i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     ("smb_dense_gemm_bf16_host", _i, [_vp, _vp, _vp, _i, _i, _i]),
+    ("smb_bf16_host_ctx_create", _i, [C.POINTER(_vp), _i, _i, _i]),
+    ("smb_bf16_host_ctx_run", _i, [_vp, _vp, _vp, _vp]),
+    ("smb_bf16_host_ctx_destroy", _i, [_vp]),
     ("smb_fp4_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, C.c_uint]),
     ("smb_fp4_plan_run", _i, [_vp, _vp]),
     ("smb_fp4_plan_check", _i, [_vp, _vp]),

@@ -154,36 +154,85 @@ extern "C" int smb_dense_gemm_bf16(const void* a, const void* bt, void* d, int M
   return rc;
 }
 
+// ------------------------------------------------------------------------------------
+// Host-buffer context: device buffers, plan and stream are created once; every run uploads
+// A and BT, launches, downloads D and synchronises.
+// ------------------------------------------------------------------------------------
+struct smb_bf16_host_ctx {
+  int M, N, K;
+  int64_t ldd;
+  void *da, *db, *dd;
+  smb_bf16_plan* plan;
+  cudaStream_t stream;
+};
+
+extern "C" int smb_bf16_host_ctx_destroy(smb_bf16_host_ctx* ctx) {
+  if (ctx == nullptr) return SMB_OK;
+  smb_bf16_plan_destroy(ctx->plan);
+  if (ctx->da) cudaFree(ctx->da);
+  if (ctx->db) cudaFree(ctx->db);
+  if (ctx->dd) cudaFree(ctx->dd);
+  if (ctx->stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return SMB_OK;
+}
+
+extern "C" int smb_bf16_host_ctx_create(smb_bf16_host_ctx** out, int M, int N, int K) {
+  if (out == nullptr) return set_error(SMB_ERR_INVALID, "host context: null output handle");
+  *out = nullptr;
+  if (M <= 0 || N <= 0 || K <= 0) return set_error(SMB_ERR_INVALID, "host context: bad dimensions");
+  smb_bf16_host_ctx* c = new (std::nothrow) smb_bf16_host_ctx();
+  if (c == nullptr) return set_error(SMB_ERR_NOMEM, "host context: out of host memory");
+  c->M = M;
+  c->N = N;
+  c->K = K;
+  // Pad rows of D to 8 elements so that the TMA-store epilogue is always usable.
+  c->ldd = (static_cast<int64_t>(N) + 7) / 8 * 8;
+  c->da = c->db = c->dd = nullptr;
+  c->plan = nullptr;
+  c->stream = nullptr;
+  int rc = SMB_OK;
+  cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMalloc(&c->da, static_cast<size_t>(M) * K * 2);
+  if (e == cudaSuccess) e = cudaMalloc(&c->db, static_cast<size_t>(N) * K * 2);
+  if (e == cudaSuccess) e = cudaMalloc(&c->dd, static_cast<size_t>(M) * c->ldd * 2);
+  if (e != cudaSuccess) rc = set_cuda_error(e, "host context: allocation");
+  if (rc == SMB_OK)
+    rc = smb_bf16_plan_create(&c->plan, c->da, c->db, c->dd, M, N, K, K, K, c->ldd, SMB_FLAG_NONE);
+  if (rc != SMB_OK) {
+    smb_bf16_host_ctx_destroy(c);
+    return rc;
+  }
+  *out = c;
+  return SMB_OK;
+}
+
+extern "C" int smb_bf16_host_ctx_run(smb_bf16_host_ctx* c, const uint16_t* a, const uint16_t* bt,
+                                     uint16_t* d) {
+  if (c == nullptr) return set_error(SMB_ERR_INVALID, "host context: null handle");
+  if (a == nullptr || bt == nullptr || d == nullptr)
+    return set_error(SMB_ERR_INVALID, "host context: null operand pointer");
+  const size_t a_bytes = static_cast<size_t>(c->M) * c->K * 2;
+  const size_t b_bytes = static_cast<size_t>(c->N) * c->K * 2;
+  cudaError_t e = cudaMemcpyAsync(c->da, a, a_bytes, cudaMemcpyHostToDevice, c->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(c->db, bt, b_bytes, cudaMemcpyHostToDevice, c->stream);
+  if (e != cudaSuccess) return set_cuda_error(e, "host context: upload");
+  int rc = smb_bf16_plan_run(c->plan, c->stream);
+  if (rc != SMB_OK) return rc;
+  e = cudaMemcpy2DAsync(d, static_cast<size_t>(c->N) * 2, c->dd, static_cast<size_t>(c->ldd) * 2,
+                        static_cast<size_t>(c->N) * 2, c->M, cudaMemcpyDeviceToHost, c->stream);
+  if (e != cudaSuccess) return set_cuda_error(e, "host context: download");
+  return smb_bf16_plan_check(c->plan, c->stream);
+}
+
 extern "C" int smb_dense_gemm_bf16_host(const uint16_t* a, const uint16_t* bt, uint16_t* d, int M,
                                         int N, int K) {
   if (a == nullptr || bt == nullptr || d == nullptr)
     return set_error(SMB_ERR_INVALID, "host GEMM: null operand pointer");
-  if (M <= 0 || N <= 0 || K <= 0) return set_error(SMB_ERR_INVALID, "host GEMM: bad dimensions");
-  const size_t a_bytes = static_cast<size_t>(M) * K * 2;
-  const size_t b_bytes = static_cast<size_t>(N) * K * 2;
-  // Pad rows of D to 8 elements so that the TMA-store epilogue is always usable.
-  const int64_t ldd = (static_cast<int64_t>(N) + 7) / 8 * 8;
-  const size_t d_bytes = static_cast<size_t>(M) * ldd * 2;
-  void *da = nullptr, *db = nullptr, *dd = nullptr;
-  int rc = SMB_OK;
-  cudaError_t e = cudaMalloc(&da, a_bytes);
-  if (e == cudaSuccess) e = cudaMalloc(&db, b_bytes);
-  if (e == cudaSuccess) e = cudaMalloc(&dd, d_bytes);
-  if (e == cudaSuccess) e = cudaMemcpy(da, a, a_bytes, cudaMemcpyHostToDevice);
-  if (e == cudaSuccess) e = cudaMemcpy(db, bt, b_bytes, cudaMemcpyHostToDevice);
-  if (e != cudaSuccess) rc = set_cuda_error(e, "host GEMM: allocation or upload");
-  smb_bf16_plan* plan = nullptr;
-  if (rc == SMB_OK) rc = smb_bf16_plan_create(&plan, da, db, dd, M, N, K, K, K, ldd, SMB_FLAG_NONE);
-  if (rc == SMB_OK) rc = smb_bf16_plan_run(plan, nullptr);
-  if (rc == SMB_OK) rc = smb_bf16_plan_check(plan, nullptr);
-  if (rc == SMB_OK) {
-    e = cudaMemcpy2D(d, static_cast<size_t>(N) * 2, dd, static_cast<size_t>(ldd) * 2,
-                     static_cast<size_t>(N) * 2, M, cudaMemcpyDeviceToHost);
-    if (e != cudaSuccess) rc = set_cuda_error(e, "host GEMM: download");
-  }
-  smb_bf16_plan_destroy(plan);
-  cudaFree(da);
-  cudaFree(db);
-  cudaFree(dd);
+  smb_bf16_host_ctx* ctx = nullptr;
+  int rc = smb_bf16_host_ctx_create(&ctx, M, N, K);
+  if (rc != SMB_OK) return rc;
+  rc = smb_bf16_host_ctx_run(ctx, a, bt, d);
+  smb_bf16_host_ctx_destroy(ctx);
   return rc;
 }

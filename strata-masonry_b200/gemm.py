@@ -85,6 +85,32 @@ class Bf16Plan:
             pass
 
 
+class Bf16HostContext:
+    """Host-buffer GEMM with device buffers, plan and stream kept between calls."""
+
+    def __init__(self, m: int, n: int, k: int):
+        self._lib = capi.lib()
+        self._h = C.c_void_p()
+        self.shape = (m, n, k)
+        capi.check(self._lib.smb_bf16_host_ctx_create(C.byref(self._h), m, n, k))
+
+    def run(self, a, bt, d) -> None:
+        """a [M,K], bt [N,K], d [M,N]: host buffers of bf16 bit patterns (NumPy arrays, pinned
+        torch tensors or raw addresses)."""
+        capi.check(self._lib.smb_bf16_host_ctx_run(self._h, _ptr(a), _ptr(bt), _ptr(d)))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.smb_bf16_host_ctx_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 # ------------------------------------------------------------------------------- fills
 def fill_bf16_device(out, rows: int, cols: int, fill: int, seed: int, index0: int = 0,
                      row_stride: int | None = None, col_stride: int = 1, ld: int | None = None,
