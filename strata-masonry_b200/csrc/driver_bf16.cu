@@ -1,0 +1,192 @@
+// kernel_sm100a_dense_gemm_bf16 -- command-line driver with the contract of the reference
+// executable of the same name (main() of src/kernels/gemm/sm100a/dense_gemm_bf16.cu:485-565):
+//   --shape=M,K,N  --fill=N  --no-benchmark  --no-gpu-verify  --raster=along-m|along-n
+//   --dump-output=PATH          (raw little-endian bf16, M*N values, row-major, no header)
+// No arguments: the reference's built-in shape inventory with the GPU self-check.
+// Beyond the reference: any positive M and N, any K that is a multiple of 8, fills 5..7
+// (Gaussian stand-ins), --json=PATH.  Operands are generated on the device.
+#include "driver_common.h"
+
+namespace {
+
+// CUDA-core reference for --gpu-verify: one block per row, fp32 dot products.
+__global__ void reference_gemm_bf16(const uint16_t* a, const uint16_t* bt, uint16_t* d, int M, int N,
+                                    int K) {
+  const int m = blockIdx.x;
+  if (m >= M) return;
+  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    float acc = 0.0f;
+    for (int k = 0; k < K; ++k) {
+      acc += __uint_as_float(static_cast<uint32_t>(a[static_cast<size_t>(m) * K + k]) << 16) *
+             __uint_as_float(static_cast<uint32_t>(bt[static_cast<size_t>(n) * K + k]) << 16);
+    }
+    uint32_t b = __float_as_uint(acc);
+    d[static_cast<size_t>(m) * N + n] = static_cast<uint16_t>((b + 0x7FFFu + ((b >> 16) & 1u)) >> 16);
+  }
+}
+
+const char* fill_label(int fill) {
+  switch (fill) {
+    case 1: return "[-0.5,0.5) /256";
+    case 2: return "[-1.0,1.0) /2048";
+    case 3: return "const 1.0";
+    case 4: return "int{-3..3} /7 (profiler)";
+    case 5: return "gauss12 * 0.1";
+    case 6: return "gauss12 * 0.05";
+    case 7: return "gauss12";
+    default: return "unknown";
+  }
+}
+
+struct Options {
+  int fill = 1;
+  bool benchmark = true;
+  bool verify = true;
+  int raster = 0;   // 0 default grouping, 1 along-n, 2 along-m
+  const char* dump = nullptr;
+  const char* json = nullptr;
+};
+
+double run_one(int M, int N, int K, const Options& o) {
+  uint16_t *a = nullptr, *bt = nullptr, *d = nullptr;
+  DRV_CUDA(cudaMalloc(&a, static_cast<size_t>(M) * K * 2));
+  DRV_CUDA(cudaMalloc(&bt, static_cast<size_t>(N) * K * 2));
+  DRV_CUDA(cudaMalloc(&d, static_cast<size_t>(M) * N * 2));
+  DRV_CUDA(cudaMemset(d, 0, static_cast<size_t>(M) * N * 2));
+  cudaStream_t stream;
+  DRV_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  // A: index m*K + k, seed 1.  BT[n][k] = B[k][n]: index k*N + n, seed 2.
+  DRV_SMB(smb_fill_bf16_device(a, M, K, K, 0, static_cast<uint64_t>(K), 1, o.fill, 1, stream));
+  DRV_SMB(smb_fill_bf16_device(bt, N, K, K, 0, 1, static_cast<uint64_t>(N), o.fill, 2, stream));
+  DRV_CUDA(cudaStreamSynchronize(stream));
+
+  smb_bf16_plan* plan = nullptr;
+  DRV_SMB(smb_bf16_plan_create(&plan, a, bt, d, M, N, K, K, K, N, SMB_FLAG_NONE));
+  if (o.raster == 1) DRV_SMB(smb_bf16_plan_tune(plan, 1, 0));
+  if (o.raster == 2) DRV_SMB(smb_bf16_plan_tune(plan, (M + 255) / 256, 0));
+  auto launch = [&]() { return smb_bf16_plan_run(plan, stream); };
+  double ms = 0.0;
+  if (o.benchmark) {
+    ms = measure_mean_ms(stream, launch);
+  } else {
+    DRV_SMB(launch());
+  }
+  // The dumped output comes from one more launch, as in the reference driver.
+  DRV_SMB(launch());
+  DRV_SMB(smb_bf16_plan_check(plan, stream));
+  double tflops = 0.0;
+  if (o.benchmark) {
+    tflops = 2.0 * M * N * K / (ms * 1e-3) / 1e12;
+    std::printf("  shape (%6d, %6d, %4d): %.6f ms  %7.1f TFLOPS\n", M, N, K, ms, tflops);
+  } else {
+    std::printf("  shape (%6d, %6d, %4d): untimed\n", M, N, K);
+  }
+  write_json(o.json, "dense_gemm_bf16", M, N, K, o.fill, ms, tflops, o.benchmark);
+  if (o.dump) dump_bf16(d, static_cast<size_t>(M) * N, o.dump);
+
+  int rc = 0;
+  if (o.verify) {
+    uint16_t* ref = nullptr;
+    DRV_CUDA(cudaMalloc(&ref, static_cast<size_t>(M) * N * 2));
+    reference_gemm_bf16<<<M, 256>>>(a, bt, ref, M, N, K);
+    DRV_CUDA(cudaDeviceSynchronize());
+    std::vector<uint16_t> got(static_cast<size_t>(M) * N), want(got.size());
+    DRV_CUDA(cudaMemcpy(got.data(), d, got.size() * 2, cudaMemcpyDeviceToHost));
+    DRV_CUDA(cudaMemcpy(want.data(), ref, want.size() * 2, cudaMemcpyDeviceToHost));
+    float max_diff = 0.0f;
+    bool ok = true;
+    for (size_t i = 0; i < got.size(); ++i) {
+      const float g = bf16_bits_to_float(got[i]), w = bf16_bits_to_float(want[i]);
+      const float diff = fabsf(g - w);
+      if (!(diff <= max_diff)) max_diff = diff;
+      if (!(diff <= 0.05f + 0.05f * fabsf(w))) ok = false;
+    }
+    std::printf("  verify (M=%d,N=%d,K=%d): max_diff=%.3f tight=%s\n", M, N, K, max_diff,
+                ok ? "OK" : "FAIL");
+    if (!ok) rc = 1;
+    cudaFree(ref);
+  }
+  smb_bf16_plan_destroy(plan);
+  cudaStreamDestroy(stream);
+  cudaFree(a);
+  cudaFree(bt);
+  cudaFree(d);
+  if (rc != 0) std::exit(rc);
+  return tflops;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  Options o;
+  int M = 0, K = 0, N = 0;
+  for (int i = 1; i < argc; ++i) {
+    if (std::strncmp(argv[i], "--fill=", 7) == 0) {
+      o.fill = std::atoi(argv[i] + 7);
+      if (o.fill < 1 || o.fill > 7) {
+        std::fprintf(stderr, "--fill must be 1, 2, 3, or 4 (5, 6, 7: Gaussian stand-ins)\n");
+        return 1;
+      }
+    } else if (std::strncmp(argv[i], "--shape=", 8) == 0) {
+      if (std::sscanf(argv[i] + 8, "%d,%d,%d", &M, &K, &N) != 3) {
+        std::fprintf(stderr, "--shape must be M,K,N\n");
+        return 1;
+      }
+    } else if (std::strcmp(argv[i], "--no-benchmark") == 0) {
+      o.benchmark = false;
+    } else if (std::strcmp(argv[i], "--no-gpu-verify") == 0) {
+      o.verify = false;
+    } else if (std::strcmp(argv[i], "--raster=along-m") == 0) {
+      o.raster = 2;
+    } else if (std::strcmp(argv[i], "--raster=along-n") == 0) {
+      o.raster = 1;
+    } else if (std::strncmp(argv[i], "--dump-output=", 14) == 0) {
+      o.dump = argv[i] + 14;
+    } else if (std::strncmp(argv[i], "--json=", 7) == 0) {
+      o.json = argv[i] + 7;
+    } else {
+      std::fprintf(stderr, "unknown argument: %s\n", argv[i]);
+      return 1;
+    }
+  }
+  DRV_CUDA(cudaFree(0));
+  std::printf("K0 dense_gemm_bf16 (Blackwell B200, sm_100a) -- fill=%d %s\n", o.fill,
+              fill_label(o.fill));
+  std::printf("=============================================\n");
+
+  if (M || K || N) {
+    if (M <= 0 || K <= 0 || N <= 0) {
+      std::fprintf(stderr, "--shape dimensions must be positive\n");
+      return 1;
+    }
+    if (K % 8 != 0) {
+      std::fprintf(stderr, "unsupported --shape for this kernel (K must be a multiple of 8)\n");
+      return 1;
+    }
+    run_one(M, N, K, o);
+    return 0;
+  }
+  if (o.dump) {
+    std::fprintf(stderr, "--dump-output requires --shape=M,K,N\n");
+    return 1;
+  }
+
+  // The reference driver's shape inventory (M padded to 14080 for the UND rows).
+  struct Shape { const char* label; int M, K, N; };
+  const Shape shapes[] = {
+      {"und-gate", 14080, 2048, 128},  {"und-qkv", 14080, 2048, 5120}, {"und-o", 14080, 4096, 2048},
+      {"gen-gate", 30720, 2048, 128},  {"gen-qkv", 30720, 2048, 5120}, {"gen-o", 30720, 4096, 2048},
+  };
+  std::printf("\n[V0 shape inventory]\n");
+  for (const Shape& s : shapes) {
+    std::printf("\n[%s]\n", s.label);
+    Options along = o;
+    std::printf("  AlongN:\n");
+    along.raster = 1;
+    run_one(s.M, s.N, s.K, along);
+    std::printf("  AlongM:\n");
+    along.raster = 2;
+    run_one(s.M, s.N, s.K, along);
+  }
+  return 0;
+}
