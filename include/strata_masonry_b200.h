@@ -157,6 +157,9 @@ int smb_bf16_host_ctx_destroy(smb_bf16_host_ctx* ctx);
  * A: [M, K/2] bytes (two E2M1 codes per byte, even k low), B: [N, K/2] bytes, row pitches in
  * bytes (multiples of 16); SFA / SFB: UE8M0 bytes in the packed layout of
  * smb_sf_packed_bytes(); D: bf16 row-major.  Any M, N >= 1; K a multiple of 32.
+ * Shapes with M <= 128 (decode: few activation rows against a large weight matrix B) run a
+ * separate HBM-bound kernel that streams B once, split evenly over the SMs along N and K; the
+ * plan owns its scratch memory (fp32 partial sums of the tiles shared by two SMs).
  * ---------------------------------------------------------------------------------- */
 typedef struct smb_fp4_plan smb_fp4_plan;
 int smb_fp4_plan_create(smb_fp4_plan** plan, const void* a, const void* sfa, const void* b,
@@ -165,7 +168,9 @@ int smb_fp4_plan_create(smb_fp4_plan** plan, const void* a, const void* sfa, con
 int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_destroy(smb_fp4_plan* plan);
-int smb_fp4_plan_tune(smb_fp4_plan* plan, int group_m, int max_clusters);
+/* Tuning: raster group height (0 = default), cluster cap (0 = all), L2 prefetch distance in
+ * 256-wide K blocks (0 = off, negative = keep). */
+int smb_fp4_plan_tune(smb_fp4_plan* plan, int group_m, int max_clusters, int prefetch);
 /* Role timers, same layout as smb_bf16_plan_set_profile. */
 int smb_fp4_plan_set_profile(smb_fp4_plan* plan, long long* counters);
 
@@ -184,6 +189,8 @@ int smb_dense_gemm_nvfp4_host(const uint8_t* a, const uint8_t* sfa_rowmajor, con
 #define SMB_FLAG_TILE_N_256 8u        /* force 256 x 256 tiles, two accumulator banks */
 #define SMB_FLAG_TILE_N_512 16u       /* force 256 x 512 tiles, one accumulator set */
 #define SMB_FLAG_TILE_N_384 32u       /* FP4 only: force 256 x 384 tiles */
+#define SMB_FLAG_NO_DECODE 64u        /* FP4 only: M <= 128 through the tiled kernel, not the decode kernel */
+#define SMB_FLAG_NO_LAUNCH_OVERLAP 128u /* decode kernel: no programmatic dependent launch */
 
 #ifdef __cplusplus
 }

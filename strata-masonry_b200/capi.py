@@ -27,6 +27,8 @@ FLAG_TILE_N_64 = 4
 FLAG_TILE_N_256 = 8
 FLAG_TILE_N_512 = 16
 FLAG_TILE_N_384 = 32
+FLAG_NO_DECODE = 64
+FLAG_NO_LAUNCH_OVERLAP = 128
 
 _vp = C.c_void_p
 _i = C.c_int
@@ -65,7 +67,7 @@ DECLARED = [
     ("smb_fp4_plan_run", _i, [_vp, _vp]),
     ("smb_fp4_plan_check", _i, [_vp, _vp]),
     ("smb_fp4_plan_destroy", _i, [_vp]),
-    ("smb_fp4_plan_tune", _i, [_vp, _i, _i]),
+    ("smb_fp4_plan_tune", _i, [_vp, _i, _i, _i]),
     ("smb_fp4_plan_set_profile", _i, [_vp, _vp]),
     ("smb_dense_gemm_nvfp4", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     ("smb_dense_gemm_nvfp4_host", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),

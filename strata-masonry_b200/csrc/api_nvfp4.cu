@@ -16,6 +16,11 @@ using namespace smb;
 struct smb_fp4_plan {
   Fp4Launch launch;
   int* status_dev;
+  // Skinny shapes (M <= 128) run the stream-K decode kernel, which needs scratch memory.
+  bool decode;
+  Fp4DecodeLaunch dlaunch;
+  void* scratch_dev;      // fp32 slabs followed by the per-tile counters
+  size_t scratch_bytes;
 };
 
 extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void* sfa, const void* b,
@@ -47,11 +52,15 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
   L.group_m = 0;
   L.max_clusters = 0;
   L.prof = nullptr;
+  L.prefetch = 0;
   L.d = d;
   L.ldd = static_cast<int>(ldd);
   L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
                 !(flags & SMB_FLAG_FORCE_PLAIN_STORE);
   p->status_dev = nullptr;
+  p->decode = (M <= 128) && !(flags & SMB_FLAG_NO_DECODE);
+  p->scratch_dev = nullptr;
+  p->scratch_bytes = 0;
 
   const uint64_t kchunks = (static_cast<uint64_t>(K) / 32 + 3) / 4;
   const uint64_t bands_a = (static_cast<uint64_t>(M) + 127) / 128;
@@ -83,21 +92,60 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
     if (e == cudaSuccess) e = cudaMemset(p->status_dev, 0, sizeof(int));
     if (e != cudaSuccess) rc = set_cuda_error(e, "fp4 plan: status word allocation");
   }
+  if (rc == SMB_OK && p->decode) {
+    // Operands swap roles: the weights (B, N rows) fill the 128 rows of the MMA, the
+    // activations (A, M rows) its N dimension.
+    Fp4DecodeLaunch& D = p->dlaunch;
+    D.M = M;
+    D.N = N;
+    D.K = K;
+    D.d = d;
+    D.ldd = static_cast<int>(ldd);
+    D.max_ctas = 0;
+    D.max_stages = 0;
+    D.no_overlap = (flags & SMB_FLAG_NO_LAUNCH_OVERLAP) != 0;
+    const int m_pad = (M + 15) / 16 * 16;
+    rc = encode_tmap_2d(&D.tmap_w, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, ldb_bytes, 128, 128, true);
+    if (rc == SMB_OK)
+      rc = encode_tmap_2d(&D.tmap_x, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, lda_bytes, m_pad, 128, true);
+    if (rc == SMB_OK)
+      rc = encode_tmap_2d(&D.tmap_sfw, sfb, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_b, kchunks * 64,
+                          kchunks * 512, 1, 128, false);
+    if (rc == SMB_OK)
+      rc = encode_tmap_2d(&D.tmap_sfx, sfa, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_a, kchunks * 64,
+                          kchunks * 512, 1, 128, false);
+    if (rc == SMB_OK) {
+      const size_t tiles = (static_cast<size_t>(N) + 127) / 128;
+      const size_t slab_bytes = tiles * m_pad * 128 * sizeof(float);
+      p->scratch_bytes = slab_bytes + tiles * sizeof(int);
+      cudaError_t e = cudaMalloc(&p->scratch_dev, p->scratch_bytes);
+      if (e == cudaSuccess) e = cudaMemset(p->scratch_dev, 0, p->scratch_bytes);
+      if (e != cudaSuccess) rc = set_cuda_error(e, "fp4 plan: decode scratch allocation");
+      D.scratch = static_cast<float*>(p->scratch_dev);
+      D.counters = reinterpret_cast<int*>(static_cast<char*>(p->scratch_dev) + slab_bytes);
+    }
+  }
   if (rc != SMB_OK) {
     if (p->status_dev) cudaFree(p->status_dev);
+    if (p->scratch_dev) cudaFree(p->scratch_dev);
     delete p;
     return rc;
   }
   L.status = p->status_dev;
+  p->dlaunch.status = p->status_dev;
   *out = p;
   return SMB_OK;
 }
 
-extern "C" int smb_fp4_plan_tune(smb_fp4_plan* plan, int group_m, int max_clusters) {
+extern "C" int smb_fp4_plan_tune(smb_fp4_plan* plan, int group_m, int max_clusters, int prefetch) {
   if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
   if (group_m < 0 || max_clusters < 0) return set_error(SMB_ERR_INVALID, "fp4 plan: negative tuning value");
   plan->launch.group_m = group_m;
   plan->launch.max_clusters = max_clusters;
+  if (prefetch >= 0) plan->launch.prefetch = prefetch;
+  // For the decode kernel the same two knobs cap the ring depth and the CTA count.
+  plan->dlaunch.max_stages = group_m;
+  plan->dlaunch.max_ctas = max_clusters;
   return SMB_OK;
 }
 
@@ -109,6 +157,7 @@ extern "C" int smb_fp4_plan_set_profile(smb_fp4_plan* plan, long long* counters)
 
 extern "C" int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream) {
   if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
+  if (plan->decode) return fp4_decode_launch(plan->dlaunch, static_cast<cudaStream_t>(stream));
   return fp4_launch(plan->launch, static_cast<cudaStream_t>(stream));
 }
 
@@ -121,6 +170,8 @@ extern "C" int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream) {
   if (e != cudaSuccess) return set_cuda_error(e, "fp4 plan check: status read");
   if (status != 0) {
     cudaMemset(plan->status_dev, 0, sizeof(int));
+    // A decode launch that gave up may have left partial sums behind.
+    if (plan->scratch_dev) cudaMemset(plan->scratch_dev, 0, plan->scratch_bytes);
     return set_error(SMB_ERR_DEVICE, "nvfp4 GEMM kernel reported status %d: %s", status,
                      device_status_name(status));
   }
@@ -130,6 +181,7 @@ extern "C" int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream) {
 extern "C" int smb_fp4_plan_destroy(smb_fp4_plan* plan) {
   if (plan == nullptr) return SMB_OK;
   if (plan->status_dev) cudaFree(plan->status_dev);
+  if (plan->scratch_dev) cudaFree(plan->scratch_dev);
   delete plan;
   return SMB_OK;
 }

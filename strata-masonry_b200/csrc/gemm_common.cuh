@@ -71,8 +71,25 @@ struct Fp4Launch {
   int ldd;
   int* status;
   long long* prof;
+  int prefetch;      // L2 prefetch distance in K blocks (0 = off)
 };
 void fp4_pick_tile(int M, int N, int K, int* w0, int* w1);
 int fp4_launch(const Fp4Launch& L, cudaStream_t stream);
+
+// --------------------------------------------------------------------------- nvfp4 decode launch
+struct Fp4DecodeLaunch {
+  CUtensorMap tmap_w, tmap_x, tmap_sfw, tmap_sfx;
+  int M, N, K;       // M <= 128 activation rows, N weight rows
+  void* d;
+  int ldd;
+  float* scratch;    // fp32 [ceil(N/128)][round_up(M,16)][128], zero between calls
+  int* counters;     // int  [ceil(N/128)], zero between calls
+  int* status;
+  int max_ctas;      // 0 = one per SM
+  int max_stages;    // 0 = as many as fit
+  bool no_overlap;   // true: plain stream order, no programmatic dependent launch
+};
+int fp4_decode_stage_bytes(int m_pad);
+int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream);
 
 }  // namespace smb

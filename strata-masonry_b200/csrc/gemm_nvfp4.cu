@@ -83,6 +83,7 @@ struct Params {
   uint16_t* d_ptr;
   int* status;
   long long* prof;
+  int prefetch;   // L2 prefetch distance in K blocks (0 = off)
 };
 
 enum { kProfLoadWait = 0, kProfLoadTotal, kProfMmaWaitFull, kProfMmaWaitAcc, kProfMmaTotal,
@@ -109,6 +110,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * kStages + 4);
   auto sf_ready_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 6 + s); };
+  auto sf_full_bar = [&](int s) { return bar_base + 8u * (3 * kStages + 6 + s); };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -123,6 +125,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
       mbar_init(sf_ready_bar(s), 1);
+      mbar_init(sf_full_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full_bar(b), 1);
@@ -153,6 +156,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------------------------------------- TMA producer
     if (lane == 0) {
       const uint32_t leader_full0 = mapa_u32(full_bar(0), 0);
+      const uint32_t leader_sf_full0 = mapa_u32(sf_full_bar(0), 0);
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -176,10 +180,20 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           if (prof) waited += clock64() - w0;
           const uint32_t bar = leader_full0 + 8u * s;
+          const uint32_t sf_bar = leader_sf_full0 + 8u * s;
           const uint32_t dst = ring_base + s * C::kStageBytes;
+          constexpr int kSfBytes = C::kSfaBytes + C::kSfbBytes;
           if (rank == 0) {
-            mbar_arrive_expect_tx(full_bar(s), 2 * (C::kStageBytes - (has_sub1 ? 0 : C::kB1Bytes)));
+            mbar_arrive_expect_tx(sf_full_bar(s), 2 * kSfBytes);
+            mbar_arrive_expect_tx(full_bar(s),
+                                  2 * (C::kStageBytes - kSfBytes - (has_sub1 ? 0 : C::kB1Bytes)));
           }
+          // Scales first and on their own barrier: the scale warp can move them into tensor
+          // memory while the (ten times larger) operand boxes are still in flight.  The packed
+          // scale buffer is viewed as [bands, K/128 * 64] 64-bit words; one stage covers 128
+          // words (two 512-byte cells) of each band.
+          tma_load_2d_pair(dst + C::kOffSfa, &tmap_sfa, sf_bar, kb * 128, band_a);
+          tma_load_2d_pair(dst + C::kOffSfb, &tmap_sfb, sf_bar, kb * 128, band_b);
           tma_load_2d_pair(dst, &tmap_a, bar, kb * kBlockKBytes, row_a);
           tma_load_2d_pair(dst + C::kOffB0, &tmap_b0, bar, kb * kBlockKBytes,
                            col0 + static_cast<int>(rank) * (W0 / 2));
@@ -187,10 +201,13 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
             tma_load_2d_pair(dst + C::kOffB1, &tmap_b1, bar, kb * kBlockKBytes,
                              col0 + W0 + static_cast<int>(rank) * (W1 / 2));
           }
-          // Scales: the packed buffer is viewed as [bands, K/128 * 64] 64-bit words; one stage
-          // covers 128 words (two 512-byte cells) of each band.
-          tma_load_2d_pair(dst + C::kOffSfa, &tmap_sfa, bar, kb * 128, band_a);
-          tma_load_2d_pair(dst + C::kOffSfb, &tmap_sfb, bar, kb * 128, band_b);
+          if (p.prefetch > 0 && kb + p.prefetch < num_kb) {
+            const int kp = (kb + p.prefetch) * kBlockKBytes;
+            tma_prefetch_l2_2d(&tmap_a, kp, row_a);
+            tma_prefetch_l2_2d(&tmap_b0, kp, col0 + static_cast<int>(rank) * (W0 / 2));
+            if (C::kSubs == 2 && has_sub1)
+              tma_prefetch_l2_2d(&tmap_b1, kp, col0 + W0 + static_cast<int>(rank) * (W1 / 2));
+          }
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
       }
@@ -229,10 +246,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tc_fence_after_sync();
         const uint32_t acc_base = tmem_base + static_cast<uint32_t>(bank * 128);
         for (int kb = 0; kb < num_kb; ++kb) {
-          // The scale warp waited for this stage's data and copied its scales into tensor memory;
-          // its commit on sf_ready therefore also says that A and B have landed.
+          // Operands in shared memory (full) and scales in tensor memory (sf_ready, committed by
+          // the scale warp).
           const long long w0 = prof ? clock64() : 0;
-          if (!mbar_wait(sf_ready_bar(s), ph)) {
+          if (!mbar_wait(full_bar(s), ph) || !mbar_wait(sf_ready_bar(s), ph)) {
             report_status(p.status, kDevTimeoutMmaFull);
             ok = false;
             break;
@@ -295,8 +312,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(full_bar(s), ph)) {
-            report_status(p.status, kDevTimeoutMmaFull);
+          if (!mbar_wait(sf_full_bar(s), ph)) {
+            report_status(p.status, kDevTimeoutSched);
             ok = false;
             break;
           }
@@ -433,6 +450,7 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   p.d_ptr = static_cast<uint16_t*>(L.d);
   p.status = L.status;
   p.prof = L.prof;
+  p.prefetch = L.prefetch;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (L.max_clusters > 0 && clusters > L.max_clusters) clusters = L.max_clusters;

@@ -163,14 +163,14 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
 }
 
-// 2-D tiled load into this CTA's shared memory; completion bytes are credited to `bar`,
-// a shared::cta address of this CTA.
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x,
-                                            int y) {
+// 2-D tiled load into this CTA's shared memory with an L2 eviction hint (kernels launched
+// without clusters: the CTA is its own cluster of one).
+__device__ __forceinline__ void tma_load_2d_cta_hint(uint32_t dst, const CUtensorMap* m, uint32_t bar,
+                                                     int x, int y, uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(m), "r"(bar), "r"(x), "r"(y)
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"(m), "r"(bar), "r"(x), "r"(y), "l"(policy)
       : "memory");
 }
 
@@ -194,15 +194,6 @@ __device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst, const CUtens
       ".mbarrier::complete_tx::bytes.L2::cache_hint"
       " [%0], [%1, {%3, %4}], [%2], %5;"
       ::"r"(dst), "l"(m), "r"(cluster_bar), "r"(x), "r"(y), "l"(policy)
-      : "memory");
-}
-
-__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* m, uint32_t bar,
-                                                 int x, int y, uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes"
-      ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
-      ::"r"(dst), "l"(m), "r"(bar), "r"(x), "r"(y), "l"(policy)
       : "memory");
 }
 
@@ -452,6 +443,13 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
                : "memory");
 }
+
+// Programmatic dependent launch: let the next grid on the stream start early / wait for the
+// previous grid to finish and its writes to become visible.
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // First writer wins.
 __device__ __forceinline__ void report_status(int* status, int code) {

@@ -205,8 +205,8 @@ class Fp4Plan:
             k // 2 if lda_bytes is None else lda_bytes, k // 2 if ldb_bytes is None else ldb_bytes,
             n if ldd is None else ldd, flags))
 
-    def tune(self, group_m: int = 0, max_clusters: int = 0) -> None:
-        capi.check(self._lib.smb_fp4_plan_tune(self._h, group_m, max_clusters))
+    def tune(self, group_m: int = 0, max_clusters: int = 0, prefetch: int = -1) -> None:
+        capi.check(self._lib.smb_fp4_plan_tune(self._h, group_m, max_clusters, prefetch))
 
     def set_profile(self, counters) -> None:
         capi.check(self._lib.smb_fp4_plan_set_profile(self._h, _ptr(counters)))

@@ -347,3 +347,67 @@ def test_fp4_8192_cubed_properties(smb, oracle, cuda_device):
     nn = torch.arange(n, device=d.device).view(1, -1)
     exact = (k * torch.exp2((mm % 5) - 2.0) * torch.exp2((nn % 3) - 1.0)).to(torch.bfloat16)
     assert torch.equal(d3, exact)
+
+
+# ------------------------------------------------------------------------------- NVFP4 decode shapes
+def _run_fp4_decode(smb, m, n, k, fill=5, flags=0, stages=0, ctas=0, runs=1):
+    """Activations: fill 6 when the weights use fill 5 (bf16-rounded Gaussian, then quantised)."""
+    torch = _torch()
+    a, sfa, sfar = _fp4_operand(smb, m, k, 6 if fill == 5 else fill, 0)
+    b, sfb, sfbr = _fp4_operand(smb, n, k, fill, 1)
+    d = torch.full((m, n), float("nan"), device=a.device, dtype=torch.bfloat16)
+    plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k, flags=flags)
+    plan.tune(stages, ctas, -1)
+    outs = []
+    for _ in range(runs):
+        d.fill_(float("nan"))
+        plan.run()
+        plan.check()
+        outs.append(d.clone())
+    plan.close()
+    return (a, sfar), (b, sfbr), outs
+
+
+@pytest.mark.parametrize("m", [16, 64, 128])
+def test_fp4_decode_shapes_of_the_baseline(smb, cuda_device, m):
+    """BASELINE config 4: M in {16, 64, 128}, N = 28672, K = 8192, full fp64 comparison.  Run
+    twice on one plan: the scratch slabs must come back to zero after every call."""
+    torch = _torch()
+    A, B, outs = _run_fp4_decode(smb, m, 28672, 8192, runs=2)
+    _check_fp4_full(A, B, outs[0], 8192)
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+
+
+@pytest.mark.parametrize("shape", [(1, 384, 256), (16, 256, 512), (100, 1000, 1056), (17, 130, 32),
+                                   (128, 4096, 4096), (48, 3000, 2048)])
+@pytest.mark.parametrize("fill", [2, 3, 5])
+def test_fp4_decode_ragged_and_small(smb, cuda_device, shape, fill):
+    m, n, k = shape
+    A, B, outs = _run_fp4_decode(smb, m, n, k, fill=fill)
+    _check_fp4_full(A, B, outs[0], k)
+
+
+def test_fp4_decode_matches_tiled_kernel_and_any_split(smb, cuda_device):
+    """The stream-K split (how many CTAs share a tile, ring depth) must not change the result
+    beyond fp32 summation order: compare against the tiled kernel and against other splits."""
+    torch = _torch()
+    m, n, k = 16, 28672, 8192
+    A, B, base = _run_fp4_decode(smb, m, n, k)
+    _, _, tiled = _run_fp4_decode(smb, m, n, k, flags=smb.capi.FLAG_NO_DECODE)
+    _check_fp4_full(A, B, tiled[0], k)
+    for ctas, stages in ((37, 0), (100, 3), (148, 6), (1, 4)):
+        _, _, other = _run_fp4_decode(smb, m, n, k, ctas=ctas, stages=stages)
+        _check_fp4_full(A, B, other[0], k)
+        diff = (other[0].float() - base[0].float()).abs()
+        scale = base[0].float().abs().clamp_min(1.0)
+        assert float((diff / scale).max()) <= 2 ** -6    # at most a couple of bf16 ulps apart
+
+
+def test_fp4_decode_constant_fill_is_exact(smb, cuda_device):
+    torch = _torch()
+    m, n, k = 64, 28672, 8192
+    _, _, outs = _run_fp4_decode(smb, m, n, k, fill=3)
+    mm = torch.arange(m, device=outs[0].device).view(-1, 1)
+    nn = torch.arange(n, device=outs[0].device).view(1, -1)
+    exact = (k * torch.exp2((mm % 5) - 2.0) * torch.exp2((nn % 3) - 1.0)).to(torch.bfloat16)
+    assert torch.equal(outs[0], exact)
