@@ -182,6 +182,24 @@ int smb_dense_gemm_nvfp4(const void* a, const void* sfa, const void* b, const vo
 int smb_dense_gemm_nvfp4_host(const uint8_t* a, const uint8_t* sfa_rowmajor, const uint8_t* b,
                               const uint8_t* sfb_rowmajor, uint16_t* d, int M, int N, int K);
 
+/* Decode-shape FP4 GEMM (M <= 128) for callers that cannot allocate device memory where the
+ * GEMM runs: a server whose start-up pool owns all of HBM, a plugin living inside another
+ * framework's allocator, a call made while a stream is being captured.  It has no counterpart
+ * in the reference.  Same operands and result as smb_dense_gemm_nvfp4 (packed scales, lda =
+ * ldb = K/2 bytes, ldd = N); the partial-sum scratch of the kernel lives in a 16 MiB array
+ * built into the library, so the call performs no cudaMalloc / cudaFree of any kind.
+ *   - Limit: ceil(N/128) * (round_up(M,16) * 512 + 4) bytes must not exceed
+ *     smb_decode_noalloc_scratch_limit() (16 MiB - 256); larger shapes return
+ *     SMB_ERR_UNSUPPORTED.  All of M in {16, 64, 128} x N = 28672 fit.
+ *   - The first call on a device looks up the array's device address; make that call outside
+ *     any stream capture.
+ *   - All calls share the one array: it is cleared on `stream` before each launch, and two
+ *     calls that overlap on the GPU (different streams) corrupt each other.
+ *   - Enqueues and returns; a kernel that gives up a bounded wait is not reported here. */
+int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sfa, const void* b,
+                                        const void* sfb, void* d, int M, int N, int K, void* stream);
+size_t smb_decode_noalloc_scratch_limit(void);
+
 #define SMB_FLAG_NONE 0u
 #define SMB_FLAG_FORCE_PLAIN_STORE 1u /* use the non-TMA epilogue even when D is aligned */
 #define SMB_FLAG_TILE_N_128 2u        /* force 256 x 128 tiles */

@@ -71,6 +71,8 @@ DECLARED = [
     ("smb_fp4_plan_set_profile", _i, [_vp, _vp]),
     ("smb_dense_gemm_nvfp4", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     ("smb_dense_gemm_nvfp4_host", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
+    ("smb_dense_gemm_nvfp4_decode_noalloc", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    ("smb_decode_noalloc_scratch_limit", C.c_size_t, []),
 ]
 
 

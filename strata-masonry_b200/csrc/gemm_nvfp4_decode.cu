@@ -407,3 +407,104 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
 }
 
 }  // namespace smb
+
+// -----------------------------------------------------------------------------------
+// Decode GEMM for callers that must not allocate
+// -----------------------------------------------------------------------------------
+// Some hosts of this library cannot call cudaMalloc on the path that runs the GEMM: an
+// inference server that has handed all device memory to its own pool at start-up, a
+// plugin running inside another framework's allocator, code between a stream capture's
+// begin and end.  For them the fp32 partial-sum slabs and tile counters of the decode
+// kernel live in the fixed array below instead of in a plan-owned allocation.  The array
+// is part of the library image: every GPU that loads the library carries these 16 MiB
+// until the process exits.
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;
+constexpr size_t kStaticStatusOffset = kStaticScratchBytes - 256;   // last 256 bytes: status word
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+// The array's name is only a host-side handle here; the kernel needs its device address,
+// which differs per device.  Looked up once per device, with that device current.
+int static_scratch_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return smb::set_cuda_error(e, "no-alloc decode: cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices)
+    return smb::set_error(SMB_ERR_UNSUPPORTED, "no-alloc decode: device ordinal %d out of range", dev);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+    if (e != cudaSuccess) return smb::set_cuda_error(e, "no-alloc decode: cudaGetSymbolAddress");
+    if (ptr == nullptr)
+      return smb::set_error(SMB_ERR_CUDA, "no-alloc decode: cudaGetSymbolAddress returned null");
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return SMB_OK;
+}
+
+}  // namespace
+
+extern "C" size_t smb_decode_noalloc_scratch_limit(void) { return kStaticStatusOffset; }
+
+extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sfa, const void* b,
+                                                   const void* sfb, void* d, int M, int N, int K,
+                                                   void* stream) {
+  using namespace smb;
+  if (a == nullptr || sfa == nullptr || b == nullptr || sfb == nullptr || d == nullptr)
+    return set_error(SMB_ERR_INVALID, "no-alloc decode: null operand pointer");
+  if (M <= 0 || N <= 0 || K <= 0)
+    return set_error(SMB_ERR_INVALID, "no-alloc decode: dimensions must be positive");
+  if (M > 128)
+    return set_error(SMB_ERR_UNSUPPORTED, "no-alloc decode: M=%d exceeds 128 activation rows", M);
+  if (K % 32 != 0)
+    return set_error(SMB_ERR_UNSUPPORTED, "no-alloc decode: K=%d must be a multiple of 32", K);
+  const int m_pad = (M + 15) / 16 * 16;
+  const size_t tiles = (static_cast<size_t>(N) + 127) / 128;
+  const size_t slab_bytes = tiles * m_pad * 128 * sizeof(float);
+  const size_t need = slab_bytes + tiles * sizeof(int);
+  if (need > kStaticStatusOffset)
+    return set_error(SMB_ERR_UNSUPPORTED,
+                     "no-alloc decode: M=%d N=%d needs %zu bytes of scratch, the built-in array "
+                     "holds %zu (ceil(N/128) * (round_up(M,16) * 512 + 4) must not exceed it)",
+                     M, N, need, kStaticStatusOffset);
+  void* base = nullptr;
+  if (int rc = static_scratch_address(&base)) return rc;
+
+  Fp4DecodeLaunch L;
+  L.M = M;
+  L.N = N;
+  L.K = K;
+  L.d = d;
+  L.ldd = N;
+  L.max_ctas = 0;
+  L.max_stages = 0;
+  L.no_overlap = true;   // the memset below must be ordered before every access of this launch
+  L.scratch = static_cast<float*>(base);
+  L.counters = reinterpret_cast<int*>(static_cast<char*>(base) + slab_bytes);
+  L.status = reinterpret_cast<int*>(static_cast<char*>(base) + kStaticStatusOffset);
+  const uint64_t kchunks = (static_cast<uint64_t>(K) / 32 + 3) / 4;
+  const uint64_t bands_a = (static_cast<uint64_t>(M) + 127) / 128;
+  const uint64_t bands_b = (static_cast<uint64_t>(N) + 127) / 128;
+  int rc = encode_tmap_2d(&L.tmap_w, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, 128, 128, true);
+  if (rc == SMB_OK)
+    rc = encode_tmap_2d(&L.tmap_x, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, K / 2, m_pad, 128, true);
+  if (rc == SMB_OK)
+    rc = encode_tmap_2d(&L.tmap_sfw, sfb, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_b, kchunks * 64,
+                        kchunks * 512, 1, 128, false);
+  if (rc == SMB_OK)
+    rc = encode_tmap_2d(&L.tmap_sfx, sfa, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_a, kchunks * 64,
+                        kchunks * 512, 1, 128, false);
+  if (rc != SMB_OK) return rc;
+  // The array keeps whatever the last call left in it (all zero after a call that ran to the
+  // end, anything after one that was cut short): clear the part this call uses, and the status.
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(base, 0, need, st);
+  if (e == cudaSuccess) e = cudaMemsetAsync(L.status, 0, sizeof(int), st);
+  if (e != cudaSuccess) return set_cuda_error(e, "no-alloc decode: scratch clear");
+  return fp4_decode_launch(L, st);
+}
