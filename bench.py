@@ -39,7 +39,11 @@ WORKLOADS = {
     "nvfp4_8192": ("nvfp4", 8192, 8192, 8192, 5, "dense NVFP4 GEMM M=N=K=8192, quantised N(0,1) stand-in"),
     "bf16_large": ("bf16", 32768, 57344, 8192, 6, "dense BF16 GEMM 32768x57344x8192, operands N(0,1)*0.05 stand-in"),
     "bf16_smoke": ("bf16", 256, 128, 64, 2, "reference smoke shape 256x128x64, fill 2"),
+    "decode_m16": ("decode", 16, 28672, 8192, 5, "NVFP4 decode GEMM M=16, N=28672, K=8192 (HBM-bound)"),
+    "decode_m64": ("decode", 64, 28672, 8192, 5, "NVFP4 decode GEMM M=64, N=28672, K=8192 (HBM-bound)"),
+    "decode_m128": ("decode", 128, 28672, 8192, 5, "NVFP4 decode GEMM M=128, N=28672, K=8192 (HBM-bound)"),
 }
+DECODE_WEIGHT_SETS = 4   # rotate weight buffers so that every step streams from HBM, not from L2
 
 # DRAM bytes per launch of the BF16 8192^3 kernel from the committed ncu capture
 # (profiles/bf16_gemm_8192.md: dram__bytes_read.sum + dram__bytes_write.sum).
@@ -65,7 +69,7 @@ def _load_oracle():
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
 
-    def __init__(self, uuid: str | None, index: int, period_s: float = 0.01):
+    def __init__(self, uuid: str | None, index: int, period_s: float = 0.005):
         self.period = period_s
         self.samples: list[tuple[int, int, float]] = []
         self.max_mhz = None
@@ -218,7 +222,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="bf16_8192", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -253,11 +257,13 @@ def main():
     g = world
 
     kind, m, n, k, fill, desc = WORKLOADS[args.workload]
-    if n % g != 0 or (n // g) % 8 != 0:
-        raise SystemExit(f"N={n} cannot be sharded {g} ways with 16-byte-aligned rows")
-    n_local = n // g
-    n0 = rank * n_local
+    try:
+        shard = smb.sharding.column_shard(n, g, rank)
+    except ValueError as err:
+        raise SystemExit(str(err))
+    n_local, n0 = shard.n_local, shard.n0
     stream = torch.cuda.current_stream()
+    plans = None
 
     # ---------------------------------------------------------------- operands, resident in HBM
     if kind == "bf16":
@@ -268,6 +274,22 @@ def main():
         plan = smb.gemm.Bf16Plan(a, bt, d, m, n_local, k)
         resident_bytes = a.numel() * 2 + bt.numel() * 2 + d.numel() * 2
         dtype = "bf16"
+    elif kind == "decode":
+        a = torch.empty(m, k // 2, device=dev, dtype=torch.uint8)
+        sfa = torch.empty(smb.gemm.sf_packed_bytes(m, k), device=dev, dtype=torch.uint8)
+        smb.gemm.fill_fp4_device(a, sfa, None, m, k, 6, 0, 0, stream=stream)
+        d = torch.empty(m, n_local, device=dev, dtype=torch.bfloat16)
+        weights, plans = [], []
+        for i in range(DECODE_WEIGHT_SETS):
+            w = torch.empty(n_local, k // 2, device=dev, dtype=torch.uint8)
+            sfw = torch.empty(smb.gemm.sf_packed_bytes(n_local, k), device=dev, dtype=torch.uint8)
+            # Different rows of the same logical generator for every set.
+            smb.gemm.fill_fp4_device(w, sfw, None, n_local, k, fill, 1, n0 + i * n, stream=stream)
+            weights.append((w, sfw))
+            plans.append(smb.gemm.Fp4Plan(a, sfa, w, sfw, d, m, n_local, k))
+        plan = plans[0]
+        resident_bytes = DECODE_WEIGHT_SETS * (weights[0][0].numel() + weights[0][1].numel())
+        dtype = "e2m1"
     else:
         a = torch.empty(m, k // 2, device=dev, dtype=torch.uint8)
         sfa = torch.empty(smb.gemm.sf_packed_bytes(m, k), device=dev, dtype=torch.uint8)
@@ -293,9 +315,12 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def run_step(i: int) -> None:
+        (plans[i % len(plans)] if plans else plan).run(stream)
+
     # ---------------------------------------------------------------- device-timed region
-    for _ in range(args.warmup):
-        plan.run(stream)
+    for i in range(args.warmup):
+        run_step(i)
     plan.check(stream)
     uuid = None
     try:
@@ -307,11 +332,12 @@ def main():
     barrier()
     with ClockSampler(uuid, local_rank) as sampler:
         e0.record(stream)
-        for _ in range(args.steps):
-            plan.run(stream)
+        for i in range(args.steps):
+            run_step(i)
         e1.record(stream)
         barrier()
-    plan.check(stream)
+    for pl in (plans or [plan]):
+        pl.check(stream)
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_local = e0.elapsed_time(e1)
     ms_step = ms_total / args.steps
@@ -324,7 +350,15 @@ def main():
     launch_ms = ms_local / args.steps
     achieved = 2.0 * m * n_local * k / (launch_ms * 1e-3) / 1e12
     timed_s = ms_total * 1e-3
-    if kind == "bf16":
+    if kind == "decode":
+        # Algorithmic bytes of one launch: weights + weight scales + activations + their scales + D.
+        algo_bytes = n_local * k // 2 + n_local * k // 32 + m * k // 2 + m * k // 32 + 2 * m * n_local
+        gbs = algo_bytes / (launch_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                    "peak_source": f"{peak_kind} device copy GB/s", "nominal_frac": gbs / 8000.0,
+                    "algorithmic_bytes_per_launch": algo_bytes}
+    elif kind == "bf16":
         peak = peaks["bf16_tflops"] if timed_s < 2.0 else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
         peak_note = f"{peak_kind} cuBLAS bf16 {'burst' if timed_s < 2.0 else 'sustained'} TFLOP/s"
     else:
@@ -333,10 +367,11 @@ def main():
         base = peaks["bf16_tflops"] if timed_s < 2.0 else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
         peak = 4.0 * base
         peak_note = f"4 x {peak_kind} cuBLAS bf16 TFLOP/s (no measured FP4 figure)"
-    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                "peak_source": peak_note,
-                "nominal_frac": achieved / (2250.0 if kind == "bf16" else 9000.0)}
+    if kind != "decode":
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                    "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                    "peak_source": peak_note,
+                    "nominal_frac": achieved / (2250.0 if kind == "bf16" else 9000.0)}
 
     # ---------------------------------------------------------------- optional all-gather of D
     allgather = None
@@ -396,7 +431,8 @@ def main():
                         "sample": sample + f" ({secs:.2f} s)",
                         "what": "reference NumPy CPU path: bf16 operands -> fp32, a @ b, round to bf16"}
 
-    plan.close()
+    for pl in (plans or [plan]):
+        pl.close()
     if rank == 0:
         line = {
             "metric": "GEMM TFLOPS", "value": value, "unit": "TFLOP/s", "n_gpus": g,
@@ -405,7 +441,9 @@ def main():
             "dtype": dtype, "data": "synthetic",
             "config": {"workload": args.workload, "description": desc, "shape_mnk": [m, n, k],
                        "sharding": f"N column-parallel over {g} GPU(s), {n_local} columns each",
-                       "l2": f"operands + output resident per GPU = {resident_bytes / 1e6:.0f} MB > 126 MB L2 (no flush)",
+                       "l2": (f"operands + output resident per GPU = {resident_bytes / 1e6:.0f} MB > 126 MB L2 (no flush)"
+                              if kind != "decode" else
+                              f"{DECODE_WEIGHT_SETS} rotating weight sets = {resident_bytes / 1e6:.0f} MB > 126 MB L2"),
                        "per_gpu_tflops": value / g},
             "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": args.steps, "allgather": allgather,

@@ -5,5 +5,5 @@ mirror of the reference drivers' command-line contract (``drivers.py``).  There 
 CPU implementation in here: if the CUDA library has not been built, importing
 ``strata_masonry_b200.capi`` raises.
 """
-from . import capi, gemm  # noqa: F401
+from . import capi, gemm, sharding  # noqa: F401
 from .capi import SmbError, lib  # noqa: F401
