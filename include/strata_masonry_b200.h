@@ -207,6 +207,9 @@ size_t smb_decode_noalloc_scratch_limit(void);
 #define SMB_FLAG_TILE_N_256 8u        /* force 256 x 256 tiles, two accumulator banks */
 #define SMB_FLAG_TILE_N_512 16u       /* force 256 x 512 tiles, one accumulator set */
 #define SMB_FLAG_TILE_N_384 32u       /* FP4 only: force 256 x 384 tiles */
+ /* Hand tiles out through the hardware work queue (clusterlaunchcontrol.try_cancel, the
+  * reference's CLC scheduler, blocks/97_sched_warp_clc.cuh) instead of the static stride walk. */
+#define SMB_FLAG_DYNAMIC_TILES 256u
 #define SMB_FLAG_NO_DECODE 64u        /* FP4 only: M <= 128 through the tiled kernel, not the decode kernel */
 #define SMB_FLAG_NO_LAUNCH_OVERLAP 128u /* decode kernel: no programmatic dependent launch */
 

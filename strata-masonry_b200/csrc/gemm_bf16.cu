@@ -20,12 +20,13 @@
 //   NB = 1: the slots are two banks, the epilogue of tile i overlaps the main loop of i + 1;
 //   NB = 2: the slots are the two N halves of one tile; the MMA role restarts half h of the
 //           next tile as soon as the epilogue has drained half h.
-// Warp roles per CTA (320 threads): warp 0 TMA producer, warp 1 MMA issue + TMEM owner,
-// warps 2-9 epilogue (warp w reads TMEM lanes 32 (w % 4) .. +31; warps 2-5 take the first
+// Warp roles per CTA (352 threads): warp 0 TMA producer, warp 1 MMA issue + TMEM owner, warp 10
+// tile scheduler (sched.cuh), warps 2-9 epilogue (warp w reads TMEM lanes 32 (w % 4) .. +31; warps 2-5 take the first
 // half of a slot's columns / slot 0, warps 6-9 the second half / slot 1).
 #include "epilogue.cuh"
 #include "gemm_common.cuh"
 #include "ptx.cuh"
+#include "sched.cuh"
 
 namespace smb {
 
@@ -33,7 +34,7 @@ namespace bf16k {
 
 constexpr int kBlockM = 128;          // rows of A per CTA
 constexpr int kBlockK = 64;           // K elements per stage (= 128 bytes per row)
-constexpr int kThreads = 320;
+constexpr int kThreads = 352;
 constexpr int kEpiWarps = 8;
 constexpr int kABytes = kBlockM * kBlockK * 2;        // 16 KiB
 constexpr int kTmemCols = 512;
@@ -69,6 +70,7 @@ struct Params {
   uint16_t* d_ptr;    // D base (used by the plain-store epilogue)
   int* status;
   long long* prof;    // optional: 8 cycle counters per CTA (see kProf* below), or null
+  int dynamic;        // 1: tiles come from the hardware work queue (one cluster launched per tile)
 };
 
 // Per-CTA role timers (cycles), written when Params::prof is set.
@@ -93,6 +95,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * kStages + 4);
+  SchedSmem sched;
+  sched.response = bar_base + 512u;
+  sched.slot_full = bar_base + 528u;
+  sched.slot_empty = bar_base + 536u;
+  // Consumers of a scheduler response: both load threads, the MMA thread, every working epilogue warp.
+  constexpr int kEpiWarpsActive = (NB == 2) ? 8 : 4 * C::kGroupsPerSlot;
+  constexpr int kSchedConsumers = 2 + 1 + 2 * kEpiWarpsActive;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -111,6 +120,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(acc_full_bar(b), 1);                 // one tcgen05.commit
       mbar_init(acc_empty_bar(b), C::kSlotReaders);  // every epilogue warp that reads the slot
     }
+    mbar_init(sched.slot_full, 1);
+    mbar_init(sched.slot_empty, kSchedConsumers);
     fence_mbar_init_cluster();
   }
   if (warp == 0 && lane == 0) {
@@ -139,7 +150,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool prof = p.prof != nullptr;
       long long waited = 0;
       const long long t_begin = prof ? clock64() : 0;
-      for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
+      TileCursor cursor;
+      cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
+      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, true, false)) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
@@ -186,7 +199,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool prof = p.prof != nullptr;
       long long wait_full = 0, wait_acc = 0;
       const long long t_begin = prof ? clock64() : 0;
-      for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++local) {
+      TileCursor cursor;
+      cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
+      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, true, false), ++local) {
         // NB = 1: slot = bank (local & 1), used every second tile.  NB = 2: slots 0 and 1 are the
         // two halves of every tile.
         const int bank = (NB == 1) ? (local & 1) : 0;
@@ -240,6 +255,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         p.prof[blockIdx.x * kProfCount + kProfTiles] = local;
       }
     }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------- tile scheduler (leader CTA)
+    if (p.dynamic != 0 && rank == 0 && lane == 0) clc_scheduler_loop(sched, p.status);
   } else {
     // ------------------------------------------------------------- epilogue (8 warps)
     const int quarter = warp & 3;           // TMEM lane quarter this warp may read
@@ -259,7 +277,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool prof = p.prof != nullptr && warp == 2 && lane == 0;
       long long waited = 0;
       const long long t_begin = prof ? clock64() : 0;
-      for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++local) {
+      TileCursor cursor;
+      cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
+      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true), ++local) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const int bank = (NB == 1) ? (local & 1) : 0;
@@ -357,6 +377,13 @@ int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (L.max_clusters > 0 && clusters > L.max_clusters) clusters = L.max_clusters;
+  // Hardware work queue: one cluster per tile is launched; those that get to run take over the
+  // tiles of those that have not started.  Pointless when every tile has a cluster anyway.
+  p.dynamic = (L.dynamic && tiles > clusters && L.max_clusters == 0) ? 1 : 0;
+  if (p.dynamic) {
+    if (tiles > (1LL << 30)) return set_error(SMB_ERR_UNSUPPORTED, "bf16: too many tiles for one grid");
+    clusters = static_cast<int>(tiles);
+  }
   kernel<<<dim3(2 * clusters, 1, 1), dim3(bf16k::kThreads, 1, 1), C::kTotal, stream>>>(
       L.tmap_a, L.tmap_b, L.tmap_d, p);
   cudaError_t e = cudaGetLastError();

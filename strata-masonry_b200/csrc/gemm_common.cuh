@@ -55,6 +55,7 @@ struct Bf16Launch {
   int ldd;
   int* status;       // device status word, may be null
   long long* prof;   // device buffer of 8 counters per CTA (role timers), or null
+  bool dynamic;      // tiles from the hardware work queue (cluster launch control) instead of a static walk
 };
 void bf16_pick_tile(int M, int N, int K, int* tile_n, int* sub_blocks);
 int bf16_launch(const Bf16Launch& L, cudaStream_t stream);
@@ -72,6 +73,7 @@ struct Fp4Launch {
   int* status;
   long long* prof;
   int prefetch;      // L2 prefetch distance in K blocks (0 = off)
+  bool dynamic;      // tiles from the hardware work queue instead of a static walk
 };
 void fp4_pick_tile(int M, int N, int K, int* w0, int* w1);
 int fp4_launch(const Fp4Launch& L, cudaStream_t stream);

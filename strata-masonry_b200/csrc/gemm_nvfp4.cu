@@ -25,6 +25,7 @@
 #include "epilogue.cuh"
 #include "gemm_common.cuh"
 #include "ptx.cuh"
+#include "sched.cuh"
 
 namespace smb {
 
@@ -33,7 +34,7 @@ namespace fp4k {
 constexpr int kBlockM = 128;          // rows of A per CTA
 constexpr int kBlockKBytes = 128;     // bytes of K per row per stage (= 256 E2M1 values)
 constexpr int kBlockK = 256;
-constexpr int kThreads = 352;
+constexpr int kThreads = 384;
 constexpr int kEpiWarps = 8;
 constexpr int kABytes = kBlockM * kBlockKBytes;   // 16 KiB
 constexpr int kSfCellBytes = 512;     // 128 rows x 4 scale bytes (K = 128)
@@ -84,6 +85,7 @@ struct Params {
   int* status;
   long long* prof;
   int prefetch;   // L2 prefetch distance in K blocks (0 = off)
+  int dynamic;    // 1: tiles come from the hardware work queue (one cluster launched per tile)
 };
 
 enum { kProfLoadWait = 0, kProfLoadTotal, kProfMmaWaitFull, kProfMmaWaitAcc, kProfMmaTotal,
@@ -111,6 +113,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tmem_slot = bar_base + 8u * (2 * kStages + 4);
   auto sf_ready_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 6 + s); };
   auto sf_full_bar = [&](int s) { return bar_base + 8u * (3 * kStages + 6 + s); };
+  SchedSmem sched;
+  sched.response = bar_base + 768u;
+  sched.slot_full = bar_base + 784u;
+  sched.slot_empty = bar_base + 792u;
+  // Consumers of a scheduler response: both load threads, MMA thread, scale thread, 16 epilogue warps.
+  constexpr int kSchedConsumers = 2 + 1 + 1 + 2 * kEpiWarps;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -131,6 +139,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(acc_full_bar(b), 1);
       mbar_init(acc_empty_bar(b), 2 * kEpiWarps);   // all epilogue warps of both CTAs
     }
+    mbar_init(sched.slot_full, 1);
+    mbar_init(sched.slot_empty, kSchedConsumers);
     fence_mbar_init_cluster();
   }
   if (warp == 0 && lane == 0) {
@@ -163,7 +173,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool prof = p.prof != nullptr;
       long long waited = 0;
       const long long t_begin = prof ? clock64() : 0;
-      for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
+      TileCursor cursor;
+      cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
+      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, true, false)) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
@@ -229,7 +241,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool prof = p.prof != nullptr;
       long long wait_full = 0, wait_acc = 0;
       const long long t_begin = prof ? clock64() : 0;
-      for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++local) {
+      TileCursor cursor;
+      cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
+      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, true, false), ++local) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const bool has_sub1 = (C::kSubs == 2) && (tn * C::kTileN + W0 < p.N);
@@ -310,7 +324,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = cluster; t < num_tiles && ok; t += n_clusters) {
+      TileCursor cursor;
+      cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
+      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, true, false)) {
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(sf_full_bar(s), ph)) {
             report_status(p.status, kDevTimeoutSched);
@@ -347,6 +363,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+  } else if (warp == 11) {
+    // ------------------------------------------------------------- tile scheduler (leader CTA)
+    if (p.dynamic != 0 && rank == 0 && lane == 0) clc_scheduler_loop(sched, p.status);
   } else {
     // ------------------------------------------------------------- epilogue (8 warps)
     const int quarter = warp & 3;
@@ -364,7 +383,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const bool prof = p.prof != nullptr && warp == 2 && lane == 0;
     long long waited = 0;
     const long long t_begin = prof ? clock64() : 0;
-    for (int t = cluster; t < num_tiles && ok; t += n_clusters, ++local) {
+    TileCursor cursor;
+    cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
+    for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true), ++local) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       const int bank = C::kTwoBanks ? (local & 1) : 0;
@@ -454,6 +475,11 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (L.max_clusters > 0 && clusters > L.max_clusters) clusters = L.max_clusters;
+  p.dynamic = (L.dynamic && tiles > clusters && L.max_clusters == 0) ? 1 : 0;
+  if (p.dynamic) {
+    if (tiles > (1LL << 30)) return set_error(SMB_ERR_UNSUPPORTED, "nvfp4: too many tiles for one grid");
+    clusters = static_cast<int>(tiles);
+  }
   kernel<<<dim3(2 * clusters, 1, 1), dim3(fp4k::kThreads, 1, 1), C::kTotal, stream>>>(
       L.tmap_a, L.tmap_b0, L.tmap_b1, L.tmap_sfa, L.tmap_sfb, L.tmap_d, p);
   cudaError_t e = cudaGetLastError();

@@ -411,3 +411,28 @@ def test_fp4_decode_constant_fill_is_exact(smb, cuda_device):
     nn = torch.arange(n, device=outs[0].device).view(1, -1)
     exact = (k * torch.exp2((mm % 5) - 2.0) * torch.exp2((nn % 3) - 1.0)).to(torch.bfloat16)
     assert torch.equal(outs[0], exact)
+
+
+# ------------------------------------------------------------------------------- hardware work queue
+@pytest.mark.parametrize("shape", [(256, 128, 64), (1024, 2048, 4096), (2048, 2624, 2048), (300, 200, 72),
+                                   (8192, 8192, 1024)])
+def test_bf16_dynamic_tile_queue(smb, oracle, cuda_device, shape):
+    """Tiles handed out by clusterlaunchcontrol.try_cancel instead of the static walk: same bits."""
+    torch = _torch()
+    m, n, k = shape
+    a, bt, d_static = _run_bf16(smb, m, n, k, 5)
+    _, _, d_dyn = _run_bf16(smb, m, n, k, 5, flags=smb.capi.FLAG_DYNAMIC_TILES)
+    assert torch.equal(d_static.view(torch.int16), d_dyn.view(torch.int16))
+    _check_bf16_full(oracle, a, bt, d_dyn, n, k)
+
+
+@pytest.mark.parametrize("shape_flags", [((512, 768, 1024), "FLAG_TILE_N_384"), ((1024, 1024, 2048), "FLAG_TILE_N_256"),
+                                         ((1024, 1024, 2048), "FLAG_TILE_N_128"), ((4096, 8192, 1024), "FLAG_NONE")])
+def test_fp4_dynamic_tile_queue(smb, cuda_device, shape_flags):
+    torch = _torch()
+    (m, n, k), name = shape_flags
+    flags = getattr(smb.capi, name)
+    A, B, d_static = _run_fp4(smb, m, n, k, 5, flags=flags)
+    _, _, d_dyn = _run_fp4(smb, m, n, k, 5, flags=flags | smb.capi.FLAG_DYNAMIC_TILES)
+    assert torch.equal(d_static.view(torch.int16), d_dyn.view(torch.int16))
+    _check_fp4_full(A, B, d_dyn, k)
