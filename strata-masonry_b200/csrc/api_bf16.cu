@@ -156,24 +156,38 @@ extern "C" int smb_dense_gemm_bf16(const void* a, const void* bt, void* d, int M
 }
 
 // ------------------------------------------------------------------------------------
-// Host-buffer context: device buffers, plan and stream are created once; every run uploads
-// A and BT, launches, downloads D and synchronises.
+// Host-buffer context: device buffers, plans, streams and events are created once; every
+// run uploads A and BT, computes and downloads D.  The work is cut into row chunks of A
+// so that the three legs overlap: while chunk i is being multiplied, chunk i+1 of A is on its
+// way up and chunk i-1 of D on its way down (PCIe is full duplex).  BT goes up first.
 // ------------------------------------------------------------------------------------
+#include <vector>
+
+namespace {
+constexpr int kHostChunkRows = 1024;
+}
+
 struct smb_bf16_host_ctx {
   int M, N, K;
   int64_t ldd;
   void *da, *db, *dd;
-  smb_bf16_plan* plan;
-  cudaStream_t stream;
+  std::vector<smb_bf16_plan*> plans;   // one per row chunk
+  std::vector<int> chunk_row0, chunk_rows;
+  std::vector<cudaEvent_t> uploaded, computed;
+  cudaStream_t up, compute, down;
 };
 
 extern "C" int smb_bf16_host_ctx_destroy(smb_bf16_host_ctx* ctx) {
   if (ctx == nullptr) return SMB_OK;
-  smb_bf16_plan_destroy(ctx->plan);
+  for (smb_bf16_plan* p : ctx->plans) smb_bf16_plan_destroy(p);
+  for (cudaEvent_t e : ctx->uploaded) cudaEventDestroy(e);
+  for (cudaEvent_t e : ctx->computed) cudaEventDestroy(e);
   if (ctx->da) cudaFree(ctx->da);
   if (ctx->db) cudaFree(ctx->db);
   if (ctx->dd) cudaFree(ctx->dd);
-  if (ctx->stream) cudaStreamDestroy(ctx->stream);
+  if (ctx->up) cudaStreamDestroy(ctx->up);
+  if (ctx->compute) cudaStreamDestroy(ctx->compute);
+  if (ctx->down) cudaStreamDestroy(ctx->down);
   delete ctx;
   return SMB_OK;
 }
@@ -190,16 +204,32 @@ extern "C" int smb_bf16_host_ctx_create(smb_bf16_host_ctx** out, int M, int N, i
   // Pad rows of D to 8 elements so that the TMA-store epilogue is always usable.
   c->ldd = (static_cast<int64_t>(N) + 7) / 8 * 8;
   c->da = c->db = c->dd = nullptr;
-  c->plan = nullptr;
-  c->stream = nullptr;
+  c->up = c->compute = c->down = nullptr;
   int rc = SMB_OK;
-  cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+  cudaError_t e = cudaStreamCreateWithFlags(&c->up, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->compute, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->down, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaMalloc(&c->da, static_cast<size_t>(M) * K * 2);
   if (e == cudaSuccess) e = cudaMalloc(&c->db, static_cast<size_t>(N) * K * 2);
   if (e == cudaSuccess) e = cudaMalloc(&c->dd, static_cast<size_t>(M) * c->ldd * 2);
   if (e != cudaSuccess) rc = set_cuda_error(e, "host context: allocation");
-  if (rc == SMB_OK)
-    rc = smb_bf16_plan_create(&c->plan, c->da, c->db, c->dd, M, N, K, K, K, c->ldd, SMB_FLAG_NONE);
+  for (int row0 = 0; rc == SMB_OK && row0 < M; row0 += kHostChunkRows) {
+    const int rows = (M - row0 < kHostChunkRows) ? (M - row0) : kHostChunkRows;
+    smb_bf16_plan* plan = nullptr;
+    rc = smb_bf16_plan_create(&plan, static_cast<char*>(c->da) + static_cast<size_t>(row0) * K * 2, c->db,
+                              static_cast<char*>(c->dd) + static_cast<size_t>(row0) * c->ldd * 2, rows,
+                              N, K, K, K, c->ldd, SMB_FLAG_NONE);
+    if (rc != SMB_OK) break;
+    c->plans.push_back(plan);
+    c->chunk_row0.push_back(row0);
+    c->chunk_rows.push_back(rows);
+    cudaEvent_t ev_up = nullptr, ev_done = nullptr;
+    e = cudaEventCreateWithFlags(&ev_up, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ev_done, cudaEventDisableTiming);
+    if (ev_up) c->uploaded.push_back(ev_up);
+    if (ev_done) c->computed.push_back(ev_done);
+    if (e != cudaSuccess) rc = set_cuda_error(e, "host context: event creation");
+  }
   if (rc != SMB_OK) {
     smb_bf16_host_ctx_destroy(c);
     return rc;
@@ -213,17 +243,41 @@ extern "C" int smb_bf16_host_ctx_run(smb_bf16_host_ctx* c, const uint16_t* a, co
   if (c == nullptr) return set_error(SMB_ERR_INVALID, "host context: null handle");
   if (a == nullptr || bt == nullptr || d == nullptr)
     return set_error(SMB_ERR_INVALID, "host context: null operand pointer");
-  const size_t a_bytes = static_cast<size_t>(c->M) * c->K * 2;
-  const size_t b_bytes = static_cast<size_t>(c->N) * c->K * 2;
-  cudaError_t e = cudaMemcpyAsync(c->da, a, a_bytes, cudaMemcpyHostToDevice, c->stream);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(c->db, bt, b_bytes, cudaMemcpyHostToDevice, c->stream);
-  if (e != cudaSuccess) return set_cuda_error(e, "host context: upload");
-  int rc = smb_bf16_plan_run(c->plan, c->stream);
-  if (rc != SMB_OK) return rc;
-  e = cudaMemcpy2DAsync(d, static_cast<size_t>(c->N) * 2, c->dd, static_cast<size_t>(c->ldd) * 2,
-                        static_cast<size_t>(c->N) * 2, c->M, cudaMemcpyDeviceToHost, c->stream);
-  if (e != cudaSuccess) return set_cuda_error(e, "host context: download");
-  return smb_bf16_plan_check(c->plan, c->stream);
+  const size_t row_bytes_a = static_cast<size_t>(c->K) * 2;
+  cudaError_t e = cudaMemcpyAsync(c->db, bt, static_cast<size_t>(c->N) * c->K * 2,
+                                  cudaMemcpyHostToDevice, c->up);
+  if (e != cudaSuccess) return set_cuda_error(e, "host context: upload of BT");
+  const size_t chunks = c->plans.size();
+  for (size_t i = 0; i < chunks; ++i) {
+    const size_t row0 = static_cast<size_t>(c->chunk_row0[i]);
+    const size_t rows = static_cast<size_t>(c->chunk_rows[i]);
+    e = cudaMemcpyAsync(static_cast<char*>(c->da) + row0 * row_bytes_a,
+                        reinterpret_cast<const char*>(a) + row0 * row_bytes_a, rows * row_bytes_a,
+                        cudaMemcpyHostToDevice, c->up);
+    if (e == cudaSuccess) e = cudaEventRecord(c->uploaded[i], c->up);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->compute, c->uploaded[i], 0);
+    if (e != cudaSuccess) return set_cuda_error(e, "host context: upload of A");
+    int rc = smb_bf16_plan_run(c->plans[i], c->compute);
+    if (rc != SMB_OK) return rc;
+    e = cudaEventRecord(c->computed[i], c->compute);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->down, c->computed[i], 0);
+    if (e == cudaSuccess)
+      e = cudaMemcpy2DAsync(reinterpret_cast<char*>(d) + row0 * static_cast<size_t>(c->N) * 2,
+                            static_cast<size_t>(c->N) * 2,
+                            static_cast<char*>(c->dd) + row0 * static_cast<size_t>(c->ldd) * 2,
+                            static_cast<size_t>(c->ldd) * 2, static_cast<size_t>(c->N) * 2, rows,
+                            cudaMemcpyDeviceToHost, c->down);
+    if (e != cudaSuccess) return set_cuda_error(e, "host context: download of D");
+  }
+  e = cudaStreamSynchronize(c->down);
+  if (e != cudaSuccess) return set_cuda_error(e, "host context: synchronize");
+  // The next run overwrites A and BT on the upload stream: every GEMM must be done by then (it
+  // is: the download stream waited for all of them).  Collect the kernels' status words.
+  for (size_t i = 0; i < chunks; ++i) {
+    int rc = smb_bf16_plan_check(c->plans[i], c->compute);
+    if (rc != SMB_OK) return rc;
+  }
+  return SMB_OK;
 }
 
 extern "C" int smb_dense_gemm_bf16_host(const uint16_t* a, const uint16_t* bt, uint16_t* d, int M,

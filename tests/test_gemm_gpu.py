@@ -436,3 +436,19 @@ def test_fp4_dynamic_tile_queue(smb, cuda_device, shape_flags):
     _, _, d_dyn = _run_fp4(smb, m, n, k, 5, flags=flags | smb.capi.FLAG_DYNAMIC_TILES)
     assert torch.equal(d_static.view(torch.int16), d_dyn.view(torch.int16))
     _check_fp4_full(A, B, d_dyn, k)
+
+
+def test_bf16_host_context_chunked_pipeline(smb, oracle, cuda_device):
+    """Host-buffer context (what `e2e` in bench.py times): several row chunks, a ragged last chunk,
+    two runs on one context; result identical to the device-resident path."""
+    torch = _torch()
+    m, n, k = 2500, 1000, 512
+    a, bt, d = _run_bf16(smb, m, n, k, 5)
+    a_host = a.view(torch.int16).cpu().numpy().view(np.uint16)
+    bt_host = bt.view(torch.int16).cpu().numpy().view(np.uint16)
+    ctx = smb.gemm.Bf16HostContext(m, n, k)
+    for _ in range(2):
+        out = np.zeros((m, n), dtype=np.uint16)
+        ctx.run(a_host, bt_host, out)
+        np.testing.assert_array_equal(out, _bits(d))
+    ctx.close()
