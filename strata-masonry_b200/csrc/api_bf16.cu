@@ -62,7 +62,7 @@ extern "C" int smb_bf16_plan_create(smb_bf16_plan** out, const void* a, const vo
   L.M = M;
   L.N = N;
   L.K = K;
-  bf16_pick_tile(M, N, K, &L.tile_n, &L.sub_blocks);
+  bf16_pick_tile(M, N, K, device_cluster_slots(), &L.tile_n, &L.sub_blocks);
   if (flags & SMB_FLAG_TILE_N_512) { L.tile_n = 256; L.sub_blocks = 2; }
   if (flags & SMB_FLAG_TILE_N_256) { L.tile_n = 256; L.sub_blocks = 1; }
   if (flags & SMB_FLAG_TILE_N_128) { L.tile_n = 128; L.sub_blocks = 1; }

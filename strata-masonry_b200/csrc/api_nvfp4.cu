@@ -45,7 +45,7 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
   L.M = M;
   L.N = N;
   L.K = K;
-  fp4_pick_tile(M, N, K, &L.w0, &L.w1);
+  fp4_pick_tile(M, N, K, device_cluster_slots(), &L.w0, &L.w1);
   if (flags & SMB_FLAG_TILE_N_128) { L.w0 = 128; L.w1 = 0; }
   if (flags & SMB_FLAG_TILE_N_256) { L.w0 = 256; L.w1 = 0; }
   if (flags & SMB_FLAG_TILE_N_384) { L.w0 = 256; L.w1 = 128; }

@@ -111,6 +111,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
 
+  // Programmatic dependent launch: the next kernel on the stream may begin its prologue while
+  // this grid is still running (it waits, below, before it loads or stores anything).
+  griddep_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), 1);    // the leader's arrive.expect_tx covers both CTAs' bytes
@@ -142,7 +145,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    // The whole warp walks the loop and waits; one elected lane issues.  Keeping the control
+    // flow warp-uniform lets the compiler hold addresses and descriptors in uniform registers,
+    // which is what the TMA and tcgen05 instructions take (measured on the FP4 kernel: the same
+    // loop run by lane 0 alone issued each instruction about 50 cycles slower).
+    {
       const uint32_t leader_full0 = mapa_u32(full_bar(0), 0);
       int s = 0;
       uint32_t ph = 0;
@@ -152,7 +159,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const long long t_begin = prof ? clock64() : 0;
       TileCursor cursor;
       cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
-      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, true, false)) {
+      // Everything before this point overlapped the tail of the previous kernel on the stream;
+      // its results (possibly this kernel's operands, certainly the old contents of D) are
+      // complete and visible once this returns.  All data flow of the kernel starts here.
+      griddep_wait();
+      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true)) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
@@ -169,13 +180,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t dst_a = ring_base + s * C::kStageBytes;
           // Only the leader arms its barrier (for both CTAs' bytes); the peer's copies credit the
           // same barrier and may land before or after the arming, which mbarrier tolerates.
-          if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * C::kStageBytes);
-          tma_load_2d_pair(dst_a, &tmap_a, bar, kb * kBlockK, row_a);
+          if (elect_one()) {
+            if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * C::kStageBytes);
+            tma_load_2d_pair(dst_a, &tmap_a, bar, kb * kBlockK, row_a);
 #pragma unroll
-          for (int h = 0; h < NB; ++h) {
-            tma_load_2d_pair(dst_a + kABytes + h * C::kBBytes, &tmap_b, bar, kb * kBlockK,
-                             row_b + h * TN);
+            for (int h = 0; h < NB; ++h) {
+              tma_load_2d_pair(dst_a + kABytes + h * C::kBBytes, &tmap_b, bar, kb * kBlockK,
+                               row_b + h * TN);
+            }
           }
+          __syncwarp();
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
       }
@@ -183,14 +197,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // Give copies already in flight time to land before this CTA's shared memory goes away.
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
       }
-      if (prof) {
+      if (prof && lane == 0) {
         p.prof[blockIdx.x * kProfCount + kProfLoadWait] = waited;
         p.prof[blockIdx.x * kProfCount + kProfLoadTotal] = clock64() - t_begin;
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issue (leader CTA only)
-    if (rank == 0 && lane == 0) {
+    if (rank == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(256, TN);
       int s = 0;
       uint32_t ph = 0;
@@ -201,7 +215,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const long long t_begin = prof ? clock64() : 0;
       TileCursor cursor;
       cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
-      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, true, false), ++local) {
+      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true), ++local) {
         // NB = 1: slot = bank (local & 1), used every second tile.  NB = 2: slots 0 and 1 are the
         // two halves of every tile.
         const int bank = (NB == 1) ? (local & 1) : 0;
@@ -235,20 +249,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(slot * TN);
             const uint64_t desc_b =
                 make_smem_desc(a_addr + kABytes + h * C::kBBytes, 1024, 16, kSwizzle128B);
+            if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < kBlockK / 16; ++k) {
-              // 16 bf16 = 32 bytes further along K inside the 128-byte swizzle row.
-              mma_bf16_ss<2>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc,
-                             (kb > 0 || k > 0) ? 1u : 0u);
+              for (int k = 0; k < kBlockK / 16; ++k) {
+                // 16 bf16 = 32 bytes further along K inside the 128-byte swizzle row.
+                mma_bf16_ss<2>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc,
+                               (kb > 0 || k > 0) ? 1u : 0u);
+              }
             }
+            __syncwarp();
           }
           if (!ok) break;
-          mma_commit_pair(empty_bar(s), 0x3);
+          if (elect_one()) mma_commit_pair(empty_bar(s), 0x3);
+          __syncwarp();
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
-        if (ok) mma_commit_pair(acc_full_bar(bank), 0x3);
+        if (ok && elect_one()) mma_commit_pair(acc_full_bar(bank), 0x3);
+        __syncwarp();
       }
-      if (prof) {
+      if (prof && lane == 0) {
         p.prof[blockIdx.x * kProfCount + kProfMmaWaitFull] = wait_full;
         p.prof[blockIdx.x * kProfCount + kProfMmaWaitAcc] = wait_acc;
         p.prof[blockIdx.x * kProfCount + kProfMmaTotal] = clock64() - t_begin;
@@ -384,9 +403,18 @@ int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
     if (tiles > (1LL << 30)) return set_error(SMB_ERR_UNSUPPORTED, "bf16: too many tiles for one grid");
     clusters = static_cast<int>(tiles);
   }
-  kernel<<<dim3(2 * clusters, 1, 1), dim3(bf16k::kThreads, 1, 1), C::kTotal, stream>>>(
-      L.tmap_a, L.tmap_b, L.tmap_d, p);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.blockDim = dim3(bf16k::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute pdl;
+  pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &pdl;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L.tmap_a, L.tmap_b, L.tmap_d, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error(e, "bf16 GEMM launch");
   return SMB_OK;
 }
@@ -398,19 +426,30 @@ int launch_bf16_store(const Bf16Launch& L, cudaStream_t stream) {
 
 }  // namespace
 
-void bf16_pick_tile(int M, int N, int K, int* tile_n, int* sub_blocks) {
-  (void)M;
+void bf16_pick_tile(int M, int N, int K, int clusters, int* tile_n, int* sub_blocks) {
   *sub_blocks = 1;
-  if (N > 128) {
-    *tile_n = 256;
-    // 256 x 512 tiles cut the L2 sector traffic per flop by a quarter but give up the
-    // overlap of epilogue and main loop: worth it once the K loop is long.
-    if (N > 256 && K >= 2048) *sub_blocks = 2;
-  } else if (N > 64) {
-    *tile_n = 128;
-  } else {
+  if (N <= 64) {
     *tile_n = 64;
+    return;
   }
+  if (N <= 128) {
+    *tile_n = 128;
+    return;
+  }
+  *tile_n = 256;
+  if (N <= 256) return;
+  // 256 x 512 tiles against 256 x 256 tiles.  Both keep the tensor pipe busy ~99 % of the
+  // cycles; the wide tile moves a quarter less data per flop through L2 and shared memory, which
+  // under the power cap is worth ~6 % of clock, but it has half as many tiles to spread over
+  // the clusters and exposes ~2500 cycles of accumulator drain per tile.  Estimated cycles:
+  if (clusters < 1) clusters = 74;
+  const long long tiles_m = (M + 255) / 256;
+  const long long kb = (K + 63) / 64;
+  const long long waves1 = (tiles_m * ((N + 255) / 256) + clusters - 1) / clusters;
+  const long long waves2 = (tiles_m * ((N + 511) / 512) + clusters - 1) / clusters;
+  const double cost1 = static_cast<double>(waves1) * (kb * 512.0);
+  const double cost2 = static_cast<double>(waves2) * (kb * 1024.0 + 2500.0) / 1.06;
+  if (cost2 < cost1) *sub_blocks = 2;
 }
 
 int bf16_launch(const Bf16Launch& L, cudaStream_t stream) {

@@ -57,7 +57,9 @@ struct Bf16Launch {
   long long* prof;   // device buffer of 8 counters per CTA (role timers), or null
   bool dynamic;      // tiles from the hardware work queue (cluster launch control) instead of a static walk
 };
-void bf16_pick_tile(int M, int N, int K, int* tile_n, int* sub_blocks);
+void bf16_pick_tile(int M, int N, int K, int clusters, int* tile_n, int* sub_blocks);
+// Number of 2-CTA clusters that can run at once on the current device (SM count / 2), 0 if unknown.
+int device_cluster_slots();
 int bf16_launch(const Bf16Launch& L, cudaStream_t stream);
 
 // --------------------------------------------------------------------------- nvfp4 launch
@@ -75,7 +77,7 @@ struct Fp4Launch {
   int prefetch;      // L2 prefetch distance in K blocks (0 = off)
   bool dynamic;      // tiles from the hardware work queue instead of a static walk
 };
-void fp4_pick_tile(int M, int N, int K, int* w0, int* w1);
+void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1);
 int fp4_launch(const Fp4Launch& L, cudaStream_t stream);
 
 // --------------------------------------------------------------------------- nvfp4 decode launch

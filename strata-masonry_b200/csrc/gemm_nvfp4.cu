@@ -128,6 +128,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
 
+  // Programmatic dependent launch: the next kernel on the stream may begin its prologue while
+  // this grid is still running (it waits, below, before it loads or stores anything).
+  griddep_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), 1);
@@ -164,7 +167,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    // The whole warp walks the loop and waits; one elected lane issues.  Keeping the control
+    // flow warp-uniform lets the compiler hold addresses and descriptors in uniform registers,
+    // which is what the TMA and tcgen05 instructions take.
+    {
       const uint32_t leader_full0 = mapa_u32(full_bar(0), 0);
       const uint32_t leader_sf_full0 = mapa_u32(sf_full_bar(0), 0);
       int s = 0;
@@ -175,7 +181,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const long long t_begin = prof ? clock64() : 0;
       TileCursor cursor;
       cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
-      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, true, false)) {
+      // Everything before this point overlapped the tail of the previous kernel on the stream;
+      // its results (possibly this kernel's operands, certainly the old contents of D) are
+      // complete and visible once this returns.  All data flow of the kernel starts here.
+      griddep_wait();
+      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true)) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
@@ -195,6 +205,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t sf_bar = leader_sf_full0 + 8u * s;
           const uint32_t dst = ring_base + s * C::kStageBytes;
           constexpr int kSfBytes = C::kSfaBytes + C::kSfbBytes;
+          if (elect_one()) {
           if (rank == 0) {
             mbar_arrive_expect_tx(sf_full_bar(s), 2 * kSfBytes);
             mbar_arrive_expect_tx(full_bar(s),
@@ -220,20 +231,22 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (C::kSubs == 2 && has_sub1)
               tma_prefetch_l2_2d(&tmap_b1, kp, col0 + W0 + static_cast<int>(rank) * (W1 / 2));
           }
+          }
+          __syncwarp();
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
       }
       if (!ok) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
       }
-      if (prof) {
+      if (prof && lane == 0) {
         p.prof[blockIdx.x * kProfCount + kProfLoadWait] = waited;
         p.prof[blockIdx.x * kProfCount + kProfLoadTotal] = clock64() - t_begin;
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issue (leader CTA only)
-    if (rank == 0 && lane == 0) {
+    if (rank == 0) {
       int s = 0;
       uint32_t ph = 0;
       int local = 0;
@@ -243,7 +256,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const long long t_begin = prof ? clock64() : 0;
       TileCursor cursor;
       cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
-      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, true, false), ++local) {
+      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true), ++local) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const bool has_sub1 = (C::kSubs == 2) && (tn * C::kTileN + W0 < p.N);
@@ -273,6 +286,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t stage = ring_base + s * C::kStageBytes;
           const uint32_t sf_t = tmem_base + static_cast<uint32_t>(C::kAccCols + s * C::kSlotCols);
           const uint64_t desc_a = make_smem_desc(stage, 1024, 16, kSwizzle128B);
+          if (elect_one()) {
 #pragma unroll
           for (int ki = 0; ki < 4; ++ki) {
             // K = 64 per instruction = 32 bytes along the swizzled row.  Atoms 2c and 2c + 1 share
@@ -300,11 +314,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
           mma_commit_pair(empty_bar(s), 0x3);
+          }
+          __syncwarp();
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
-        if (ok) mma_commit_pair(acc_full_bar(bank), 0x3);
+        if (ok && elect_one()) mma_commit_pair(acc_full_bar(bank), 0x3);
+        __syncwarp();
       }
-      if (prof) {
+      if (prof && lane == 0) {
         p.prof[blockIdx.x * kProfCount + kProfMmaWaitFull] = wait_full;
         p.prof[blockIdx.x * kProfCount + kProfMmaWaitAcc] = wait_acc;
         p.prof[blockIdx.x * kProfCount + kProfMmaTotal] = clock64() - t_begin;
@@ -320,13 +337,13 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // The copies are issued from this warp, not from the MMA thread: issued in line with the MMAs
     // they cost the tensor pipe about 50 cycles each (measured: 256 x 256 tiles went from 3.6 to
     // 5.1 PFLOP/s when they moved here), from a second warp they overlap the MMAs.
-    if (rank == 0 && lane == 0) {
+    if (rank == 0) {
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
       TileCursor cursor;
       cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
-      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, true, false)) {
+      for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true)) {
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(sf_full_bar(s), ph)) {
             report_status(p.status, kDevTimeoutSched);
@@ -338,6 +355,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t sf_t = tmem_base + static_cast<uint32_t>(C::kAccCols + s * C::kSlotCols);
           const uint64_t sfa_desc = make_smem_desc(stage + C::kOffSfa, 128, 16, kSwizzleNone);
           const uint64_t sfb_desc = make_smem_desc(stage + C::kOffSfb, 128, 16, kSwizzleNone);
+          if (elect_one()) {
 #pragma unroll
           for (int cell = 0; cell < 2; ++cell) {
             tmem_cp_32x128b_warpx4<2>(sf_t + 4u * cell, sfa_desc + cell * (kSfCellBytes / 16));
@@ -359,6 +377,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
             col += static_cast<uint32_t>(bands * 8);
           }
           mma_commit_pair(sf_ready_bar(s), 0x1);
+          }
+          __syncwarp();
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
       }
@@ -480,9 +500,19 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
     if (tiles > (1LL << 30)) return set_error(SMB_ERR_UNSUPPORTED, "nvfp4: too many tiles for one grid");
     clusters = static_cast<int>(tiles);
   }
-  kernel<<<dim3(2 * clusters, 1, 1), dim3(fp4k::kThreads, 1, 1), C::kTotal, stream>>>(
-      L.tmap_a, L.tmap_b0, L.tmap_b1, L.tmap_sfa, L.tmap_sfb, L.tmap_d, p);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.blockDim = dim3(fp4k::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute pdl;
+  pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &pdl;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L.tmap_a, L.tmap_b0, L.tmap_b1, L.tmap_sfa,
+                                     L.tmap_sfb, L.tmap_d, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error(e, "nvfp4 GEMM launch");
   return SMB_OK;
 }
@@ -494,18 +524,25 @@ int launch_fp4_store(const Fp4Launch& L, cudaStream_t stream) {
 
 }  // namespace
 
-void fp4_pick_tile(int M, int N, int K, int* w0, int* w1) {
-  (void)M;
+void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1) {
+  *w1 = 0;
   if (N <= 128) {
     *w0 = 128;
-    *w1 = 0;
-  } else if (N <= 256 || K < 2048) {
-    *w0 = 256;
-    *w1 = 0;
-  } else {
-    *w0 = 256;
-    *w1 = 128;
+    return;
   }
+  *w0 = 256;
+  if (N <= 256) return;
+  // 256 x 384 against 256 x 256 tiles (one accumulator set each, ~2000 cycles of drain per
+  // tile): the wider tile moves less data per flop, the narrower one spreads better over the
+  // clusters.  Estimated cycles, 768 / 512 MMA cycles per 256-wide K block:
+  if (clusters < 1) clusters = 74;
+  const long long tiles_m = (M + 255) / 256;
+  const long long kb = (K + 255) / 256;
+  const long long waves256 = (tiles_m * ((N + 255) / 256) + clusters - 1) / clusters;
+  const long long waves384 = (tiles_m * ((N + 383) / 384) + clusters - 1) / clusters;
+  const double cost256 = static_cast<double>(waves256) * (kb * 512.0 + 2000.0) / 0.985;
+  const double cost384 = static_cast<double>(waves384) * (kb * 768.0 + 2000.0);
+  if (cost384 <= cost256) *w1 = 128;
 }
 
 int fp4_launch(const Fp4Launch& L, cudaStream_t stream) {

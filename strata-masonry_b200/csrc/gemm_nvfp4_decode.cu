@@ -127,7 +127,9 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    // (All role loops are walked by the whole warp with one elected lane issuing: warp-uniform
+    // control flow keeps descriptors and addresses in uniform registers.)
+    {
       const uint64_t stream_once = l2_policy_evict_first();   // weights: read exactly once
       const uint64_t keep = l2_policy_evict_last();           // activations: re-read by every CTA
       int s = 0;
@@ -141,18 +143,21 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
           break;
         }
         const uint32_t dst = ring_base + static_cast<uint32_t>(s * p.stage_bytes);
-        mbar_arrive_expect_tx(sf_full_bar(s), 2 * kSfBytes);
-        tma_load_2d_cta_hint(dst + sfw_off, &tmap_sfw, sf_full_bar(s), kb * 128, tile, stream_once);
-        tma_load_2d_cta_hint(dst + sfx_off, &tmap_sfx, sf_full_bar(s), kb * 128, 0, keep);
-        mbar_arrive_expect_tx(full_bar(s), kWBytes + static_cast<uint32_t>(p.m_pad) * kBlockKBytes);
-        tma_load_2d_cta_hint(dst, &tmap_w, full_bar(s), kb * kBlockKBytes, tile * 128, stream_once);
-        tma_load_2d_cta_hint(dst + x_off, &tmap_x, full_bar(s), kb * kBlockKBytes, 0, keep);
+        if (elect_one()) {
+          mbar_arrive_expect_tx(sf_full_bar(s), 2 * kSfBytes);
+          tma_load_2d_cta_hint(dst + sfw_off, &tmap_sfw, sf_full_bar(s), kb * 128, tile, stream_once);
+          tma_load_2d_cta_hint(dst + sfx_off, &tmap_sfx, sf_full_bar(s), kb * 128, 0, keep);
+          mbar_arrive_expect_tx(full_bar(s), kWBytes + static_cast<uint32_t>(p.m_pad) * kBlockKBytes);
+          tma_load_2d_cta_hint(dst, &tmap_w, full_bar(s), kb * kBlockKBytes, tile * 128, stream_once);
+          tma_load_2d_cta_hint(dst + x_off, &tmap_x, full_bar(s), kb * kBlockKBytes, 0, keep);
+        }
+        __syncwarp();
         if (++s == stages) { s = 0; ph ^= 1u; }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issue
-    if (lane == 0) {
+    {
       int s = 0;
       uint32_t ph = 0;
       int seg = 0;
@@ -182,26 +187,30 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
           const uint32_t sf_t = tmem_base + static_cast<uint32_t>(kAccCols + s * kSlotCols);
           const uint64_t desc_w = make_smem_desc(stage, 1024, 16, kSwizzle128B);
           const uint64_t desc_x = make_smem_desc(stage + x_off, 1024, 16, kSwizzle128B);
+          if (elect_one()) {
 #pragma unroll
-          for (int ki = 0; ki < 4; ++ki) {
-            const uint32_t sf_id = (ki & 1) ? 2u : 0u;
-            const uint32_t cell = static_cast<uint32_t>(ki >> 1);
-            const uint32_t idesc = make_idesc_mxf4(128, p.m_pad, sf_id, sf_id, true);
-            mma_mxf4_ss<1>(acc, desc_w + 2u * ki, desc_x + 2u * ki, idesc, sf_t + 4u * cell,
-                           sf_t + 8u + 4u * cell, (i > 0 || ki > 0) ? 1u : 0u);
+            for (int ki = 0; ki < 4; ++ki) {
+              const uint32_t sf_id = (ki & 1) ? 2u : 0u;
+              const uint32_t cell = static_cast<uint32_t>(ki >> 1);
+              const uint32_t idesc = make_idesc_mxf4(128, p.m_pad, sf_id, sf_id, true);
+              mma_mxf4_ss<1>(acc, desc_w + 2u * ki, desc_x + 2u * ki, idesc, sf_t + 4u * cell,
+                             sf_t + 8u + 4u * cell, (i > 0 || ki > 0) ? 1u : 0u);
+            }
+            mma_commit_1cta(empty_bar(s));
           }
-          mma_commit_1cta(empty_bar(s));
+          __syncwarp();
           if (++s == stages) { s = 0; ph ^= 1u; }
         }
         (void)kb0;
-        if (ok) mma_commit_1cta(acc_full_bar(bank));
+        if (ok && elect_one()) mma_commit_1cta(acc_full_bar(bank));
+        __syncwarp();
         u = seg_end;
         ++seg;
       }
     }
   } else if (warp == 2) {
     // ------------------------------------------------------------- scale copies
-    if (lane == 0) {
+    {
       int s = 0;
       uint32_t ph = 0;
       for (long long u = u_begin; u < u_end; ++u) {
@@ -214,12 +223,15 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const uint32_t sf_t = tmem_base + static_cast<uint32_t>(kAccCols + s * kSlotCols);
         const uint64_t sfw_desc = make_smem_desc(stage + sfw_off, 128, 16, kSwizzleNone);
         const uint64_t sfx_desc = make_smem_desc(stage + sfx_off, 128, 16, kSwizzleNone);
+        if (elect_one()) {
 #pragma unroll
-        for (int cell = 0; cell < 2; ++cell) {
-          tmem_cp_32x128b_warpx4<1>(sf_t + 4u * cell, sfw_desc + cell * 32);
-          tmem_cp_32x128b_warpx4<1>(sf_t + 8u + 4u * cell, sfx_desc + cell * 32);
+          for (int cell = 0; cell < 2; ++cell) {
+            tmem_cp_32x128b_warpx4<1>(sf_t + 4u * cell, sfw_desc + cell * 32);
+            tmem_cp_32x128b_warpx4<1>(sf_t + 8u + 4u * cell, sfx_desc + cell * 32);
+          }
+          mma_commit_1cta(sf_ready_bar(s));
         }
-        mma_commit_1cta(sf_ready_bar(s));
+        __syncwarp();
         if (++s == stages) { s = 0; ph ^= 1u; }
       }
     }

@@ -27,6 +27,16 @@ int set_cuda_error(cudaError_t e, const char* what) {
   return SMB_ERR_CUDA;
 }
 
+int device_cluster_slots() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return sms / 2;
+}
+
 namespace {
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
