@@ -274,7 +274,7 @@ def main():
         bt = torch.empty(n_local, k, device=dev, dtype=torch.bfloat16)
         d = torch.empty(m, n_local, device=dev, dtype=torch.bfloat16)
         smb.gemm.bf16_operands_device(a, bt, m, n_local, k, fill, n0=n0, n_total=n, stream=stream)
-        plan = smb.gemm.Bf16Plan(a, bt, d, m, n_local, k)
+        plan = smb.gemm.Bf16Plan(a, bt, d, m, n_local, k, flags=smb.capi.FLAG_OPERANDS_STATIC)
         resident_bytes = a.numel() * 2 + bt.numel() * 2 + d.numel() * 2
         dtype = "bf16"
     elif kind == "decode":
@@ -301,7 +301,7 @@ def main():
         d = torch.empty(m, n_local, device=dev, dtype=torch.bfloat16)
         smb.gemm.fill_fp4_device(a, sfa, None, m, k, fill, 0, 0, stream=stream)
         smb.gemm.fill_fp4_device(bt, sfb, None, n_local, k, fill, 1, n0, stream=stream)
-        plan = smb.gemm.Fp4Plan(a, sfa, bt, sfb, d, m, n_local, k)
+        plan = smb.gemm.Fp4Plan(a, sfa, bt, sfb, d, m, n_local, k, flags=smb.capi.FLAG_OPERANDS_STATIC)
         resident_bytes = a.numel() + bt.numel() + sfa.numel() + sfb.numel() + d.numel() * 2
         dtype = "e2m1"
     torch.cuda.synchronize()
@@ -450,7 +450,9 @@ def main():
                        "l2": (f"operands + output resident per GPU = {resident_bytes / 1e6:.0f} MB > 126 MB L2 (no flush)"
                               if kind != "decode" else
                               f"{DECODE_WEIGHT_SETS} rotating weight sets = {resident_bytes / 1e6:.0f} MB > 126 MB L2"),
-                       "per_gpu_tflops": value / g},
+                       "per_gpu_tflops": value / g,
+                       "launch": "operands static across steps: consecutive launches may overlap head and tail "
+                                 "(programmatic dependent launch); stores to D stay ordered"},
             "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": args.steps, "allgather": allgather,
         }

@@ -210,6 +210,13 @@ size_t smb_decode_noalloc_scratch_limit(void);
  /* Hand tiles out through the hardware work queue (clusterlaunchcontrol.try_cancel, the
   * reference's CLC scheduler, blocks/97_sched_warp_clc.cuh) instead of the static stride walk. */
 #define SMB_FLAG_DYNAMIC_TILES 256u
+/* The GEMM kernels are launched with programmatic stream serialisation: their prologue overlaps
+ * the tail of the previous kernel on the stream and by default they wait for that kernel before
+ * loading anything.  With this flag the caller vouches that the operand (and scale) buffers are
+ * not written by that previous kernel; then only the stores to D wait, and loads and MMAs of
+ * this launch overlap the previous kernel's tail (what the reference drivers' timing loops do:
+ * dense_gemm_bf16.cu:355-361, blocks/97_sched_warp_clc.cuh:118-129). */
+#define SMB_FLAG_OPERANDS_STATIC 1024u
 #define SMB_FLAG_NO_DECODE 64u        /* FP4 only: M <= 128 through the tiled kernel, not the decode kernel */
 #define SMB_FLAG_NO_LAUNCH_OVERLAP 128u /* decode kernel: no programmatic dependent launch */
 

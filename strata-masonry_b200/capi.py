@@ -30,6 +30,7 @@ FLAG_TILE_N_384 = 32
 FLAG_NO_DECODE = 64
 FLAG_NO_LAUNCH_OVERLAP = 128
 FLAG_DYNAMIC_TILES = 256
+FLAG_OPERANDS_STATIC = 1024
 
 _vp = C.c_void_p
 _i = C.c_int

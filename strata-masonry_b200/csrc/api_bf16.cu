@@ -71,6 +71,7 @@ extern "C" int smb_bf16_plan_create(smb_bf16_plan** out, const void* a, const vo
   L.max_clusters = 0;
   L.prof = nullptr;
   L.dynamic = (flags & SMB_FLAG_DYNAMIC_TILES) != 0;
+  L.operands_static = (flags & SMB_FLAG_OPERANDS_STATIC) != 0;
   L.d = d;
   L.ldd = static_cast<int>(ldd);
   L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&

@@ -61,7 +61,7 @@ double run_one(int M, int N, int K, const Options& o) {
   DRV_CUDA(cudaStreamSynchronize(stream));
 
   smb_bf16_plan* plan = nullptr;
-  DRV_SMB(smb_bf16_plan_create(&plan, a, bt, d, M, N, K, K, K, N, SMB_FLAG_NONE));
+  DRV_SMB(smb_bf16_plan_create(&plan, a, bt, d, M, N, K, K, K, N, SMB_FLAG_OPERANDS_STATIC));
   if (o.raster == 1) DRV_SMB(smb_bf16_plan_tune(plan, 1, 0));
   if (o.raster == 2) DRV_SMB(smb_bf16_plan_tune(plan, (M + 255) / 256, 0));
   auto launch = [&]() { return smb_bf16_plan_run(plan, stream); };

@@ -64,7 +64,7 @@ double run_one(int M, int N, int K, const Options& o) {
   DRV_CUDA(cudaStreamSynchronize(stream));
 
   smb_fp4_plan* plan = nullptr;
-  DRV_SMB(smb_fp4_plan_create(&plan, a, sfa, b, sfb, d, M, N, K, K / 2, K / 2, N, SMB_FLAG_NONE));
+  DRV_SMB(smb_fp4_plan_create(&plan, a, sfa, b, sfb, d, M, N, K, K / 2, K / 2, N, SMB_FLAG_OPERANDS_STATIC));
   auto launch = [&]() { return smb_fp4_plan_run(plan, stream); };
   double ms = 0.0;
   if (o.benchmark) {

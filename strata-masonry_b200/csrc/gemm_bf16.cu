@@ -71,6 +71,7 @@ struct Params {
   int* status;
   long long* prof;    // optional: 8 cycle counters per CTA (see kProf* below), or null
   int dynamic;        // 1: tiles come from the hardware work queue (one cluster launched per tile)
+  int operands_static;  // 1: A and BT are not written by the previous kernel on the stream
 };
 
 // Per-CTA role timers (cycles), written when Params::prof is set.
@@ -161,8 +162,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
       // Everything before this point overlapped the tail of the previous kernel on the stream;
       // its results (possibly this kernel's operands, certainly the old contents of D) are
-      // complete and visible once this returns.  All data flow of the kernel starts here.
-      griddep_wait();
+      // complete and visible once this returns.  Unless the caller vouches that the operands are
+      // not that kernel's output, all data flow of this kernel starts here; if it does, only the
+      // epilogue waits (before it overwrites D) and loads and MMAs overlap the previous tail.
+      if (!p.operands_static) griddep_wait();
       for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true)) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
@@ -293,6 +296,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       out.N = p.N;
       int local = 0;
       bool ok = true;
+      if (p.operands_static) griddep_wait();
       const bool prof = p.prof != nullptr && warp == 2 && lane == 0;
       long long waited = 0;
       const long long t_begin = prof ? clock64() : 0;
@@ -393,6 +397,7 @@ int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
   p.d_ptr = static_cast<uint16_t*>(L.d);
   p.status = L.status;
   p.prof = L.prof;
+  p.operands_static = L.operands_static ? 1 : 0;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (L.max_clusters > 0 && clusters > L.max_clusters) clusters = L.max_clusters;

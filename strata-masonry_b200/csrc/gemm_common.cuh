@@ -56,6 +56,7 @@ struct Bf16Launch {
   int* status;       // device status word, may be null
   long long* prof;   // device buffer of 8 counters per CTA (role timers), or null
   bool dynamic;      // tiles from the hardware work queue (cluster launch control) instead of a static walk
+  bool operands_static;  // loads need not wait for the previous kernel on the stream
 };
 void bf16_pick_tile(int M, int N, int K, int clusters, int* tile_n, int* sub_blocks);
 // Number of 2-CTA clusters that can run at once on the current device (SM count / 2), 0 if unknown.
@@ -76,6 +77,7 @@ struct Fp4Launch {
   long long* prof;
   int prefetch;      // L2 prefetch distance in K blocks (0 = off)
   bool dynamic;      // tiles from the hardware work queue instead of a static walk
+  bool operands_static;  // loads need not wait for the previous kernel on the stream
 };
 void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1);
 int fp4_launch(const Fp4Launch& L, cudaStream_t stream);

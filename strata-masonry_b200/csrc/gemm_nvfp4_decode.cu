@@ -31,8 +31,6 @@ constexpr int kBlockKBytes = 128;     // 256 E2M1 values
 constexpr int kBlockK = 256;
 constexpr int kWBytes = 128 * kBlockKBytes;   // 16 KiB weight box
 constexpr int kSfBytes = 1024;        // one 128-row band x 8 scales (two 512-byte cells)
-constexpr int kTmemCols = 512;
-constexpr int kAccCols = 256;         // two banks of up to 128 columns
 constexpr int kSlotCols = 16;         // SFW cells (8 columns) + SFX cells (8 columns) per stage
 constexpr int kMaxStages = 16;
 constexpr int kBarrierBytes = 1024;
@@ -42,6 +40,8 @@ struct Params {
   int m_pad;          // activation rows rounded up to 16
   int stages;
   int stage_bytes;
+  int tmem_cols;      // 512 with one CTA per SM, 256 with two
+  int bank_stride;    // columns between the two accumulator banks (128 or 64)
   int ldd;
   uint16_t* d;
   float* scratch;     // [tiles][m_pad][128] fp32 partial sums (zero between calls)
@@ -116,7 +116,7 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
     tma_prefetch_desc(&tmap_sfx);
   }
   if (warp == 1) {
-    tmem_alloc<1>(tmem_slot, kTmemCols);
+    tmem_alloc<1>(tmem_slot, static_cast<uint32_t>(p.tmem_cols));
     tmem_relinquish<1>();
   }
   tc_fence_before_sync();
@@ -175,7 +175,7 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
           break;
         }
         tc_fence_after_sync();
-        const uint32_t acc = tmem_base + static_cast<uint32_t>(bank * 128);
+        const uint32_t acc = tmem_base + static_cast<uint32_t>(bank * p.bank_stride);
         for (int i = 0; i < count; ++i) {
           if (!mbar_wait(full_bar(s), ph) || !mbar_wait(sf_ready_bar(s), ph)) {
             report_status(p.status, kDevTimeoutMmaFull);
@@ -184,7 +184,7 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
           }
           tc_fence_after_sync();
           const uint32_t stage = ring_base + static_cast<uint32_t>(s * p.stage_bytes);
-          const uint32_t sf_t = tmem_base + static_cast<uint32_t>(kAccCols + s * kSlotCols);
+          const uint32_t sf_t = tmem_base + static_cast<uint32_t>(2 * p.bank_stride + s * kSlotCols);
           const uint64_t desc_w = make_smem_desc(stage, 1024, 16, kSwizzle128B);
           const uint64_t desc_x = make_smem_desc(stage + x_off, 1024, 16, kSwizzle128B);
           if (elect_one()) {
@@ -220,7 +220,7 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
         tc_fence_after_sync();
         const uint32_t stage = ring_base + static_cast<uint32_t>(s * p.stage_bytes);
-        const uint32_t sf_t = tmem_base + static_cast<uint32_t>(kAccCols + s * kSlotCols);
+        const uint32_t sf_t = tmem_base + static_cast<uint32_t>(2 * p.bank_stride + s * kSlotCols);
         const uint64_t sfw_desc = make_smem_desc(stage + sfw_off, 128, 16, kSwizzleNone);
         const uint64_t sfx_desc = make_smem_desc(stage + sfx_off, 128, 16, kSwizzleNone);
         if (elect_one()) {
@@ -255,7 +255,7 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const int row = quarter * 32 + lane;            // weight row inside the tile
       const int n = tile * 128 + row;                 // output column
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                             static_cast<uint32_t>(bank * 128);
+                             static_cast<uint32_t>(bank * p.bank_stride);
       const bool whole = (count == num_kb);
       float* slab = p.scratch + static_cast<size_t>(tile) * p.m_pad * 128;
       if (!waited_for_previous_grid) {
@@ -357,7 +357,7 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc<1>(tmem_base, kTmemCols);
+    tmem_dealloc<1>(tmem_base, static_cast<uint32_t>(p.tmem_cols));
   }
 }
 
@@ -385,7 +385,15 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   p.K = L.K;
   p.m_pad = (L.M + 15) / 16 * 16;
   p.stage_bytes = fp4_decode_stage_bytes(p.m_pad);
-  int stages = (kSmemBudget - 1024 - fp4d::kBarrierBytes) / p.stage_bytes;
+  // One CTA per SM.  (Two co-resident CTAs with half the ring each were measured slower, 22.8
+  // against 21.0-21.7 us at M = 16, and would let three CTAs share a tile.)
+  const int per_sm = 1;
+  const int budget = (per_sm == 2 ? 113 * 1024 : kSmemBudget) - 1024 - fp4d::kBarrierBytes;
+  int stages = budget / p.stage_bytes;
+  p.tmem_cols = per_sm == 2 ? 256 : 512;
+  p.bank_stride = per_sm == 2 ? 64 : 128;
+  const int max_slots = (p.tmem_cols - 2 * p.bank_stride) / fp4d::kSlotCols;
+  if (stages > max_slots) stages = max_slots;
   if (stages > fp4d::kMaxStages) stages = fp4d::kMaxStages;
   if (L.max_stages > 0 && stages > L.max_stages) stages = L.max_stages;
   if (stages < 2) return set_error(SMB_ERR_UNSUPPORTED, "decode: activation tile too large");
@@ -397,8 +405,8 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   p.status = L.status;
   const int num_kb = (L.K + fp4d::kBlockK - 1) / fp4d::kBlockK;
   const long long units = static_cast<long long>((L.N + 127) / 128) * num_kb;
-  int grid = L.max_ctas > 0 ? L.max_ctas : sm_count;
-  if (grid > sm_count) grid = sm_count;   // every CTA must be resident: one per SM
+  int grid = L.max_ctas > 0 ? L.max_ctas : per_sm * sm_count;
+  if (grid > per_sm * sm_count) grid = per_sm * sm_count;
   if (units < grid) grid = static_cast<int>(units);
   const int smem = 1024 + stages * p.stage_bytes + fp4d::kBarrierBytes;
   cudaLaunchConfig_t cfg = {};

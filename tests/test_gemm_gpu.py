@@ -452,3 +452,38 @@ def test_bf16_host_context_chunked_pipeline(smb, oracle, cuda_device):
         ctx.run(a_host, bt_host, out)
         np.testing.assert_array_equal(out, _bits(d))
     ctx.close()
+
+
+def test_back_to_back_launches_with_overlap_flag(smb, oracle, cuda_device):
+    """FLAG_OPERANDS_STATIC lets a launch load and multiply while the previous kernel on the stream
+    is still finishing; its stores to D still wait.  Two plans sharing D, launched back to back
+    many times: the last writer must win completely, every time."""
+    torch = _torch()
+    m, n, k = 1024, 1024, 512
+    dev = torch.device("cuda:0")
+    a1 = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
+    a2 = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
+    bt = torch.empty(n, k, device=dev, dtype=torch.bfloat16)
+    d = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+    smb.gemm.bf16_operands_device(a1, bt, m, n, k, 5)
+    smb.gemm.fill_bf16_device(a2, m, k, 2, 7, 0, k, 1)
+    f = smb.capi.FLAG_OPERANDS_STATIC
+    p1 = smb.gemm.Bf16Plan(a1, bt, d, m, n, k, flags=f)
+    p2 = smb.gemm.Bf16Plan(a2, bt, d, m, n, k, flags=f)
+    for _ in range(20):
+        p1.run()
+        p2.run()
+    p2.check()
+    want2 = d.clone()
+    for _ in range(20):
+        p2.run()
+        p1.run()
+    p1.check()
+    want1 = d.clone()
+    ref1 = a1.double() @ bt.double().t()
+    ref2 = a2.double() @ bt.double().t()
+    for got, ref in ((want1, ref1), (want2, ref2)):
+        bound = 2.0 ** -7 * ref.abs() + 2.0 ** -10 * (k ** 0.5) * float(ref.pow(2).mean().sqrt())
+        assert int(((got.double() - ref).abs() > bound).sum()) == 0
+    p1.close()
+    p2.close()
