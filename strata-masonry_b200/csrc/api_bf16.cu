@@ -16,6 +16,7 @@ using namespace smb;
 struct smb_bf16_plan {
   Bf16Launch launch;
   int* status_dev;
+  bool owns_status;
 };
 
 extern "C" int smb_version(void) { return 1000; }
@@ -38,9 +39,13 @@ const char* device_status_name(int code) {
 }
 }  // namespace smb
 
-extern "C" int smb_bf16_plan_create(smb_bf16_plan** out, const void* a, const void* bt, void* d,
-                                    int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd,
-                                    unsigned flags) {
+namespace {
+
+// `shared_status`: device status word owned by the caller (several plans reporting into one
+// word), or null for a word owned by the plan.
+int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, void* d, int M, int N,
+                          int K, int64_t lda, int64_t ldb, int64_t ldd, unsigned flags,
+                          int* shared_status) {
   if (out == nullptr) return set_error(SMB_ERR_INVALID, "plan: null output handle");
   *out = nullptr;
   if (a == nullptr || bt == nullptr || d == nullptr)
@@ -89,19 +94,30 @@ extern "C" int smb_bf16_plan_create(smb_bf16_plan** out, const void* a, const vo
       L.tmap_d = L.tmap_a;  // never dereferenced by the plain-store kernel
     }
   }
-  if (rc == SMB_OK) {
+  p->owns_status = (shared_status == nullptr);
+  if (rc == SMB_OK && p->owns_status) {
     cudaError_t e = cudaMalloc(&p->status_dev, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(p->status_dev, 0, sizeof(int));
     if (e != cudaSuccess) rc = set_cuda_error(e, "plan: status word allocation");
+  } else if (rc == SMB_OK) {
+    p->status_dev = shared_status;
   }
   if (rc != SMB_OK) {
-    if (p->status_dev) cudaFree(p->status_dev);
+    if (p->status_dev && p->owns_status) cudaFree(p->status_dev);
     delete p;
     return rc;
   }
   L.status = p->status_dev;
   *out = p;
   return SMB_OK;
+}
+
+}  // namespace
+
+extern "C" int smb_bf16_plan_create(smb_bf16_plan** out, const void* a, const void* bt, void* d,
+                                    int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd,
+                                    unsigned flags) {
+  return bf16_plan_create_impl(out, a, bt, d, M, N, K, lda, ldb, ldd, flags, nullptr);
 }
 
 extern "C" int smb_bf16_plan_tune(smb_bf16_plan* plan, int group_m, int max_clusters) {
@@ -140,7 +156,7 @@ extern "C" int smb_bf16_plan_check(smb_bf16_plan* plan, void* stream) {
 
 extern "C" int smb_bf16_plan_destroy(smb_bf16_plan* plan) {
   if (plan == nullptr) return SMB_OK;
-  if (plan->status_dev) cudaFree(plan->status_dev);
+  if (plan->status_dev && plan->owns_status) cudaFree(plan->status_dev);
   delete plan;
   return SMB_OK;
 }
@@ -161,17 +177,30 @@ extern "C" int smb_dense_gemm_bf16(const void* a, const void* bt, void* d, int M
 // run uploads A and BT, computes and downloads D.  The work is cut into row chunks of A
 // so that the three legs overlap: while chunk i is being multiplied, chunk i+1 of A is on its
 // way up and chunk i-1 of D on its way down (PCIe is full duplex).  BT goes up first.
+// What cannot overlap is the last chunk's GEMM and download, so the chunks shrink towards the
+// end: 1024 rows while much is left, then a quarter of the rest, never less than 256.
+// All chunk GEMMs report into one status word, read once per run together with the last download.
 // ------------------------------------------------------------------------------------
 #include <vector>
 
 namespace {
 constexpr int kHostChunkRows = 1024;
+constexpr int kHostChunkMinRows = 256;
+
+int next_chunk_rows(int rows_left) {
+  if (rows_left >= 4 * kHostChunkRows) return kHostChunkRows;
+  int rows = (rows_left / 4 + kHostChunkMinRows - 1) / kHostChunkMinRows * kHostChunkMinRows;
+  if (rows < kHostChunkMinRows) rows = kHostChunkMinRows;
+  return rows < rows_left ? rows : rows_left;
 }
+}  // namespace
 
 struct smb_bf16_host_ctx {
   int M, N, K;
   int64_t ldd;
   void *da, *db, *dd;
+  int* status_dev;
+  int* status_host;   // pinned
   std::vector<smb_bf16_plan*> plans;   // one per row chunk
   std::vector<int> chunk_row0, chunk_rows;
   std::vector<cudaEvent_t> uploaded, computed;
@@ -186,6 +215,8 @@ extern "C" int smb_bf16_host_ctx_destroy(smb_bf16_host_ctx* ctx) {
   if (ctx->da) cudaFree(ctx->da);
   if (ctx->db) cudaFree(ctx->db);
   if (ctx->dd) cudaFree(ctx->dd);
+  if (ctx->status_dev) cudaFree(ctx->status_dev);
+  if (ctx->status_host) cudaFreeHost(ctx->status_host);
   if (ctx->up) cudaStreamDestroy(ctx->up);
   if (ctx->compute) cudaStreamDestroy(ctx->compute);
   if (ctx->down) cudaStreamDestroy(ctx->down);
@@ -205,6 +236,7 @@ extern "C" int smb_bf16_host_ctx_create(smb_bf16_host_ctx** out, int M, int N, i
   // Pad rows of D to 8 elements so that the TMA-store epilogue is always usable.
   c->ldd = (static_cast<int64_t>(N) + 7) / 8 * 8;
   c->da = c->db = c->dd = nullptr;
+  c->status_dev = c->status_host = nullptr;
   c->up = c->compute = c->down = nullptr;
   int rc = SMB_OK;
   cudaError_t e = cudaStreamCreateWithFlags(&c->up, cudaStreamNonBlocking);
@@ -213,13 +245,18 @@ extern "C" int smb_bf16_host_ctx_create(smb_bf16_host_ctx** out, int M, int N, i
   if (e == cudaSuccess) e = cudaMalloc(&c->da, static_cast<size_t>(M) * K * 2);
   if (e == cudaSuccess) e = cudaMalloc(&c->db, static_cast<size_t>(N) * K * 2);
   if (e == cudaSuccess) e = cudaMalloc(&c->dd, static_cast<size_t>(M) * c->ldd * 2);
+  if (e == cudaSuccess) e = cudaMalloc(&c->status_dev, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(c->status_dev, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaMallocHost(&c->status_host, sizeof(int));
   if (e != cudaSuccess) rc = set_cuda_error(e, "host context: allocation");
-  for (int row0 = 0; rc == SMB_OK && row0 < M; row0 += kHostChunkRows) {
-    const int rows = (M - row0 < kHostChunkRows) ? (M - row0) : kHostChunkRows;
+  for (int row0 = 0; rc == SMB_OK && row0 < M;) {
+    const int rows = next_chunk_rows(M - row0);
     smb_bf16_plan* plan = nullptr;
-    rc = smb_bf16_plan_create(&plan, static_cast<char*>(c->da) + static_cast<size_t>(row0) * K * 2, c->db,
-                              static_cast<char*>(c->dd) + static_cast<size_t>(row0) * c->ldd * 2, rows,
-                              N, K, K, K, c->ldd, SMB_FLAG_NONE);
+    // The operands of a chunk's GEMM come from host copies ordered by events, never from the
+    // GEMM launched before it, so consecutive chunk GEMMs may overlap.
+    rc = bf16_plan_create_impl(&plan, static_cast<char*>(c->da) + static_cast<size_t>(row0) * K * 2,
+                               c->db, static_cast<char*>(c->dd) + static_cast<size_t>(row0) * c->ldd * 2,
+                               rows, N, K, K, K, c->ldd, SMB_FLAG_OPERANDS_STATIC, c->status_dev);
     if (rc != SMB_OK) break;
     c->plans.push_back(plan);
     c->chunk_row0.push_back(row0);
@@ -230,6 +267,7 @@ extern "C" int smb_bf16_host_ctx_create(smb_bf16_host_ctx** out, int M, int N, i
     if (ev_up) c->uploaded.push_back(ev_up);
     if (ev_done) c->computed.push_back(ev_done);
     if (e != cudaSuccess) rc = set_cuda_error(e, "host context: event creation");
+    row0 += rows;
   }
   if (rc != SMB_OK) {
     smb_bf16_host_ctx_destroy(c);
@@ -262,21 +300,31 @@ extern "C" int smb_bf16_host_ctx_run(smb_bf16_host_ctx* c, const uint16_t* a, co
     if (rc != SMB_OK) return rc;
     e = cudaEventRecord(c->computed[i], c->compute);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(c->down, c->computed[i], 0);
-    if (e == cudaSuccess)
-      e = cudaMemcpy2DAsync(reinterpret_cast<char*>(d) + row0 * static_cast<size_t>(c->N) * 2,
-                            static_cast<size_t>(c->N) * 2,
-                            static_cast<char*>(c->dd) + row0 * static_cast<size_t>(c->ldd) * 2,
-                            static_cast<size_t>(c->ldd) * 2, static_cast<size_t>(c->N) * 2, rows,
-                            cudaMemcpyDeviceToHost, c->down);
+    if (e == cudaSuccess) {
+      char* dst = reinterpret_cast<char*>(d) + row0 * static_cast<size_t>(c->N) * 2;
+      const char* src = static_cast<char*>(c->dd) + row0 * static_cast<size_t>(c->ldd) * 2;
+      if (c->ldd == c->N) {
+        e = cudaMemcpyAsync(dst, src, rows * static_cast<size_t>(c->N) * 2, cudaMemcpyDeviceToHost,
+                            c->down);
+      } else {
+        e = cudaMemcpy2DAsync(dst, static_cast<size_t>(c->N) * 2, src,
+                              static_cast<size_t>(c->ldd) * 2, static_cast<size_t>(c->N) * 2, rows,
+                              cudaMemcpyDeviceToHost, c->down);
+      }
+    }
     if (e != cudaSuccess) return set_cuda_error(e, "host context: download of D");
   }
-  e = cudaStreamSynchronize(c->down);
+  // The download stream has waited for every GEMM: the status word is final when it gets there.
+  e = cudaMemcpyAsync(c->status_host, c->status_dev, sizeof(int), cudaMemcpyDeviceToHost, c->down);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(c->down);
   if (e != cudaSuccess) return set_cuda_error(e, "host context: synchronize");
   // The next run overwrites A and BT on the upload stream: every GEMM must be done by then (it
-  // is: the download stream waited for all of them).  Collect the kernels' status words.
-  for (size_t i = 0; i < chunks; ++i) {
-    int rc = smb_bf16_plan_check(c->plans[i], c->compute);
-    if (rc != SMB_OK) return rc;
+  // is: the download stream waited for all of them).
+  const int status = *c->status_host;
+  if (status != 0) {
+    cudaMemset(c->status_dev, 0, sizeof(int));
+    return set_error(SMB_ERR_DEVICE, "bf16 GEMM kernel reported status %d: %s", status,
+                     device_status_name(status));
   }
   return SMB_OK;
 }

@@ -438,11 +438,13 @@ def test_fp4_dynamic_tile_queue(smb, cuda_device, shape_flags):
     _check_fp4_full(A, B, d_dyn, k)
 
 
-def test_bf16_host_context_chunked_pipeline(smb, oracle, cuda_device):
-    """Host-buffer context (what `e2e` in bench.py times): several row chunks, a ragged last chunk,
-    two runs on one context; result identical to the device-resident path."""
+@pytest.mark.parametrize("shape", [(2500, 1000, 512), (5000, 1001, 256), (100, 72, 64)])
+def test_bf16_host_context_chunked_pipeline(smb, oracle, cuda_device, shape):
+    """Host-buffer context (what `e2e` in bench.py times): row chunks that shrink towards the end,
+    a ragged last chunk, a D whose rows need padding on the device (N = 1001), two runs on one
+    context; result identical to the device-resident path."""
     torch = _torch()
-    m, n, k = 2500, 1000, 512
+    m, n, k = shape
     a, bt, d = _run_bf16(smb, m, n, k, 5)
     a_host = a.view(torch.int16).cpu().numpy().view(np.uint16)
     bt_host = bt.view(torch.int16).cpu().numpy().view(np.uint16)
