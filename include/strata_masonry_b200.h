@@ -200,6 +200,40 @@ int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sfa, const vo
                                         const void* sfb, void* d, int M, int N, int K, void* stream);
 size_t smb_decode_noalloc_scratch_limit(void);
 
+/* ----------------------------------------------------------------------------------
+ * Column-sharded GEMM across the GPUs of one box (one process per GPU).  The reference is
+ * single-GPU: nothing below has a counterpart there.  Rank r of g holds rows
+ * [r N/g, (r+1) N/g) of BT and computes D[:, r N/g : (r+1) N/g].
+ *
+ * Fused all-gather: with peer copies set, the epilogue of a plan writes every box of D it
+ * stores also into `count` (<= 7) further buffers with plain 16-byte stores, normally the
+ * same [M, N/g] column slab inside the full row-major D of every other GPU, mapped into this
+ * process with smb_peer_open().  dst[i] is the address of element (0, 0) of this plan's D in
+ * destination i, `ld` the row pitch (elements) of all destinations.  Needs the aligned store
+ * path (D 16-byte aligned, ldd % 8 == 0), N % 8 == 0, dst[i] 16-byte aligned, ld % 8 == 0.
+ * The kernel waits on no other GPU; a destination is complete once the writing kernel has
+ * completed (synchronise the stream, then tell the owner, e.g. with a barrier).
+ * count = 0 switches the copies off.  Decode-path FP4 plans (M <= 128) refuse them. */
+int smb_bf16_plan_set_peer_copies(smb_bf16_plan* plan, int count, void* const* dst, int64_t ld);
+int smb_fp4_plan_set_peer_copies(smb_fp4_plan* plan, int count, void* const* dst, int64_t ld);
+
+/* Device memory that other processes of the box can map: allocate, export a 64-byte handle
+ * (send it to the peers by any host channel), map a peer's handle into this process, unmap,
+ * free.  A mapped pointer is valid for kernels and copies of this process; peer access over
+ * NVLink is switched on by the mapping. */
+#define SMB_PEER_HANDLE_BYTES 64
+int smb_peer_alloc(void** ptr, size_t bytes);
+int smb_peer_export(void* ptr, unsigned char handle[SMB_PEER_HANDLE_BYTES]);
+int smb_peer_open(const unsigned char handle[SMB_PEER_HANDLE_BYTES], void** ptr);
+int smb_peer_close(void* ptr);
+int smb_peer_free(void* ptr);
+
+/* Unfused path: an all-gather of the [M, N/g] slabs (NCCL concatenates them rank-major as
+ * [g, M, N/g]) followed by this copy into row-major [M, g * n_local] (pitch ldd elements).
+ * n_local % 8 == 0, both buffers 16-byte aligned, ldd % 8 == 0.  Stream-ordered. */
+int smb_unshard_columns_device(const void* gathered, void* d, int g, int M, int n_local, int64_t ldd,
+                               void* stream);
+
 #define SMB_FLAG_NONE 0u
 #define SMB_FLAG_FORCE_PLAIN_STORE 1u /* use the non-TMA epilogue even when D is aligned */
 #define SMB_FLAG_TILE_N_128 2u        /* force 256 x 128 tiles */

@@ -75,7 +75,18 @@ DECLARED = [
     ("smb_dense_gemm_nvfp4_host", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     ("smb_dense_gemm_nvfp4_decode_noalloc", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     ("smb_decode_noalloc_scratch_limit", C.c_size_t, []),
+    ("smb_bf16_plan_set_peer_copies", _i, [_vp, _i, C.POINTER(_vp), _i64]),
+    ("smb_fp4_plan_set_peer_copies", _i, [_vp, _i, C.POINTER(_vp), _i64]),
+    ("smb_peer_alloc", _i, [C.POINTER(_vp), C.c_size_t]),
+    ("smb_peer_export", _i, [_vp, C.c_char_p]),
+    ("smb_peer_open", _i, [C.c_char_p, C.POINTER(_vp)]),
+    ("smb_peer_close", _i, [_vp]),
+    ("smb_peer_free", _i, [_vp]),
+    ("smb_unshard_columns_device", _i, [_vp, _vp, _i, _i, _i, _i64, _vp]),
 ]
+
+PEER_HANDLE_BYTES = 64
+MAX_PEER_COPIES = 7
 
 
 class SmbError(RuntimeError):

@@ -77,6 +77,7 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
   L.prof = nullptr;
   L.dynamic = (flags & SMB_FLAG_DYNAMIC_TILES) != 0;
   L.operands_static = (flags & SMB_FLAG_OPERANDS_STATIC) != 0;
+  L.peers.count = 0;
   L.d = d;
   L.ldd = static_cast<int>(ldd);
   L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
@@ -126,6 +127,12 @@ extern "C" int smb_bf16_plan_tune(smb_bf16_plan* plan, int group_m, int max_clus
   plan->launch.group_m = group_m;
   plan->launch.max_clusters = max_clusters;
   return SMB_OK;
+}
+
+extern "C" int smb_bf16_plan_set_peer_copies(smb_bf16_plan* plan, int count, void* const* dst,
+                                             int64_t ld) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "plan: null handle");
+  return set_peer_copies(&plan->launch.peers, plan->launch.tma_store, count, dst, ld, plan->launch.N);
 }
 
 extern "C" int smb_bf16_plan_set_profile(smb_bf16_plan* plan, long long* counters) {

@@ -55,6 +55,7 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
   L.prefetch = 0;
   L.dynamic = (flags & SMB_FLAG_DYNAMIC_TILES) != 0;
   L.operands_static = (flags & SMB_FLAG_OPERANDS_STATIC) != 0;
+  L.peers.count = 0;
   L.d = d;
   L.ldd = static_cast<int>(ldd);
   L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
@@ -149,6 +150,14 @@ extern "C" int smb_fp4_plan_tune(smb_fp4_plan* plan, int group_m, int max_cluste
   plan->dlaunch.max_stages = group_m;
   plan->dlaunch.max_ctas = max_clusters;
   return SMB_OK;
+}
+
+extern "C" int smb_fp4_plan_set_peer_copies(smb_fp4_plan* plan, int count, void* const* dst,
+                                            int64_t ld) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
+  if (plan->decode && count != 0)
+    return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: the decode kernel (M <= 128) has no peer copies");
+  return set_peer_copies(&plan->launch.peers, plan->launch.tma_store, count, dst, ld, plan->launch.N);
 }
 
 extern "C" int smb_fp4_plan_set_profile(smb_fp4_plan* plan, long long* counters) {

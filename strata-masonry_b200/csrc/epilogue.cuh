@@ -4,6 +4,7 @@
 // the per-warp store chains of nvfp4/dense_gemm_nvfp4.cu:1343-1424), without CTA-wide barriers.
 #pragma once
 
+#include "gemm_common.cuh"
 #include "ptx.cuh"
 
 namespace smb {
@@ -11,11 +12,19 @@ namespace smb {
 constexpr int kStoreCols = 64;                        // columns per store box (128 bytes of bf16)
 constexpr int kStoreBufBytes = 32 * kStoreCols * 2;   // one warp's 32 x 64 bf16 staging box
 
+// Extra destinations of every stored box: the same [M, N] block written into other buffers,
+// normally the full D of the other GPUs of the box (the all-gather of a column-sharded GEMM done
+// by the epilogue itself, over peer-mapped memory).  Plain 16-byte stores: peer memory takes
+// ordinary stores, and nothing here waits on another GPU; the data is visible to the peer once
+// this kernel has completed.  No counterpart in the reference (it is single-GPU).
+// (struct PeerCopies: gemm_common.cuh)
+
 struct StoreTarget {
   const CUtensorMap* tmap_d;   // D as [M, N] bf16, box 32 x 64, 128-byte swizzle (TMA path)
   uint16_t* d_ptr;             // D base and pitch (plain-store path)
   int ldd;
   int M, N;
+  const PeerCopies* peers;     // kernel parameter, TMA path only (N % 8 == 0 there)
 };
 
 // One warp drains kCols fp32 columns of its 32 TMEM lanes starting at `taddr`, then writes them
@@ -64,6 +73,25 @@ __device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, c
       if (lane == 0) {
         if (row0 < out.M && gcol0 < out.N) tma_store_2d(out.tmap_d, sbuf, gcol0, row0);
         bulk_commit_group();
+      }
+      const int n_peers = out.peers->count;
+      if (n_peers > 0) {
+        // Lane l copies 16-byte chunk (l % 8) of rows (l / 8) + 4 i: a warp instruction covers
+        // four whole 128-byte row segments, read back from the swizzled staging box.
+        const int chunk = lane & 7;
+        const int gcol = gcol0 + chunk * 8;
+#pragma unroll 1
+        for (int i = 0; i < 8; ++i) {
+          const int r = i * 4 + (lane >> 3);
+          uint32_t x0, x1, x2, x3;
+          ld_shared_v4(sbuf + r * 128 + ((chunk ^ (r & 7)) << 4), x0, x1, x2, x3);
+          const int grow = row0 + r;
+          if (grow < out.M && gcol < out.N) {
+            const long long off = static_cast<long long>(grow) * out.peers->ld + gcol;
+#pragma unroll 1
+            for (int q = 0; q < n_peers; ++q) st_global_v4(out.peers->base[q] + off, x0, x1, x2, x3);
+          }
+        }
       }
     } else {
       // Read the staged box back so that consecutive lanes write consecutive columns of a row.

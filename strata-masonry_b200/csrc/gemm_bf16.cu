@@ -71,6 +71,7 @@ struct Params {
   int* status;
   long long* prof;    // optional: 8 cycle counters per CTA (see kProf* below), or null
   int dynamic;        // 1: tiles come from the hardware work queue (one cluster launched per tile)
+  PeerCopies peers;     // extra destinations of every stored box (count 0: none)
   int operands_static;  // 1: A and BT are not written by the previous kernel on the stream
 };
 
@@ -82,7 +83,7 @@ template <int TN, int NB, bool kTmaStore>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_d, const Params p) {
+                 const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ Params p) {
   using C = Cfg<TN, NB>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -294,6 +295,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       out.ldd = p.ldd;
       out.M = p.M;
       out.N = p.N;
+      out.peers = &p.peers;
       int local = 0;
       bool ok = true;
       if (p.operands_static) griddep_wait();
@@ -398,6 +400,7 @@ int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
   p.status = L.status;
   p.prof = L.prof;
   p.operands_static = L.operands_static ? 1 : 0;
+  p.peers = L.peers;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (L.max_clusters > 0 && clusters > L.max_clusters) clusters = L.max_clusters;

@@ -42,6 +42,17 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype
                    uint64_t rows, uint64_t cols, uint64_t ld_bytes, uint32_t box_rows,
                    uint32_t box_cols, bool swizzle128);
 
+// Extra destinations of every stored box of D (see epilogue.cuh): the all-gather of a
+// column-sharded GEMM fused into the epilogue.
+constexpr int kMaxPeerCopies = 7;
+struct PeerCopies {
+  int count;                        // 0: none
+  long long ld;                     // elements between rows in every destination
+  uint16_t* base[kMaxPeerCopies];   // element (0, 0) of this kernel's D inside destination i
+};
+// Validates and fills `out`; `tma_store` is the plan's store path (peer copies need it).
+int set_peer_copies(PeerCopies* out, bool tma_store, int count, void* const* dst, long long ld, int N);
+
 // --------------------------------------------------------------------------- bf16 launch
 struct Bf16Launch {
   CUtensorMap tmap_a, tmap_b, tmap_d;
@@ -57,6 +68,7 @@ struct Bf16Launch {
   long long* prof;   // device buffer of 8 counters per CTA (role timers), or null
   bool dynamic;      // tiles from the hardware work queue (cluster launch control) instead of a static walk
   bool operands_static;  // loads need not wait for the previous kernel on the stream
+  PeerCopies peers;
 };
 void bf16_pick_tile(int M, int N, int K, int clusters, int* tile_n, int* sub_blocks);
 // Number of 2-CTA clusters that can run at once on the current device (SM count / 2), 0 if unknown.
@@ -78,6 +90,7 @@ struct Fp4Launch {
   int prefetch;      // L2 prefetch distance in K blocks (0 = off)
   bool dynamic;      // tiles from the hardware work queue instead of a static walk
   bool operands_static;  // loads need not wait for the previous kernel on the stream
+  PeerCopies peers;
 };
 void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1);
 int fp4_launch(const Fp4Launch& L, cudaStream_t stream);

@@ -86,6 +86,7 @@ struct Params {
   long long* prof;
   int prefetch;   // L2 prefetch distance in K blocks (0 = off)
   int dynamic;    // 1: tiles come from the hardware work queue (one cluster launched per tile)
+  PeerCopies peers;     // extra destinations of every stored box (count 0: none)
   int operands_static;  // 1: operands and scales are not written by the previous kernel on the stream
 };
 
@@ -99,7 +100,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b1,
                   const __grid_constant__ CUtensorMap tmap_sfa,
                   const __grid_constant__ CUtensorMap tmap_sfb,
-                  const __grid_constant__ CUtensorMap tmap_d, const Params p) {
+                  const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ Params p) {
   using C = Cfg<W0, W1>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -401,6 +402,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     out.ldd = p.ldd;
     out.M = p.M;
     out.N = p.N;
+    out.peers = &p.peers;
     int local = 0;
     bool ok = true;
     if (p.operands_static) griddep_wait();
@@ -496,6 +498,7 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   p.status = L.status;
   p.prof = L.prof;
   p.operands_static = L.operands_static ? 1 : 0;
+  p.peers = L.peers;
   p.prefetch = L.prefetch;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);

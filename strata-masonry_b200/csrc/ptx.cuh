@@ -444,6 +444,21 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
                : "memory");
 }
 
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c,
+                                             uint32_t& d) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+               : "r"(addr)
+               : "memory");
+}
+
+// 16-byte store to (possibly another GPU's) global memory; `ptr` must be 16-byte aligned.
+__device__ __forceinline__ void st_global_v4(void* ptr, uint32_t a, uint32_t b, uint32_t c,
+                                             uint32_t d) {
+  asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
 // Programmatic dependent launch: let the next grid on the stream start early / wait for the
 // previous grid to finish and its writes to become visible.
 __device__ __forceinline__ void griddep_launch_dependents() {

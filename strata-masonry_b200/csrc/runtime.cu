@@ -37,6 +37,31 @@ int device_cluster_slots() {
   return sms / 2;
 }
 
+int set_peer_copies(PeerCopies* out, bool tma_store, int count, void* const* dst, long long ld, int N) {
+  if (count < 0 || count > kMaxPeerCopies)
+    return set_error(SMB_ERR_INVALID, "peer copies: count %d outside 0..%d", count, kMaxPeerCopies);
+  if (count == 0) {
+    out->count = 0;
+    return SMB_OK;
+  }
+  if (dst == nullptr) return set_error(SMB_ERR_INVALID, "peer copies: null destination list");
+  if (!tma_store)
+    return set_error(SMB_ERR_UNSUPPORTED,
+                     "peer copies need the 16-byte-aligned store path (D 16-byte aligned, ldd %% 8 == 0)");
+  if (N % 8 != 0) return set_error(SMB_ERR_UNSUPPORTED, "peer copies: N=%d must be a multiple of 8", N);
+  if (ld < N || ld % 8 != 0)
+    return set_error(SMB_ERR_INVALID, "peer copies: row pitch %lld must be >= N and a multiple of 8", ld);
+  for (int i = 0; i < count; ++i) {
+    if (dst[i] == nullptr || reinterpret_cast<uintptr_t>(dst[i]) % 16 != 0)
+      return set_error(SMB_ERR_INVALID, "peer copies: destination %d (%p) is null or not 16-byte aligned", i,
+                       dst[i]);
+  }
+  out->count = count;
+  out->ld = ld;
+  for (int i = 0; i < count; ++i) out->base[i] = static_cast<uint16_t*>(dst[i]);
+  return SMB_OK;
+}
+
 namespace {
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,

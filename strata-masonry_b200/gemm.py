@@ -48,6 +48,14 @@ def dense_gemm_bf16_host(a_bits: np.ndarray, bt_bits: np.ndarray) -> np.ndarray:
     return d
 
 
+
+def _peer_array(dst):
+    """List of destination addresses (ints, tensors, arrays) -> (count, ctypes array)."""
+    addrs = [_ptr(x) if not isinstance(x, int) else x for x in dst]
+    arr = (C.c_void_p * max(1, len(addrs)))(*addrs)
+    return len(addrs), arr
+
+
 class Bf16Plan:
     """Tensor maps + tile choice for one (A, BT, D) device buffer set."""
 
@@ -66,6 +74,12 @@ class Bf16Plan:
 
     def set_profile(self, counters) -> None:
         capi.check(self._lib.smb_bf16_plan_set_profile(self._h, _ptr(counters)))
+
+    def set_peer_copies(self, dst, ld: int) -> None:
+        """Every stored box of D also goes to dst[i] + row * ld (elements): the fused all-gather."""
+        count, arr = _peer_array(dst)
+        self._peer_keep = dst
+        capi.check(self._lib.smb_bf16_plan_set_peer_copies(self._h, count, arr, ld))
 
     def run(self, stream=None) -> None:
         capi.check(self._lib.smb_bf16_plan_run(self._h, _stream_ptr(stream)))
@@ -211,6 +225,11 @@ class Fp4Plan:
     def set_profile(self, counters) -> None:
         capi.check(self._lib.smb_fp4_plan_set_profile(self._h, _ptr(counters)))
 
+    def set_peer_copies(self, dst, ld: int) -> None:
+        count, arr = _peer_array(dst)
+        self._peer_keep = dst
+        capi.check(self._lib.smb_fp4_plan_set_peer_copies(self._h, count, arr, ld))
+
     def run(self, stream=None) -> None:
         capi.check(self._lib.smb_fp4_plan_run(self._h, _stream_ptr(stream)))
 
@@ -227,6 +246,13 @@ class Fp4Plan:
             self.close()
         except Exception:
             pass
+
+
+def unshard_columns_device(gathered, d, g: int, m: int, n_local: int, ldd: int | None = None,
+                           stream=None) -> None:
+    """[g, M, N/g] (all-gathered slabs) -> row-major [M, N] on the device."""
+    capi.check(capi.lib().smb_unshard_columns_device(
+        _ptr(gathered), _ptr(d), g, m, n_local, g * n_local if ldd is None else ldd, _stream_ptr(stream)))
 
 
 def fill_fp4_device(data, sf_packed, sf_rowmajor, rows: int, k: int, fill: int, which: int,

@@ -44,3 +44,109 @@ def gathered_to_row_major(gathered: np.ndarray) -> np.ndarray:
 def allgather_bytes_received(m: int, n_total: int, world: int, elem_bytes: int = 2) -> int:
     """Bytes every GPU receives in the all-gather of D."""
     return (world - 1) * m * (n_total // world) * elem_bytes
+
+
+# ------------------------------------------------------------------ fused all-gather plumbing
+def peer_copy_order(rank: int, world: int) -> list[int]:
+    """Other ranks in the order a rank writes to them: r+1, r+2, ... (mod g), so that at any
+    moment the g ranks target g different GPUs."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world of {world}")
+    return [(rank + i) % world for i in range(1, world)]
+
+
+def peer_copy_targets(bases: list[int], shard: ColumnShard, elem_bytes: int = 2) -> list[int]:
+    """Address of element (0, n0) of this rank's slab inside the full row-major D of every other
+    rank (`bases[r]` = address of rank r's D as mapped into this process)."""
+    if len(bases) != shard.world:
+        raise ValueError("one base address per rank")
+    return [bases[r] + shard.n0 * elem_bytes for r in peer_copy_order(shard.rank, shard.world)]
+
+
+class _CudaPeerMemory:
+    """Exportable device memory through the library's C entry points."""
+
+    def __init__(self):
+        import ctypes as C
+
+        from . import capi
+        self._C, self._capi, self._lib = C, capi, capi.lib()
+
+    def alloc(self, nbytes: int) -> int:
+        p = self._C.c_void_p()
+        self._capi.check(self._lib.smb_peer_alloc(self._C.byref(p), nbytes))
+        return int(p.value)
+
+    def export(self, ptr: int) -> bytes:
+        buf = self._C.create_string_buffer(self._capi.PEER_HANDLE_BYTES)
+        self._capi.check(self._lib.smb_peer_export(ptr, buf))
+        return buf.raw
+
+    def open(self, handle: bytes) -> int:
+        p = self._C.c_void_p()
+        self._capi.check(self._lib.smb_peer_open(handle, self._C.byref(p)))
+        return int(p.value)
+
+    def close(self, ptr: int) -> None:
+        self._capi.check(self._lib.smb_peer_close(ptr))
+
+    def free(self, ptr: int) -> None:
+        self._capi.check(self._lib.smb_peer_free(ptr))
+
+
+class SharedOutput:
+    """A full row-major D [M, N] on every GPU of the box, each one mapped into every process, so
+    that the GEMM epilogue of rank r can write its column slab into all g copies.
+
+    `dist` is `torch.distributed` (initialised; any backend: only objects are exchanged here).
+    `memory` is an object with alloc/export/open/close/free (default: CUDA IPC through the
+    library); tests on CPU pass a fake."""
+
+    def __init__(self, m: int, n_total: int, dist, memory=None, elem_bytes: int = 2):
+        self.m, self.n_total, self.elem_bytes = m, n_total, elem_bytes
+        self._dist = dist
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        if self.world - 1 > 7:
+            raise ValueError("at most 8 ranks (7 peer copies per stored box)")
+        self._mem = memory if memory is not None else _CudaPeerMemory()
+        self.nbytes = m * n_total * elem_bytes
+        self.local = self._mem.alloc(self.nbytes)
+        handles: list = [None] * self.world
+        dist.all_gather_object(handles, self._mem.export(self.local))
+        self.bases = [self.local if r == self.rank else self._mem.open(handles[r])
+                      for r in range(self.world)]
+        self._open = True
+
+    def shard(self) -> ColumnShard:
+        return column_shard(self.n_total, self.world, self.rank)
+
+    def slab_address(self) -> int:
+        """Where this rank's GEMM writes its own slab: element (0, n0) of the local D."""
+        return self.local + self.shard().n0 * self.elem_bytes
+
+    def peer_targets(self) -> list[int]:
+        return peer_copy_targets(self.bases, self.shard(), self.elem_bytes)
+
+    def local_tensor(self):
+        """The local D as a torch uint16-sized view ([M, N] of bfloat16)."""
+        import torch
+
+        class _Raw:
+            pass
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (self.nbytes,), "typestr": "|u1",
+                                        "data": (self.local, False), "version": 2}
+        flat = torch.as_tensor(raw, device=torch.device("cuda", torch.cuda.current_device()))
+        return flat.view(torch.bfloat16).view(self.m, self.n_total)
+
+    def close(self) -> None:
+        """Collective: nobody may still be writing into a buffer that is about to be freed."""
+        if not self._open:
+            return
+        self._open = False
+        self._dist.barrier()
+        for r, base in enumerate(self.bases):
+            if r != self.rank:
+                self._mem.close(base)
+        self._dist.barrier()
+        self._mem.free(self.local)

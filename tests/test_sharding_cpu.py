@@ -86,3 +86,109 @@ def test_column_shard_rules(smb):
     g = np.arange(2 * 3 * 4).reshape(2, 3, 4)
     rm = smb.sharding.gathered_to_row_major(g)
     assert rm.shape == (3, 8) and list(rm[1]) == [4, 5, 6, 7, 16, 17, 18, 19]
+
+
+# ------------------------------------------------------------------ fused all-gather plumbing
+class _FileBackedMemory:
+    """Stand-in for peer-mappable device memory: every rank's "allocation" is a region of one
+    shared file, an address is an offset into it (plus a base, so that 0 is never valid)."""
+    BASE = 1 << 20
+
+    def __init__(self, path, rank, region_bytes):
+        self.path, self.rank, self.region = path, rank, region_bytes
+        self.opened, self.closed, self.freed = [], [], []
+
+    def alloc(self, nbytes):
+        assert nbytes <= self.region
+        return self.BASE + self.rank * self.region
+
+    def export(self, ptr):
+        return int(ptr).to_bytes(8, "little") + bytes(56)
+
+    def open(self, handle):
+        assert len(handle) == 64
+        addr = int.from_bytes(handle[:8], "little")
+        self.opened.append(addr)
+        return addr
+
+    def close(self, ptr):
+        self.closed.append(ptr)
+
+    def free(self, ptr):
+        self.freed.append(ptr)
+
+
+def _fused_worker(rank, world, port, path, out):
+    import torch.distributed as dist
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__ as entry
+    smb = entry.load_package()
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        m, n = 12, 8 * world * 3
+        region = m * n * 2
+        mem = _FileBackedMemory(path, rank, region)
+        shared = smb.sharding.SharedOutput(m, n, dist, memory=mem)
+        sh = shared.shard()
+        backing = np.memmap(path, dtype=np.uint8, mode="r+", shape=(world * region,))
+        # What the epilogue does: the slab goes to the local D and, with the same row pitch, to
+        # every peer target.
+        slab = (np.arange(m)[:, None] * 1000 + sh.n0 + np.arange(sh.n_local)[None, :]).astype(np.uint16)
+        targets = [shared.slab_address()] + shared.peer_targets()
+        assert len(targets) == world and len(set(targets)) == world
+        for addr in targets:
+            off = addr - mem.BASE
+            for row in range(m):
+                start = off + row * n * 2
+                backing[start:start + sh.n_local * 2] = slab[row].view(np.uint8)
+        backing.flush()
+        dist.barrier()
+        mine = np.memmap(path, dtype=np.uint16, mode="r", offset=rank * region, shape=(m, n))
+        want = (np.arange(m)[:, None] * 1000 + np.arange(n)[None, :]).astype(np.uint16)
+        ok = np.array_equal(np.asarray(mine), want)
+        order = smb.sharding.peer_copy_order(rank, world)
+        ok &= order == [(rank + i) % world for i in range(1, world)]
+        ok &= sorted(mem.opened) == sorted(mem.BASE + r * region for r in range(world) if r != rank)
+        shared.close()
+        ok &= sorted(mem.closed) == sorted(mem.opened) and mem.freed == [shared.local]
+        out.put(bool(ok))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_shared_output_addresses_on_gloo(smb, tmp_path, world):
+    """Every rank writes its column slab into every rank's full D through the addresses that
+    SharedOutput hands to the plans; each full D must come out complete and row-major."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    path = str(tmp_path / "peers.bin")
+    m, n = 12, 8 * world * 3
+    with open(path, "wb") as f:
+        f.write(bytes(world * m * n * 2))
+    procs = [ctx.Process(target=_fused_worker, args=(r, world, port, path, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert all(out.get(timeout=5) is True for _ in range(world))
+
+
+def test_peer_copy_rules(smb):
+    sh = smb.sharding.column_shard(64, 4, 1)
+    bases = [0x1000, 0x2000, 0x3000, 0x4000]
+    assert smb.sharding.peer_copy_targets(bases, sh) == [0x3000 + 32, 0x4000 + 32, 0x1000 + 32]
+    with pytest.raises(ValueError):
+        smb.sharding.peer_copy_targets(bases[:3], sh)
+    lib = smb.capi.lib()
+    # No plan: the setters validate the handle before anything else.
+    assert lib.smb_bf16_plan_set_peer_copies(None, 0, None, 0) == smb.capi.SMB_ERR_INVALID
+    assert lib.smb_fp4_plan_set_peer_copies(None, 0, None, 0) == smb.capi.SMB_ERR_INVALID
+    assert lib.smb_unshard_columns_device(None, None, 2, 4, 8, 16, None) == smb.capi.SMB_ERR_INVALID
+    assert lib.smb_peer_export(None, None) == smb.capi.SMB_ERR_INVALID
