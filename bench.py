@@ -7,7 +7,9 @@ One "step" is one pass of the hot path over one batch of synthetic input: one GE
 named workload (default: BF16 8192^3, operands N(0,1)*0.1 stand-in, FP32 accumulate, BF16 out).
 With N > 1 (launched under torch.distributed.run, one rank per GPU) the N dimension is sharded
 column-parallel: rank r computes D[:, r*N/g : (r+1)*N/g] with no communication in the kernel;
-the optional all-gather of D is timed separately and reported under "allgather".
+the optional all-gather of D is timed separately and reported under "allgather" (--allgather: NCCL
+all-gather + the library's unshard copy; --fused-allgather: the GEMM whose epilogue writes its
+slab into the full D of every GPU over peer-mapped memory).
 
 Rank 0 prints ONE JSON line.  `value` is whole-job TFLOP/s with operands resident in HBM
 (device-timed, max over ranks); `e2e` is the same metric through the host-buffer entry point of
@@ -230,6 +232,8 @@ def main():
     ap.add_argument("--workload", default="bf16_8192", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--allgather", action="store_true", help="also time the all-gather of D (N > 1)")
+    ap.add_argument("--fused-allgather", action="store_true",
+                    help="also time the GEMM whose epilogue writes D into every GPU's full D (N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=8)
     args = ap.parse_args()
@@ -395,10 +399,73 @@ def main():
         g1.record()
         barrier()
         ag_ms = max_over_ranks(g0.elapsed_time(g1)) / reps
+        # Rank-major [g, M, N/g] -> row-major [M, N] (the library's copy kernel).
+        full = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        smb.gemm.unshard_columns_device(gathered, full, g, m, n_local, stream=torch.cuda.current_stream())
+        barrier()
+        u0 = torch.cuda.Event(enable_timing=True)
+        u1 = torch.cuda.Event(enable_timing=True)
+        u0.record()
+        for _ in range(reps):
+            smb.gemm.unshard_columns_device(gathered, full, g, m, n_local, stream=torch.cuda.current_stream())
+        u1.record()
+        barrier()
+        un_ms = max_over_ranks(u0.elapsed_time(u1)) / reps
         recv = (g - 1) * m * n_local * 2
         allgather = {"ms": ag_ms, "recv_gb_per_s_per_gpu": recv / (ag_ms * 1e-3) / 1e9,
-                     "layout": "rank-major [g, M, N/g]"}
-        del gathered
+                     "layout": "rank-major [g, M, N/g]", "unshard_ms": un_ms,
+                     "unshard_gb_per_s": 2.0 * m * n * 2 / (un_ms * 1e-3) / 1e9,
+                     "unfused_total_ms": ms_step + ag_ms + un_ms}
+        del gathered, full
+
+    # ---------------------------------------------------------------- GEMM + all-gather in one kernel
+    # Every rank holds a full row-major D [M, N] that all processes map; the epilogue of rank r
+    # stores its column slab into all g of them (plain stores over NVLink for the g - 1 remote
+    # ones).  Timed like the main region: barrier + synchronize on both sides, max over ranks.
+    if dist is not None and args.fused_allgather and kind != "decode":
+        shared = smb.sharding.SharedOutput(m, n, dist)
+        d_full = shared.local_tensor()
+        if kind == "bf16":
+            fplan = smb.gemm.Bf16Plan(a, bt, shared.slab_address(), m, n_local, k, ldd=n,
+                                      flags=smb.capi.FLAG_OPERANDS_STATIC)
+        else:
+            fplan = smb.gemm.Fp4Plan(a, sfa, bt, sfb, shared.slab_address(), m, n_local, k, ldd=n,
+                                     flags=smb.capi.FLAG_OPERANDS_STATIC)
+        fplan.set_peer_copies(shared.peer_targets(), n)
+        for _ in range(3):
+            fplan.run(stream)
+        fplan.check(stream)
+        barrier()
+        f0 = torch.cuda.Event(enable_timing=True)
+        f1 = torch.cuda.Event(enable_timing=True)
+        reps = max(5, min(args.steps, 50))
+        f0.record(stream)
+        for _ in range(reps):
+            fplan.run(stream)
+        f1.record(stream)
+        barrier()
+        fplan.check(stream)
+        fused_ms = max_over_ranks(f0.elapsed_time(f1)) / reps
+        # Every rank's full D must hold every rank's slab: own slab equals the unfused result, and
+        # a checksum over the whole matrix is the same on all ranks.
+        own_ok = bool(torch.equal(d_full[:, n0:n0 + n_local].view(torch.int16), d.view(torch.int16)))
+        checksum = d_full.view(torch.int16).to(torch.int64).sum().reshape(1)
+        lo, hi = checksum.clone(), checksum.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        ok_t = torch.tensor([1 if own_ok else 0], device=dev)
+        dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
+        sent = (g - 1) * m * n_local * 2
+        allgather = dict(allgather or {})
+        allgather.update({
+            "fused_ms": fused_ms, "gemm_only_ms": ms_step,
+            "fused_sent_gb_per_s_per_gpu": sent / (fused_ms * 1e-3) / 1e9,
+            "fused_matches_unfused": bool(ok_t.item() == 1 and lo.item() == hi.item()),
+            "fused_bound_ms": {"nvlink_at_770_gb_s": sent / 770e9 * 1e3, "gemm": ms_step},
+            "fused_layout": "row-major [M, N] on every GPU"})
+        fplan.close()
+        del d_full
+        shared.close()
 
     # ---------------------------------------------------------------- end to end, host buffers
     e2e = None
