@@ -85,6 +85,10 @@ int smb_quantize_mx_device(const float* src, int64_t ld_src, uint8_t* data, int6
                            void* stream);
 int smb_quantize_mx_host(const float* src, int64_t ld_src, uint8_t* data, int64_t ld_bytes,
                          uint8_t* sf_packed, uint8_t* sf_rowmajor, int64_t rows, int64_t K);
+/* The same quantiser on BF16 bit patterns (every bf16 is an fp32: same rule, same result). */
+int smb_quantize_mx_bf16_device(const uint16_t* src, int64_t ld_src, uint8_t* data, int64_t ld_bytes,
+                                uint8_t* sf_packed, uint8_t* sf_rowmajor, int64_t rows, int64_t K,
+                                void* stream);
 
 /* Packed scale layout (sf_pack, nvfp4/dense_gemm_nvfp4.cu:2418-2435): bands of 128 rows, each
  * band (K/32 + 3) / 4 chunks of 512 bytes, byte (r, j) of a band at
@@ -165,6 +169,16 @@ typedef struct smb_fp4_plan smb_fp4_plan;
 int smb_fp4_plan_create(smb_fp4_plan** plan, const void* a, const void* sfa, const void* b,
                         const void* sfb, void* d, int M, int N, int K, int64_t lda_bytes,
                         int64_t ldb_bytes, int64_t ldd, unsigned flags);
+/* The same GEMM fed with BF16 activations [M, K] (row pitch ldx elements), as a model hands them
+ * to a decode step: the plan owns the E2M1 codes and packed scales of A, and every
+ * smb_fp4_plan_run first quantises `x_bf16` into them (the rule of smb_quantize_mx_*) and then
+ * multiplies, as two kernels chained on the stream.  For M <= 128 the GEMM starts streaming its
+ * weights while the quantiser (and the tail of the previous kernel) still runs and waits only
+ * before it loads activations.  The reference has no quantiser; its drivers generate codes and
+ * scales directly (nvfp4/dense_gemm_nvfp4.cu:2279-2290). */
+int smb_fp4_plan_create_bf16_activations(smb_fp4_plan** plan, const void* x_bf16, int64_t ldx,
+                                         const void* b, const void* sfb, void* d, int M, int N, int K,
+                                         int64_t ldb_bytes, int64_t ldd, unsigned flags);
 int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_destroy(smb_fp4_plan* plan);

@@ -47,6 +47,7 @@ DECLARED = [
     ("smb_fill_fp4_host", _i, [_vp, _i64, _vp, _vp, _i64, _i64, _u64, _i, _i]),
     ("smb_quantize_mx_device", _i, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _vp]),
     ("smb_quantize_mx_host", _i, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64]),
+    ("smb_quantize_mx_bf16_device", _i, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _vp]),
     ("smb_sf_packed_bytes", C.c_size_t, [_i64, _i64]),
     ("smb_sf_pack_host", _i, [_vp, _i64, _i64, _vp]),
     ("smb_debug_smem_desc", _u64, [_u32, _u32, _u32, _u32]),
@@ -66,6 +67,8 @@ DECLARED = [
     ("smb_bf16_host_ctx_run", _i, [_vp, _vp, _vp, _vp]),
     ("smb_bf16_host_ctx_destroy", _i, [_vp]),
     ("smb_fp4_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, C.c_uint]),
+    ("smb_fp4_plan_create_bf16_activations", _i,
+     [C.POINTER(_vp), _vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, C.c_uint]),
     ("smb_fp4_plan_run", _i, [_vp, _vp]),
     ("smb_fp4_plan_check", _i, [_vp, _vp]),
     ("smb_fp4_plan_destroy", _i, [_vp]),

@@ -21,6 +21,11 @@ struct smb_fp4_plan {
   Fp4DecodeLaunch dlaunch;
   void* scratch_dev;      // fp32 slabs followed by the per-tile counters
   size_t scratch_bytes;
+  // Plans created from BF16 activations quantise them into plan-owned buffers before every run.
+  const void* act_src;
+  int64_t act_ld;
+  void* act_codes;
+  void* act_sf;
 };
 
 extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void* sfa, const void* b,
@@ -64,6 +69,9 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
   p->decode = (M <= 128) && !(flags & SMB_FLAG_NO_DECODE);
   p->scratch_dev = nullptr;
   p->scratch_bytes = 0;
+  p->act_src = nullptr;
+  p->act_ld = 0;
+  p->act_codes = p->act_sf = nullptr;
 
   const uint64_t kchunks = (static_cast<uint64_t>(K) / 32 + 3) / 4;
   const uint64_t bands_a = (static_cast<uint64_t>(M) + 127) / 128;
@@ -107,6 +115,7 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
     D.max_ctas = 0;
     D.max_stages = 0;
     D.no_overlap = (flags & SMB_FLAG_NO_LAUNCH_OVERLAP) != 0;
+    D.activations_dynamic = false;
     const int m_pad = (M + 15) / 16 * 16;
     rc = encode_tmap_2d(&D.tmap_w, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, ldb_bytes, 128, 128, true);
     if (rc == SMB_OK)
@@ -166,8 +175,51 @@ extern "C" int smb_fp4_plan_set_profile(smb_fp4_plan* plan, long long* counters)
   return SMB_OK;
 }
 
+extern "C" int smb_fp4_plan_create_bf16_activations(smb_fp4_plan** out, const void* x_bf16, int64_t ldx,
+                                                    const void* b, const void* sfb, void* d, int M, int N,
+                                                    int K, int64_t ldb_bytes, int64_t ldd, unsigned flags) {
+  if (out == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null output handle");
+  *out = nullptr;
+  if (x_bf16 == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null activation pointer");
+  if (M <= 0 || K <= 0 || K % 32 != 0)
+    return set_error(SMB_ERR_INVALID, "fp4 plan: bad activation shape (K must be a multiple of 32)");
+  if (ldx < K || ldx % 8 != 0 || reinterpret_cast<uintptr_t>(x_bf16) % 16 != 0)
+    return set_error(SMB_ERR_INVALID, "fp4 plan: activation rows must be 16-byte aligned, pitch >= K");
+  void *codes = nullptr, *sf = nullptr;
+  const size_t sf_bytes = smb_sf_packed_bytes(M, K / 32);
+  cudaError_t e = cudaMalloc(&codes, static_cast<size_t>(M) * K / 2);
+  if (e == cudaSuccess) e = cudaMalloc(&sf, sf_bytes);
+  // Rows of the last 128-row band that no activation row fills keep the neutral scale byte.
+  if (e == cudaSuccess) e = cudaMemset(sf, 127, sf_bytes);
+  int rc = e == cudaSuccess ? SMB_OK : set_cuda_error(e, "fp4 plan: activation buffers");
+  smb_fp4_plan* p = nullptr;
+  // The quantised activations are written on the stream right before every GEMM: never static.
+  if (rc == SMB_OK)
+    rc = smb_fp4_plan_create(&p, codes, sf, b, sfb, d, M, N, K, K / 2, ldb_bytes, ldd,
+                             flags & ~SMB_FLAG_OPERANDS_STATIC);
+  if (rc != SMB_OK) {
+    if (codes) cudaFree(codes);
+    if (sf) cudaFree(sf);
+    return rc;
+  }
+  p->act_src = x_bf16;
+  p->act_ld = ldx;
+  p->act_codes = codes;
+  p->act_sf = sf;
+  p->dlaunch.activations_dynamic = true;
+  *out = p;
+  return SMB_OK;
+}
+
 extern "C" int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream) {
   if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
+  if (plan->act_src != nullptr) {
+    const bool chained = !(plan->decode && plan->dlaunch.no_overlap);
+    int rc = quantize_bf16_launch(plan->act_src, plan->act_ld, plan->act_codes, plan->launch.K / 2,
+                                  plan->act_sf, nullptr, plan->launch.M, plan->launch.K, chained,
+                                  static_cast<cudaStream_t>(stream));
+    if (rc != SMB_OK) return rc;
+  }
   if (plan->decode) return fp4_decode_launch(plan->dlaunch, static_cast<cudaStream_t>(stream));
   return fp4_launch(plan->launch, static_cast<cudaStream_t>(stream));
 }
@@ -193,6 +245,8 @@ extern "C" int smb_fp4_plan_destroy(smb_fp4_plan* plan) {
   if (plan == nullptr) return SMB_OK;
   if (plan->status_dev) cudaFree(plan->status_dev);
   if (plan->scratch_dev) cudaFree(plan->scratch_dev);
+  if (plan->act_codes) cudaFree(plan->act_codes);
+  if (plan->act_sf) cudaFree(plan->act_sf);
   delete plan;
   return SMB_OK;
 }

@@ -164,6 +164,46 @@ __global__ void quantize_mx_kernel(const float* src, int64_t ld_src, uint8_t* da
   }
 }
 
+// BF16 source (the activations a model hands to the decode GEMM).  `chained`: launched with
+// programmatic stream serialisation in front of a GEMM; lets the GEMM start its weight loads at
+// once and itself waits for the previous kernel on the stream (which may still read the codes
+// and scales this kernel overwrites) before it writes anything.
+__global__ void quantize_mx_bf16_kernel(const uint16_t* src, int64_t ld_src, uint8_t* data,
+                                        int64_t ld_bytes, uint8_t* sf_packed, uint8_t* sf_rowmajor,
+                                        int64_t rows, uint32_t K, int chained) {
+  if (chained) {
+    griddep_launch_dependents();
+    griddep_wait();
+  }
+  const uint32_t kblocks = K / 32u;
+  const int64_t total = rows * kblocks;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t r = i / kblocks;
+    const uint32_t kb = static_cast<uint32_t>(i - r * kblocks);
+    float v[32];
+    const uint4* s4 = reinterpret_cast<const uint4*>(src + r * ld_src + kb * 32);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 q = s4[j];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        v[8 * j + 2 * t] = __uint_as_float(w[t] << 16);
+        v[8 * j + 2 * t + 1] = __uint_as_float(w[t] & 0xFFFF0000u);
+      }
+    }
+    uint8_t codes[16];
+    uint8_t sb;
+    quantize_block(v, codes, &sb);
+    uint4 packed;
+    memcpy(&packed, codes, 16);
+    *reinterpret_cast<uint4*>(data + r * ld_bytes + kb * 16) = packed;
+    if (sf_packed) sf_packed[fmt::sf_packed_offset(static_cast<uint32_t>(r), kb, kblocks)] = sb;
+    if (sf_rowmajor) sf_rowmajor[r * kblocks + kb] = sb;
+  }
+}
+
 int check_fp4_args(const void* data, int64_t rows, int64_t K, int64_t ld_bytes) {
   if (data == nullptr) return set_error(SMB_ERR_INVALID, "fp4: null data pointer");
   if (rows < 0 || K <= 0 || K % 32 != 0)
@@ -180,6 +220,27 @@ int grid_for(int64_t total) {
 }
 
 }  // namespace
+
+int quantize_bf16_launch(const void* src, int64_t ld_src, void* data, int64_t ld_bytes, void* sf_packed,
+                         void* sf_rowmajor, int64_t rows, int64_t K, bool chained, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid_for(rows * (K / 32))), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = st;
+  cudaLaunchAttribute pdl;
+  pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &pdl;
+  cfg.numAttrs = chained ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, quantize_mx_bf16_kernel, static_cast<const uint16_t*>(src), ld_src,
+                                     static_cast<uint8_t*>(data), ld_bytes, static_cast<uint8_t*>(sf_packed),
+                                     static_cast<uint8_t*>(sf_rowmajor), rows, static_cast<uint32_t>(K),
+                                     chained ? 1 : 0);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return set_cuda_error(e, "bf16 quantize launch");
+  return SMB_OK;
+}
+
 }  // namespace smb
 
 extern "C" size_t smb_sf_packed_bytes(int64_t rows, int64_t kblocks) {
@@ -277,6 +338,22 @@ extern "C" int smb_quantize_mx_device(const float* src, int64_t ld_src, uint8_t*
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error(e, "quantize launch");
   return SMB_OK;
+}
+
+extern "C" int smb_quantize_mx_bf16_device(const uint16_t* src, int64_t ld_src, uint8_t* data,
+                                           int64_t ld_bytes, uint8_t* sf_packed, uint8_t* sf_rowmajor,
+                                           int64_t rows, int64_t K, void* stream) {
+  if (src == nullptr) return set_error(SMB_ERR_INVALID, "quantize: null source");
+  if (int rc = check_fp4_args(data, rows, K, ld_bytes)) return rc;
+  if (ld_src < K || ld_src % 8 != 0 || reinterpret_cast<uintptr_t>(src) % 16 != 0)
+    return set_error(SMB_ERR_INVALID, "quantize: source rows must be 16-byte aligned");
+  if (rows == 0) return SMB_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (sf_packed) {
+    cudaError_t e = cudaMemsetAsync(sf_packed, 127, smb_sf_packed_bytes(rows, K / 32), st);
+    if (e != cudaSuccess) return set_cuda_error(e, "quantize: scale buffer memset");
+  }
+  return quantize_bf16_launch(src, ld_src, data, ld_bytes, sf_packed, sf_rowmajor, rows, K, false, st);
 }
 
 // ------------------------------------------------------------------------------------

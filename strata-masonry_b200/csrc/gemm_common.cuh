@@ -107,8 +107,13 @@ struct Fp4DecodeLaunch {
   int max_ctas;      // 0 = one per SM
   int max_stages;    // 0 = as many as fit
   bool no_overlap;   // true: plain stream order, no programmatic dependent launch
+  bool activations_dynamic;  // X and its scales are written by the previous kernel on the stream
 };
 int fp4_decode_stage_bytes(int m_pad);
+// BF16 [rows, K] -> E2M1 codes + UE8M0 scales (packed and/or row-major).  `chained`: launched so
+// that the next kernel on the stream may start early (see fills.cu).
+int quantize_bf16_launch(const void* src, int64_t ld_src, void* data, int64_t ld_bytes, void* sf_packed,
+                         void* sf_rowmajor, int64_t rows, int64_t K, bool chained, cudaStream_t st);
 int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream);
 
 }  // namespace smb

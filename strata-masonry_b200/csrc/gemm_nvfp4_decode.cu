@@ -47,6 +47,7 @@ struct Params {
   float* scratch;     // [tiles][m_pad][128] fp32 partial sums (zero between calls)
   int* counters;      // [tiles] K blocks accumulated so far (zero between calls)
   int* status;
+  int activations_dynamic;  // 1: X and SFX are written by the previous kernel on the stream
 };
 
 // Tensor memory read-back of 16 columns.
@@ -134,7 +135,43 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const uint64_t keep = l2_policy_evict_last();           // activations: re-read by every CTA
       int s = 0;
       uint32_t ph = 0;
-      for (long long u = u_begin; u < u_end; ++u) {
+      long long u = u_begin;
+      const uint32_t op_bytes = kWBytes + static_cast<uint32_t>(p.m_pad) * kBlockKBytes;
+      if (p.activations_dynamic) {
+        // The activations (codes and scales) come from the kernel launched just before this one
+        // (the quantiser): fill the whole ring with weights and weight scales first, they do not
+        // depend on it, then wait for that kernel and add the activation boxes to the same
+        // stages.  Each barrier expects the bytes of both parts, so a stage is full only when
+        // both have landed.
+        const int pre = (u_end - u_begin) < stages ? static_cast<int>(u_end - u_begin) : stages;
+        for (int i = 0; i < pre; ++i) {
+          const long long uu = u_begin + i;
+          const int tile = static_cast<int>(uu / num_kb);
+          const int kb = static_cast<int>(uu - static_cast<long long>(tile) * num_kb);
+          const uint32_t dst = ring_base + static_cast<uint32_t>(i * p.stage_bytes);
+          if (elect_one()) {
+            mbar_arrive_expect_tx(sf_full_bar(i), 2 * kSfBytes);
+            tma_load_2d_cta_hint(dst + sfw_off, &tmap_sfw, sf_full_bar(i), kb * 128, tile, stream_once);
+            mbar_arrive_expect_tx(full_bar(i), op_bytes);
+            tma_load_2d_cta_hint(dst, &tmap_w, full_bar(i), kb * kBlockKBytes, tile * 128, stream_once);
+          }
+          __syncwarp();
+        }
+        griddep_wait();
+        for (int i = 0; i < pre; ++i) {
+          const long long uu = u_begin + i;
+          const int kb = static_cast<int>(uu % num_kb);
+          const uint32_t dst = ring_base + static_cast<uint32_t>(i * p.stage_bytes);
+          if (elect_one()) {
+            tma_load_2d_cta_hint(dst + sfx_off, &tmap_sfx, sf_full_bar(i), kb * 128, 0, keep);
+            tma_load_2d_cta_hint(dst + x_off, &tmap_x, full_bar(i), kb * kBlockKBytes, 0, keep);
+          }
+          __syncwarp();
+        }
+        u += pre;
+        if (pre == stages) ph ^= 1u; else s = pre;
+      }
+      for (; u < u_end; ++u) {
         const int tile = static_cast<int>(u / num_kb);
         const int kb = static_cast<int>(u - static_cast<long long>(tile) * num_kb);
         if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
@@ -147,7 +184,7 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
           mbar_arrive_expect_tx(sf_full_bar(s), 2 * kSfBytes);
           tma_load_2d_cta_hint(dst + sfw_off, &tmap_sfw, sf_full_bar(s), kb * 128, tile, stream_once);
           tma_load_2d_cta_hint(dst + sfx_off, &tmap_sfx, sf_full_bar(s), kb * 128, 0, keep);
-          mbar_arrive_expect_tx(full_bar(s), kWBytes + static_cast<uint32_t>(p.m_pad) * kBlockKBytes);
+          mbar_arrive_expect_tx(full_bar(s), op_bytes);
           tma_load_2d_cta_hint(dst, &tmap_w, full_bar(s), kb * kBlockKBytes, tile * 128, stream_once);
           tma_load_2d_cta_hint(dst + x_off, &tmap_x, full_bar(s), kb * kBlockKBytes, 0, keep);
         }
@@ -403,6 +440,7 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   p.scratch = L.scratch;
   p.counters = L.counters;
   p.status = L.status;
+  p.activations_dynamic = L.activations_dynamic ? 1 : 0;
   const int num_kb = (L.K + fp4d::kBlockK - 1) / fp4d::kBlockK;
   const long long units = static_cast<long long>((L.N + 127) / 128) * num_kb;
   int grid = L.max_ctas > 0 ? L.max_ctas : per_sm * sm_count;
@@ -503,6 +541,7 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
   L.ldd = N;
   L.max_ctas = 0;
   L.max_stages = 0;
+  L.activations_dynamic = false;
   L.no_overlap = true;   // the memset below must be ordered before every access of this launch
   L.scratch = static_cast<float*>(base);
   L.counters = reinterpret_cast<int*>(static_cast<char*>(base) + slab_bytes);

@@ -219,6 +219,20 @@ class Fp4Plan:
             k // 2 if lda_bytes is None else lda_bytes, k // 2 if ldb_bytes is None else ldb_bytes,
             n if ldd is None else ldd, flags))
 
+    @classmethod
+    def from_bf16_activations(cls, x, b, sfb, d, m: int, n: int, k: int, ldx: int | None = None,
+                              ldb_bytes: int | None = None, ldd: int | None = None, flags: int = 0):
+        """Plan whose every run first quantises the BF16 activations `x` [M, K] on the device."""
+        self = cls.__new__(cls)
+        self._lib = capi.lib()
+        self._h = C.c_void_p()
+        self.shape = (m, n, k)
+        self._keep = (x, b, sfb, d)
+        capi.check(self._lib.smb_fp4_plan_create_bf16_activations(
+            C.byref(self._h), _ptr(x), k if ldx is None else ldx, _ptr(b), _ptr(sfb), _ptr(d), m, n, k,
+            k // 2 if ldb_bytes is None else ldb_bytes, n if ldd is None else ldd, flags))
+        return self
+
     def tune(self, group_m: int = 0, max_clusters: int = 0, prefetch: int = -1) -> None:
         capi.check(self._lib.smb_fp4_plan_tune(self._h, group_m, max_clusters, prefetch))
 

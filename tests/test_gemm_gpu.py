@@ -489,3 +489,54 @@ def test_back_to_back_launches_with_overlap_flag(smb, oracle, cuda_device):
         assert int(((got.double() - ref).abs() > bound).sum()) == 0
     p1.close()
     p2.close()
+
+
+# ------------------------------------------------------------------------------- BF16 activations
+def test_bf16_quantizer_is_bit_identical_to_oracle(smb, oracle, cuda_device):
+    torch = _torch()
+    g = torch.Generator(device="cpu").manual_seed(5)
+    x = (torch.randn(40, 512, generator=g) * torch.exp2(torch.randint(-6, 6, (40, 1), generator=g).float()))
+    x[0, :32] = 0
+    xb = x.to(torch.bfloat16).to(cuda_device)
+    data = torch.empty(40, 256, device=cuda_device, dtype=torch.uint8)
+    sfp = torch.empty(smb.gemm.sf_packed_bytes(40, 512), device=cuda_device, dtype=torch.uint8)
+    sfr = torch.empty(40, 16, device=cuda_device, dtype=torch.uint8)
+    smb.capi.check(smb.capi.lib().smb_quantize_mx_bf16_device(
+        xb.data_ptr(), 512, data.data_ptr(), 256, sfp.data_ptr(), sfr.data_ptr(), 40, 512, None))
+    torch.cuda.synchronize()
+    codes, sf = oracle.quantize_mx(xb.float().cpu().numpy())
+    np.testing.assert_array_equal(sfr.cpu().numpy(), sf)
+    np.testing.assert_array_equal(data.cpu().numpy(), oracle.pack_codes(codes))
+    np.testing.assert_array_equal(sfp.cpu().numpy(), oracle.sf_pack(sf))
+
+
+@pytest.mark.parametrize("shape", [(16, 1024, 2048), (64, 2560, 1024), (128, 1152, 512), (7, 300, 96),
+                                   (300, 512, 256)])
+def test_fp4_plan_fed_with_bf16_activations(smb, cuda_device, shape):
+    """The plan that quantises BF16 activations before every run (decode kernel for M <= 128, tiled
+    kernel above) equals quantise-then-multiply done as two separate calls, and follows the
+    activations when they change between runs."""
+    torch = _torch()
+    m, n, k = shape
+    g = torch.Generator(device="cpu").manual_seed(m * 7 + n)
+    w, sfw, _ = _fp4_operand(smb, n, k, 5, 1)
+    d = torch.empty(m, n, device=cuda_device, dtype=torch.bfloat16)
+    x = torch.empty(m, k, device=cuda_device, dtype=torch.bfloat16)
+    plan = smb.gemm.Fp4Plan.from_bf16_activations(x, w, sfw, d, m, n, k)
+    codes = torch.empty(m, k // 2, device=cuda_device, dtype=torch.uint8)
+    sfp = torch.empty(smb.gemm.sf_packed_bytes(m, k), device=cuda_device, dtype=torch.uint8)
+    d_ref = torch.empty(m, n, device=cuda_device, dtype=torch.bfloat16)
+    ref_plan = smb.gemm.Fp4Plan(codes, sfp, w, sfw, d_ref, m, n, k)
+    for step in range(3):
+        x.copy_((torch.randn(m, k, generator=g) * (0.5 + step)).to(torch.bfloat16))
+        d.fill_(float("nan"))
+        plan.run()
+        plan.run()     # back to back: the second quantiser must not disturb the first GEMM
+        plan.check()
+        smb.capi.check(smb.capi.lib().smb_quantize_mx_bf16_device(
+            x.data_ptr(), k, codes.data_ptr(), k // 2, sfp.data_ptr(), None, m, k, None))
+        ref_plan.run()
+        ref_plan.check()
+        assert torch.equal(d.view(torch.int16), d_ref.view(torch.int16)), f"step {step}"
+    plan.close()
+    ref_plan.close()
