@@ -200,11 +200,13 @@ int smb_dense_gemm_nvfp4_host(const uint8_t* a, const uint8_t* sfa_rowmajor, con
  * GEMM runs: a server whose start-up pool owns all of HBM, a plugin living inside another
  * framework's allocator, a call made while a stream is being captured.  It has no counterpart
  * in the reference.  Same operands and result as smb_dense_gemm_nvfp4 (packed scales, lda =
- * ldb = K/2 bytes, ldd = N); the partial-sum scratch of the kernel lives in a 16 MiB array
+ * ldb = K/2 bytes, ldd = N); the partial-sum scratch of the kernel lives in a 20 MiB array
  * built into the library, so the call performs no cudaMalloc / cudaFree of any kind.
- *   - Limit: ceil(N/128) * (round_up(M,16) * 512 + 4) bytes must not exceed
- *     smb_decode_noalloc_scratch_limit() (16 MiB - 256); larger shapes return
- *     SMB_ERR_UNSUPPORTED.  All of M in {16, 64, 128} x N = 28672 fit.
+ *   - The array holds two fp32 partial-tile slots per CTA (round_up(M,16) * 512 bytes each) and
+ *     one 4-byte counter per 128 columns of N, within smb_decode_noalloc_scratch_limit() bytes
+ *     (20 MiB - 256).  The call uses as many CTAs as have slots (all 148 SMs of a B200 for every
+ *     M <= 128 and N up to 50 million); a shape whose counters leave room for not even one CTA
+ *     returns SMB_ERR_UNSUPPORTED.
  *   - The first call on a device looks up the array's device address; make that call outside
  *     any stream capture.
  *   - All calls share the one array: it is cleared on `stream` before each launch, and two

@@ -110,8 +110,6 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
     D.M = M;
     D.N = N;
     D.K = K;
-    D.d = d;
-    D.ldd = static_cast<int>(ldd);
     D.max_ctas = 0;
     D.max_stages = 0;
     D.no_overlap = (flags & SMB_FLAG_NO_LAUNCH_OVERLAP) != 0;
@@ -126,15 +124,19 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
     if (rc == SMB_OK)
       rc = encode_tmap_2d(&D.tmap_sfx, sfa, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_a, kchunks * 64,
                           kchunks * 512, 1, 128, false);
+    if (rc == SMB_OK) rc = fp4_decode_bind_output(&D, d, M, N, ldd, !(flags & SMB_FLAG_FORCE_PLAIN_STORE));
     if (rc == SMB_OK) {
-      const size_t tiles = (static_cast<size_t>(N) + 127) / 128;
-      const size_t slab_bytes = tiles * m_pad * 128 * sizeof(float);
-      p->scratch_bytes = slab_bytes + tiles * sizeof(int);
+      // Two partial-sum slots per CTA (one CTA per SM of this device) and one counter per tile.
+      int sms = 2 * device_cluster_slots();
+      if (sms <= 0) sms = 148;
+      const size_t slot_bytes = 2 * static_cast<size_t>(sms) * fp4_decode_slot_bytes(M);
+      p->scratch_bytes = fp4_decode_scratch_bytes(M, N, sms);
       cudaError_t e = cudaMalloc(&p->scratch_dev, p->scratch_bytes);
       if (e == cudaSuccess) e = cudaMemset(p->scratch_dev, 0, p->scratch_bytes);
       if (e != cudaSuccess) rc = set_cuda_error(e, "fp4 plan: decode scratch allocation");
       D.scratch = static_cast<float*>(p->scratch_dev);
-      D.counters = reinterpret_cast<int*>(static_cast<char*>(p->scratch_dev) + slab_bytes);
+      D.scratch_ctas = sms;
+      D.counters = reinterpret_cast<int*>(static_cast<char*>(p->scratch_dev) + slot_bytes);
     }
   }
   if (rc != SMB_OK) {

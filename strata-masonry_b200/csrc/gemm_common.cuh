@@ -98,10 +98,13 @@ int fp4_launch(const Fp4Launch& L, cudaStream_t stream);
 // --------------------------------------------------------------------------- nvfp4 decode launch
 struct Fp4DecodeLaunch {
   CUtensorMap tmap_w, tmap_x, tmap_sfw, tmap_sfx;
+  CUtensorMap tmap_d;   // D as [M, N] bf16, boxes of fp4_decode_box_rows(M) x 128, no swizzle (d_tma only)
   int M, N, K;       // M <= 128 activation rows, N weight rows
   void* d;
   int ldd;
-  float* scratch;    // fp32 [ceil(N/128)][round_up(M,16)][128], zero between calls
+  bool d_tma;        // false: D is not 16-byte aligned, every thread stores its own elements
+  float* scratch;    // 2 * scratch_ctas slots of fp4_decode_slot_bytes(M); need no clearing
+  int scratch_ctas;  // CTAs the scratch has slots for (caps the grid)
   int* counters;     // int  [ceil(N/128)], zero between calls
   int* status;
   int max_ctas;      // 0 = one per SM
@@ -110,6 +113,10 @@ struct Fp4DecodeLaunch {
   bool activations_dynamic;  // X and its scales are written by the previous kernel on the stream
 };
 int fp4_decode_stage_bytes(int m_pad);
+size_t fp4_decode_slot_bytes(int M);                       // one fp32 partial tile
+size_t fp4_decode_scratch_bytes(int M, int N, int ctas);   // slots for `ctas` CTAs + tile counters
+int fp4_decode_box_rows(int M);
+int fp4_decode_bind_output(Fp4DecodeLaunch* L, void* d, int M, int N, long long ldd, bool allow_tma);
 // BF16 [rows, K] -> E2M1 codes + UE8M0 scales (packed and/or row-major).  `chained`: launched so
 // that the next kernel on the stream may start early (see fills.cu).
 int quantize_bf16_launch(const void* src, int64_t ld_src, void* data, int64_t ld_bytes, void* sf_packed,

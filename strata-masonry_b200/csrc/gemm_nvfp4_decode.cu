@@ -13,9 +13,10 @@
 // contiguous range per CTA ("stream-K"): every SM streams the same number of bytes from HBM
 // whatever the tile count.  A range covers parts of up to three tiles:
 //   * a tile covered completely by one CTA is converted to bf16 and stored directly;
-//   * a partly covered tile is added (red.global.add.f32) into a per-tile fp32 scratch slab, a
-//     per-tile counter is raised by the K blocks contributed, and the CTA that completes the
-//     count converts the slab to bf16, stores it, and zeroes slab and counter for the next call.
+//   * of a partly covered tile every contributor but the last to arrive writes its fp32 partial
+//     sums into a scratch slot of its own and raises a per-tile counter by the K blocks it
+//     contributed; the CTA that completes the count adds the other parts to its own, converts,
+//     stores, and resets the counter for the next call.
 // Warp roles (256 threads): warp 0 TMA producer, warp 1 MMA issue + TMEM owner, warp 2 scale
 // copies (tcgen05.cp, issued apart from the MMAs so that they overlap them), warp 3 idle,
 // warps 4-7 epilogue (warp w reads TMEM lanes 32 (w % 4) .. +31).
@@ -33,7 +34,12 @@ constexpr int kWBytes = 128 * kBlockKBytes;   // 16 KiB weight box
 constexpr int kSfBytes = 1024;        // one 128-row band x 8 scales (two 512-byte cells)
 constexpr int kSlotCols = 16;         // SFW cells (8 columns) + SFX cells (8 columns) per stage
 constexpr int kMaxStages = 16;
+constexpr int kDefaultStages = 6;
+constexpr int kWholeTileStages = 8;
+constexpr int kMaxPad = 128;         // activation rows, padded
+constexpr int kStageRows = 64;       // activation rows of D staged in shared memory per TMA store
 constexpr int kBarrierBytes = 1024;
+constexpr int kMaxRegs = 200;
 
 struct Params {
   int M, N, K;
@@ -44,8 +50,10 @@ struct Params {
   int bank_stride;    // columns between the two accumulator banks (128 or 64)
   int ldd;
   uint16_t* d;
-  float* scratch;     // [tiles][m_pad][128] fp32 partial sums (zero between calls)
+  float* scratch;     // [2 * CTAs][m_pad / 4][128] float4 partial sums (need no clearing)
   int* counters;      // [tiles] K blocks accumulated so far (zero between calls)
+  int d_tma;          // 1: D is written by TMA from a transposed staging buffer
+  int tiles_per_cta;  // > 0: CTA b owns the whole tiles [b t, (b+1) t); 0: stream-K ranges
   int* status;
   int activations_dynamic;  // 1: X and SFX are written by the previous kernel on the stream
 };
@@ -64,16 +72,15 @@ __device__ __forceinline__ uint16_t to_bf16(float v) {
   return static_cast<uint16_t>((b + 0x7FFFu + ((b >> 16) & 1u)) >> 16);
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
-                         const __grid_constant__ CUtensorMap tmap_x,
-                         const __grid_constant__ CUtensorMap tmap_sfw,
-                         const __grid_constant__ CUtensorMap tmap_sfx, const Params p) {
+__device__ __forceinline__ void decode_body(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x,
+                                            const CUtensorMap& tmap_sfw, const CUtensorMap& tmap_sfx,
+                                            const CUtensorMap& tmap_d, const Params& p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int stages = p.stages;
   const uint32_t ring_base = smem_base;
-  const uint32_t bar_base = ring_base + static_cast<uint32_t>(stages * p.stage_bytes);
+  const uint32_t stage_base = ring_base + static_cast<uint32_t>(stages * p.stage_bytes);   // D staging
+  const uint32_t bar_base = stage_base + static_cast<uint32_t>((p.m_pad < kStageRows ? p.m_pad : kStageRows) * 256);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
   auto sf_full_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + s); };
@@ -88,8 +95,17 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
   const int tiles = (p.N + 127) / 128;
   const long long units = static_cast<long long>(tiles) * num_kb;
-  const long long u_begin = units * blockIdx.x / gridDim.x;
-  const long long u_end = units * (blockIdx.x + 1) / gridDim.x;
+  // Work split.  Default: whole tiles, t per CTA, on ceil(tiles / t) CTAs: no tile is shared, so
+  // nothing goes through the scratch.  HBM is saturated by far fewer than all SMs (112 CTAs with
+  // two tiles each: 18.0 us at M = 16, N = 28672; 148 CTAs with 1.51 tiles each and the fix-up
+  // that implies: 19.4 us; the gap grows with M and for small N), so idle SMs cost nothing.
+  // Stream-K ranges over all CTAs remain for callers that ask for a CTA count.
+  const long long t_first = static_cast<long long>(blockIdx.x) * p.tiles_per_cta;
+  const long long t_last = t_first + p.tiles_per_cta;
+  const long long u_begin = p.tiles_per_cta > 0 ? (t_first < tiles ? t_first : tiles) * num_kb
+                                                : units * blockIdx.x / gridDim.x;
+  const long long u_end = p.tiles_per_cta > 0 ? (t_last < tiles ? t_last : tiles) * num_kb
+                                              : units * (blockIdx.x + 1) / gridDim.x;
   const uint32_t x_off = kWBytes;
   const uint32_t sfw_off = kWBytes + static_cast<uint32_t>(p.m_pad) * kBlockKBytes;
   const uint32_t sfx_off = sfw_off + kSfBytes;
@@ -115,6 +131,7 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
     tma_prefetch_desc(&tmap_x);
     tma_prefetch_desc(&tmap_sfw);
     tma_prefetch_desc(&tmap_sfx);
+    if (p.d_tma) tma_prefetch_desc(&tmap_d);
   }
   if (warp == 1) {
     tmem_alloc<1>(tmem_slot, static_cast<uint32_t>(p.tmem_cols));
@@ -274,37 +291,66 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------- epilogue (4 warps)
+    // Thread `row` (0..127) owns weight row `row` of the tile = output column n, and reads its
+    // m_pad accumulator columns (one per activation row) from tensor memory.
+    //
+    // Output: the tile's [m_pad x 128] block of D is transposed through shared memory (at most 64
+    // activation rows at a time) and written with one TMA store per chunk; where D is not
+    // 16-byte aligned every thread writes its own 2-byte elements instead.
+    //
+    // Tiles shared by several CTAs: every contributor but the last to arrive writes its fp32
+    // partial sums into a slot of its own (two per CTA: slot 0 for the segment its range starts
+    // with, slot 1 for any other), raises the tile's counter by the K blocks it added, and the
+    // CTA that completes the count adds the others' slots to its own part and stores the tile.
+    // Plain 16-byte stores and loads, no atomics on the data and nothing to clear afterwards;
+    // slot layout [m_pad / 4][128 rows] float4, so that a warp moves 512 contiguous bytes.
     const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const bool first_thread = (threadIdx.x == 128);
+    const int groups = p.m_pad / 4;
+    float4* const slots = reinterpret_cast<float4*>(p.scratch);
+    const long long n_ctas = gridDim.x;
+    auto range_begin = [&](long long cta) { return units * cta / n_ctas; };
+    // Slot that CTA `cta` uses for its segment starting at unit `seg_start`.
+    auto slot_of = [&](long long cta, long long seg_start) {
+      const long long which = (seg_start == range_begin(cta)) ? 0 : 1;
+      return slots + (cta * 2 + which) * groups * 128;
+    };
+    const int chunk_rows = p.m_pad < kStageRows ? p.m_pad : kStageRows;
     int seg = 0;
     bool waited_for_previous_grid = false;
+    bool store_pending = false;     // first_thread: a TMA store may still be reading the staging buffer
     long long u = u_begin;
-    while (u < u_end) {
-      const int tile = static_cast<int>(u / num_kb);
-      const long long seg_end = (static_cast<long long>(tile) + 1) * num_kb < u_end
-                                    ? (static_cast<long long>(tile) + 1) * num_kb : u_end;
-      const int count = static_cast<int>(seg_end - u);
-      const int bank = seg & 1;
-      if (!mbar_wait(acc_full_bar(bank), static_cast<uint32_t>(seg >> 1) & 1u)) {
-        if (lane == 0) report_status(p.status, kDevTimeoutEpilogue);
-        break;
-      }
-      tc_fence_after_sync();
-      const int row = quarter * 32 + lane;            // weight row inside the tile
-      const int n = tile * 128 + row;                 // output column
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                             static_cast<uint32_t>(bank * p.bank_stride);
-      const bool whole = (count == num_kb);
-      float* slab = p.scratch + static_cast<size_t>(tile) * p.m_pad * 128;
-      if (!waited_for_previous_grid) {
-        // First touch of D / scratch / counters: the previous launch on the stream (which may
-        // be this same kernel, started early under programmatic dependent launch) must be done.
-        griddep_wait();
-        waited_for_previous_grid = true;
-      }
-      if (whole) {
+
+    // Writes the finished tile.  fetch(c, v) delivers the final fp32 values of columns c..c+15.
+    auto store_tile = [&](int tile, auto&& fetch) {
+      const int n = tile * 128 + row;
+      if (p.d_tma) {
+        for (int c0 = 0; c0 < p.m_pad; c0 += chunk_rows) {
+          if (first_thread && store_pending) bulk_wait_group_read<0>();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          for (int c = c0; c < c0 + chunk_rows && c < p.m_pad; c += 16) {
+            float v[16];
+            fetch(c, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t dst = stage_base + static_cast<uint32_t>((c - c0 + j) * 256 + row * 2);
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst), "h"(to_bf16(v[j])) : "memory");
+            }
+          }
+          fence_proxy_async_smem();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (first_thread) {
+            // Rows >= M and columns >= N of the box are clipped by the tensor map.
+            tma_store_2d(&tmap_d, stage_base, tile * 128, c0);
+            bulk_commit_group();
+            store_pending = true;
+          }
+        }
+      } else {
         for (int c = 0; c < p.m_pad; c += 16) {
           float v[16];
-          ld16(taddr + c, v);
+          fetch(c, v);
           if (n < p.N) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -312,75 +358,137 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
             }
           }
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty_bar(bank));
-      } else {
-        // Partly covered tile.  If every other contribution is already in the slab (the usual
-        // case for the segment at the end of a CTA's range: its partner handled the other
-        // part of the tile at the start of its own range), merge straight from registers.
-        if (warp == 4 && lane == 0) {
+      }
+    };
+
+    while (u < u_end) {
+      const int tile = static_cast<int>(u / num_kb);
+      const long long tile_begin = static_cast<long long>(tile) * num_kb;
+      const long long tile_end = tile_begin + num_kb;
+      const long long seg_end = tile_end < u_end ? tile_end : u_end;
+      const int count = static_cast<int>(seg_end - u);
+      const int bank = seg & 1;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(bank * p.bank_stride);
+      const bool whole = (count == num_kb);
+      // CTAs whose ranges meet this tile: c_lo .. c_hi (this CTA among them).
+      long long c_lo = 0, c_hi = 0;
+      bool early = false;
+      float pre[kMaxPad];
+      if (!whole) {
+        c_lo = tile_begin * n_ctas / units;
+        while (c_lo + 1 < n_ctas && range_begin(c_lo + 1) <= tile_begin) ++c_lo;
+        while (c_lo > 0 && range_begin(c_lo) > tile_begin) --c_lo;
+        c_hi = (tile_end - 1) * n_ctas / units;
+        while (c_hi + 1 < n_ctas && range_begin(c_hi + 1) < tile_end) ++c_hi;
+        while (c_hi > 0 && range_begin(c_hi) >= tile_end) --c_hi;
+        if (!waited_for_previous_grid) {
+          // First touch of the counters and slots: the previous launch on the stream (which may
+          // be this same kernel, started early under programmatic dependent launch) must be done.
+          griddep_wait();
+          waited_for_previous_grid = true;
+        }
+        // If every other part of the tile has been published already (the usual case for the
+        // segment at the END of a range: the neighbour handled its part at the start of its own
+        // range), add those parts up in registers while the MMAs of this segment are running.
+        if (first_thread) {
           const int seen = atomicAdd(p.counters + tile, 0);
-          const uint32_t f = (seen + count == num_kb) ? 2u : 0u;
+          const uint32_t f = (seen + count == num_kb) ? 1u : 0u;
           asm volatile("st.shared.b32 [%0], %1;" ::"r"(last_flag), "r"(f) : "memory");
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        uint32_t flag;
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(flag) : "r"(last_flag) : "memory");
-        if (flag == 2u) {
+        uint32_t f;
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(f) : "r"(last_flag) : "memory");
+        early = (f != 0u);
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // everyone has read the flag word
+        if (early) {
           __threadfence();
-          for (int c = 0; c < p.m_pad; c += 16) {
-            float v[16], o[16];
-            ld16(taddr + c, v);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) o[j] = __ldcg(slab + (c + j) * 128 + row);
+          for (int c = 0; c < kMaxPad; ++c) pre[c] = 0.0f;
+          for (long long c = c_lo; c <= c_hi; ++c) {
+            if (c == static_cast<long long>(blockIdx.x)) continue;
+            const long long rb = range_begin(c);
+            const float4* src = slot_of(c, rb > tile_begin ? rb : tile_begin);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (c + j < p.M && n < p.N)
-                p.d[static_cast<size_t>(c + j) * p.ldd + n] = to_bf16(v[j] + o[j]);
-              __stcg(slab + (c + j) * 128 + row, 0.0f);
-            }
-          }
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty_bar(bank));
-          if (warp == 4 && lane == 0) p.counters[tile] = 0;
-        } else {
-          for (int c = 0; c < p.m_pad; c += 16) {
-            float v[16];
-            ld16(taddr + c, v);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) atomicAdd(slab + (c + j) * 128 + row, v[j]);
-          }
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty_bar(bank));
-          // Publish the partial sums, then find out whether this CTA completed the tile after all.
-          __threadfence();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (warp == 4 && lane == 0) {
-            const int before = atomicAdd(p.counters + tile, count);
-            const uint32_t last = (before + count == num_kb) ? 1u : 0u;
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(last_flag), "r"(last) : "memory");
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          uint32_t last;
-          asm volatile("ld.shared.b32 %0, [%1];" : "=r"(last) : "r"(last_flag) : "memory");
-          if (last) {
-            __threadfence();
-            for (int c = 0; c < p.m_pad; c += 16) {
-              float o[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) o[j] = __ldcg(slab + (c + j) * 128 + row);
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (c + j < p.M && n < p.N)
-                  p.d[static_cast<size_t>(c + j) * p.ldd + n] = to_bf16(o[j]);
-                __stcg(slab + (c + j) * 128 + row, 0.0f);
+            for (int g = 0; g < kMaxPad / 4; ++g) {
+              if (g < groups) {
+                const float4 q = __ldcg(src + g * 128 + row);
+                pre[4 * g] += q.x; pre[4 * g + 1] += q.y; pre[4 * g + 2] += q.z; pre[4 * g + 3] += q.w;
               }
             }
-            if (warp == 4 && lane == 0) p.counters[tile] = 0;
           }
+        }
+      }
+      if (!mbar_wait(acc_full_bar(bank), static_cast<uint32_t>(seg >> 1) & 1u)) {
+        if (lane == 0) report_status(p.status, kDevTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after_sync();
+      if (!waited_for_previous_grid) {
+        griddep_wait();   // first store to D
+        waited_for_previous_grid = true;
+      }
+      if (whole || early) {
+        if (early) {
+          // Static register indexing: the column loop of store_tile is not unrolled, so add the
+          // other parts here, 16 columns at a time, with a fully unrolled selector.
+          store_tile(tile, [&](int c, float (&v)[16]) {
+            ld16(taddr + c, v);
+#pragma unroll
+            for (int cc = 0; cc < kMaxPad; cc += 16) {
+              if (cc == c) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += pre[cc + j];
+              }
+            }
+          });
+        } else {
+          store_tile(tile, [&](int c, float (&v)[16]) { ld16(taddr + c, v); });
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty_bar(bank));
+        if (early && first_thread) p.counters[tile] = 0;
+      } else {
+        // Publish this part, then find out whether it was the last one after all.
+        float4* mine = slot_of(blockIdx.x, u);
+        for (int c = 0; c < p.m_pad; c += 16) {
+          float v[16];
+          ld16(taddr + c, v);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            __stcg(mine + (c / 4 + q) * 128 + row, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty_bar(bank));
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (first_thread) {
+          const int before = atomicAdd(p.counters + tile, count);
+          const uint32_t last = (before + count == num_kb) ? 1u : 0u;
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(last_flag), "r"(last) : "memory");
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        uint32_t last;
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(last) : "r"(last_flag) : "memory");
+        if (last) {
+          // All parts, this CTA's included, are in their slots: add them in CTA order.
+          __threadfence();
+          store_tile(tile, [&](int c, float (&v)[16]) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+            for (long long cc = c_lo; cc <= c_hi; ++cc) {
+              const long long rb = range_begin(cc);
+              const float4* src = slot_of(cc, rb > tile_begin ? rb : tile_begin);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float4 x = __ldcg(src + (c / 4 + q) * 128 + row);
+                v[4 * q] += x.x; v[4 * q + 1] += x.y; v[4 * q + 2] += x.z; v[4 * q + 3] += x.w;
+              }
+            }
+          });
+          if (first_thread) p.counters[tile] = 0;
         }
         // The flag word is reused by the next partial segment.
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -388,6 +496,7 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
       u = seg_end;
       ++seg;
     }
+    if (first_thread && store_pending) bulk_wait_group<0>();
   }
   __syncwarp();
   tc_fence_before_sync();
@@ -398,9 +507,47 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
   }
 }
 
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                         const __grid_constant__ CUtensorMap tmap_x,
+                         const __grid_constant__ CUtensorMap tmap_sfw,
+                         const __grid_constant__ CUtensorMap tmap_sfx,
+                         const __grid_constant__ CUtensorMap tmap_d,
+                         const __grid_constant__ Params p) {
+  decode_body(tmap_w, tmap_x, tmap_sfw, tmap_sfx, tmap_d, p);
+}
+
+// The same kernel with registers capped, launched when the activation quantiser is chained in
+// front (activations_dynamic): the quantiser of the NEXT decode step is resident, waiting for
+// this grid, while this grid runs, and one of its blocks (256 threads x 48 registers) must fit
+// on an SM beside a CTA of this kernel; uncapped (240 registers) it kept the next GEMM's CTAs
+// off the SMs it sat on until it had run.  The cap costs the main loop about 1 us per launch,
+// so plans with resident activations use the uncapped kernel.
+__global__ void __maxnreg__(kMaxRegs)
+gemm_nvfp4_decode_kernel_capped(const __grid_constant__ CUtensorMap tmap_w,
+                                const __grid_constant__ CUtensorMap tmap_x,
+                                const __grid_constant__ CUtensorMap tmap_sfw,
+                                const __grid_constant__ CUtensorMap tmap_sfx,
+                                const __grid_constant__ CUtensorMap tmap_d,
+                                const __grid_constant__ Params p) {
+  decode_body(tmap_w, tmap_x, tmap_sfw, tmap_sfx, tmap_d, p);
+}
+
 }  // namespace fp4d
 
 int fp4_decode_stage_bytes(int m_pad) { return fp4d::kWBytes + m_pad * fp4d::kBlockKBytes + 2 * fp4d::kSfBytes; }
+
+size_t fp4_decode_slot_bytes(int M) { return static_cast<size_t>((M + 15) / 16 * 16) * 128 * sizeof(float); }
+
+size_t fp4_decode_scratch_bytes(int M, int N, int ctas) {
+  return 2 * static_cast<size_t>(ctas) * fp4_decode_slot_bytes(M) + (static_cast<size_t>(N) + 127) / 128 * sizeof(int);
+}
+
+int fp4_decode_box_rows(int M) {
+  const int m_pad = (M + 15) / 16 * 16;
+  return m_pad < fp4d::kStageRows ? m_pad : fp4d::kStageRows;
+}
 
 int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   static thread_local int configured_device = -1;
@@ -411,6 +558,9 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   if (configured_device != dev) {
     cudaError_t e = cudaFuncSetAttribute(fp4d::gemm_nvfp4_decode_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(fp4d::gemm_nvfp4_decode_kernel_capped,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e != cudaSuccess) return set_cuda_error(e, "cudaFuncSetAttribute(decode smem)");
     e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return set_cuda_error(e, "cudaDeviceGetAttribute(SM count)");
@@ -424,14 +574,21 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   p.stage_bytes = fp4_decode_stage_bytes(p.m_pad);
   // One CTA per SM.  (Two co-resident CTAs with half the ring each were measured slower, 22.8
   // against 21.0-21.7 us at M = 16, and would let three CTAs share a tile.)
-  const int per_sm = 1;
-  const int budget = (per_sm == 2 ? 113 * 1024 : kSmemBudget) - 1024 - fp4d::kBarrierBytes;
+  const int staging = fp4_decode_box_rows(L.M) * 256;   // transposed [rows x 128] bf16 block of D
+  const int budget = kSmemBudget - 1024 - fp4d::kBarrierBytes - staging;
   int stages = budget / p.stage_bytes;
-  p.tmem_cols = per_sm == 2 ? 256 : 512;
-  p.bank_stride = per_sm == 2 ? 64 : 128;
+  p.tmem_cols = 512;
+  p.bank_stride = 128;
   const int max_slots = (p.tmem_cols - 2 * p.bank_stride) / fp4d::kSlotCols;
   if (stages > max_slots) stages = max_slots;
   if (stages > fp4d::kMaxStages) stages = fp4d::kMaxStages;
+  // With stream-K ranges over all SMs, six stages (96 KiB of weights in flight per SM) cover the
+  // HBM latency and deeper rings measured slower (M = 16: 19.4 us with 6 stages, 19.8 with 8,
+  // 20.4 with 11).  With whole tiles on fewer CTAs each SM carries more of the stream: 8 stages
+  // (M = 16, 112 CTAs: 17.8 us against 18.05 with 6 and 19.3 with 4).
+  const bool whole_tiles = (L.max_ctas == 0);
+  if (L.max_stages == 0 && stages > (whole_tiles ? fp4d::kWholeTileStages : fp4d::kDefaultStages))
+    stages = whole_tiles ? fp4d::kWholeTileStages : fp4d::kDefaultStages;
   if (L.max_stages > 0 && stages > L.max_stages) stages = L.max_stages;
   if (stages < 2) return set_error(SMB_ERR_UNSUPPORTED, "decode: activation tile too large");
   p.stages = stages;
@@ -440,13 +597,24 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   p.scratch = L.scratch;
   p.counters = L.counters;
   p.status = L.status;
+  p.d_tma = L.d_tma ? 1 : 0;
   p.activations_dynamic = L.activations_dynamic ? 1 : 0;
   const int num_kb = (L.K + fp4d::kBlockK - 1) / fp4d::kBlockK;
   const long long units = static_cast<long long>((L.N + 127) / 128) * num_kb;
-  int grid = L.max_ctas > 0 ? L.max_ctas : per_sm * sm_count;
-  if (grid > per_sm * sm_count) grid = per_sm * sm_count;
-  if (units < grid) grid = static_cast<int>(units);
-  const int smem = 1024 + stages * p.stage_bytes + fp4d::kBarrierBytes;
+  int grid;
+  if (whole_tiles) {
+    const int tiles = (L.N + 127) / 128;
+    p.tiles_per_cta = (tiles + sm_count - 1) / sm_count;
+    grid = (tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;
+  } else {
+    p.tiles_per_cta = 0;
+    grid = L.max_ctas;
+    if (grid > sm_count) grid = sm_count;
+    if (grid > L.scratch_ctas) grid = L.scratch_ctas;   // two scratch slots per CTA exist for so many
+    if (units < grid) grid = static_cast<int>(units);
+    if (grid < 1) return set_error(SMB_ERR_INVALID, "decode: no scratch slots");
+  }
+  const int smem = 1024 + stages * p.stage_bytes + staging + fp4d::kBarrierBytes;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(fp4d::kThreads, 1, 1);
@@ -457,10 +625,23 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   attr.val.programmaticStreamSerializationAllowed = L.no_overlap ? 0 : 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, fp4d::gemm_nvfp4_decode_kernel, L.tmap_w, L.tmap_x,
-                                     L.tmap_sfw, L.tmap_sfx, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, L.activations_dynamic ? fp4d::gemm_nvfp4_decode_kernel_capped
+                                                                 : fp4d::gemm_nvfp4_decode_kernel,
+                                     L.tmap_w, L.tmap_x, L.tmap_sfw, L.tmap_sfx, L.tmap_d, p);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error(e, "nvfp4 decode launch");
+  return SMB_OK;
+}
+
+// Fills the output side of a decode launch: the TMA view of D when D allows one.
+int fp4_decode_bind_output(Fp4DecodeLaunch* L, void* d, int M, int N, long long ldd, bool allow_tma) {
+  L->d = d;
+  L->ldd = static_cast<int>(ldd);
+  L->d_tma = allow_tma && (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0);
+  if (L->d_tma)
+    return encode_tmap_2d(&L->tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldd * 2,
+                          fp4_decode_box_rows(M), 128, false);
+  L->tmap_d = L->tmap_w;   // never dereferenced
   return SMB_OK;
 }
 
@@ -472,13 +653,13 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
 // Some hosts of this library cannot call cudaMalloc on the path that runs the GEMM: an
 // inference server that has handed all device memory to its own pool at start-up, a
 // plugin running inside another framework's allocator, code between a stream capture's
-// begin and end.  For them the fp32 partial-sum slabs and tile counters of the decode
+// begin and end.  For them the fp32 partial-sum slots and tile counters of the decode
 // kernel live in the fixed array below instead of in a plan-owned allocation.  The array
-// is part of the library image: every GPU that loads the library carries these 16 MiB
+// is part of the library image: every GPU that loads the library carries these 20 MiB
 // until the process exits.
 namespace {
 
-constexpr size_t kStaticScratchBytes = size_t(16) << 20;
+constexpr size_t kStaticScratchBytes = size_t(20) << 20;
 constexpr size_t kStaticStatusOffset = kStaticScratchBytes - 256;   // last 256 bytes: status word
 static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
 
@@ -522,14 +703,18 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
   if (K % 32 != 0)
     return set_error(SMB_ERR_UNSUPPORTED, "no-alloc decode: K=%d must be a multiple of 32", K);
   const int m_pad = (M + 15) / 16 * 16;
-  const size_t tiles = (static_cast<size_t>(N) + 127) / 128;
-  const size_t slab_bytes = tiles * m_pad * 128 * sizeof(float);
-  const size_t need = slab_bytes + tiles * sizeof(int);
-  if (need > kStaticStatusOffset)
+  // Two slots per CTA plus one counter per tile.  As many CTAs as the array has slots for (and
+  // the device has SMs); a shape whose counters alone leave room for none is refused.
+  const size_t counter_bytes = (static_cast<size_t>(N) + 127) / 128 * sizeof(int);
+  const size_t per_cta = 2 * fp4_decode_slot_bytes(M);
+  if (counter_bytes + per_cta > kStaticStatusOffset)
     return set_error(SMB_ERR_UNSUPPORTED,
-                     "no-alloc decode: M=%d N=%d needs %zu bytes of scratch, the built-in array "
-                     "holds %zu (ceil(N/128) * (round_up(M,16) * 512 + 4) must not exceed it)",
-                     M, N, need, kStaticStatusOffset);
+                     "no-alloc decode: M=%d N=%d needs %zu bytes of scratch for its tile counters and "
+                     "one CTA, the built-in array holds %zu",
+                     M, N, counter_bytes + per_cta, kStaticStatusOffset);
+  const size_t fit = (kStaticStatusOffset - counter_bytes) / per_cta;
+  const int ctas = fit > 4096 ? 4096 : static_cast<int>(fit);
+  const size_t slot_bytes = static_cast<size_t>(ctas) * per_cta;
   void* base = nullptr;
   if (int rc = static_scratch_address(&base)) return rc;
 
@@ -537,14 +722,13 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
   L.M = M;
   L.N = N;
   L.K = K;
-  L.d = d;
-  L.ldd = N;
   L.max_ctas = 0;
   L.max_stages = 0;
   L.activations_dynamic = false;
   L.no_overlap = true;   // the memset below must be ordered before every access of this launch
   L.scratch = static_cast<float*>(base);
-  L.counters = reinterpret_cast<int*>(static_cast<char*>(base) + slab_bytes);
+  L.scratch_ctas = ctas;
+  L.counters = reinterpret_cast<int*>(static_cast<char*>(base) + slot_bytes);
   L.status = reinterpret_cast<int*>(static_cast<char*>(base) + kStaticStatusOffset);
   const uint64_t kchunks = (static_cast<uint64_t>(K) / 32 + 3) / 4;
   const uint64_t bands_a = (static_cast<uint64_t>(M) + 127) / 128;
@@ -558,11 +742,13 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
   if (rc == SMB_OK)
     rc = encode_tmap_2d(&L.tmap_sfx, sfa, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_a, kchunks * 64,
                         kchunks * 512, 1, 128, false);
+  if (rc == SMB_OK) rc = fp4_decode_bind_output(&L, d, M, N, N, true);
   if (rc != SMB_OK) return rc;
-  // The array keeps whatever the last call left in it (all zero after a call that ran to the
-  // end, anything after one that was cut short): clear the part this call uses, and the status.
+  // The counters keep whatever the last call left in them (all zero after a call that ran to
+  // the end, anything after one that was cut short): clear them, and the status.  The slots
+  // need no clearing: a slot is read only after its writer has counted itself in.
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e = cudaMemsetAsync(base, 0, need, st);
+  cudaError_t e = cudaMemsetAsync(L.counters, 0, counter_bytes, st);
   if (e == cudaSuccess) e = cudaMemsetAsync(L.status, 0, sizeof(int), st);
   if (e != cudaSuccess) return set_cuda_error(e, "no-alloc decode: scratch clear");
   return fp4_decode_launch(L, st);
