@@ -267,6 +267,14 @@ int smb_unshard_columns_device(const void* gathered, void* d, int g, int M, int 
  * this launch overlap the previous kernel's tail (what the reference drivers' timing loops do:
  * dense_gemm_bf16.cu:355-361, blocks/97_sched_warp_clc.cuh:118-129). */
 #define SMB_FLAG_OPERANDS_STATIC 1024u
+/* Stronger: the previous kernel on the stream neither writes this plan's operands nor reads or
+ * writes its D, so this launch waits for nothing and consecutive launches may run side by side
+ * and finish in any order (later stream operations still wait for all of them).  This is the
+ * launch behaviour of the reference kernels, whose only wait is compiled out
+ * (blocks/97_sched_warp_clc.cuh:108, USE_GRIDDEP_WAIT = false); the drivers here use it in their
+ * timing loops, which launch the same GEMM repeatedly.  Implies SMB_FLAG_OPERANDS_STATIC.  Tiled
+ * kernels only; the decode kernel ignores it (its scratch protocol needs the order). */
+#define SMB_FLAG_LAUNCH_INDEPENDENT 4096u
 #define SMB_FLAG_NO_DECODE 64u        /* FP4 only: M <= 128 through the tiled kernel, not the decode kernel */
 #define SMB_FLAG_NO_LAUNCH_OVERLAP 128u /* decode kernel: no programmatic dependent launch */
 

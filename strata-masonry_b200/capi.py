@@ -31,6 +31,7 @@ FLAG_NO_DECODE = 64
 FLAG_NO_LAUNCH_OVERLAP = 128
 FLAG_DYNAMIC_TILES = 256
 FLAG_OPERANDS_STATIC = 1024
+FLAG_LAUNCH_INDEPENDENT = 4096
 
 _vp = C.c_void_p
 _i = C.c_int

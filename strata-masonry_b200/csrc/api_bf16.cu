@@ -76,7 +76,8 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
   L.max_clusters = 0;
   L.prof = nullptr;
   L.dynamic = (flags & SMB_FLAG_DYNAMIC_TILES) != 0;
-  L.operands_static = (flags & SMB_FLAG_OPERANDS_STATIC) != 0;
+  L.operands_static = (flags & (SMB_FLAG_OPERANDS_STATIC | SMB_FLAG_LAUNCH_INDEPENDENT)) != 0;
+  L.output_independent = (flags & SMB_FLAG_LAUNCH_INDEPENDENT) != 0;
   L.peers.count = 0;
   L.d = d;
   L.ldd = static_cast<int>(ldd);

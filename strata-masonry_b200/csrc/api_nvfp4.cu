@@ -59,7 +59,8 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
   L.prof = nullptr;
   L.prefetch = 0;
   L.dynamic = (flags & SMB_FLAG_DYNAMIC_TILES) != 0;
-  L.operands_static = (flags & SMB_FLAG_OPERANDS_STATIC) != 0;
+  L.operands_static = (flags & (SMB_FLAG_OPERANDS_STATIC | SMB_FLAG_LAUNCH_INDEPENDENT)) != 0;
+  L.output_independent = (flags & SMB_FLAG_LAUNCH_INDEPENDENT) != 0;
   L.peers.count = 0;
   L.d = d;
   L.ldd = static_cast<int>(ldd);

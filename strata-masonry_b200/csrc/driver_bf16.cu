@@ -4,7 +4,9 @@
 //   --dump-output=PATH          (raw little-endian bf16, M*N values, row-major, no header)
 // No arguments: the reference's built-in shape inventory with the GPU self-check.
 // Beyond the reference: any positive M and N, any K that is a multiple of 8, fills 5..7
-// (Gaussian stand-ins), --json=PATH.  Operands are generated on the device.
+// (Gaussian stand-ins), --json=PATH, --ordered-launches (stores of a launch wait for the
+// previous launch; by default the timing loop's launches are independent, as the reference's
+// are).  Operands are generated on the device.
 #include "driver_common.h"
 
 namespace {
@@ -45,6 +47,9 @@ struct Options {
   int raster = 0;   // 0 default grouping, 1 along-n, 2 along-m
   const char* dump = nullptr;
   const char* json = nullptr;
+  // false (default): launches of the timing loop are independent of one another, as the
+  // reference kernels' are; true: every launch orders its stores after the previous launch.
+  bool ordered = false;
 };
 
 double run_one(int M, int N, int K, const Options& o) {
@@ -61,7 +66,8 @@ double run_one(int M, int N, int K, const Options& o) {
   DRV_CUDA(cudaStreamSynchronize(stream));
 
   smb_bf16_plan* plan = nullptr;
-  DRV_SMB(smb_bf16_plan_create(&plan, a, bt, d, M, N, K, K, K, N, SMB_FLAG_OPERANDS_STATIC));
+  DRV_SMB(smb_bf16_plan_create(&plan, a, bt, d, M, N, K, K, K, N,
+                               o.ordered ? SMB_FLAG_OPERANDS_STATIC : SMB_FLAG_LAUNCH_INDEPENDENT));
   if (o.raster == 1) DRV_SMB(smb_bf16_plan_tune(plan, 1, 0));
   if (o.raster == 2) DRV_SMB(smb_bf16_plan_tune(plan, (M + 255) / 256, 0));
   auto launch = [&]() { return smb_bf16_plan_run(plan, stream); };
@@ -136,6 +142,8 @@ int main(int argc, char** argv) {
       o.benchmark = false;
     } else if (std::strcmp(argv[i], "--no-gpu-verify") == 0) {
       o.verify = false;
+    } else if (std::strcmp(argv[i], "--ordered-launches") == 0) {
+      o.ordered = true;
     } else if (std::strcmp(argv[i], "--raster=along-m") == 0) {
       o.raster = 2;
     } else if (std::strcmp(argv[i], "--raster=along-n") == 0) {

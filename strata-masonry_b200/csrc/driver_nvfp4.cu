@@ -6,7 +6,8 @@
 // against the closed form (exact), the other fills on 2048 hashed samples against a host fp32
 // reference with tolerance max(0.8 % |ref|, 16).  FILL environment variable as default fill.
 // Beyond the reference: any positive M and N, any K that is a multiple of 32, fills 5 and 6
-// (quantised Gaussian stand-ins), --json=PATH; no arguments runs a short shape list.
+// (quantised Gaussian stand-ins), --json=PATH, --ordered-launches; no arguments runs a short
+// shape list.
 #include <cmath>
 
 #include "driver_common.h"
@@ -30,6 +31,9 @@ struct Options {
   bool verify = true;
   const char* dump = nullptr;
   const char* json = nullptr;
+  // false (default): launches of the timing loop are independent of one another, as the
+  // reference kernels' are; true: every launch orders its stores after the previous launch.
+  bool ordered = false;
 };
 
 // One logical row of an operand on the host: values (code * scale) as floats.
@@ -64,7 +68,8 @@ double run_one(int M, int N, int K, const Options& o) {
   DRV_CUDA(cudaStreamSynchronize(stream));
 
   smb_fp4_plan* plan = nullptr;
-  DRV_SMB(smb_fp4_plan_create(&plan, a, sfa, b, sfb, d, M, N, K, K / 2, K / 2, N, SMB_FLAG_OPERANDS_STATIC));
+  DRV_SMB(smb_fp4_plan_create(&plan, a, sfa, b, sfb, d, M, N, K, K / 2, K / 2, N,
+                              o.ordered ? SMB_FLAG_OPERANDS_STATIC : SMB_FLAG_LAUNCH_INDEPENDENT));
   auto launch = [&]() { return smb_fp4_plan_run(plan, stream); };
   double ms = 0.0;
   if (o.benchmark) {
@@ -188,6 +193,8 @@ int main(int argc, char** argv) {
       o.benchmark = false;
     } else if (std::strcmp(argv[i], "--no-gpu-verify") == 0) {
       o.verify = false;
+    } else if (std::strcmp(argv[i], "--ordered-launches") == 0) {
+      o.ordered = true;
     } else if (std::strncmp(argv[i], "--dump-output=", 14) == 0 && argv[i][14]) {
       o.dump = argv[i] + 14;
     } else if (std::strncmp(argv[i], "--json=", 7) == 0 && argv[i][7]) {

@@ -114,11 +114,14 @@ __device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, c
   }
 }
 
-// Call once per warp after its last tile: outstanding stores must finish before the CTA exits.
+// Call once per warp after its last tile: the CTA's shared memory must outlive the reads of its
+// outstanding TMA stores.  Waiting for the reads is enough: the global writes themselves are
+// ordinary memory traffic in flight, which completes before the grid is reported complete (and
+// before a dependent grid's griddepcontrol.wait returns).
 template <bool kTmaStore>
 __device__ __forceinline__ void drain_store_groups(int lane) {
   if (kTmaStore) {
-    if (lane == 0) bulk_wait_group<0>();
+    if (lane == 0) bulk_wait_group_read<0>();
   }
   __syncwarp();
 }

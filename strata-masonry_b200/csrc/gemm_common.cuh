@@ -68,6 +68,7 @@ struct Bf16Launch {
   long long* prof;   // device buffer of 8 counters per CTA (role timers), or null
   bool dynamic;      // tiles from the hardware work queue (cluster launch control) instead of a static walk
   bool operands_static;  // loads need not wait for the previous kernel on the stream
+  bool output_independent;  // with operands_static: stores need not wait either
   PeerCopies peers;
 };
 void bf16_pick_tile(int M, int N, int K, int clusters, int* tile_n, int* sub_blocks);
@@ -90,6 +91,7 @@ struct Fp4Launch {
   int prefetch;      // L2 prefetch distance in K blocks (0 = off)
   bool dynamic;      // tiles from the hardware work queue instead of a static walk
   bool operands_static;  // loads need not wait for the previous kernel on the stream
+  bool output_independent;  // with operands_static: stores need not wait either
   PeerCopies peers;
 };
 void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1);

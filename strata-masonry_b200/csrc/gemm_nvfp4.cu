@@ -405,7 +405,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     out.peers = &p.peers;
     int local = 0;
     bool ok = true;
-    if (p.operands_static) griddep_wait();
+    if (p.operands_static == 1) griddep_wait();   // 2: D is independent too, no wait at all
     const bool prof = p.prof != nullptr && warp == 2 && lane == 0;
     long long waited = 0;
     const long long t_begin = prof ? clock64() : 0;
@@ -497,7 +497,7 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   p.d_ptr = static_cast<uint16_t*>(L.d);
   p.status = L.status;
   p.prof = L.prof;
-  p.operands_static = L.operands_static ? 1 : 0;
+  p.operands_static = L.operands_static ? (L.output_independent ? 2 : 1) : 0;
   p.peers = L.peers;
   p.prefetch = L.prefetch;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;

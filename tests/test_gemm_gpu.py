@@ -540,3 +540,36 @@ def test_fp4_plan_fed_with_bf16_activations(smb, cuda_device, shape):
         assert torch.equal(d.view(torch.int16), d_ref.view(torch.int16)), f"step {step}"
     plan.close()
     ref_plan.close()
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp4"])
+def test_independent_launches_run_side_by_side(smb, oracle, cuda_device, kind):
+    """FLAG_LAUNCH_INDEPENDENT: no launch waits for the previous one (the reference kernels'
+    behaviour).  Small one-wave GEMMs into two different outputs, launched alternately many times
+    without a pause: both outputs must be complete and right at the end."""
+    torch = _torch()
+    f = smb.capi.FLAG_LAUNCH_INDEPENDENT
+    m, n, k = 2048, 256, 1024
+    outs = [torch.full((m, n), float("nan"), device=cuda_device, dtype=torch.bfloat16) for _ in range(2)]
+    if kind == "bf16":
+        a = torch.empty(m, k, device=cuda_device, dtype=torch.bfloat16)
+        bt = torch.empty(n, k, device=cuda_device, dtype=torch.bfloat16)
+        smb.gemm.bf16_operands_device(a, bt, m, n, k, 5)
+        plans = [smb.gemm.Bf16Plan(a, bt, d, m, n, k, flags=f) for d in outs]
+    else:
+        a, sfa, sfar = _fp4_operand(smb, m, k, 5, 0)
+        b, sfb, sfbr = _fp4_operand(smb, n, k, 5, 1)
+        plans = [smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k, flags=f) for d in outs]
+    for _ in range(25):
+        for p in plans:
+            p.run()
+    for p in plans:
+        p.check()
+    for d in outs:
+        if kind == "bf16":
+            _check_bf16_full(oracle, a, bt, d, n, k)
+        else:
+            _check_fp4_full((a, sfar), (b, sfbr), d, k)
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    for p in plans:
+        p.close()
