@@ -236,6 +236,8 @@ def main():
     ap.add_argument("--allgather", action="store_true", help="also time the all-gather of D (N > 1)")
     ap.add_argument("--fused-allgather", action="store_true",
                     help="also time the GEMM whose epilogue writes D into every GPU's full D (N > 1)")
+    ap.add_argument("--swiglu", action="store_true",
+                    help="also time the GEMM with the gated-activation epilogue (D = silu(gate) * up, [M, N/2])")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=8)
     args = ap.parse_args()
@@ -491,6 +493,46 @@ def main():
                      "unfused_total_ms": ms_step + ag_ms + un_ms}
         del gathered, full
 
+    # ---------------------------------------------------------------- gated-activation epilogue
+    # The rows of BT are read as interleaved (up, gate) pairs; the fused plan writes
+    # silu(gate) * up, half as wide, against the plain GEMM followed by the same activation as
+    # separate PyTorch element-wise kernels on its bf16 output.
+    swiglu = None
+    if args.swiglu and kind != "decode" and n_local % 2 == 0:
+        d_act = torch.empty(m, n_local // 2, device=dev, dtype=torch.bfloat16)
+        sflags = smb.capi.FLAG_OPERANDS_STATIC | smb.capi.FLAG_EPILOGUE_SWIGLU
+        if kind == "bf16":
+            splan = smb.gemm.Bf16Plan(a, bt, d_act, m, n_local, k, ldd=n_local // 2, flags=sflags)
+        else:
+            splan = smb.gemm.Fp4Plan(a, sfa, bt, sfb, d_act, m, n_local, k, ldd=n_local // 2, flags=sflags)
+        reps = max(5, min(args.steps, 100))
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            barrier()
+            t0 = torch.cuda.Event(enable_timing=True)
+            t1 = torch.cuda.Event(enable_timing=True)
+            t0.record(stream)
+            for _ in range(reps):
+                fn()
+            t1.record(stream)
+            barrier()
+            return max_over_ranks(t0.elapsed_time(t1)) / reps
+
+        def unfused():
+            plan.run(stream)
+            torch.mul(torch.nn.functional.silu(d[:, 1::2]), d[:, 0::2], out=d_act)
+
+        fused_ms = timed(lambda: splan.run(stream))
+        splan.check(stream)
+        unfused_ms = timed(unfused)
+        swiglu = {"fused_ms": fused_ms, "gemm_then_torch_elementwise_ms": unfused_ms,
+                  "gemm_only_ms": ms_step, "d_bytes_fused": m * (n_local // 2) * 2,
+                  "tflops_fused": flops_step / g / (fused_ms * 1e-3) / 1e12}
+        splan.close()
+        del d_act
+
     # ---------------------------------------------------------------- GEMM + all-gather in one kernel
     # Every rank holds a full row-major D [M, N] that all processes map; the epilogue of rank r
     # stores its column slab into all g of them (plain stores over NVLink for the g - 1 remote
@@ -595,7 +637,7 @@ def main():
                        "launch": "operands static across steps: consecutive launches may overlap head and tail "
                                  "(programmatic dependent launch); stores to D stay ordered"},
             "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-            "gpu_launches": args.steps, "allgather": allgather, "from_bf16_activations": act_step,
+            "gpu_launches": args.steps, "allgather": allgather, "from_bf16_activations": act_step, "swiglu": swiglu,
         }
         print(json.dumps(line))
     if dist is not None:

@@ -275,8 +275,20 @@ int smb_unshard_columns_device(const void* gathered, void* d, int g, int M, int 
  * timing loops, which launch the same GEMM repeatedly.  Implies SMB_FLAG_OPERANDS_STATIC.  Tiled
  * kernels only; the decode kernel ignores it (its scratch protocol needs the order). */
 #define SMB_FLAG_LAUNCH_INDEPENDENT 4096u
+/* Gated-activation epilogue, the reference's SwiGLU epilogue block
+ * (blocks/93_epi_warp_blackwell.cuh:439-596, composites/130_swiglu_act.cuh): the rows of BT (B
+ * for FP4) are interleaved, row 2n = up projection n, row 2n + 1 = gate projection n, and the
+ * kernel stores D[m, n] = bf16(silu(acc[m, 2n + 1]) * acc[m, 2n]) with silu(z) = 0.5 z (1 +
+ * tanh(z / 2)) on the hardware tanh approximation.  D is [M, N / 2] (ldd >= N / 2, 16-byte
+ * aligned, ldd % 8 == 0), N even; the plan uses 256-wide tiles.  Tiled kernels only. */
+#define SMB_FLAG_EPILOGUE_SWIGLU 8192u
 #define SMB_FLAG_NO_DECODE 64u        /* FP4 only: M <= 128 through the tiled kernel, not the decode kernel */
 #define SMB_FLAG_NO_LAUNCH_OVERLAP 128u /* decode kernel: no programmatic dependent launch */
+/* Decode kernel (FP4, M <= 128): force the form in which a CTA multiplies two adjacent weight
+ * tiles against one copy of the activations (default from 64 padded activation rows up), or the
+ * form with one weight tile per activation box. */
+#define SMB_FLAG_DECODE_DUAL 512u
+#define SMB_FLAG_DECODE_SINGLE 2048u
 
 #ifdef __cplusplus
 }

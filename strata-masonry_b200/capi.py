@@ -31,7 +31,10 @@ FLAG_NO_DECODE = 64
 FLAG_NO_LAUNCH_OVERLAP = 128
 FLAG_DYNAMIC_TILES = 256
 FLAG_OPERANDS_STATIC = 1024
+FLAG_DECODE_DUAL = 512
+FLAG_DECODE_SINGLE = 2048
 FLAG_LAUNCH_INDEPENDENT = 4096
+FLAG_EPILOGUE_SWIGLU = 8192
 
 _vp = C.c_void_p
 _i = C.c_int

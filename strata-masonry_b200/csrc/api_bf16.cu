@@ -54,7 +54,11 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
     return set_error(SMB_ERR_INVALID, "plan: dimensions must be positive (M=%d N=%d K=%d)", M, N, K);
   if (K % 8 != 0)
     return set_error(SMB_ERR_UNSUPPORTED, "plan: K=%d must be a multiple of 8 (16-byte operand rows)", K);
-  if (lda < K || ldb < K || ldd < N)
+  const bool swiglu = (flags & SMB_FLAG_EPILOGUE_SWIGLU) != 0;
+  if (swiglu && N % 2 != 0)
+    return set_error(SMB_ERR_INVALID, "plan: the gated epilogue needs an even N (up/gate row pairs of BT)");
+  const int n_out = swiglu ? N / 2 : N;
+  if (lda < K || ldb < K || ldd < n_out)
     return set_error(SMB_ERR_INVALID, "plan: leading dimension smaller than the row length");
   if (lda % 8 != 0 || ldb % 8 != 0)
     return set_error(SMB_ERR_INVALID, "plan: lda and ldb must be multiples of 8 elements");
@@ -83,6 +87,15 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
   L.ldd = static_cast<int>(ldd);
   L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
                 !(flags & SMB_FLAG_FORCE_PLAIN_STORE);
+  L.swiglu = swiglu;
+  if (swiglu) {
+    if (!L.tma_store) {
+      delete p;
+      return set_error(SMB_ERR_UNSUPPORTED,
+                       "plan: the gated epilogue needs a 16-byte-aligned D with ldd %% 8 == 0");
+    }
+    L.tile_n = 256;   // 64 output columns per store box = 128 accumulator columns per warp
+  }
   p->status_dev = nullptr;
 
   int rc = encode_tmap_2d(&L.tmap_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda * 2, 128, 64, true);
@@ -91,7 +104,7 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
                         L.tile_n / 2, 64, true);
   if (rc == SMB_OK) {
     if (L.tma_store) {
-      rc = encode_tmap_2d(&L.tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldd * 2, 32, 64, true);
+      rc = encode_tmap_2d(&L.tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, n_out, ldd * 2, 32, 64, true);
     } else {
       L.tmap_d = L.tmap_a;  // never dereferenced by the plain-store kernel
     }
@@ -133,7 +146,8 @@ extern "C" int smb_bf16_plan_tune(smb_bf16_plan* plan, int group_m, int max_clus
 extern "C" int smb_bf16_plan_set_peer_copies(smb_bf16_plan* plan, int count, void* const* dst,
                                              int64_t ld) {
   if (plan == nullptr) return set_error(SMB_ERR_INVALID, "plan: null handle");
-  return set_peer_copies(&plan->launch.peers, plan->launch.tma_store, count, dst, ld, plan->launch.N);
+  return set_peer_copies(&plan->launch.peers, plan->launch.tma_store, count, dst, ld,
+                         plan->launch.swiglu ? plan->launch.N / 2 : plan->launch.N);
 }
 
 extern "C" int smb_bf16_plan_set_profile(smb_bf16_plan* plan, long long* counters) {

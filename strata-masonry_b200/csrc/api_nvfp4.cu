@@ -39,7 +39,12 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
     return set_error(SMB_ERR_INVALID, "fp4 plan: dimensions must be positive (M=%d N=%d K=%d)", M, N, K);
   if (K % 32 != 0)
     return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: K=%d must be a multiple of 32 (one scale per 32 K)", K);
-  if (lda_bytes < K / 2 || ldb_bytes < K / 2 || ldd < N)
+  const bool swiglu = (flags & SMB_FLAG_EPILOGUE_SWIGLU) != 0;
+  if (swiglu && (N % 2 != 0 || M <= 128))
+    return set_error(SMB_ERR_UNSUPPORTED,
+                     "fp4 plan: the gated epilogue needs an even N and the tiled kernel (M > 128)");
+  const int n_out = swiglu ? N / 2 : N;
+  if (lda_bytes < K / 2 || ldb_bytes < K / 2 || ldd < n_out)
     return set_error(SMB_ERR_INVALID, "fp4 plan: leading dimension smaller than the row length");
   if (lda_bytes % 16 != 0 || ldb_bytes % 16 != 0)
     return set_error(SMB_ERR_INVALID, "fp4 plan: operand row pitches must be multiples of 16 bytes");
@@ -66,6 +71,16 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
   L.ldd = static_cast<int>(ldd);
   L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
                 !(flags & SMB_FLAG_FORCE_PLAIN_STORE);
+  L.swiglu = swiglu;
+  if (swiglu) {
+    if (!L.tma_store) {
+      delete p;
+      return set_error(SMB_ERR_UNSUPPORTED,
+                       "fp4 plan: the gated epilogue needs a 16-byte-aligned D with ldd %% 8 == 0");
+    }
+    L.w0 = 256;
+    L.w1 = 0;
+  }
   p->status_dev = nullptr;
   p->decode = (M <= 128) && !(flags & SMB_FLAG_NO_DECODE);
   p->scratch_dev = nullptr;
@@ -95,7 +110,7 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
                         kchunks * 512, tile_n / 128, 128, false);
   if (rc == SMB_OK) {
     if (L.tma_store)
-      rc = encode_tmap_2d(&L.tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldd * 2, 32, 64, true);
+      rc = encode_tmap_2d(&L.tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, n_out, ldd * 2, 32, 64, true);
     else
       L.tmap_d = L.tmap_a;
   }
@@ -115,6 +130,9 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
     D.max_stages = 0;
     D.no_overlap = (flags & SMB_FLAG_NO_LAUNCH_OVERLAP) != 0;
     D.activations_dynamic = false;
+    D.dual = fp4_decode_prefers_dual(M);
+    if (flags & SMB_FLAG_DECODE_DUAL) D.dual = true;
+    if (flags & SMB_FLAG_DECODE_SINGLE) D.dual = false;
     const int m_pad = (M + 15) / 16 * 16;
     rc = encode_tmap_2d(&D.tmap_w, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, ldb_bytes, 128, 128, true);
     if (rc == SMB_OK)
@@ -169,7 +187,8 @@ extern "C" int smb_fp4_plan_set_peer_copies(smb_fp4_plan* plan, int count, void*
   if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
   if (plan->decode && count != 0)
     return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: the decode kernel (M <= 128) has no peer copies");
-  return set_peer_copies(&plan->launch.peers, plan->launch.tma_store, count, dst, ld, plan->launch.N);
+  return set_peer_copies(&plan->launch.peers, plan->launch.tma_store, count, dst, ld,
+                         plan->launch.swiglu ? plan->launch.N / 2 : plan->launch.N);
 }
 
 extern "C" int smb_fp4_plan_set_profile(smb_fp4_plan* plan, long long* counters) {

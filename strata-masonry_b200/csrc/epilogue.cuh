@@ -34,25 +34,43 @@ struct StoreTarget {
 //   before any store is issued.
 //   Phase 2: 64-column boxes go through the warp's staging buffer `sbuf` (1024-byte aligned).
 // kTmaStore = false is the path for a D whose rows are not 16-byte aligned.
-template <int kCols, bool kTmaStore>
+//
+// kSwiglu: gated-activation epilogue (the reference's epi_warp_blackwell_*_bf16_swiglu,
+// blocks/93_epi_warp_blackwell.cuh:439-596, with composites/130_swiglu_act.cuh): B rows are
+// interleaved, even = up, odd = gate, so accumulator column 2n is up_n and 2n + 1 is gate_n;
+// the output is D[m, n] = bf16(silu(gate_n) * up_n), half as wide as the accumulator.  col0 is
+// then the accumulator column; out.N and the tensor map describe the [M, N/2] output.
+template <int kCols, bool kTmaStore, bool kSwiglu = false>
 __device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, const StoreTarget& out,
                                                 int row0, int col0, uint32_t release_bar, int lane) {
-  static_assert(kCols % kStoreCols == 0, "whole store boxes only");
-  uint32_t packed[kCols / 2];
+  constexpr int kOutCols = kSwiglu ? kCols / 2 : kCols;
+  static_assert(kOutCols % kStoreCols == 0, "whole store boxes only");
+  static_assert(!kSwiglu || kTmaStore, "the gated epilogue uses the aligned store path");
+  if (kSwiglu) col0 /= 2;
+  uint32_t packed[kOutCols / 2];
 #pragma unroll
   for (int g = 0; g < kCols / 32; ++g) {
     uint32_t v[32];
     tmem_ld_32x32b_x32(taddr + g * 32, v);
     tmem_ld_wait();
+    if (kSwiglu) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) packed[g * 16 + i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+      for (int i = 0; i < 8; ++i) {
+        const float o0 = swiglu_f32(__uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i]));
+        const float o1 = swiglu_f32(__uint_as_float(v[4 * i + 3]), __uint_as_float(v[4 * i + 2]));
+        packed[g * 8 + i] = pack_bf16x2(__float_as_uint(o0), __float_as_uint(o1));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) packed[g * 16 + i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+    }
   }
   tc_fence_before_sync();
   __syncwarp();
   if (lane == 0) mbar_arrive_cluster(release_bar);
 
 #pragma unroll
-  for (int c = 0; c < kCols / kStoreCols; ++c) {
+  for (int c = 0; c < kOutCols / kStoreCols; ++c) {
     // The TMA store that last read the staging buffer must have finished reading it.
     if (kTmaStore) {
       if (lane == 0) bulk_wait_group_read<0>();

@@ -38,6 +38,7 @@ constexpr int kThreads = 352;
 constexpr int kEpiWarps = 8;
 constexpr int kABytes = kBlockM * kBlockK * 2;        // 16 KiB
 constexpr int kTmemCols = 512;
+enum { kStorePlain = 0, kStoreTma = 1, kStoreSwiglu = 2 };   // epilogue variants
 constexpr int kRingBudget = 192 * 1024;
 
 template <int TN, int NB>
@@ -79,12 +80,15 @@ struct Params {
 enum { kProfLoadWait = 0, kProfLoadTotal, kProfMmaWaitFull, kProfMmaWaitAcc, kProfMmaTotal,
        kProfEpiWait, kProfEpiTotal, kProfTiles, kProfCount };
 
-template <int TN, int NB, bool kTmaStore>
+template <int TN, int NB, int kStore>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ Params p) {
   using C = Cfg<TN, NB>;
+  constexpr bool kTmaStore = (kStore != kStorePlain);
+  constexpr bool kSwiglu = (kStore == kStoreSwiglu);   // D is [M, N/2]: silu(gate) * up
+  static_assert(!kSwiglu || C::kColsPerWarp % 128 == 0, "gated epilogue: 64 output columns per box");
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -294,7 +298,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       out.d_ptr = p.d_ptr;
       out.ldd = p.ldd;
       out.M = p.M;
-      out.N = p.N;
+      out.N = kSwiglu ? p.N / 2 : p.N;
       out.peers = &p.peers;
       int local = 0;
       bool ok = true;
@@ -328,8 +332,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // Pull this warp's share of the slot out of tensor memory, hand the slot back to the MMA
         // role, then store.  With 256 x 512 tiles the main loop of the next tile cannot start
         // until the slot is handed back, so no store sits in front of that.
-        drain_and_store<C::kColsPerWarp, kTmaStore>(taddr, sbuf, out, row0, col0,
-                                                     leader_acc_empty0 + 8u * slot, lane);
+        drain_and_store<C::kColsPerWarp, kTmaStore, kSwiglu>(taddr, sbuf, out, row0, col0,
+                                                              leader_acc_empty0 + 8u * slot, lane);
       }
       drain_store_groups<kTmaStore>(lane);
       if (prof) {
@@ -356,10 +360,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // -----------------------------------------------------------------------------------
 namespace {
 
-template <int TN, int NB, bool kTmaStore>
+template <int TN, int NB, int kStore>
 int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
   using C = bf16k::Cfg<TN, NB>;
-  auto kernel = bf16k::gemm_bf16_kernel<TN, NB, kTmaStore>;
+  auto kernel = bf16k::gemm_bf16_kernel<TN, NB, kStore>;
   static thread_local int configured_device = -1;
   static thread_local int max_clusters = 0;
   int dev = 0;
@@ -429,7 +433,15 @@ int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
 
 template <int TN, int NB>
 int launch_bf16_store(const Bf16Launch& L, cudaStream_t stream) {
-  return L.tma_store ? launch_bf16<TN, NB, true>(L, stream) : launch_bf16<TN, NB, false>(L, stream);
+  if (L.swiglu) {
+    if constexpr (TN == 256) {
+      return launch_bf16<TN, NB, bf16k::kStoreSwiglu>(L, stream);
+    } else {
+      return set_error(SMB_ERR_UNSUPPORTED, "bf16: the gated epilogue needs 256-wide tiles");
+    }
+  }
+  return L.tma_store ? launch_bf16<TN, NB, bf16k::kStoreTma>(L, stream)
+                     : launch_bf16<TN, NB, bf16k::kStorePlain>(L, stream);
 }
 
 }  // namespace

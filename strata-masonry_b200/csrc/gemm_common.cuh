@@ -60,6 +60,7 @@ struct Bf16Launch {
   int tile_n;        // width of one N sub-block: 64, 128 or 256
   int sub_blocks;    // N sub-blocks per tile: 1, or 2 (256 x 512 tiles, tile_n = 256 only)
   bool tma_store;    // false: D rows are not 16-byte aligned, use plain stores
+  bool swiglu;       // gated epilogue: D is [M, N/2] = silu(acc[:, 1::2]) * acc[:, 0::2] (tma_store only)
   int group_m;       // raster group height (0 = default)
   int max_clusters;  // 0 = as many as fit
   void* d;
@@ -82,6 +83,7 @@ struct Fp4Launch {
   int M, N, K;
   int w0, w1;        // widths of the tile's N sub-blocks (w1 = 0: one sub-block)
   bool tma_store;
+  bool swiglu;       // gated epilogue (256-wide tiles only), as in Bf16Launch
   int group_m;
   int max_clusters;
   void* d;
@@ -113,8 +115,10 @@ struct Fp4DecodeLaunch {
   int max_stages;    // 0 = as many as fit
   bool no_overlap;   // true: plain stream order, no programmatic dependent launch
   bool activations_dynamic;  // X and its scales are written by the previous kernel on the stream
+  bool dual;         // two weight tiles per activation box (whole tile pairs; ignored with max_ctas > 0)
 };
 int fp4_decode_stage_bytes(int m_pad);
+bool fp4_decode_prefers_dual(int M);   // default choice of Fp4DecodeLaunch::dual for M activation rows
 size_t fp4_decode_slot_bytes(int M);                       // one fp32 partial tile
 size_t fp4_decode_scratch_bytes(int M, int N, int ctas);   // slots for `ctas` CTAs + tile counters
 int fp4_decode_box_rows(int M);

@@ -39,6 +39,7 @@ constexpr int kEpiWarps = 8;
 constexpr int kABytes = kBlockM * kBlockKBytes;   // 16 KiB
 constexpr int kSfCellBytes = 512;     // 128 rows x 4 scale bytes (K = 128)
 constexpr int kTmemCols = 512;
+enum { kStorePlain = 0, kStoreTma = 1, kStoreSwiglu = 2 };   // epilogue variants
 constexpr int kRingBudget = 192 * 1024;
 
 template <int W0, int W1>
@@ -93,7 +94,7 @@ struct Params {
 enum { kProfLoadWait = 0, kProfLoadTotal, kProfMmaWaitFull, kProfMmaWaitAcc, kProfMmaTotal,
        kProfEpiWait, kProfEpiTotal, kProfTiles, kProfCount };
 
-template <int W0, int W1, bool kTmaStore>
+template <int W0, int W1, int kStore>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b0,
@@ -102,6 +103,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_sfb,
                   const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ Params p) {
   using C = Cfg<W0, W1>;
+  constexpr bool kTmaStore = (kStore != kStorePlain);
+  constexpr bool kSwiglu = (kStore == kStoreSwiglu);   // D is [M, N/2]: silu(gate) * up
+  static_assert(!kSwiglu || C::kColsPerWarp % 128 == 0, "gated epilogue: 64 output columns per box");
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -401,7 +405,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     out.d_ptr = p.d_ptr;
     out.ldd = p.ldd;
     out.M = p.M;
-    out.N = p.N;
+    out.N = kSwiglu ? p.N / 2 : p.N;
     out.peers = &p.peers;
     int local = 0;
     bool ok = true;
@@ -429,8 +433,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int col0 = tn * C::kTileN + tile_col;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(bank * 128 + tile_col);
-      drain_and_store<C::kColsPerWarp, kTmaStore>(taddr, sbuf, out, row0, col0,
-                                                   leader_acc_empty0 + 8u * bank, lane);
+      drain_and_store<C::kColsPerWarp, kTmaStore, kSwiglu>(taddr, sbuf, out, row0, col0,
+                                                            leader_acc_empty0 + 8u * bank, lane);
     }
     drain_store_groups<kTmaStore>(lane);
     if (prof) {
@@ -456,10 +460,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // -----------------------------------------------------------------------------------
 namespace {
 
-template <int W0, int W1, bool kTmaStore>
+template <int W0, int W1, int kStore>
 int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   using C = fp4k::Cfg<W0, W1>;
-  auto kernel = fp4k::gemm_nvfp4_kernel<W0, W1, kTmaStore>;
+  auto kernel = fp4k::gemm_nvfp4_kernel<W0, W1, kStore>;
   static thread_local int configured_device = -1;
   static thread_local int max_clusters = 0;
   int dev = 0;
@@ -527,7 +531,15 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
 
 template <int W0, int W1>
 int launch_fp4_store(const Fp4Launch& L, cudaStream_t stream) {
-  return L.tma_store ? launch_fp4<W0, W1, true>(L, stream) : launch_fp4<W0, W1, false>(L, stream);
+  if (L.swiglu) {
+    if constexpr (W0 == 256 && W1 == 0) {
+      return launch_fp4<W0, W1, fp4k::kStoreSwiglu>(L, stream);
+    } else {
+      return set_error(SMB_ERR_UNSUPPORTED, "nvfp4: the gated epilogue needs 256-wide tiles");
+    }
+  }
+  return L.tma_store ? launch_fp4<W0, W1, fp4k::kStoreTma>(L, stream)
+                     : launch_fp4<W0, W1, fp4k::kStorePlain>(L, stream);
 }
 
 }  // namespace

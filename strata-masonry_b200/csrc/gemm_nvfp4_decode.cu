@@ -35,6 +35,7 @@ constexpr int kSfBytes = 1024;        // one 128-row band x 8 scales (two 512-by
 constexpr int kSlotCols = 16;         // SFW cells (8 columns) + SFX cells (8 columns) per stage
 constexpr int kMaxStages = 16;
 constexpr int kDefaultStages = 6;
+constexpr int kDualFromPad = 64;      // padded activation rows from which two tiles share one activation box
 constexpr int kWholeTileStages = 8;
 constexpr int kMaxPad = 128;         // activation rows, padded
 constexpr int kStageRows = 64;       // activation rows of D staged in shared memory per TMA store
@@ -534,6 +535,322 @@ gemm_nvfp4_decode_kernel_capped(const __grid_constant__ CUtensorMap tmap_w,
   decode_body(tmap_w, tmap_x, tmap_sfw, tmap_sfx, tmap_d, p);
 }
 
+
+// -----------------------------------------------------------------------------------
+// Dual-tile form: one CTA multiplies TWO adjacent weight tiles per K block against one copy of the
+// activations.  At M = 128 the activation box of a stage is as large as a weight box, and loaded
+// once per weight tile it made the kernel L2 -> SM bound (250 MB per launch through that path at
+// 112 CTAs, 100 GB/s per SM, for 125 MB of HBM traffic); loaded once per tile PAIR it is a third of
+// the stage.  Whole tile pairs only: CTA b owns the pairs [b t, (b+1) t), nothing is shared between
+// CTAs, so there is no scratch and no hand-over.  Roles as in the single form.
+//   stage:  [W tile 0 16 KiB][W tile 1 16 KiB][X m_pad x 128 B][SFW0 1 KiB][SFW1 1 KiB][SFX 1 KiB]
+//   TMEM :  banks of 2 x m_pad accumulator columns (two banks when they fit beside the scale
+//           slots, else one), then per stage 24 scale columns (SFW0 | SFW1 | SFX).
+// -----------------------------------------------------------------------------------
+struct DualParams {
+  int M, N, K;
+  int m_pad;
+  int stages;
+  int stage_bytes;
+  int banks;            // 1 or 2 accumulator banks of 2 * m_pad columns
+  int pairs_per_cta;
+  int ldd;
+  uint16_t* d;
+  int* status;
+  int d_tma;
+  int activations_dynamic;
+};
+
+constexpr int kDualSlotCols = 24;
+
+__device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x,
+                                                 const CUtensorMap& tmap_sfw, const CUtensorMap& tmap_sfx,
+                                                 const CUtensorMap& tmap_d, const DualParams& p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int stages = p.stages;
+  const uint32_t ring_base = smem_base;
+  const uint32_t stage_base = ring_base + static_cast<uint32_t>(stages * p.stage_bytes);   // D staging
+  const int chunk_rows = p.m_pad < kStageRows ? p.m_pad : kStageRows;
+  const uint32_t bar_base = stage_base + static_cast<uint32_t>(chunk_rows * 256);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+  auto sf_full_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + s); };
+  auto sf_ready_bar = [&](int s) { return bar_base + 8u * (3 * kMaxStages + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (4 * kMaxStages + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (4 * kMaxStages + 2 + b); };
+  const uint32_t tmem_slot = bar_base + 8u * (4 * kMaxStages + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+  const int tiles = (p.N + 127) / 128;
+  const int pairs = (tiles + 1) / 2;
+  const int q_begin = min(static_cast<int>(blockIdx.x) * p.pairs_per_cta, pairs);
+  const int q_end = min(q_begin + p.pairs_per_cta, pairs);
+  const uint32_t w1_off = kWBytes;
+  const uint32_t x_off = 2 * kWBytes;
+  const uint32_t sfw0_off = x_off + static_cast<uint32_t>(p.m_pad) * kBlockKBytes;
+  const uint32_t sfw1_off = sfw0_off + kSfBytes;
+  const uint32_t sfx_off = sfw1_off + kSfBytes;
+  const uint32_t bank_cols = 2u * static_cast<uint32_t>(p.m_pad);
+  const uint32_t slot_base = static_cast<uint32_t>(p.banks) * bank_cols;
+
+  griddep_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(sf_full_bar(s), 1);
+      mbar_init(sf_ready_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 4);
+    }
+    fence_mbar_init_cluster();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+    tma_prefetch_desc(&tmap_sfw);
+    tma_prefetch_desc(&tmap_sfx);
+    if (p.d_tma) tma_prefetch_desc(&tmap_d);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(tmem_slot, 512);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    const uint64_t stream_once = l2_policy_evict_first();
+    const uint64_t keep = l2_policy_evict_last();
+    const uint32_t op_bytes = 2 * kWBytes + static_cast<uint32_t>(p.m_pad) * kBlockKBytes;
+    int s = 0;
+    uint32_t ph = 0;
+    bool waited = !p.activations_dynamic;
+    int issued = 0;
+    for (int q = q_begin; q < q_end; ++q) {
+      for (int kb = 0; kb < num_kb; ++kb, ++issued) {
+        // Activations written by the kernel launched just before this one (the quantiser): the
+        // first ring of weight boxes goes out before the wait, the activation boxes after it.
+        if (!waited && issued == stages) {
+          griddep_wait();
+          waited = true;
+          for (int j = 0; j < stages; ++j) {
+            const int kbj = (j) % num_kb;
+            const uint32_t dstj = ring_base + static_cast<uint32_t>(j * p.stage_bytes);
+            if (elect_one()) {
+              tma_load_2d_cta_hint(dstj + sfx_off, &tmap_sfx, sf_full_bar(j), kbj * 128, 0, keep);
+              tma_load_2d_cta_hint(dstj + x_off, &tmap_x, full_bar(j), kbj * kBlockKBytes, 0, keep);
+            }
+            __syncwarp();
+          }
+        }
+        if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
+          report_status(p.status, kDevTimeoutProducer);
+          for (int i = 0; i < 64; ++i) __nanosleep(1000);
+          q = q_end;
+          break;
+        }
+        const uint32_t dst = ring_base + static_cast<uint32_t>(s * p.stage_bytes);
+        if (elect_one()) {
+          mbar_arrive_expect_tx(sf_full_bar(s), 3 * kSfBytes);
+          tma_load_2d_cta_hint(dst + sfw0_off, &tmap_sfw, sf_full_bar(s), kb * 128, 2 * q, stream_once);
+          tma_load_2d_cta_hint(dst + sfw1_off, &tmap_sfw, sf_full_bar(s), kb * 128, 2 * q + 1, stream_once);
+          mbar_arrive_expect_tx(full_bar(s), op_bytes);
+          tma_load_2d_cta_hint(dst, &tmap_w, full_bar(s), kb * kBlockKBytes, (2 * q) * 128, stream_once);
+          tma_load_2d_cta_hint(dst + w1_off, &tmap_w, full_bar(s), kb * kBlockKBytes, (2 * q + 1) * 128,
+                               stream_once);
+          if (waited) {
+            tma_load_2d_cta_hint(dst + sfx_off, &tmap_sfx, sf_full_bar(s), kb * 128, 0, keep);
+            tma_load_2d_cta_hint(dst + x_off, &tmap_x, full_bar(s), kb * kBlockKBytes, 0, keep);
+          }
+        }
+        __syncwarp();
+        if (++s == stages) { s = 0; ph ^= 1u; }
+      }
+    }
+    if (!waited) {
+      // Fewer units than ring slots: the activation boxes of everything issued are still owed.
+      griddep_wait();
+      for (int j = 0; j < issued; ++j) {
+        const int kbj = j % num_kb;
+        const uint32_t dstj = ring_base + static_cast<uint32_t>(j * p.stage_bytes);
+        if (elect_one()) {
+          tma_load_2d_cta_hint(dstj + sfx_off, &tmap_sfx, sf_full_bar(j), kbj * 128, 0, keep);
+          tma_load_2d_cta_hint(dstj + x_off, &tmap_x, full_bar(j), kbj * kBlockKBytes, 0, keep);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issue
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    int seg = 0;
+    for (int q = q_begin; q < q_end && ok; ++q, ++seg) {
+      const int bank = p.banks == 2 ? (seg & 1) : 0;
+      const uint32_t use = static_cast<uint32_t>(p.banks == 2 ? (seg >> 1) : seg) & 1u;
+      if (!mbar_wait(acc_empty_bar(bank), use ^ 1u)) {
+        report_status(p.status, kDevTimeoutMmaAcc);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t acc0 = tmem_base + static_cast<uint32_t>(bank) * bank_cols;
+      const uint32_t acc1 = acc0 + static_cast<uint32_t>(p.m_pad);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(full_bar(s), ph) || !mbar_wait(sf_ready_bar(s), ph)) {
+          report_status(p.status, kDevTimeoutMmaFull);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t stage = ring_base + static_cast<uint32_t>(s * p.stage_bytes);
+        const uint32_t sf_t = tmem_base + slot_base + static_cast<uint32_t>(s * kDualSlotCols);
+        const uint64_t desc_w0 = make_smem_desc(stage, 1024, 16, kSwizzle128B);
+        const uint64_t desc_w1 = make_smem_desc(stage + w1_off, 1024, 16, kSwizzle128B);
+        const uint64_t desc_x = make_smem_desc(stage + x_off, 1024, 16, kSwizzle128B);
+        if (elect_one()) {
+#pragma unroll
+          for (int ki = 0; ki < 4; ++ki) {
+            const uint32_t sf_id = (ki & 1) ? 2u : 0u;
+            const uint32_t cell = static_cast<uint32_t>(ki >> 1);
+            const uint32_t idesc = make_idesc_mxf4(128, p.m_pad, sf_id, sf_id, true);
+            const uint32_t accum = (kb > 0 || ki > 0) ? 1u : 0u;
+            mma_mxf4_ss<1>(acc0, desc_w0 + 2u * ki, desc_x + 2u * ki, idesc, sf_t + 4u * cell,
+                           sf_t + 16u + 4u * cell, accum);
+            mma_mxf4_ss<1>(acc1, desc_w1 + 2u * ki, desc_x + 2u * ki, idesc, sf_t + 8u + 4u * cell,
+                           sf_t + 16u + 4u * cell, accum);
+          }
+          mma_commit_1cta(empty_bar(s));
+        }
+        __syncwarp();
+        if (++s == stages) { s = 0; ph ^= 1u; }
+      }
+      if (ok && elect_one()) mma_commit_1cta(acc_full_bar(bank));
+      __syncwarp();
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------- scale copies
+    int s = 0;
+    uint32_t ph = 0;
+    const int total = (q_end - q_begin) * num_kb;
+    for (int i = 0; i < total; ++i) {
+      if (!mbar_wait(sf_full_bar(s), ph)) {
+        report_status(p.status, kDevTimeoutSched);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t stage = ring_base + static_cast<uint32_t>(s * p.stage_bytes);
+      const uint32_t sf_t = tmem_base + slot_base + static_cast<uint32_t>(s * kDualSlotCols);
+      const uint64_t d0 = make_smem_desc(stage + sfw0_off, 128, 16, kSwizzleNone);
+      const uint64_t d1 = make_smem_desc(stage + sfw1_off, 128, 16, kSwizzleNone);
+      const uint64_t dx = make_smem_desc(stage + sfx_off, 128, 16, kSwizzleNone);
+      if (elect_one()) {
+#pragma unroll
+        for (int cell = 0; cell < 2; ++cell) {
+          tmem_cp_32x128b_warpx4<1>(sf_t + 4u * cell, d0 + cell * 32);
+          tmem_cp_32x128b_warpx4<1>(sf_t + 8u + 4u * cell, d1 + cell * 32);
+          tmem_cp_32x128b_warpx4<1>(sf_t + 16u + 4u * cell, dx + cell * 32);
+        }
+        mma_commit_1cta(sf_ready_bar(s));
+      }
+      __syncwarp();
+      if (++s == stages) { s = 0; ph ^= 1u; }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------- epilogue (4 warps)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const bool first_thread = (threadIdx.x == 128);
+    bool store_pending = false;
+    bool waited_for_previous_grid = false;
+    int seg = 0;
+    for (int q = q_begin; q < q_end; ++q, ++seg) {
+      const int bank = p.banks == 2 ? (seg & 1) : 0;
+      const uint32_t use = static_cast<uint32_t>(p.banks == 2 ? (seg >> 1) : seg) & 1u;
+      if (!mbar_wait(acc_full_bar(bank), use)) {
+        if (lane == 0) report_status(p.status, kDevTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after_sync();
+      if (!waited_for_previous_grid) {
+        griddep_wait();   // first store to D
+        waited_for_previous_grid = true;
+      }
+      for (int sub = 0; sub < 2; ++sub) {
+        const int tile = 2 * q + sub;
+        if (tile >= tiles) break;
+        const int n = tile * 128 + row;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                               static_cast<uint32_t>(bank) * bank_cols + static_cast<uint32_t>(sub * p.m_pad);
+        if (p.d_tma) {
+          for (int c0 = 0; c0 < p.m_pad; c0 += chunk_rows) {
+            if (first_thread && store_pending) bulk_wait_group_read<0>();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            for (int c = c0; c < c0 + chunk_rows && c < p.m_pad; c += 16) {
+              float v[16];
+              ld16(taddr + c, v);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const uint32_t dst = stage_base + static_cast<uint32_t>((c - c0 + j) * 256 + row * 2);
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst), "h"(to_bf16(v[j])) : "memory");
+              }
+            }
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (first_thread) {
+              tma_store_2d(&tmap_d, stage_base, tile * 128, c0);
+              bulk_commit_group();
+              store_pending = true;
+            }
+          }
+        } else {
+          for (int c = 0; c < p.m_pad; c += 16) {
+            float v[16];
+            ld16(taddr + c, v);
+            if (n < p.N) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (c + j < p.M) p.d[static_cast<size_t>(c + j) * p.ldd + n] = to_bf16(v[j]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(bank));
+    }
+    if (first_thread && store_pending) bulk_wait_group_read<0>();
+  }
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<1>(tmem_base, 512);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_nvfp4_decode_dual_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                              const __grid_constant__ CUtensorMap tmap_x,
+                              const __grid_constant__ CUtensorMap tmap_sfw,
+                              const __grid_constant__ CUtensorMap tmap_sfx,
+                              const __grid_constant__ CUtensorMap tmap_d,
+                              const __grid_constant__ DualParams p) {
+  decode_dual_body(tmap_w, tmap_x, tmap_sfw, tmap_sfx, tmap_d, p);
+}
+
 }  // namespace fp4d
 
 int fp4_decode_stage_bytes(int m_pad) { return fp4d::kWBytes + m_pad * fp4d::kBlockKBytes + 2 * fp4d::kSfBytes; }
@@ -549,7 +866,71 @@ int fp4_decode_box_rows(int M) {
   return m_pad < fp4d::kStageRows ? m_pad : fp4d::kStageRows;
 }
 
+namespace {
+
+int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
+  static thread_local int configured_device = -1;
+  static thread_local int sm_count = 0;
+  constexpr int kSmemBudget = 227 * 1024;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return set_error(SMB_ERR_CUDA, "cudaGetDevice failed");
+  if (configured_device != dev) {
+    cudaError_t e = cudaFuncSetAttribute(fp4d::gemm_nvfp4_decode_dual_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return set_cuda_error(e, "decode (dual) kernel setup");
+    configured_device = dev;
+  }
+  fp4d::DualParams p;
+  p.M = L.M;
+  p.N = L.N;
+  p.K = L.K;
+  p.m_pad = (L.M + 15) / 16 * 16;
+  p.stage_bytes = 2 * fp4d::kWBytes + p.m_pad * fp4d::kBlockKBytes + 3 * fp4d::kSfBytes;
+  const int staging = fp4_decode_box_rows(L.M) * 256;
+  int stages = (kSmemBudget - 1024 - fp4d::kBarrierBytes - staging) / p.stage_bytes;
+  if (stages > fp4d::kMaxStages) stages = fp4d::kMaxStages;
+  // Two accumulator banks (a tile pair is drained while the next one is multiplied) when they fit
+  // beside at least three scale slots, else one.
+  p.banks = (4 * p.m_pad + 3 * fp4d::kDualSlotCols <= 512) ? 2 : 1;
+  const int max_slots = (512 - p.banks * 2 * p.m_pad) / fp4d::kDualSlotCols;
+  if (stages > max_slots) stages = max_slots;
+  if (L.max_stages > 0 && stages > L.max_stages) stages = L.max_stages;
+  if (stages < 2) return set_error(SMB_ERR_UNSUPPORTED, "decode (dual): activation tile too large");
+  p.stages = stages;
+  p.ldd = L.ldd;
+  p.d = static_cast<uint16_t*>(L.d);
+  p.status = L.status;
+  p.d_tma = L.d_tma ? 1 : 0;
+  p.activations_dynamic = L.activations_dynamic ? 1 : 0;
+  const int pairs = ((L.N + 127) / 128 + 1) / 2;
+  p.pairs_per_cta = (pairs + sm_count - 1) / sm_count;
+  const int grid = (pairs + p.pairs_per_cta - 1) / p.pairs_per_cta;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(fp4d::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = 1024 + stages * p.stage_bytes + staging + fp4d::kBarrierBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = L.no_overlap ? 0 : 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, fp4d::gemm_nvfp4_decode_dual_kernel, L.tmap_w, L.tmap_x,
+                                     L.tmap_sfw, L.tmap_sfx, L.tmap_d, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return set_cuda_error(e, "nvfp4 decode (dual) launch");
+  return SMB_OK;
+}
+
+}  // namespace
+
+bool fp4_decode_prefers_dual(int M) { return (M + 15) / 16 * 16 >= fp4d::kDualFromPad; }
+
 int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
+  // The dual-tile form has whole tile pairs only: a caller that asks for a CTA count gets the
+  // stream-K ranges of the single form.
+  if (L.dual && L.max_ctas == 0) return fp4_decode_dual_launch(L, stream);
   static thread_local int configured_device = -1;
   static thread_local int sm_count = 0;
   constexpr int kSmemBudget = 227 * 1024;
@@ -725,6 +1106,7 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
   L.max_ctas = 0;
   L.max_stages = 0;
   L.activations_dynamic = false;
+  L.dual = fp4_decode_prefers_dual(M);
   L.no_overlap = true;   // the memset below must be ordered before every access of this launch
   L.scratch = static_cast<float*>(base);
   L.scratch_ctas = ctas;

@@ -438,6 +438,16 @@ __device__ __forceinline__ uint32_t pack_bf16x2(uint32_t lo_f32_bits, uint32_t h
   return out;
 }
 
+// silu(gate) * up with silu(z) = 0.5 z (1 + tanh(z / 2)) on the hardware tanh approximation: the
+// form of the reference's gated epilogue (composites/130_swiglu_act.cuh:33-50); finite for all
+// finite inputs.
+__device__ __forceinline__ float swiglu_f32(float gate, float up) {
+  const float half_z = 0.5f * gate;
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(half_z));
+  return __fmaf_rn(half_z, t, half_z) * up;
+}
+
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
                                              uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)

@@ -573,3 +573,89 @@ def test_independent_launches_run_side_by_side(smb, oracle, cuda_device, kind):
     assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
     for p in plans:
         p.close()
+
+
+# ------------------------------------------------------------------------------- gated epilogue
+def _check_swiglu(oracle, acc64, d, k):
+    ref = oracle.swiglu(acc64)
+    bound = oracle.swiglu_bound(acc64, k)
+    got = d.double().cpu().numpy()
+    assert got.shape == ref.shape
+    bad = ~np.isfinite(got) | (np.abs(got - ref) > bound)
+    assert int(bad.sum()) == 0, f"{int(bad.sum())} of {bad.size} outside the bound; worst {np.max(np.abs(got - ref) / bound):.2f}"
+
+
+@pytest.mark.parametrize("shape_flags", [((512, 512, 256), "FLAG_NONE"), ((1024, 1024, 512), "FLAG_TILE_N_512"),
+                                         ((300, 200, 72), "FLAG_NONE"), ((2048, 4096, 1024), "FLAG_NONE"),
+                                         ((256, 66, 64), "FLAG_TILE_N_256")])
+def test_bf16_gated_epilogue(smb, oracle, cuda_device, shape_flags):
+    """FLAG_EPILOGUE_SWIGLU: D[m, n] = bf16(silu(acc[m, 2n+1]) * acc[m, 2n]) against the float64
+    definition; D is [M, N/2] with a padded pitch, nothing outside it is written."""
+    torch = _torch()
+    (m, n, k), name = shape_flags
+    a = torch.empty(m, k, device=cuda_device, dtype=torch.bfloat16)
+    bt = torch.empty(n, k, device=cuda_device, dtype=torch.bfloat16)
+    smb.gemm.bf16_operands_device(a, bt, m, n, k, 7)          # N(0,1): gates of both signs, |z| up to ~30
+    n_out = n // 2
+    ldd = (n_out + 7) // 8 * 8 + 8
+    d = torch.full((m, ldd), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    flags = smb.capi.FLAG_EPILOGUE_SWIGLU | getattr(smb.capi, name)
+    plan = smb.gemm.Bf16Plan(a, bt, d, m, n, k, ldd=ldd, flags=flags)
+    plan.run(); plan.run(); plan.check(); plan.close()
+    acc = (a.double() @ bt.double().t()).cpu().numpy()
+    _check_swiglu(oracle, acc, d[:, :n_out], k)
+    assert bool(torch.isnan(d[:, n_out:]).all())
+
+
+def test_fp4_gated_epilogue(smb, oracle, cuda_device):
+    torch = _torch()
+    m, n, k = 768, 1024, 512
+    a, sfa, sfar = _fp4_operand(smb, m, k, 5, 0)
+    b, sfb, sfbr = _fp4_operand(smb, n, k, 5, 1)
+    d = torch.full((m, n // 2), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k, ldd=n // 2, flags=smb.capi.FLAG_EPILOGUE_SWIGLU)
+    plan.run(); plan.check(); plan.close()
+    acc = (_dequant(a, sfar) @ _dequant(b, sfbr).t()).cpu().numpy()
+    _check_swiglu(oracle, acc, d, k)
+
+
+def test_gated_epilogue_is_refused_where_it_cannot_work(smb, cuda_device):
+    torch = _torch()
+    capi = smb.capi
+    a = torch.zeros(256, 64, device=cuda_device, dtype=torch.bfloat16)
+    bt = torch.zeros(130, 64, device=cuda_device, dtype=torch.bfloat16)
+    d = torch.zeros(256, 72, device=cuda_device, dtype=torch.bfloat16)
+    with pytest.raises(capi.SmbError):       # odd N
+        smb.gemm.Bf16Plan(a, bt, d, 256, 129, 64, ldd=72, flags=capi.FLAG_EPILOGUE_SWIGLU)
+    with pytest.raises(capi.SmbError):       # pitch not a multiple of 8 elements
+        smb.gemm.Bf16Plan(a, bt, d, 256, 130, 64, ldd=70, flags=capi.FLAG_EPILOGUE_SWIGLU)
+    with pytest.raises(capi.SmbError):       # pitch shorter than N/2
+        smb.gemm.Bf16Plan(a, bt, d, 256, 130, 64, ldd=64, flags=capi.FLAG_EPILOGUE_SWIGLU)
+    xa, xsfa, _ = _fp4_operand(smb, 16, 256, 6, 0)
+    w, wsf, _ = _fp4_operand(smb, 256, 256, 5, 1)
+    dd = torch.zeros(16, 128, device=cuda_device, dtype=torch.bfloat16)
+    with pytest.raises(capi.SmbError):       # decode shapes have no gated epilogue
+        smb.gemm.Fp4Plan(xa, xsfa, w, wsf, dd, 16, 256, 256, ldd=128, flags=capi.FLAG_EPILOGUE_SWIGLU)
+
+
+@pytest.mark.parametrize("form", ["FLAG_DECODE_DUAL", "FLAG_DECODE_SINGLE"])
+@pytest.mark.parametrize("shape", [(16, 256, 512), (1, 384, 256), (100, 1100, 1056), (128, 4096, 4096),
+                                   (64, 28672, 8192), (33, 130, 96), (128, 28672 + 128, 2048), (128, 300 * 128, 512)])
+def test_fp4_decode_both_forms(smb, cuda_device, shape, form):
+    """The two forms of the decode kernel (one weight tile per activation box; two adjacent weight
+    tiles sharing it) on the same shapes: even and odd tile counts, more tile pairs than SMs,
+    ragged M and N, several K; two runs per plan, bit-identical."""
+    torch = _torch()
+    m, n, k = shape
+    A, B, outs = _run_fp4_decode(smb, m, n, k, flags=getattr(smb.capi, form), runs=2)
+    _check_fp4_full(A, B, outs[0], k)
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+
+
+def test_fp4_decode_forms_agree_bit_for_bit(smb, cuda_device):
+    """Whole tiles in both forms: the same fp32 accumulation order, so the same bits."""
+    torch = _torch()
+    for m in (16, 128):
+        _, _, single = _run_fp4_decode(smb, m, 28672, 8192, flags=smb.capi.FLAG_DECODE_SINGLE)
+        _, _, dual = _run_fp4_decode(smb, m, 28672, 8192, flags=smb.capi.FLAG_DECODE_DUAL)
+        assert torch.equal(single[0].view(torch.int16), dual[0].view(torch.int16))

@@ -198,3 +198,16 @@ def test_tile_raster_is_a_permutation(oracle):
         seen = {oracle.tile_coords(t, tiles_m, tiles_n, gm) for t in range(tiles_m * tiles_n)}
         assert len(seen) == tiles_m * tiles_n
         assert all(0 <= m < tiles_m and 0 <= n < tiles_n for m, n in seen)
+
+
+def test_swiglu_definition(oracle):
+    acc = np.array([[2.0, 0.0, -3.0, 1.0, 0.5, 40.0, 7.0, -40.0]])
+    out = oracle.swiglu(acc)
+    # up = (2, -3, 0.5, 7), gate = (0, 1, 40, -40)
+    want = np.array([[0.0, -3.0 / (1.0 + np.exp(-1.0)), 0.5 * 40.0, 7.0 * -40.0 / (1.0 + np.exp(40.0))]])
+    np.testing.assert_allclose(out, want, rtol=1e-12, atol=1e-300)
+    assert out.shape == (1, 4)
+    # The tanh form the device uses is the same function.
+    z = np.linspace(-20, 20, 4001)
+    np.testing.assert_allclose(0.5 * z * (1 + np.tanh(z / 2)), z / (1 + np.exp(-z)), rtol=1e-12, atol=1e-15)
+    assert np.all(oracle.swiglu_bound(acc, 64) > 0)
