@@ -112,6 +112,10 @@ uint64_t smb_debug_sf_offset(uint32_t row, uint32_t kblock, uint32_t kblocks);
  * A is row-major [M,K] (lda elements between rows), BT row-major [N,K] (ldb), D row-major
  * [M,N] (ldd).  Any M, N >= 1; K >= 8 and K % 8 == 0 (rows of A and BT must start on
  * 16-byte boundaries: lda % 8 == 0, ldb % 8 == 0, base pointers 16-byte aligned).
+ * A D that is 16-byte aligned with ldd % 8 == 0 is written in whole 16-byte chunks: when the
+ * row length is not a multiple of 8 elements, the row's padding up to the next multiple of 8
+ * (always inside the pitch) is overwritten too.  Any other D is written element by element.
+ * The same holds for the FP4 GEMM.
  * ---------------------------------------------------------------------------------- */
 typedef struct smb_bf16_plan smb_bf16_plan;
 
@@ -285,7 +289,7 @@ int smb_unshard_columns_device(const void* gathered, void* d, int g, int M, int 
 #define SMB_FLAG_NO_DECODE 64u        /* FP4 only: M <= 128 through the tiled kernel, not the decode kernel */
 #define SMB_FLAG_NO_LAUNCH_OVERLAP 128u /* decode kernel: no programmatic dependent launch */
 /* Decode kernel (FP4, M <= 128): force the form in which a CTA multiplies two adjacent weight
- * tiles against one copy of the activations (default from 64 padded activation rows up), or the
+ * tiles against one copy of the activations (the default), or the
  * form with one weight tile per activation box. */
 #define SMB_FLAG_DECODE_DUAL 512u
 #define SMB_FLAG_DECODE_SINGLE 2048u

@@ -168,7 +168,7 @@ __global__ void quantize_mx_kernel(const float* src, int64_t ld_src, uint8_t* da
 // programmatic stream serialisation in front of a GEMM; lets the GEMM start its weight loads at
 // once and itself waits for the previous kernel on the stream (which may still read the codes
 // and scales this kernel overwrites) before it writes anything.
-__global__ void __maxnreg__(48) quantize_mx_bf16_kernel(const uint16_t* src, int64_t ld_src, uint8_t* data,
+__global__ void quantize_mx_bf16_kernel(const uint16_t* src, int64_t ld_src, uint8_t* data,
                                         int64_t ld_bytes, uint8_t* sf_packed, uint8_t* sf_rowmajor,
                                         int64_t rows, uint32_t K, int chained) {
   if (chained) {

@@ -35,12 +35,11 @@ constexpr int kSfBytes = 1024;        // one 128-row band x 8 scales (two 512-by
 constexpr int kSlotCols = 16;         // SFW cells (8 columns) + SFX cells (8 columns) per stage
 constexpr int kMaxStages = 16;
 constexpr int kDefaultStages = 6;
-constexpr int kDualFromPad = 64;      // padded activation rows from which two tiles share one activation box
+constexpr int kDualFromPad = 16;      // padded activation rows from which two tiles share one activation box
 constexpr int kWholeTileStages = 8;
 constexpr int kMaxPad = 128;         // activation rows, padded
 constexpr int kStageRows = 64;       // activation rows of D staged in shared memory per TMA store
 constexpr int kBarrierBytes = 1024;
-constexpr int kMaxRegs = 200;
 
 struct Params {
   int M, N, K;
@@ -519,23 +518,6 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
   decode_body(tmap_w, tmap_x, tmap_sfw, tmap_sfx, tmap_d, p);
 }
 
-// The same kernel with registers capped, launched when the activation quantiser is chained in
-// front (activations_dynamic): the quantiser of the NEXT decode step is resident, waiting for
-// this grid, while this grid runs, and one of its blocks (256 threads x 48 registers) must fit
-// on an SM beside a CTA of this kernel; uncapped (240 registers) it kept the next GEMM's CTAs
-// off the SMs it sat on until it had run.  The cap costs the main loop about 1 us per launch,
-// so plans with resident activations use the uncapped kernel.
-__global__ void __maxnreg__(kMaxRegs)
-gemm_nvfp4_decode_kernel_capped(const __grid_constant__ CUtensorMap tmap_w,
-                                const __grid_constant__ CUtensorMap tmap_x,
-                                const __grid_constant__ CUtensorMap tmap_sfw,
-                                const __grid_constant__ CUtensorMap tmap_sfx,
-                                const __grid_constant__ CUtensorMap tmap_d,
-                                const __grid_constant__ Params p) {
-  decode_body(tmap_w, tmap_x, tmap_sfw, tmap_sfx, tmap_d, p);
-}
-
-
 // -----------------------------------------------------------------------------------
 // Dual-tile form: one CTA multiplies TWO adjacent weight tiles per K block against one copy of the
 // activations.  At M = 128 the activation box of a stage is as large as a weight box, and loaded
@@ -939,9 +921,6 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   if (configured_device != dev) {
     cudaError_t e = cudaFuncSetAttribute(fp4d::gemm_nvfp4_decode_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(fp4d::gemm_nvfp4_decode_kernel_capped,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e != cudaSuccess) return set_cuda_error(e, "cudaFuncSetAttribute(decode smem)");
     e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return set_cuda_error(e, "cudaDeviceGetAttribute(SM count)");
@@ -1006,9 +985,8 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   attr.val.programmaticStreamSerializationAllowed = L.no_overlap ? 0 : 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, L.activations_dynamic ? fp4d::gemm_nvfp4_decode_kernel_capped
-                                                                 : fp4d::gemm_nvfp4_decode_kernel,
-                                     L.tmap_w, L.tmap_x, L.tmap_sfw, L.tmap_sfx, L.tmap_d, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, fp4d::gemm_nvfp4_decode_kernel, L.tmap_w, L.tmap_x, L.tmap_sfw,
+                                     L.tmap_sfx, L.tmap_d, p);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error(e, "nvfp4 decode launch");
   return SMB_OK;

@@ -604,7 +604,9 @@ def test_bf16_gated_epilogue(smb, oracle, cuda_device, shape_flags):
     plan.run(); plan.run(); plan.check(); plan.close()
     acc = (a.double() @ bt.double().t()).cpu().numpy()
     _check_swiglu(oracle, acc, d[:, :n_out], k)
-    assert bool(torch.isnan(d[:, n_out:]).all())
+    # The aligned store path writes whole 16-byte chunks: the padding of a row may be overwritten
+    # up to the next multiple of 8 columns, nothing beyond that.
+    assert bool(torch.isnan(d[:, (n_out + 7) // 8 * 8:]).all())
 
 
 def test_fp4_gated_epilogue(smb, oracle, cuda_device):
