@@ -204,13 +204,14 @@ int smb_dense_gemm_nvfp4_host(const uint8_t* a, const uint8_t* sfa_rowmajor, con
  * GEMM runs: a server whose start-up pool owns all of HBM, a plugin living inside another
  * framework's allocator, a call made while a stream is being captured.  It has no counterpart
  * in the reference.  Same operands and result as smb_dense_gemm_nvfp4 (packed scales, lda =
- * ldb = K/2 bytes, ldd = N); the partial-sum scratch of the kernel lives in a 20 MiB array
- * built into the library, so the call performs no cudaMalloc / cudaFree of any kind.
- *   - The array holds two fp32 partial-tile slots per CTA (round_up(M,16) * 512 bytes each) and
- *     one 4-byte counter per 128 columns of N, within smb_decode_noalloc_scratch_limit() bytes
- *     (20 MiB - 256).  The call uses as many CTAs as have slots (all 148 SMs of a B200 for every
- *     M <= 128 and N up to 50 million); a shape whose counters leave room for not even one CTA
- *     returns SMB_ERR_UNSUPPORTED.
+ * ldb = K/2 bytes, ldd = N); what the kernel needs besides its operands (a status word, and for
+ * its stream-K work split tile counters and partial-sum slots) lives in a 2 MiB array built
+ * into the library, so the call performs no cudaMalloc / cudaFree of any kind.
+ *   - The array must hold one 4-byte counter per 128 columns of N and two fp32 partial-tile
+ *     slots (round_up(M,16) * 512 bytes each) for at least one CTA within
+ *     smb_decode_noalloc_scratch_limit() bytes (2 MiB - 256); a shape that does not fit
+ *     returns SMB_ERR_UNSUPPORTED.  The default work split (whole tile pairs per CTA) uses
+ *     only the status word.
  *   - The first call on a device looks up the array's device address; make that call outside
  *     any stream capture.
  *   - All calls share the one array: it is cleared on `stream` before each launch, and two

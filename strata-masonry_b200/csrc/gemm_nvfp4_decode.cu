@@ -1012,13 +1012,16 @@ int fp4_decode_bind_output(Fp4DecodeLaunch* L, void* d, int M, int N, long long 
 // Some hosts of this library cannot call cudaMalloc on the path that runs the GEMM: an
 // inference server that has handed all device memory to its own pool at start-up, a
 // plugin running inside another framework's allocator, code between a stream capture's
-// begin and end.  For them the fp32 partial-sum slots and tile counters of the decode
-// kernel live in the fixed array below instead of in a plan-owned allocation.  The array
-// is part of the library image: every GPU that loads the library carries these 20 MiB
-// until the process exits.
+// begin and end.  For them the status word, the tile counters and the fp32 partial-sum slots
+// of the decode kernel live in the fixed array below instead of in a plan-owned allocation.
+// The default work split (whole tile pairs per CTA) shares no tile between CTAs and touches
+// only the status word; counters and slots are what the stream-K split needs, and the array
+// has room for the counters of 500 000 columns and a few CTAs' slots.  The array is part of
+// the library image: every GPU that loads the library carries these 2 MiB until the process
+// exits.
 namespace {
 
-constexpr size_t kStaticScratchBytes = size_t(20) << 20;
+constexpr size_t kStaticScratchBytes = size_t(2) << 20;
 constexpr size_t kStaticStatusOffset = kStaticScratchBytes - 256;   // last 256 bytes: status word
 static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
 

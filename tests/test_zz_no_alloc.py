@@ -62,10 +62,9 @@ def test_no_alloc_decode_rejects_what_does_not_fit(smb, cuda_device):
     t = torch.zeros(4096, device=cuda_device, dtype=torch.uint8)
     p = t.data_ptr()
     limit = lib.smb_decode_noalloc_scratch_limit()
-    assert limit == (20 << 20) - 256
-    # The array holds two partial-sum slots per CTA and one counter per tile; the CTA count adapts,
-    # so only a shape whose counters leave no room for a single CTA is refused: 2^31 - 1 columns
-    # are 16.8 M tiles = 67 MB of counters.
+    assert limit == (2 << 20) - 256
+    # The array holds one counter per tile and partial-sum slots for at least one CTA: 2^31 - 1
+    # columns are 16.8 M tiles = 67 MB of counters.
     assert lib.smb_dense_gemm_nvfp4_decode_noalloc(p, p, p, p, p, 128, 2 ** 31 - 1, 256, None) == smb.capi.SMB_ERR_UNSUPPORTED
     assert "scratch" in smb.capi.last_error()
     assert lib.smb_dense_gemm_nvfp4_decode_noalloc(p, p, p, p, p, 129, 256, 256, None) == smb.capi.SMB_ERR_UNSUPPORTED
