@@ -39,6 +39,8 @@ WORKLOADS = {
     # name: (kind, M, N, K, fill, description)
     "bf16_8192": ("bf16", 8192, 8192, 8192, 5, "dense BF16 GEMM M=N=K=8192, operands N(0,1)*0.1 stand-in"),
     "nvfp4_8192": ("nvfp4", 8192, 8192, 8192, 5, "dense NVFP4 GEMM M=N=K=8192, quantised N(0,1) stand-in"),
+    "nvf4b16_8192": ("nvfp4", 8192, 8192, 8192, 16,
+                     "dense NVFP4-proper GEMM M=N=K=8192: E4M3 scale per 16 K, quantised N(0,1) (secondary workload)"),
     "bf16_large": ("bf16", 32768, 57344, 8192, 6, "dense BF16 GEMM 32768x57344x8192, operands N(0,1)*0.05 stand-in"),
     "bf16_smoke": ("bf16", 256, 128, 64, 2, "reference smoke shape 256x128x64, fill 2"),
     "decode_m16": ("decode", 16, 28672, 8192, 5, "NVFP4 decode GEMM M=16, N=28672, K=8192 (HBM-bound)"),
@@ -275,6 +277,7 @@ def main():
     n_local, n0 = shard.n_local, shard.n0
     stream = torch.cuda.current_stream()
     plans = None
+    lib_q = smb.capi.lib()
 
     # ---------------------------------------------------------------- operands, resident in HBM
     if kind == "bf16":
@@ -307,9 +310,29 @@ def main():
         bt = torch.empty(n_local, k // 2, device=dev, dtype=torch.uint8)
         sfb = torch.empty(smb.gemm.sf_packed_bytes(n_local, k), device=dev, dtype=torch.uint8)
         d = torch.empty(m, n_local, device=dev, dtype=torch.bfloat16)
-        smb.gemm.fill_fp4_device(a, sfa, None, m, k, fill, 0, 0, stream=stream)
-        smb.gemm.fill_fp4_device(bt, sfb, None, n_local, k, fill, 1, n0, stream=stream)
-        plan = smb.gemm.Fp4Plan(a, sfa, bt, sfb, d, m, n_local, k, flags=smb.capi.FLAG_OPERANDS_STATIC)
+        if fill == 16:
+            # NVFP4 proper: Gaussian data quantised on the device, E4M3 scale per 16 K, the two
+            # per-tensor factors folded into the plan's output factor.
+            import ctypes as C
+            sfa = torch.empty(smb.gemm.sf_packed_bytes(m, 2 * k), device=dev, dtype=torch.uint8)
+            sfb = torch.empty(smb.gemm.sf_packed_bytes(n_local, 2 * k), device=dev, dtype=torch.uint8)
+            gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+            factors = []
+            for rows_, codes_, sf_ in ((m, a, sfa), (n_local, bt, sfb)):
+                x = torch.randn(rows_, k, device=dev, generator=gen)
+                gs = 448.0 * 6.0 / float(x.abs().max())
+                smb.capi.check(lib_q.smb_quantize_nvf4_device(x.data_ptr(), k, C.c_float(gs), codes_.data_ptr(), k // 2,
+                                                              sf_.data_ptr(), None, rows_, k, int(stream.cuda_stream)))
+                factors.append(gs)
+                torch.cuda.synchronize()
+                del x
+            plan = smb.gemm.Fp4Plan(a, sfa, bt, sfb, d, m, n_local, k,
+                                    flags=smb.capi.FLAG_OPERANDS_STATIC | smb.capi.FLAG_SCALE_BLOCK16)
+            plan.set_alpha(1.0 / (factors[0] * factors[1]))
+        else:
+            smb.gemm.fill_fp4_device(a, sfa, None, m, k, fill, 0, 0, stream=stream)
+            smb.gemm.fill_fp4_device(bt, sfb, None, n_local, k, fill, 1, n0, stream=stream)
+            plan = smb.gemm.Fp4Plan(a, sfa, bt, sfb, d, m, n_local, k, flags=smb.capi.FLAG_OPERANDS_STATIC)
         resident_bytes = a.numel() + bt.numel() + sfa.numel() + sfb.numel() + d.numel() * 2
         dtype = "e2m1"
     torch.cuda.synchronize()

@@ -85,6 +85,20 @@ int smb_quantize_mx_device(const float* src, int64_t ld_src, uint8_t* data, int6
                            void* stream);
 int smb_quantize_mx_host(const float* src, int64_t ld_src, uint8_t* data, int64_t ld_bytes,
                          uint8_t* sf_packed, uint8_t* sf_rowmajor, int64_t rows, int64_t K);
+/* NVFP4 proper (no counterpart in the reference, which documents the layout it would need,
+ * nvfp4/dense_gemm_nvfp4.cu:109-129, but builds only the block-32 UE8M0 form): E2M1 codes with
+ * one E4M3 scale per 16 consecutive k and a per-tensor factor chosen by the caller (typically
+ * 448 * 6 / max|tensor|).  scale = e4m3_rne(max|v| * global_scale / 6), saturating at 448;
+ * code = e2m1(v * global_scale / scale); the represented value is e2m1 * e4m3 / global_scale.
+ * K % 32 == 0 (16-byte rows of codes); scales as [rows, K/16] bytes row-major and/or in the
+ * packed layout of smb_sf_packed_bytes(rows, K/16), padding 0.  A GEMM over such operands is a
+ * plan created with SMB_FLAG_SCALE_BLOCK16 and smb_fp4_plan_set_alpha(1 / (gs_a * gs_b)). */
+int smb_quantize_nvf4_device(const float* src, int64_t ld_src, float global_scale, uint8_t* data,
+                             int64_t ld_bytes, uint8_t* sf_packed, uint8_t* sf_rowmajor, int64_t rows,
+                             int64_t K, void* stream);
+int smb_quantize_nvf4_host(const float* src, int64_t ld_src, float global_scale, uint8_t* data,
+                           int64_t ld_bytes, uint8_t* sf_packed, uint8_t* sf_rowmajor, int64_t rows,
+                           int64_t K);
 /* The same quantiser on BF16 bit patterns (every bf16 is an fp32: same rule, same result). */
 int smb_quantize_mx_bf16_device(const uint16_t* src, int64_t ld_src, uint8_t* data, int64_t ld_bytes,
                                 uint8_t* sf_packed, uint8_t* sf_rowmajor, int64_t rows, int64_t K,
@@ -183,6 +197,9 @@ int smb_fp4_plan_create(smb_fp4_plan** plan, const void* a, const void* sfa, con
 int smb_fp4_plan_create_bf16_activations(smb_fp4_plan** plan, const void* x_bf16, int64_t ldx,
                                          const void* b, const void* sfb, void* d, int M, int N, int K,
                                          int64_t ldb_bytes, int64_t ldd, unsigned flags);
+/* Factor applied to every accumulator before the result is rounded to bf16; plans created with
+ * SMB_FLAG_SCALE_BLOCK16 only (the product of the operands' inverse per-tensor factors). */
+int smb_fp4_plan_set_alpha(smb_fp4_plan* plan, float alpha);
 int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_destroy(smb_fp4_plan* plan);
@@ -287,6 +304,10 @@ int smb_unshard_columns_device(const void* gathered, void* d, int g, int M, int 
  * tanh(z / 2)) on the hardware tanh approximation.  D is [M, N / 2] (ldd >= N / 2, 16-byte
  * aligned, ldd % 8 == 0), N even; the plan uses 256-wide tiles.  Tiled kernels only. */
 #define SMB_FLAG_EPILOGUE_SWIGLU 8192u
+/* FP4 plans: the scale buffers hold one E4M3 byte per 16 K (NVFP4 proper, issued as
+ * kind::mxf4nvf4.block_scale.scale_vec::4X) instead of one UE8M0 byte per 32 K, packed with
+ * smb_sf_packed_bytes(rows, K / 16).  K % 64 == 0; 256-wide tiles; any M (no decode kernel). */
+#define SMB_FLAG_SCALE_BLOCK16 16384u
 #define SMB_FLAG_NO_DECODE 64u        /* FP4 only: M <= 128 through the tiled kernel, not the decode kernel */
 #define SMB_FLAG_NO_LAUNCH_OVERLAP 128u /* decode kernel: no programmatic dependent launch */
 /* Decode kernel (FP4, M <= 128): force the form in which a CTA multiplies two adjacent weight

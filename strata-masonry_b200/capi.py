@@ -35,6 +35,7 @@ FLAG_DECODE_DUAL = 512
 FLAG_DECODE_SINGLE = 2048
 FLAG_LAUNCH_INDEPENDENT = 4096
 FLAG_EPILOGUE_SWIGLU = 8192
+FLAG_SCALE_BLOCK16 = 16384
 
 _vp = C.c_void_p
 _i = C.c_int
@@ -51,6 +52,8 @@ DECLARED = [
     ("smb_fill_fp4_host", _i, [_vp, _i64, _vp, _vp, _i64, _i64, _u64, _i, _i]),
     ("smb_quantize_mx_device", _i, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _vp]),
     ("smb_quantize_mx_host", _i, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64]),
+    ("smb_quantize_nvf4_device", _i, [_vp, _i64, C.c_float, _vp, _i64, _vp, _vp, _i64, _i64, _vp]),
+    ("smb_quantize_nvf4_host", _i, [_vp, _i64, C.c_float, _vp, _i64, _vp, _vp, _i64, _i64]),
     ("smb_quantize_mx_bf16_device", _i, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _vp]),
     ("smb_sf_packed_bytes", C.c_size_t, [_i64, _i64]),
     ("smb_sf_pack_host", _i, [_vp, _i64, _i64, _vp]),
@@ -73,6 +76,7 @@ DECLARED = [
     ("smb_fp4_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, C.c_uint]),
     ("smb_fp4_plan_create_bf16_activations", _i,
      [C.POINTER(_vp), _vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, C.c_uint]),
+    ("smb_fp4_plan_set_alpha", _i, [_vp, C.c_float]),
     ("smb_fp4_plan_run", _i, [_vp, _vp]),
     ("smb_fp4_plan_check", _i, [_vp, _vp]),
     ("smb_fp4_plan_destroy", _i, [_vp]),

@@ -39,8 +39,13 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
     return set_error(SMB_ERR_INVALID, "fp4 plan: dimensions must be positive (M=%d N=%d K=%d)", M, N, K);
   if (K % 32 != 0)
     return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: K=%d must be a multiple of 32 (one scale per 32 K)", K);
+  const bool block16 = (flags & SMB_FLAG_SCALE_BLOCK16) != 0;
+  if (block16 && K % 64 != 0)
+    return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: block-16 scales need K %% 64 == 0 (K=%d)", K);
+  if (block16 && (flags & SMB_FLAG_EPILOGUE_SWIGLU))
+    return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: no gated epilogue for block-16 scales");
   const bool swiglu = (flags & SMB_FLAG_EPILOGUE_SWIGLU) != 0;
-  if (swiglu && (N % 2 != 0 || M <= 128))
+  if (swiglu && (N % 2 != 0 || (M <= 128 && !(flags & SMB_FLAG_NO_DECODE))))
     return set_error(SMB_ERR_UNSUPPORTED,
                      "fp4 plan: the gated epilogue needs an even N and the tiled kernel (M > 128)");
   const int n_out = swiglu ? N / 2 : N;
@@ -71,6 +76,12 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
   L.ldd = static_cast<int>(ldd);
   L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
                 !(flags & SMB_FLAG_FORCE_PLAIN_STORE);
+  L.block16 = block16;
+  L.alpha = 1.0f;
+  if (block16) {
+    L.w0 = 256;
+    L.w1 = 0;
+  }
   L.swiglu = swiglu;
   if (swiglu) {
     if (!L.tma_store) {
@@ -82,14 +93,17 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
     L.w1 = 0;
   }
   p->status_dev = nullptr;
-  p->decode = (M <= 128) && !(flags & SMB_FLAG_NO_DECODE);
+  p->decode = (M <= 128) && !(flags & SMB_FLAG_NO_DECODE) && !block16;
   p->scratch_dev = nullptr;
   p->scratch_bytes = 0;
   p->act_src = nullptr;
   p->act_ld = 0;
   p->act_codes = p->act_sf = nullptr;
 
-  const uint64_t kchunks = (static_cast<uint64_t>(K) / 32 + 3) / 4;
+  // Packed scales: chunks of 4 scale bytes per row, i.e. K = 128 (one scale per 32) or K = 64
+  // (one per 16); a stage (K = 256) reads 2 or 4 chunks of 64 words.
+  const uint64_t kchunks = block16 ? static_cast<uint64_t>(K) / 64 : (static_cast<uint64_t>(K) / 32 + 3) / 4;
+  const uint32_t sf_box = block16 ? 256 : 128;
   const uint64_t bands_a = (static_cast<uint64_t>(M) + 127) / 128;
   const uint64_t bands_b = (static_cast<uint64_t>(N) + 127) / 128;
   const int tile_n = L.w0 + L.w1;
@@ -104,10 +118,10 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
   }
   if (rc == SMB_OK)
     rc = encode_tmap_2d(&L.tmap_sfa, sfa, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_a, kchunks * 64,
-                        kchunks * 512, 1, 128, false);
+                        kchunks * 512, 1, sf_box, false);
   if (rc == SMB_OK)
     rc = encode_tmap_2d(&L.tmap_sfb, sfb, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_b, kchunks * 64,
-                        kchunks * 512, tile_n / 128, 128, false);
+                        kchunks * 512, tile_n / 128, sf_box, false);
   if (rc == SMB_OK) {
     if (L.tma_store)
       rc = encode_tmap_2d(&L.tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, n_out, ldd * 2, 32, 64, true);
@@ -189,6 +203,14 @@ extern "C" int smb_fp4_plan_set_peer_copies(smb_fp4_plan* plan, int count, void*
     return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: the decode kernel (M <= 128) has no peer copies");
   return set_peer_copies(&plan->launch.peers, plan->launch.tma_store, count, dst, ld,
                          plan->launch.swiglu ? plan->launch.N / 2 : plan->launch.N);
+}
+
+extern "C" int smb_fp4_plan_set_alpha(smb_fp4_plan* plan, float alpha) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
+  if (!plan->launch.block16)
+    return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: the output factor belongs to block-16 plans");
+  plan->launch.alpha = alpha;
+  return SMB_OK;
 }
 
 extern "C" int smb_fp4_plan_set_profile(smb_fp4_plan* plan, long long* counters) {

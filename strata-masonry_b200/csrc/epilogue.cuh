@@ -25,6 +25,7 @@ struct StoreTarget {
   int ldd;
   int M, N;
   const PeerCopies* peers;     // kernel parameter, TMA path only (N % 8 == 0 there)
+  float alpha;                 // factor on every accumulator (kScaled instantiations only)
 };
 
 // One warp drains kCols fp32 columns of its 32 TMEM lanes starting at `taddr`, then writes them
@@ -40,7 +41,8 @@ struct StoreTarget {
 // interleaved, even = up, odd = gate, so accumulator column 2n is up_n and 2n + 1 is gate_n;
 // the output is D[m, n] = bf16(silu(gate_n) * up_n), half as wide as the accumulator.  col0 is
 // then the accumulator column; out.N and the tensor map describe the [M, N/2] output.
-template <int kCols, bool kTmaStore, bool kSwiglu = false>
+// kScaled: every accumulator is multiplied by out.alpha first (the per-tensor scales of NVFP4).
+template <int kCols, bool kTmaStore, bool kSwiglu = false, bool kScaled = false>
 __device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, const StoreTarget& out,
                                                 int row0, int col0, uint32_t release_bar, int lane) {
   constexpr int kOutCols = kSwiglu ? kCols / 2 : kCols;
@@ -53,6 +55,10 @@ __device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, c
     uint32_t v[32];
     tmem_ld_32x32b_x32(taddr + g * 32, v);
     tmem_ld_wait();
+    if (kScaled) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * out.alpha);
+    }
     if (kSwiglu) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {

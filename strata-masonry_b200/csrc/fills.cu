@@ -204,6 +204,34 @@ __global__ void quantize_mx_bf16_kernel(const uint16_t* src, int64_t ld_src, uin
   }
 }
 
+// NVFP4 proper: one thread per 16-value block (64 bytes in, 8 + 1 bytes out).
+__global__ void quantize_nvf4_kernel(const float* src, int64_t ld_src, float gs, uint8_t* data,
+                                     int64_t ld_bytes, uint8_t* sf_packed, uint8_t* sf_rowmajor,
+                                     int64_t rows, uint32_t K) {
+  const uint32_t kblocks = K / 16u;
+  const int64_t total = rows * kblocks;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t r = i / kblocks;
+    const uint32_t kb = static_cast<uint32_t>(i - r * kblocks);
+    float v[16];
+    const float4* s4 = reinterpret_cast<const float4*>(src + r * ld_src + kb * 16);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 q = s4[j];
+      v[4 * j] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w;
+    }
+    uint8_t codes[8];
+    uint8_t sb;
+    fmt::quantize_nvf4_block(v, gs, codes, &sb);
+    uint2 packed;
+    memcpy(&packed, codes, 8);
+    *reinterpret_cast<uint2*>(data + r * ld_bytes + kb * 8) = packed;
+    if (sf_packed) sf_packed[fmt::sf_packed_offset(static_cast<uint32_t>(r), kb, kblocks)] = sb;
+    if (sf_rowmajor) sf_rowmajor[r * kblocks + kb] = sb;
+  }
+}
+
 int check_fp4_args(const void* data, int64_t rows, int64_t K, int64_t ld_bytes) {
   if (data == nullptr) return set_error(SMB_ERR_INVALID, "fp4: null data pointer");
   if (rows < 0 || K <= 0 || K % 32 != 0)
@@ -354,6 +382,50 @@ extern "C" int smb_quantize_mx_bf16_device(const uint16_t* src, int64_t ld_src, 
     if (e != cudaSuccess) return set_cuda_error(e, "quantize: scale buffer memset");
   }
   return quantize_bf16_launch(src, ld_src, data, ld_bytes, sf_packed, sf_rowmajor, rows, K, false, st);
+}
+
+extern "C" int smb_quantize_nvf4_host(const float* src, int64_t ld_src, float global_scale, uint8_t* data,
+                                      int64_t ld_bytes, uint8_t* sf_packed, uint8_t* sf_rowmajor,
+                                      int64_t rows, int64_t K) {
+  if (src == nullptr) return set_error(SMB_ERR_INVALID, "quantize: null source");
+  if (int rc = check_fp4_args(data, rows, K, ld_bytes)) return rc;
+  if (ld_src < K) return set_error(SMB_ERR_INVALID, "quantize: source pitch smaller than K");
+  if (!(global_scale > 0.0f)) return set_error(SMB_ERR_INVALID, "quantize: global scale must be positive");
+  const uint32_t kblocks = static_cast<uint32_t>(K / 16);
+  if (sf_packed) memset(sf_packed, 0, smb_sf_packed_bytes(rows, kblocks));
+  for (int64_t r = 0; r < rows; ++r) {
+    for (uint32_t kb = 0; kb < kblocks; ++kb) {
+      uint8_t sb;
+      fmt::quantize_nvf4_block(src + r * ld_src + kb * 16, global_scale, data + r * ld_bytes + kb * 8, &sb);
+      if (sf_packed) sf_packed[fmt::sf_packed_offset(static_cast<uint32_t>(r), kb, kblocks)] = sb;
+      if (sf_rowmajor) sf_rowmajor[r * kblocks + kb] = sb;
+    }
+  }
+  return SMB_OK;
+}
+
+extern "C" int smb_quantize_nvf4_device(const float* src, int64_t ld_src, float global_scale, uint8_t* data,
+                                        int64_t ld_bytes, uint8_t* sf_packed, uint8_t* sf_rowmajor,
+                                        int64_t rows, int64_t K, void* stream) {
+  if (src == nullptr) return set_error(SMB_ERR_INVALID, "quantize: null source");
+  if (int rc = check_fp4_args(data, rows, K, ld_bytes)) return rc;
+  if (ld_src < K || ld_src % 4 != 0 || reinterpret_cast<uintptr_t>(src) % 16 != 0)
+    return set_error(SMB_ERR_INVALID, "quantize: source rows must be 16-byte aligned");
+  if (!(global_scale > 0.0f)) return set_error(SMB_ERR_INVALID, "quantize: global scale must be positive");
+  if (rows == 0) return SMB_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t kblocks = K / 16;
+  if (sf_packed) {
+    // Padding rows of the last 128-row band: scale 0 (they multiply zero-filled data).
+    cudaError_t e = cudaMemsetAsync(sf_packed, 0, smb_sf_packed_bytes(rows, kblocks), st);
+    if (e != cudaSuccess) return set_cuda_error(e, "quantize: scale buffer memset");
+  }
+  quantize_nvf4_kernel<<<grid_for(rows * kblocks), 256, 0, st>>>(src, ld_src, global_scale, data, ld_bytes,
+                                                                 sf_packed, sf_rowmajor, rows,
+                                                                 static_cast<uint32_t>(K));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_cuda_error(e, "nvf4 quantize launch");
+  return SMB_OK;
 }
 
 // ------------------------------------------------------------------------------------

@@ -135,6 +135,67 @@ SMB_HD int ue8m0_exponent(float amax) {
 }
 SMB_HD float exp2i(int e) { return bits_f32(static_cast<uint32_t>(e + 127) << 23); }
 
+// ------------------------------------------------------------------------------- E4M3 (unsigned use)
+// OCP FP8 E4M3: bias 7, three mantissa bits, subnormals m * 2^-9, largest finite value 448
+// (0x7E); 0x7F is NaN and never produced.  Scale bytes of NVFP4 (one per 16 K) use the
+// non-negative half.
+SMB_HD float add_rn(float a, float b) {
+#if defined(__CUDA_ARCH__)
+  return __fadd_rn(a, b);
+#else
+  return a + b;
+#endif
+}
+SMB_HD float div_rn(float a, float b) {
+#if defined(__CUDA_ARCH__)
+  return __fdiv_rn(a, b);
+#else
+  return a / b;
+#endif
+}
+
+// Nearest E4M3 code of x >= 0 (round to nearest even, saturating at 448).
+SMB_HD uint32_t e4m3_encode(float x) {
+  if (!(x > 0.0f)) return 0u;
+  if (x >= 464.0f) return 0x7Eu;                     // above the rounding boundary of 448
+  if (x < 0.015625f) {                                // below 2^-6: subnormal grid of 2^-9
+    const float t = add_rn(mul_rn(x, 512.0f), 12582912.0f);   // 1.5 * 2^23: rounds to an integer
+    return f32_bits(t) & 0xFu;                        // 0..8; 8 is the smallest normal, code 0x08
+  }
+  const uint32_t b = f32_bits(x);
+  const uint32_t r = b + 0x7FFFFu + ((b >> 20) & 1u);  // round the mantissa to three bits
+  const uint32_t code = ((((r >> 23) & 0xFFu) - 120u) << 3) | ((r >> 20) & 7u);
+  return code > 0x7Eu ? 0x7Eu : code;
+}
+
+SMB_HD float e4m3_decode(uint32_t code) {
+  const uint32_t e = (code >> 3) & 0xFu, m = code & 7u;
+  if (e == 0) return static_cast<float>(m) * 0.001953125f;                  // m * 2^-9
+  return mul_rn(1.0f + static_cast<float>(m) * 0.125f, exp2i(static_cast<int>(e) - 7));
+}
+
+// NVFP4 proper: 16 values share one E4M3 scale; `gs` is the caller's per-tensor factor
+// (typically 448 * 6 / max|tensor|).  scale = e4m3(max|v| * gs / 6); code = e2m1(v * gs / scale).
+// The represented value is e2m1(code) * e4m3(scale) / gs.
+SMB_HD void quantize_nvf4_block(const float* v, float gs, uint8_t* codes8, uint8_t* scale_byte) {
+  float amax = 0.0f;
+  for (int i = 0; i < 16; ++i) {
+    const float a = v[i] < 0.0f ? -v[i] : v[i];
+    amax = a > amax ? a : amax;
+  }
+  const uint32_t sb = e4m3_encode(div_rn(mul_rn(amax, gs), 6.0f));
+  const float s = e4m3_decode(sb);
+  for (int i = 0; i < 8; ++i) {
+    uint32_t lo = 0, hi = 0;
+    if (s > 0.0f) {
+      lo = e2m1_encode(div_rn(mul_rn(v[2 * i], gs), s));
+      hi = e2m1_encode(div_rn(mul_rn(v[2 * i + 1], gs), s));
+    }
+    codes8[i] = static_cast<uint8_t>(lo | (hi << 4));
+  }
+  *scale_byte = static_cast<uint8_t>(sb);
+}
+
 // ------------------------------------------------------------------------------- FP4 fills
 // E2M1 code of reference fills 1-4 for element `index` (= row * K + k, 32-bit wrap).
 SMB_HD uint32_t fp4_fill_code(uint32_t index, int fill, uint32_t seed) {

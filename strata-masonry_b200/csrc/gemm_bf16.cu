@@ -300,6 +300,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       out.M = p.M;
       out.N = kSwiglu ? p.N / 2 : p.N;
       out.peers = &p.peers;
+      out.alpha = 1.0f;
       int local = 0;
       bool ok = true;
       if (p.operands_static == 1) griddep_wait();   // 2: D is independent too, no wait at all

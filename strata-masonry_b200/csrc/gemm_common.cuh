@@ -95,6 +95,8 @@ struct Fp4Launch {
   bool operands_static;  // loads need not wait for the previous kernel on the stream
   bool output_independent;  // with operands_static: stores need not wait either
   PeerCopies peers;
+  bool block16;      // NVFP4 proper: UE4M3 scales per 16 K (256-wide tiles only)
+  float alpha;       // factor on every accumulator (block16 only; 1 otherwise)
 };
 void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1);
 int fp4_launch(const Fp4Launch& L, cudaStream_t stream);

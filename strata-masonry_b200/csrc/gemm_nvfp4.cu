@@ -42,7 +42,10 @@ constexpr int kTmemCols = 512;
 enum { kStorePlain = 0, kStoreTma = 1, kStoreSwiglu = 2 };   // epilogue variants
 constexpr int kRingBudget = 192 * 1024;
 
-template <int W0, int W1>
+// V4: NVFP4 proper, one UE4M3 scale per 16 K (scale_vec::4X): a 4-byte scale cell per K=64
+// instruction, four cells per stage instead of two (the layout the reference sketches but does
+// not build, nvfp4/dense_gemm_nvfp4.cu:109-129).
+template <int W0, int W1, bool V4 = false>
 struct Cfg {
   static_assert(W0 == 128 || W0 == 256, "first sub-block width");
   static_assert(W1 == 0 || W1 == 128 || W1 == 256, "second sub-block width");
@@ -51,8 +54,9 @@ struct Cfg {
   static constexpr bool kTwoBanks = (kTileN == 128);              // epilogue overlaps next main loop
   static constexpr int kB0Bytes = (W0 / 2) * kBlockKBytes;
   static constexpr int kB1Bytes = (W1 / 2) * kBlockKBytes;
-  static constexpr int kSfaBytes = 2 * kSfCellBytes;              // this CTA's 128 rows, K = 256
-  static constexpr int kSfbBytes = (kTileN / 128) * 2 * kSfCellBytes;
+  static constexpr int kCells = V4 ? 4 : 2;                       // 4-byte scale cells per row and stage
+  static constexpr int kSfaBytes = kCells * kSfCellBytes;         // this CTA's 128 rows, K = 256
+  static constexpr int kSfbBytes = (kTileN / 128) * kCells * kSfCellBytes;
   static constexpr int kStageBytes = kABytes + kB0Bytes + kB1Bytes + kSfaBytes + kSfbBytes;
   static constexpr int kOffB0 = kABytes;
   static constexpr int kOffB1 = kOffB0 + kB0Bytes;
@@ -60,8 +64,8 @@ struct Cfg {
   static constexpr int kOffSfb = kOffSfa + kSfaBytes;
   // Tensor memory map.
   static constexpr int kAccCols = kTwoBanks ? 256 : kTileN;
-  static constexpr int kSfaCols = 8;                               // 2 cells x 4 columns
-  static constexpr int kSfbCols = (kTileN / 128) * 8;
+  static constexpr int kSfaCols = kCells * 4;                      // cells x 4 columns
+  static constexpr int kSfbCols = (kTileN / 128) * kCells * 4;
   static constexpr int kSlotCols = kSfaCols + kSfbCols;
   static constexpr int kMaxSlots = (kTmemCols - kAccCols) / kSlotCols;
   static constexpr int kStagesBySmem = kRingBudget / kStageBytes;
@@ -88,13 +92,14 @@ struct Params {
   int prefetch;   // L2 prefetch distance in K blocks (0 = off)
   int dynamic;    // 1: tiles come from the hardware work queue (one cluster launched per tile)
   PeerCopies peers;     // extra destinations of every stored box (count 0: none)
+  float alpha;          // factor on every accumulator (block-16 variant: 1 / (global scale A x B))
   int operands_static;  // 1: operands and scales are not written by the previous kernel on the stream
 };
 
 enum { kProfLoadWait = 0, kProfLoadTotal, kProfMmaWaitFull, kProfMmaWaitAcc, kProfMmaTotal,
        kProfEpiWait, kProfEpiTotal, kProfTiles, kProfCount };
 
-template <int W0, int W1, int kStore>
+template <int W0, int W1, int kStore, bool V4 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b0,
@@ -102,7 +107,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_sfa,
                   const __grid_constant__ CUtensorMap tmap_sfb,
                   const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ Params p) {
-  using C = Cfg<W0, W1>;
+  using C = Cfg<W0, W1, V4>;
+  constexpr int kCells = C::kCells;
   constexpr bool kTmaStore = (kStore != kStorePlain);
   constexpr bool kSwiglu = (kStore == kStoreSwiglu);   // D is [M, N/2]: silu(gate) * up
   static_assert(!kSwiglu || C::kColsPerWarp % 128 == 0, "gated epilogue: 64 output columns per box");
@@ -223,8 +229,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // memory while the (ten times larger) operand boxes are still in flight.  The packed
           // scale buffer is viewed as [bands, K/128 * 64] 64-bit words; one stage covers 128
           // words (two 512-byte cells) of each band.
-          tma_load_2d_pair(dst + C::kOffSfa, &tmap_sfa, sf_bar, kb * 128, band_a);
-          tma_load_2d_pair(dst + C::kOffSfb, &tmap_sfb, sf_bar, kb * 128, band_b);
+          tma_load_2d_pair(dst + C::kOffSfa, &tmap_sfa, sf_bar, kb * (kCells * 64), band_a);
+          tma_load_2d_pair(dst + C::kOffSfb, &tmap_sfb, sf_bar, kb * (kCells * 64), band_b);
           tma_load_2d_pair(dst, &tmap_a, bar, kb * kBlockKBytes, row_a);
           tma_load_2d_pair(dst + C::kOffB0, &tmap_b0, bar, kb * kBlockKBytes,
                            col0 + static_cast<int>(rank) * (W0 / 2));
@@ -300,8 +306,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // K = 64 per instruction = 32 bytes along the swizzled row.  Atoms 2c and 2c + 1 share
             // scale cell c: the first reads bytes 0-1 of each cell (scale id 0), the second bytes
             // 2-3 (scale id 2).
-            const uint32_t sf_id = (ki & 1) ? 2u : 0u;
-            const uint32_t cell = static_cast<uint32_t>(ki >> 1);
+            const uint32_t sf_id = V4 ? 0u : ((ki & 1) ? 2u : 0u);
+            const uint32_t cell = static_cast<uint32_t>(V4 ? ki : (ki >> 1));
             uint32_t sfb_col = C::kSfaCols;
             uint32_t acc_col = 0;
 #pragma unroll
@@ -311,13 +317,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
               if (h == 0 || has_sub1) {
                 const uint64_t desc_b = make_smem_desc(stage + (h == 0 ? C::kOffB0 : C::kOffB1),
                                                        1024, 16, kSwizzle128B);
-                const uint32_t idesc = make_idesc_mxf4(256, width, sf_id, sf_id, true);
-                mma_mxf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc,
-                               sf_t + 4u * cell,
-                               sf_t + sfb_col + cell * static_cast<uint32_t>(bands * 4),
-                               (kb > 0 || ki > 0) ? 1u : 0u);
+                const uint32_t idesc = make_idesc_mxf4(256, width, sf_id, sf_id, !V4);
+                const uint32_t sfa_t = sf_t + 4u * cell;
+                const uint32_t sfb_t = sf_t + sfb_col + cell * static_cast<uint32_t>(bands * 4);
+                const uint32_t accum = (kb > 0 || ki > 0) ? 1u : 0u;
+                if (V4) mma_nvf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc, sfa_t, sfb_t, accum);
+                else mma_mxf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc, sfa_t, sfb_t, accum);
               }
-              sfb_col += static_cast<uint32_t>(bands * 8);
+              sfb_col += static_cast<uint32_t>(bands * kCells * 4);
               acc_col += static_cast<uint32_t>(width);
             }
           }
@@ -365,7 +372,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint64_t sfb_desc = make_smem_desc(stage + C::kOffSfb, 128, 16, kSwizzleNone);
           if (elect_one()) {
 #pragma unroll
-          for (int cell = 0; cell < 2; ++cell) {
+          for (int cell = 0; cell < kCells; ++cell) {
             tmem_cp_32x128b_warpx4<2>(sf_t + 4u * cell, sfa_desc + cell * (kSfCellBytes / 16));
           }
           int band0 = 0;
@@ -374,15 +381,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int h = 0; h < C::kSubs; ++h) {
             const int bands = (h == 0 ? W0 : W1) / 128;
 #pragma unroll
-            for (int cell = 0; cell < 2; ++cell) {
+            for (int cell = 0; cell < kCells; ++cell) {
 #pragma unroll
               for (int b = 0; b < bands; ++b) {
                 tmem_cp_32x128b_warpx4<2>(sf_t + col + static_cast<uint32_t>((cell * bands + b) * 4),
-                                          sfb_desc + ((band0 + b) * 2 + cell) * (kSfCellBytes / 16));
+                                          sfb_desc + ((band0 + b) * kCells + cell) * (kSfCellBytes / 16));
               }
             }
             band0 += bands;
-            col += static_cast<uint32_t>(bands * 8);
+            col += static_cast<uint32_t>(bands * kCells * 4);
           }
           mma_commit_pair(sf_ready_bar(s), 0x1);
           }
@@ -407,6 +414,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     out.M = p.M;
     out.N = kSwiglu ? p.N / 2 : p.N;
     out.peers = &p.peers;
+    out.alpha = p.alpha;
     int local = 0;
     bool ok = true;
     if (p.operands_static == 1) griddep_wait();   // 2: D is independent too, no wait at all
@@ -433,8 +441,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int col0 = tn * C::kTileN + tile_col;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(bank * 128 + tile_col);
-      drain_and_store<C::kColsPerWarp, kTmaStore, kSwiglu>(taddr, sbuf, out, row0, col0,
-                                                            leader_acc_empty0 + 8u * bank, lane);
+      drain_and_store<C::kColsPerWarp, kTmaStore, kSwiglu, V4>(taddr, sbuf, out, row0, col0,
+                                                                leader_acc_empty0 + 8u * bank, lane);
     }
     drain_store_groups<kTmaStore>(lane);
     if (prof) {
@@ -460,10 +468,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // -----------------------------------------------------------------------------------
 namespace {
 
-template <int W0, int W1, int kStore>
+template <int W0, int W1, int kStore, bool V4 = false>
 int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
-  using C = fp4k::Cfg<W0, W1>;
-  auto kernel = fp4k::gemm_nvfp4_kernel<W0, W1, kStore>;
+  using C = fp4k::Cfg<W0, W1, V4>;
+  auto kernel = fp4k::gemm_nvfp4_kernel<W0, W1, kStore, V4>;
   static thread_local int configured_device = -1;
   static thread_local int max_clusters = 0;
   int dev = 0;
@@ -503,6 +511,7 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   p.prof = L.prof;
   p.operands_static = L.operands_static ? (L.output_independent ? 2 : 1) : 0;
   p.peers = L.peers;
+  p.alpha = L.alpha;
   p.prefetch = L.prefetch;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
@@ -531,6 +540,15 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
 
 template <int W0, int W1>
 int launch_fp4_store(const Fp4Launch& L, cudaStream_t stream) {
+  if (L.block16) {
+    if constexpr (W0 == 256 && W1 == 0) {
+      if (L.swiglu) return set_error(SMB_ERR_UNSUPPORTED, "nvfp4: no gated epilogue for block-16 scales");
+      return L.tma_store ? launch_fp4<W0, W1, fp4k::kStoreTma, true>(L, stream)
+                         : launch_fp4<W0, W1, fp4k::kStorePlain, true>(L, stream);
+    } else {
+      return set_error(SMB_ERR_UNSUPPORTED, "nvfp4: block-16 scales need 256-wide tiles");
+    }
+  }
   if (L.swiglu) {
     if constexpr (W0 == 256 && W1 == 0) {
       return launch_fp4<W0, W1, fp4k::kStoreSwiglu>(L, stream);

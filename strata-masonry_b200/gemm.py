@@ -244,6 +244,10 @@ class Fp4Plan:
         self._peer_keep = dst
         capi.check(self._lib.smb_fp4_plan_set_peer_copies(self._h, count, arr, ld))
 
+    def set_alpha(self, alpha: float) -> None:
+        """Output factor of a FLAG_SCALE_BLOCK16 plan: 1 / (global scale of A x global scale of B)."""
+        capi.check(self._lib.smb_fp4_plan_set_alpha(self._h, alpha))
+
     def run(self, stream=None) -> None:
         capi.check(self._lib.smb_fp4_plan_run(self._h, _stream_ptr(stream)))
 

@@ -167,3 +167,45 @@ def test_missing_library_is_loud(smb, tmp_path, monkeypatch):
     monkeypatch.setattr(capi, "LIB_PATH", tmp_path / "absent.so")
     with pytest.raises(ImportError, match="no CPU fallback"):
         capi.lib()
+
+
+# ------------------------------------------------------------------------------- NVFP4 proper
+def test_nvf4_host_quantizer_matches_oracle(smb, oracle):
+    """E4M3 scale per 16 values + caller's per-tensor factor: the C++ quantiser against the NumPy
+    definition, on random data of many magnitudes and on crafted blocks whose maximum sits on
+    every E4M3 grid point and every midpoint between neighbours (ties go to the even code)."""
+    import ctypes as C
+    lib = smb.capi.lib()
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal((40, 256)) * np.exp2(rng.integers(-12, 6, (40, 16)).repeat(16, axis=1))).astype(np.float32)
+    x[0, :16] = 0
+    grid = oracle.e4m3_decode(np.arange(0x7F)).astype(np.float64)
+    probes = np.concatenate([grid, (grid[:-1] + grid[1:]) / 2, [448.0, 460.0, 464.0, 500.0, 1e6, 2.0 ** -10, 2.0 ** -11]])
+    crafted = np.zeros((len(probes), 16), dtype=np.float32)
+    crafted[:, 0] = probes.astype(np.float32)
+    crafted[:, 1] = -probes.astype(np.float32) / 3
+    for data_in, gs in ((x, 37.5), (x, 0.01), (crafted, 6.0)):
+        rows, k = data_in.shape
+        data = np.zeros((rows, k // 2), dtype=np.uint8)
+        sfr = np.zeros((rows, k // 16), dtype=np.uint8)
+        sfp = np.zeros(lib.smb_sf_packed_bytes(rows, k // 16), dtype=np.uint8)
+        src = np.ascontiguousarray(data_in)
+        if k // 2 % 16 != 0:      # rows of codes must be 16-byte aligned: pad K to 32
+            src = np.zeros((rows, 32), dtype=np.float32); src[:, :k] = data_in; k = 32
+            data = np.zeros((rows, 16), dtype=np.uint8); sfr = np.zeros((rows, 2), dtype=np.uint8)
+            sfp = np.zeros(lib.smb_sf_packed_bytes(rows, 2), dtype=np.uint8)
+        smb.capi.check(lib.smb_quantize_nvf4_host(src.ctypes.data, k, C.c_float(gs), data.ctypes.data, k // 2,
+                                                  sfp.ctypes.data, sfr.ctypes.data, rows, k))
+        codes, sb = oracle.quantize_nvf4(src, gs)
+        np.testing.assert_array_equal(sfr, sb)
+        np.testing.assert_array_equal(data, oracle.pack_codes(codes))
+        np.testing.assert_array_equal(sfp, oracle.sf_pack(sb, pad=0))
+        assert sb.max() <= 0x7E
+    # Round trip: the represented values are within half an E2M1 step of the block maximum.
+    gs = 448.0 * 6.0 / float(np.abs(x).max())      # the usual choice: the largest block scale is 448
+    codes, sb = oracle.quantize_nvf4(x, gs)
+    back = oracle.dequantize_nvf4(codes, sb, gs)
+    amax = np.abs(x.reshape(40, 16, 16)).max(axis=2).repeat(16, axis=1)
+    assert np.all(np.abs(back - x) <= 0.26 * np.maximum(amax, 1e-30) + 2.0 ** -9 / gs * 6)
+    assert lib.smb_quantize_nvf4_host(None, 0, C.c_float(1.0), None, 0, None, None, 1, 32) == smb.capi.SMB_ERR_INVALID
+    assert lib.smb_fp4_plan_set_alpha(None, C.c_float(1.0)) == smb.capi.SMB_ERR_INVALID

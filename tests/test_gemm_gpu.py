@@ -661,3 +661,61 @@ def test_fp4_decode_forms_agree_bit_for_bit(smb, cuda_device):
         _, _, single = _run_fp4_decode(smb, m, 28672, 8192, flags=smb.capi.FLAG_DECODE_SINGLE)
         _, _, dual = _run_fp4_decode(smb, m, 28672, 8192, flags=smb.capi.FLAG_DECODE_DUAL)
         assert torch.equal(single[0].view(torch.int16), dual[0].view(torch.int16))
+
+
+# ------------------------------------------------------------------------------- NVFP4 proper
+def _nvf4_operand(smb, oracle, rows, k, seed, sigma=1.0):
+    """Gaussian data quantised on the device to E2M1 + E4M3 scale per 16 K; returns device buffers
+    (codes, packed scales), the global scale and the represented values in float64."""
+    torch = _torch()
+    import ctypes as C
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = (torch.randn(rows, k, generator=g) * sigma).to(dev)
+    gs = 448.0 * 6.0 / float(x.abs().max())
+    codes = torch.empty(rows, k // 2, device=dev, dtype=torch.uint8)
+    sfp = torch.empty(smb.gemm.sf_packed_bytes(rows, k * 2), device=dev, dtype=torch.uint8)   # K/16 blocks
+    sfr = torch.empty(rows, k // 16, device=dev, dtype=torch.uint8)
+    smb.capi.check(smb.capi.lib().smb_quantize_nvf4_device(
+        x.data_ptr(), k, C.c_float(gs), codes.data_ptr(), k // 2, sfp.data_ptr(), sfr.data_ptr(), rows, k, None))
+    torch.cuda.synchronize()
+    want_codes, want_sb = oracle.quantize_nvf4(x.cpu().numpy(), gs)
+    np.testing.assert_array_equal(sfr.cpu().numpy(), want_sb)
+    np.testing.assert_array_equal(codes.cpu().numpy(), oracle.pack_codes(want_codes))
+    np.testing.assert_array_equal(sfp.cpu().numpy(), oracle.sf_pack(want_sb, pad=0))
+    values = oracle.dequantize_nvf4(want_codes, want_sb, gs)
+    return codes, sfp, gs, values
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 256), (512, 768, 1024), (300, 200, 192), (64, 1024, 512),
+                                   (2048, 2048, 4096)])
+def test_nvf4_block16_gemm(smb, oracle, cuda_device, shape):
+    """NVFP4 proper (E4M3 scale per 16 K, scale_vec::4X, per-tensor factors folded into alpha):
+    device quantiser bit-identical to the oracle, GEMM within the north-star bound of the float64
+    product of the represented values."""
+    torch = _torch()
+    m, n, k = shape
+    a, sfa, gsa, va = _nvf4_operand(smb, oracle, m, k, 3)
+    b, sfb, gsb, vb = _nvf4_operand(smb, oracle, n, k, 4, sigma=0.05)
+    d = torch.full((m, n), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k, flags=smb.capi.FLAG_SCALE_BLOCK16)
+    plan.set_alpha(1.0 / (gsa * gsb))
+    plan.run(); plan.run(); plan.check(); plan.close()
+    ref = va @ vb.T
+    ok, worst, bad = oracle.check_north_star(_bits(d), ref, k)
+    assert ok, f"{bad} elements outside the bound, worst ratio {worst:.2f}"
+
+
+def test_nvf4_block16_is_refused_where_it_cannot_work(smb, cuda_device):
+    torch = _torch()
+    t = torch.zeros(1 << 16, device=cuda_device, dtype=torch.uint8)
+    d = torch.zeros(256, 256, device=cuda_device, dtype=torch.bfloat16)
+    with pytest.raises(smb.capi.SmbError):     # K % 64 != 0
+        smb.gemm.Fp4Plan(t, t, t, t, d, 256, 256, 96, flags=smb.capi.FLAG_SCALE_BLOCK16)
+    with pytest.raises(smb.capi.SmbError):     # no gated epilogue for this variant
+        smb.gemm.Fp4Plan(t, t, t, t, d, 256, 256, 128, ldd=128,
+                         flags=smb.capi.FLAG_SCALE_BLOCK16 | smb.capi.FLAG_EPILOGUE_SWIGLU)
+    plain = smb.gemm.Fp4Plan(t, t, t, t, d, 256, 256, 128)
+    with pytest.raises(smb.capi.SmbError):     # alpha belongs to block-16 plans
+        plain.set_alpha(0.5)
+    plain.close()
