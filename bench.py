@@ -44,6 +44,8 @@ WORKLOADS = {
     "bf16_large": ("bf16", 32768, 57344, 8192, 6, "dense BF16 GEMM 32768x57344x8192, operands N(0,1)*0.05 stand-in"),
     "bf16_smoke": ("bf16", 256, 128, 64, 2, "reference smoke shape 256x128x64, fill 2"),
     "decode_m16": ("decode", 16, 28672, 8192, 5, "NVFP4 decode GEMM M=16, N=28672, K=8192 (HBM-bound)"),
+    "decode_m16_b16": ("decode", 16, 28672, 8192, 16,
+                       "NVFP4-proper decode GEMM M=16, N=28672, K=8192: E4M3 scale per 16 K (secondary workload)"),
     "decode_m64": ("decode", 64, 28672, 8192, 5, "NVFP4 decode GEMM M=64, N=28672, K=8192 (HBM-bound)"),
     "decode_m128": ("decode", 128, 28672, 8192, 5, "NVFP4 decode GEMM M=128, N=28672, K=8192 (HBM-bound)"),
 }
@@ -294,13 +296,35 @@ def main():
         smb.gemm.fill_fp4_device(a, sfa, None, m, k, 6, 0, 0, stream=stream)
         d = torch.empty(m, n_local, device=dev, dtype=torch.bfloat16)
         weights, plans = [], []
+        block16 = (fill == 16)
+
+        def quantize_b16(rows_, codes_, seed_):
+            """Gaussian data quantised on the device: E2M1 + E4M3 scale per 16 K."""
+            import ctypes as C
+            sf_ = torch.empty(smb.gemm.sf_packed_bytes(rows_, 2 * k), device=dev, dtype=torch.uint8)
+            gen = torch.Generator(device=dev).manual_seed(seed_)
+            x = torch.randn(rows_, k, device=dev, generator=gen)
+            gs = 448.0 * 6.0 / float(x.abs().max())
+            smb.capi.check(lib_q.smb_quantize_nvf4_device(x.data_ptr(), k, C.c_float(gs), codes_.data_ptr(), k // 2,
+                                                          sf_.data_ptr(), None, rows_, k, int(stream.cuda_stream)))
+            torch.cuda.synchronize()
+            return sf_, gs
+
+        if block16:
+            sfa, gs_a = quantize_b16(m, a, 99)
         for i in range(DECODE_WEIGHT_SETS):
             w = torch.empty(n_local, k // 2, device=dev, dtype=torch.uint8)
-            sfw = torch.empty(smb.gemm.sf_packed_bytes(n_local, k), device=dev, dtype=torch.uint8)
-            # Different rows of the same logical generator for every set.
-            smb.gemm.fill_fp4_device(w, sfw, None, n_local, k, fill, 1, n0 + i * n, stream=stream)
+            if block16:
+                sfw, gs_w = quantize_b16(n_local, w, 1000 + rank * 16 + i)
+                pl = smb.gemm.Fp4Plan(a, sfa, w, sfw, d, m, n_local, k, flags=smb.capi.FLAG_SCALE_BLOCK16)
+                pl.set_alpha(1.0 / (gs_a * gs_w))
+            else:
+                sfw = torch.empty(smb.gemm.sf_packed_bytes(n_local, k), device=dev, dtype=torch.uint8)
+                # Different rows of the same logical generator for every set.
+                smb.gemm.fill_fp4_device(w, sfw, None, n_local, k, fill, 1, n0 + i * n, stream=stream)
+                pl = smb.gemm.Fp4Plan(a, sfa, w, sfw, d, m, n_local, k)
             weights.append((w, sfw))
-            plans.append(smb.gemm.Fp4Plan(a, sfa, w, sfw, d, m, n_local, k))
+            plans.append(pl)
         plan = plans[0]
         resident_bytes = DECODE_WEIGHT_SETS * (weights[0][0].numel() + weights[0][1].numel())
         dtype = "e2m1"
@@ -406,7 +430,8 @@ def main():
     timed_s = ms_total * 1e-3
     if kind == "decode":
         # Algorithmic bytes of one launch: weights + weight scales + activations + their scales + D.
-        algo_bytes = n_local * k // 2 + n_local * k // 32 + m * k // 2 + m * k // 32 + 2 * m * n_local
+        sf_k = 16 if fill == 16 else 32   # K values per scale byte
+        algo_bytes = n_local * k // 2 + n_local * k // sf_k + m * k // 2 + m * k // sf_k + 2 * m * n_local
         gbs = algo_bytes / (launch_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if g == 1 else None,
@@ -435,7 +460,7 @@ def main():
     # by a kernel chained in front of every GEMM (two launches per step).  Secondary figure; the
     # headline above starts from quantised activations, as the reference's metric does.
     act_step = None
-    if kind == "decode":
+    if kind == "decode" and fill != 16:
         x16 = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
         smb.gemm.fill_bf16_device(x16, m, k, 5, 1, stream=stream)
         aplans = [smb.gemm.Fp4Plan.from_bf16_activations(x16, w, sfw, d, m, n_local, k) for (w, sfw) in weights]

@@ -306,7 +306,8 @@ int smb_unshard_columns_device(const void* gathered, void* d, int g, int M, int 
 #define SMB_FLAG_EPILOGUE_SWIGLU 8192u
 /* FP4 plans: the scale buffers hold one E4M3 byte per 16 K (NVFP4 proper, issued as
  * kind::mxf4nvf4.block_scale.scale_vec::4X) instead of one UE8M0 byte per 32 K, packed with
- * smb_sf_packed_bytes(rows, K / 16).  K % 64 == 0; 256-wide tiles; any M (no decode kernel). */
+ * smb_sf_packed_bytes(rows, K / 16).  K % 64 == 0; 256-wide tiles, or for M <= 128 the
+ * dual-tile form of the decode kernel. */
 #define SMB_FLAG_SCALE_BLOCK16 16384u
 #define SMB_FLAG_NO_DECODE 64u        /* FP4 only: M <= 128 through the tiled kernel, not the decode kernel */
 #define SMB_FLAG_NO_LAUNCH_OVERLAP 128u /* decode kernel: no programmatic dependent launch */

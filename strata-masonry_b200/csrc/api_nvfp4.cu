@@ -93,7 +93,7 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
     L.w1 = 0;
   }
   p->status_dev = nullptr;
-  p->decode = (M <= 128) && !(flags & SMB_FLAG_NO_DECODE) && !block16;
+  p->decode = (M <= 128) && !(flags & SMB_FLAG_NO_DECODE);
   p->scratch_dev = nullptr;
   p->scratch_bytes = 0;
   p->act_src = nullptr;
@@ -144,6 +144,8 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
     D.max_stages = 0;
     D.no_overlap = (flags & SMB_FLAG_NO_LAUNCH_OVERLAP) != 0;
     D.activations_dynamic = false;
+    D.block16 = block16;
+    D.alpha = 1.0f;
     D.dual = fp4_decode_prefers_dual(M);
     if (flags & SMB_FLAG_DECODE_DUAL) D.dual = true;
     if (flags & SMB_FLAG_DECODE_SINGLE) D.dual = false;
@@ -153,10 +155,10 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
       rc = encode_tmap_2d(&D.tmap_x, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, lda_bytes, m_pad, 128, true);
     if (rc == SMB_OK)
       rc = encode_tmap_2d(&D.tmap_sfw, sfb, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_b, kchunks * 64,
-                          kchunks * 512, 1, 128, false);
+                          kchunks * 512, 1, sf_box, false);
     if (rc == SMB_OK)
       rc = encode_tmap_2d(&D.tmap_sfx, sfa, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_a, kchunks * 64,
-                          kchunks * 512, 1, 128, false);
+                          kchunks * 512, 1, sf_box, false);
     if (rc == SMB_OK) rc = fp4_decode_bind_output(&D, d, M, N, ldd, !(flags & SMB_FLAG_FORCE_PLAIN_STORE));
     if (rc == SMB_OK) {
       // Two partial-sum slots per CTA (one CTA per SM of this device) and one counter per tile.
@@ -210,6 +212,7 @@ extern "C" int smb_fp4_plan_set_alpha(smb_fp4_plan* plan, float alpha) {
   if (!plan->launch.block16)
     return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: the output factor belongs to block-16 plans");
   plan->launch.alpha = alpha;
+  plan->dlaunch.alpha = alpha;
   return SMB_OK;
 }
 
@@ -225,6 +228,9 @@ extern "C" int smb_fp4_plan_create_bf16_activations(smb_fp4_plan** out, const vo
   if (out == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null output handle");
   *out = nullptr;
   if (x_bf16 == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null activation pointer");
+  if (flags & SMB_FLAG_SCALE_BLOCK16)
+    return set_error(SMB_ERR_UNSUPPORTED,
+                     "fp4 plan: the chained activation quantiser produces UE8M0 scales per 32 K only");
   if (M <= 0 || K <= 0 || K % 32 != 0)
     return set_error(SMB_ERR_INVALID, "fp4 plan: bad activation shape (K must be a multiple of 32)");
   if (ldx < K || ldx % 8 != 0 || reinterpret_cast<uintptr_t>(x_bf16) % 16 != 0)

@@ -118,6 +118,8 @@ struct Fp4DecodeLaunch {
   bool no_overlap;   // true: plain stream order, no programmatic dependent launch
   bool activations_dynamic;  // X and its scales are written by the previous kernel on the stream
   bool dual;         // two weight tiles per activation box (whole tile pairs; ignored with max_ctas > 0)
+  bool block16;      // E4M3 scales per 16 K (dual form only); tmap_sfw / tmap_sfx boxes are 256 words
+  float alpha;       // factor on every accumulator (block16 only)
 };
 int fp4_decode_stage_bytes(int m_pad);
 bool fp4_decode_prefers_dual(int M);   // default choice of Fp4DecodeLaunch::dual for M activation rows

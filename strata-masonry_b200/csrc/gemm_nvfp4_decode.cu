@@ -541,15 +541,23 @@ struct DualParams {
   int* status;
   int d_tma;
   int activations_dynamic;
+  float alpha;          // factor on every accumulator (block-16 scales: 1 / (global scale X x W))
 };
 
-constexpr int kDualSlotCols = 24;
 
+// V4: one E4M3 scale per 16 K (scale_vec::4X): four 4-byte scale cells per band and stage
+// instead of two, 2 KiB of scales per band, 48 instead of 24 tensor-memory columns per slot.
+template <bool V4>
 __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x,
                                                  const CUtensorMap& tmap_sfw, const CUtensorMap& tmap_sfx,
                                                  const CUtensorMap& tmap_d, const DualParams& p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  constexpr int kCells = V4 ? 4 : 2;
+  constexpr uint32_t kBandBytes = kCells * 512;            // scales of one 128-row band, one stage
+  constexpr uint32_t kOperandCols = kCells * 4;            // tensor-memory columns of one band
+  constexpr uint32_t kSlotCols = 3 * kOperandCols;         // SFW0 | SFW1 | SFX
+  constexpr int kSfBox = kCells * 64;                      // 64-bit words per band and stage
   const int stages = p.stages;
   const uint32_t ring_base = smem_base;
   const uint32_t stage_base = ring_base + static_cast<uint32_t>(stages * p.stage_bytes);   // D staging
@@ -573,8 +581,8 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
   const uint32_t w1_off = kWBytes;
   const uint32_t x_off = 2 * kWBytes;
   const uint32_t sfw0_off = x_off + static_cast<uint32_t>(p.m_pad) * kBlockKBytes;
-  const uint32_t sfw1_off = sfw0_off + kSfBytes;
-  const uint32_t sfx_off = sfw1_off + kSfBytes;
+  const uint32_t sfw1_off = sfw0_off + kBandBytes;
+  const uint32_t sfx_off = sfw1_off + kBandBytes;
   const uint32_t bank_cols = 2u * static_cast<uint32_t>(p.m_pad);
   const uint32_t slot_base = static_cast<uint32_t>(p.banks) * bank_cols;
 
@@ -629,7 +637,7 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
             const int kbj = (j) % num_kb;
             const uint32_t dstj = ring_base + static_cast<uint32_t>(j * p.stage_bytes);
             if (elect_one()) {
-              tma_load_2d_cta_hint(dstj + sfx_off, &tmap_sfx, sf_full_bar(j), kbj * 128, 0, keep);
+              tma_load_2d_cta_hint(dstj + sfx_off, &tmap_sfx, sf_full_bar(j), kbj * kSfBox, 0, keep);
               tma_load_2d_cta_hint(dstj + x_off, &tmap_x, full_bar(j), kbj * kBlockKBytes, 0, keep);
             }
             __syncwarp();
@@ -643,15 +651,15 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
         }
         const uint32_t dst = ring_base + static_cast<uint32_t>(s * p.stage_bytes);
         if (elect_one()) {
-          mbar_arrive_expect_tx(sf_full_bar(s), 3 * kSfBytes);
-          tma_load_2d_cta_hint(dst + sfw0_off, &tmap_sfw, sf_full_bar(s), kb * 128, 2 * q, stream_once);
-          tma_load_2d_cta_hint(dst + sfw1_off, &tmap_sfw, sf_full_bar(s), kb * 128, 2 * q + 1, stream_once);
+          mbar_arrive_expect_tx(sf_full_bar(s), 3 * kBandBytes);
+          tma_load_2d_cta_hint(dst + sfw0_off, &tmap_sfw, sf_full_bar(s), kb * kSfBox, 2 * q, stream_once);
+          tma_load_2d_cta_hint(dst + sfw1_off, &tmap_sfw, sf_full_bar(s), kb * kSfBox, 2 * q + 1, stream_once);
           mbar_arrive_expect_tx(full_bar(s), op_bytes);
           tma_load_2d_cta_hint(dst, &tmap_w, full_bar(s), kb * kBlockKBytes, (2 * q) * 128, stream_once);
           tma_load_2d_cta_hint(dst + w1_off, &tmap_w, full_bar(s), kb * kBlockKBytes, (2 * q + 1) * 128,
                                stream_once);
           if (waited) {
-            tma_load_2d_cta_hint(dst + sfx_off, &tmap_sfx, sf_full_bar(s), kb * 128, 0, keep);
+            tma_load_2d_cta_hint(dst + sfx_off, &tmap_sfx, sf_full_bar(s), kb * kSfBox, 0, keep);
             tma_load_2d_cta_hint(dst + x_off, &tmap_x, full_bar(s), kb * kBlockKBytes, 0, keep);
           }
         }
@@ -666,7 +674,7 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
         const int kbj = j % num_kb;
         const uint32_t dstj = ring_base + static_cast<uint32_t>(j * p.stage_bytes);
         if (elect_one()) {
-          tma_load_2d_cta_hint(dstj + sfx_off, &tmap_sfx, sf_full_bar(j), kbj * 128, 0, keep);
+          tma_load_2d_cta_hint(dstj + sfx_off, &tmap_sfx, sf_full_bar(j), kbj * kSfBox, 0, keep);
           tma_load_2d_cta_hint(dstj + x_off, &tmap_x, full_bar(j), kbj * kBlockKBytes, 0, keep);
         }
         __syncwarp();
@@ -696,21 +704,26 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
         }
         tc_fence_after_sync();
         const uint32_t stage = ring_base + static_cast<uint32_t>(s * p.stage_bytes);
-        const uint32_t sf_t = tmem_base + slot_base + static_cast<uint32_t>(s * kDualSlotCols);
+        const uint32_t sf_t = tmem_base + slot_base + static_cast<uint32_t>(s) * kSlotCols;
         const uint64_t desc_w0 = make_smem_desc(stage, 1024, 16, kSwizzle128B);
         const uint64_t desc_w1 = make_smem_desc(stage + w1_off, 1024, 16, kSwizzle128B);
         const uint64_t desc_x = make_smem_desc(stage + x_off, 1024, 16, kSwizzle128B);
         if (elect_one()) {
 #pragma unroll
           for (int ki = 0; ki < 4; ++ki) {
-            const uint32_t sf_id = (ki & 1) ? 2u : 0u;
-            const uint32_t cell = static_cast<uint32_t>(ki >> 1);
-            const uint32_t idesc = make_idesc_mxf4(128, p.m_pad, sf_id, sf_id, true);
+            const uint32_t sf_id = V4 ? 0u : ((ki & 1) ? 2u : 0u);
+            const uint32_t cell = static_cast<uint32_t>(V4 ? ki : (ki >> 1));
+            const uint32_t idesc = make_idesc_mxf4(128, p.m_pad, sf_id, sf_id, !V4);
             const uint32_t accum = (kb > 0 || ki > 0) ? 1u : 0u;
-            mma_mxf4_ss<1>(acc0, desc_w0 + 2u * ki, desc_x + 2u * ki, idesc, sf_t + 4u * cell,
-                           sf_t + 16u + 4u * cell, accum);
-            mma_mxf4_ss<1>(acc1, desc_w1 + 2u * ki, desc_x + 2u * ki, idesc, sf_t + 8u + 4u * cell,
-                           sf_t + 16u + 4u * cell, accum);
+            const uint32_t s0 = sf_t + 4u * cell, s1 = sf_t + kOperandCols + 4u * cell;
+            const uint32_t sx = sf_t + 2u * kOperandCols + 4u * cell;
+            if (V4) {
+              mma_nvf4_ss<1>(acc0, desc_w0 + 2u * ki, desc_x + 2u * ki, idesc, s0, sx, accum);
+              mma_nvf4_ss<1>(acc1, desc_w1 + 2u * ki, desc_x + 2u * ki, idesc, s1, sx, accum);
+            } else {
+              mma_mxf4_ss<1>(acc0, desc_w0 + 2u * ki, desc_x + 2u * ki, idesc, s0, sx, accum);
+              mma_mxf4_ss<1>(acc1, desc_w1 + 2u * ki, desc_x + 2u * ki, idesc, s1, sx, accum);
+            }
           }
           mma_commit_1cta(empty_bar(s));
         }
@@ -732,16 +745,16 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
       }
       tc_fence_after_sync();
       const uint32_t stage = ring_base + static_cast<uint32_t>(s * p.stage_bytes);
-      const uint32_t sf_t = tmem_base + slot_base + static_cast<uint32_t>(s * kDualSlotCols);
+      const uint32_t sf_t = tmem_base + slot_base + static_cast<uint32_t>(s) * kSlotCols;
       const uint64_t d0 = make_smem_desc(stage + sfw0_off, 128, 16, kSwizzleNone);
       const uint64_t d1 = make_smem_desc(stage + sfw1_off, 128, 16, kSwizzleNone);
       const uint64_t dx = make_smem_desc(stage + sfx_off, 128, 16, kSwizzleNone);
       if (elect_one()) {
 #pragma unroll
-        for (int cell = 0; cell < 2; ++cell) {
+        for (int cell = 0; cell < kCells; ++cell) {
           tmem_cp_32x128b_warpx4<1>(sf_t + 4u * cell, d0 + cell * 32);
-          tmem_cp_32x128b_warpx4<1>(sf_t + 8u + 4u * cell, d1 + cell * 32);
-          tmem_cp_32x128b_warpx4<1>(sf_t + 16u + 4u * cell, dx + cell * 32);
+          tmem_cp_32x128b_warpx4<1>(sf_t + kOperandCols + 4u * cell, d1 + cell * 32);
+          tmem_cp_32x128b_warpx4<1>(sf_t + 2u * kOperandCols + 4u * cell, dx + cell * 32);
         }
         mma_commit_1cta(sf_ready_bar(s));
       }
@@ -781,6 +794,10 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
             for (int c = c0; c < c0 + chunk_rows && c < p.m_pad; c += 16) {
               float v[16];
               ld16(taddr + c, v);
+              if (V4) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
+              }
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const uint32_t dst = stage_base + static_cast<uint32_t>((c - c0 + j) * 256 + row * 2);
@@ -799,6 +816,10 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
           for (int c = 0; c < p.m_pad; c += 16) {
             float v[16];
             ld16(taddr + c, v);
+            if (V4) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
+            }
             if (n < p.N) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
@@ -823,6 +844,7 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
   }
 }
 
+template <bool V4>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_nvfp4_decode_dual_kernel(const __grid_constant__ CUtensorMap tmap_w,
                               const __grid_constant__ CUtensorMap tmap_x,
@@ -830,7 +852,7 @@ gemm_nvfp4_decode_dual_kernel(const __grid_constant__ CUtensorMap tmap_w,
                               const __grid_constant__ CUtensorMap tmap_sfx,
                               const __grid_constant__ CUtensorMap tmap_d,
                               const __grid_constant__ DualParams p) {
-  decode_dual_body(tmap_w, tmap_x, tmap_sfw, tmap_sfx, tmap_d, p);
+  decode_dual_body<V4>(tmap_w, tmap_x, tmap_sfw, tmap_sfx, tmap_d, p);
 }
 
 }  // namespace fp4d
@@ -850,15 +872,18 @@ int fp4_decode_box_rows(int M) {
 
 namespace {
 
+template <bool V4>
 int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
+  constexpr int kBandBytes = V4 ? 2048 : 1024;
+  constexpr int kSlotCols = V4 ? 48 : 24;
+  auto kernel = fp4d::gemm_nvfp4_decode_dual_kernel<V4>;
   static thread_local int configured_device = -1;
   static thread_local int sm_count = 0;
   constexpr int kSmemBudget = 227 * 1024;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return set_error(SMB_ERR_CUDA, "cudaGetDevice failed");
   if (configured_device != dev) {
-    cudaError_t e = cudaFuncSetAttribute(fp4d::gemm_nvfp4_decode_dual_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return set_cuda_error(e, "decode (dual) kernel setup");
     configured_device = dev;
@@ -868,14 +893,14 @@ int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   p.N = L.N;
   p.K = L.K;
   p.m_pad = (L.M + 15) / 16 * 16;
-  p.stage_bytes = 2 * fp4d::kWBytes + p.m_pad * fp4d::kBlockKBytes + 3 * fp4d::kSfBytes;
+  p.stage_bytes = 2 * fp4d::kWBytes + p.m_pad * fp4d::kBlockKBytes + 3 * kBandBytes;
   const int staging = fp4_decode_box_rows(L.M) * 256;
   int stages = (kSmemBudget - 1024 - fp4d::kBarrierBytes - staging) / p.stage_bytes;
   if (stages > fp4d::kMaxStages) stages = fp4d::kMaxStages;
   // Two accumulator banks (a tile pair is drained while the next one is multiplied) when they fit
   // beside at least three scale slots, else one.
-  p.banks = (4 * p.m_pad + 3 * fp4d::kDualSlotCols <= 512) ? 2 : 1;
-  const int max_slots = (512 - p.banks * 2 * p.m_pad) / fp4d::kDualSlotCols;
+  p.banks = (4 * p.m_pad + 3 * kSlotCols <= 512) ? 2 : 1;
+  const int max_slots = (512 - p.banks * 2 * p.m_pad) / kSlotCols;
   if (stages > max_slots) stages = max_slots;
   if (L.max_stages > 0 && stages > L.max_stages) stages = L.max_stages;
   if (stages < 2) return set_error(SMB_ERR_UNSUPPORTED, "decode (dual): activation tile too large");
@@ -885,6 +910,7 @@ int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   p.status = L.status;
   p.d_tma = L.d_tma ? 1 : 0;
   p.activations_dynamic = L.activations_dynamic ? 1 : 0;
+  p.alpha = L.alpha;
   const int pairs = ((L.N + 127) / 128 + 1) / 2;
   p.pairs_per_cta = (pairs + sm_count - 1) / sm_count;
   const int grid = (pairs + p.pairs_per_cta - 1) / p.pairs_per_cta;
@@ -898,8 +924,7 @@ int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   attr.val.programmaticStreamSerializationAllowed = L.no_overlap ? 0 : 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, fp4d::gemm_nvfp4_decode_dual_kernel, L.tmap_w, L.tmap_x,
-                                     L.tmap_sfw, L.tmap_sfx, L.tmap_d, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L.tmap_w, L.tmap_x, L.tmap_sfw, L.tmap_sfx, L.tmap_d, p);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error(e, "nvfp4 decode (dual) launch");
   return SMB_OK;
@@ -912,7 +937,8 @@ bool fp4_decode_prefers_dual(int M) { return (M + 15) / 16 * 16 >= fp4d::kDualFr
 int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   // The dual-tile form has whole tile pairs only: a caller that asks for a CTA count gets the
   // stream-K ranges of the single form.
-  if (L.dual && L.max_ctas == 0) return fp4_decode_dual_launch(L, stream);
+  if (L.block16) return fp4_decode_dual_launch<true>(L, stream);   // this format has the dual form only
+  if (L.dual && L.max_ctas == 0) return fp4_decode_dual_launch<false>(L, stream);
   static thread_local int configured_device = -1;
   static thread_local int sm_count = 0;
   constexpr int kSmemBudget = 227 * 1024;
@@ -1088,6 +1114,8 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
   L.max_stages = 0;
   L.activations_dynamic = false;
   L.dual = fp4_decode_prefers_dual(M);
+  L.block16 = false;
+  L.alpha = 1.0f;
   L.no_overlap = true;   // the memset below must be ordered before every access of this launch
   L.scratch = static_cast<float*>(base);
   L.scratch_ctas = ctas;

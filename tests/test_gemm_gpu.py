@@ -688,7 +688,8 @@ def _nvf4_operand(smb, oracle, rows, k, seed, sigma=1.0):
 
 
 @pytest.mark.parametrize("shape", [(256, 256, 256), (512, 768, 1024), (300, 200, 192), (64, 1024, 512),
-                                   (2048, 2048, 4096)])
+                                   (2048, 2048, 4096), (16, 4096, 2048), (128, 2304, 1024), (100, 1100, 192),
+                                   (1, 128, 64)])
 def test_nvf4_block16_gemm(smb, oracle, cuda_device, shape):
     """NVFP4 proper (E4M3 scale per 16 K, scale_vec::4X, per-tensor factors folded into alpha):
     device quantiser bit-identical to the oracle, GEMM within the north-star bound of the float64
