@@ -143,6 +143,17 @@ int smb_bf16_plan_run(smb_bf16_plan* plan, void* stream);
  * the role that gave up in smb_last_error(). */
 int smb_bf16_plan_check(smb_bf16_plan* plan, void* stream);
 int smb_bf16_plan_destroy(smb_bf16_plan* plan);
+/* Grouped GEMM for mixture-of-experts layers ("shared N and K, varying M", the case of the
+ * reference's tile map composites/83_grouped_gemm_tile_map.cuh:71-101, which no kernel of its
+ * tree uses): A [M_total, K] holds the rows of all groups back to back, every group padded to a
+ * multiple of 256 rows; BT is [groups, N, K] stacked as [groups * N, K]; D is [M_total, N];
+ * mtile_group_dev[t] (device memory, M_total / 256 ints, valid for the life of the plan) is the
+ * group of rows [256 t, 256 t + 256).  Row r of D is A[r] times the BT of r's group.  Contiguous
+ * operands (lda = ldb = K, ldd = N); run, check, destroy, peer copies and the gated epilogue as
+ * for any other plan. */
+int smb_bf16_grouped_plan_create(smb_bf16_plan** plan, const void* a, const void* bt_stacked, void* d,
+                                 int M_total, int N, int K, int groups, const int* mtile_group_dev,
+                                 unsigned flags);
 /* Tuning knobs (tests and sweeps): raster group height in tiles (0 = default), cap on
  * clusters (0 = all that fit). */
 int smb_bf16_plan_tune(smb_bf16_plan* plan, int group_m, int max_clusters);

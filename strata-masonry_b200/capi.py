@@ -63,6 +63,7 @@ DECLARED = [
     ("smb_debug_tile_coords", None, [_i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
     ("smb_debug_sf_offset", _u64, [_u32, _u32, _u32]),
     ("smb_bf16_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, C.c_uint]),
+    ("smb_bf16_grouped_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, _i, _vp, C.c_uint]),
     ("smb_bf16_plan_run", _i, [_vp, _vp]),
     ("smb_bf16_plan_check", _i, [_vp, _vp]),
     ("smb_bf16_plan_destroy", _i, [_vp]),

@@ -45,7 +45,7 @@ namespace {
 // word), or null for a word owned by the plan.
 int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, void* d, int M, int N,
                           int K, int64_t lda, int64_t ldb, int64_t ldd, unsigned flags,
-                          int* shared_status) {
+                          int* shared_status, int groups = 1, const int* mtile_group = nullptr) {
   if (out == nullptr) return set_error(SMB_ERR_INVALID, "plan: null output handle");
   *out = nullptr;
   if (a == nullptr || bt == nullptr || d == nullptr)
@@ -83,6 +83,7 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
   L.operands_static = (flags & (SMB_FLAG_OPERANDS_STATIC | SMB_FLAG_LAUNCH_INDEPENDENT)) != 0;
   L.output_independent = (flags & SMB_FLAG_LAUNCH_INDEPENDENT) != 0;
   L.peers.count = 0;
+  L.mtile_group = mtile_group;
   L.d = d;
   L.ldd = static_cast<int>(ldd);
   L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
@@ -100,8 +101,8 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
 
   int rc = encode_tmap_2d(&L.tmap_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda * 2, 128, 64, true);
   if (rc == SMB_OK)
-    rc = encode_tmap_2d(&L.tmap_b, bt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb * 2,
-                        L.tile_n / 2, 64, true);
+    rc = encode_tmap_2d(&L.tmap_b, bt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                        static_cast<uint64_t>(groups) * N, K, ldb * 2, L.tile_n / 2, 64, true);
   if (rc == SMB_OK) {
     if (L.tma_store) {
       rc = encode_tmap_2d(&L.tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, n_out, ldd * 2, 32, 64, true);
@@ -133,6 +134,20 @@ extern "C" int smb_bf16_plan_create(smb_bf16_plan** out, const void* a, const vo
                                     int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd,
                                     unsigned flags) {
   return bf16_plan_create_impl(out, a, bt, d, M, N, K, lda, ldb, ldd, flags, nullptr);
+}
+
+extern "C" int smb_bf16_grouped_plan_create(smb_bf16_plan** out, const void* a, const void* bt_stacked,
+                                            void* d, int M_total, int N, int K, int groups,
+                                            const int* mtile_group_dev, unsigned flags) {
+  if (groups < 1) return set_error(SMB_ERR_INVALID, "grouped plan: at least one group");
+  if (mtile_group_dev == nullptr) return set_error(SMB_ERR_INVALID, "grouped plan: null tile-to-group map");
+  if (M_total <= 0 || M_total % 256 != 0)
+    return set_error(SMB_ERR_UNSUPPORTED,
+                     "grouped plan: every group's rows must be padded to a multiple of 256 (M_total=%d)", M_total);
+  if (static_cast<long long>(groups) * N > 0x7FFFFFFFLL)
+    return set_error(SMB_ERR_UNSUPPORTED, "grouped plan: groups * N too large");
+  return bf16_plan_create_impl(out, a, bt_stacked, d, M_total, N, K, K, K, N, flags, nullptr, groups,
+                               mtile_group_dev);
 }
 
 extern "C" int smb_bf16_plan_tune(smb_bf16_plan* plan, int group_m, int max_clusters) {

@@ -73,6 +73,7 @@ struct Params {
   long long* prof;    // optional: 8 cycle counters per CTA (see kProf* below), or null
   int dynamic;        // 1: tiles come from the hardware work queue (one cluster launched per tile)
   PeerCopies peers;     // extra destinations of every stored box (count 0: none)
+  const int* mtile_group;  // grouped GEMM: group of every 256-row tile of A (device), or null
   int operands_static;  // 1: A and BT are not written by the previous kernel on the stream
 };
 
@@ -175,7 +176,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
-        const int row_b = tn * C::kTileN + static_cast<int>(rank) * (TN / 2);
+        // Grouped GEMM: BT is [groups * N, K]; the rows of this 256-row tile of A belong to one
+        // group (every group's row count is a multiple of 256) and meet that group's N rows.
+        const int group_row = p.mtile_group != nullptr ? __ldg(p.mtile_group + tm) * p.N : 0;
+        const int row_b = group_row + tn * C::kTileN + static_cast<int>(rank) * (TN / 2);
         for (int kb = 0; kb < num_kb; ++kb) {
           const long long w0 = prof ? clock64() : 0;
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
@@ -406,6 +410,7 @@ int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
   p.prof = L.prof;
   p.operands_static = L.operands_static ? (L.output_independent ? 2 : 1) : 0;
   p.peers = L.peers;
+  p.mtile_group = L.mtile_group;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (L.max_clusters > 0 && clusters > L.max_clusters) clusters = L.max_clusters;

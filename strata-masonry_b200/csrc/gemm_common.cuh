@@ -71,6 +71,7 @@ struct Bf16Launch {
   bool operands_static;  // loads need not wait for the previous kernel on the stream
   bool output_independent;  // with operands_static: stores need not wait either
   PeerCopies peers;
+  const int* mtile_group;  // grouped GEMM (device array, one group id per 256-row tile of A), or null
 };
 void bf16_pick_tile(int M, int N, int K, int clusters, int* tile_n, int* sub_blocks);
 // Number of 2-CTA clusters that can run at once on the current device (SM count / 2), 0 if unknown.

@@ -69,6 +69,20 @@ class Bf16Plan:
             C.byref(self._h), _ptr(a), _ptr(bt), _ptr(d), m, n, k,
             k if lda is None else lda, k if ldb is None else ldb, n if ldd is None else ldd, flags))
 
+    @classmethod
+    def grouped(cls, a, bt_stacked, d, m_total: int, n: int, k: int, groups: int, mtile_group, flags: int = 0):
+        """Grouped (mixture-of-experts) GEMM: rows of A sorted by group, every group padded to a
+        multiple of 256 rows; `mtile_group` is a device int32 array with the group of every
+        256-row tile."""
+        self = cls.__new__(cls)
+        self._lib = capi.lib()
+        self._h = C.c_void_p()
+        self.shape = (m_total, n, k)
+        self._keep = (a, bt_stacked, d, mtile_group)
+        capi.check(self._lib.smb_bf16_grouped_plan_create(
+            C.byref(self._h), _ptr(a), _ptr(bt_stacked), _ptr(d), m_total, n, k, groups, _ptr(mtile_group), flags))
+        return self
+
     def tune(self, group_m: int = 0, max_clusters: int = 0) -> None:
         capi.check(self._lib.smb_bf16_plan_tune(self._h, group_m, max_clusters))
 

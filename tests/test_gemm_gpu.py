@@ -720,3 +720,33 @@ def test_nvf4_block16_is_refused_where_it_cannot_work(smb, cuda_device):
     with pytest.raises(smb.capi.SmbError):     # alpha belongs to block-16 plans
         plain.set_alpha(0.5)
     plain.close()
+
+
+# ------------------------------------------------------------------------------- grouped GEMM
+@pytest.mark.parametrize("case", [((512, 256, 0, 768), 384, 256, "FLAG_NONE"),
+                                  ((256, 256, 256, 256, 512, 1024, 256, 256), 1000, 512, "FLAG_NONE"),
+                                  ((2048, 4096), 2048, 1024, "FLAG_TILE_N_512"),
+                                  ((256, 512), 130, 64, "FLAG_TILE_N_128")])
+def test_bf16_grouped_gemm(smb, oracle, cuda_device, case):
+    """Mixture-of-experts form: rows of A sorted by group (each padded to 256 rows), one BT per
+    group; every row block must meet its own group's weights."""
+    torch = _torch()
+    rows, n, k, name = case
+    groups = len(rows)
+    m_total = sum(rows)
+    a = torch.empty(m_total, k, device=cuda_device, dtype=torch.bfloat16)
+    bt = torch.empty(groups * n, k, device=cuda_device, dtype=torch.bfloat16)
+    smb.gemm.fill_bf16_device(a, m_total, k, 5, 1, 0, k, 1)
+    smb.gemm.fill_bf16_device(bt, groups * n, k, 5, 2, 0, k, 1)
+    tile_group = torch.tensor([g for g, r in enumerate(rows) for _ in range(r // 256)], device=cuda_device,
+                              dtype=torch.int32)
+    d = torch.full((m_total, n), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    plan = smb.gemm.Bf16Plan.grouped(a, bt, d, m_total, n, k, groups, tile_group, flags=getattr(smb.capi, name))
+    plan.run(); plan.run(); plan.check(); plan.close()
+    row0 = 0
+    for g, r in enumerate(rows):
+        if r:
+            _check_bf16_full(oracle, a[row0:row0 + r], bt[g * n:(g + 1) * n], d[row0:row0 + r], n, k)
+        row0 += r
+    lib = smb.capi.lib()
+    assert lib.smb_bf16_grouped_plan_create(None, None, None, None, 300, 128, 64, 1, None, 0) == smb.capi.SMB_ERR_INVALID
