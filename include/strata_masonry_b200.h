@@ -211,6 +211,12 @@ int smb_fp4_plan_create_bf16_activations(smb_fp4_plan** plan, const void* x_bf16
 /* Factor applied to every accumulator before the result is rounded to bf16; plans created with
  * SMB_FLAG_SCALE_BLOCK16 only (the product of the operands' inverse per-tensor factors). */
 int smb_fp4_plan_set_alpha(smb_fp4_plan* plan, float alpha);
+/* Grouped FP4 GEMM, the FP4 twin of smb_bf16_grouped_plan_create: B [groups * N, K/2] and its
+ * scales (packed over all groups * N rows) stacked, N % 128 == 0, every group of A padded to a
+ * multiple of 256 rows; SMB_FLAG_SCALE_BLOCK16 and the gated epilogue apply as usual. */
+int smb_fp4_grouped_plan_create(smb_fp4_plan** plan, const void* a, const void* sfa, const void* b_stacked,
+                                const void* sfb_stacked, void* d, int M_total, int N, int K, int groups,
+                                const int* mtile_group_dev, unsigned flags);
 int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_destroy(smb_fp4_plan* plan);

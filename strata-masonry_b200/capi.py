@@ -78,6 +78,8 @@ DECLARED = [
     ("smb_fp4_plan_create_bf16_activations", _i,
      [C.POINTER(_vp), _vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, C.c_uint]),
     ("smb_fp4_plan_set_alpha", _i, [_vp, C.c_float]),
+    ("smb_fp4_grouped_plan_create", _i,
+     [C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, C.c_uint]),
     ("smb_fp4_plan_run", _i, [_vp, _vp]),
     ("smb_fp4_plan_check", _i, [_vp, _vp]),
     ("smb_fp4_plan_destroy", _i, [_vp]),

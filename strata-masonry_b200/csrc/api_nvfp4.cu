@@ -28,9 +28,11 @@ struct smb_fp4_plan {
   void* act_sf;
 };
 
-extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void* sfa, const void* b,
-                                   const void* sfb, void* d, int M, int N, int K, int64_t lda_bytes,
-                                   int64_t ldb_bytes, int64_t ldd, unsigned flags) {
+namespace {
+
+int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, const void* b, const void* sfb,
+                         void* d, int M, int N, int K, int64_t lda_bytes, int64_t ldb_bytes, int64_t ldd,
+                         unsigned flags, int groups, const int* mtile_group) {
   if (out == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null output handle");
   *out = nullptr;
   if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || d == nullptr)
@@ -72,6 +74,7 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
   L.operands_static = (flags & (SMB_FLAG_OPERANDS_STATIC | SMB_FLAG_LAUNCH_INDEPENDENT)) != 0;
   L.output_independent = (flags & SMB_FLAG_LAUNCH_INDEPENDENT) != 0;
   L.peers.count = 0;
+  L.mtile_group = mtile_group;
   L.d = d;
   L.ldd = static_cast<int>(ldd);
   L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
@@ -93,7 +96,7 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
     L.w1 = 0;
   }
   p->status_dev = nullptr;
-  p->decode = (M <= 128) && !(flags & SMB_FLAG_NO_DECODE);
+  p->decode = (M <= 128) && !(flags & SMB_FLAG_NO_DECODE) && mtile_group == nullptr;
   p->scratch_dev = nullptr;
   p->scratch_bytes = 0;
   p->act_src = nullptr;
@@ -105,14 +108,15 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
   const uint64_t kchunks = block16 ? static_cast<uint64_t>(K) / 64 : (static_cast<uint64_t>(K) / 32 + 3) / 4;
   const uint32_t sf_box = block16 ? 256 : 128;
   const uint64_t bands_a = (static_cast<uint64_t>(M) + 127) / 128;
-  const uint64_t bands_b = (static_cast<uint64_t>(N) + 127) / 128;
+  const uint64_t rows_b = static_cast<uint64_t>(groups) * N;   // B (and its scales) of all groups stacked
+  const uint64_t bands_b = (rows_b + 127) / 128;
   const int tile_n = L.w0 + L.w1;
   int rc = encode_tmap_2d(&L.tmap_a, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, lda_bytes, 128, 128, true);
   if (rc == SMB_OK)
-    rc = encode_tmap_2d(&L.tmap_b0, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, ldb_bytes, L.w0 / 2, 128, true);
+    rc = encode_tmap_2d(&L.tmap_b0, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows_b, K / 2, ldb_bytes, L.w0 / 2, 128, true);
   if (rc == SMB_OK) {
     if (L.w1 > 0)
-      rc = encode_tmap_2d(&L.tmap_b1, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, ldb_bytes, L.w1 / 2, 128, true);
+      rc = encode_tmap_2d(&L.tmap_b1, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows_b, K / 2, ldb_bytes, L.w1 / 2, 128, true);
     else
       L.tmap_b1 = L.tmap_b0;
   }
@@ -184,6 +188,34 @@ extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void
   p->dlaunch.status = p->status_dev;
   *out = p;
   return SMB_OK;
+}
+
+}  // namespace
+
+extern "C" int smb_fp4_plan_create(smb_fp4_plan** out, const void* a, const void* sfa, const void* b,
+                                   const void* sfb, void* d, int M, int N, int K, int64_t lda_bytes,
+                                   int64_t ldb_bytes, int64_t ldd, unsigned flags) {
+  return fp4_plan_create_impl(out, a, sfa, b, sfb, d, M, N, K, lda_bytes, ldb_bytes, ldd, flags, 1, nullptr);
+}
+
+extern "C" int smb_fp4_grouped_plan_create(smb_fp4_plan** out, const void* a, const void* sfa,
+                                           const void* b_stacked, const void* sfb_stacked, void* d,
+                                           int M_total, int N, int K, int groups, const int* mtile_group_dev,
+                                           unsigned flags) {
+  if (groups < 1) return set_error(SMB_ERR_INVALID, "grouped fp4 plan: at least one group");
+  if (mtile_group_dev == nullptr)
+    return set_error(SMB_ERR_INVALID, "grouped fp4 plan: null tile-to-group map");
+  if (M_total <= 0 || M_total % 256 != 0)
+    return set_error(SMB_ERR_UNSUPPORTED,
+                     "grouped fp4 plan: every group's rows must be padded to a multiple of 256 (M_total=%d)",
+                     M_total);
+  if (N % 128 != 0)
+    return set_error(SMB_ERR_UNSUPPORTED,
+                     "grouped fp4 plan: N=%d must be a multiple of 128 (scale bands of the stacked B)", N);
+  if (static_cast<long long>(groups) * N > 0x7FFFFFFFLL)
+    return set_error(SMB_ERR_UNSUPPORTED, "grouped fp4 plan: groups * N too large");
+  return fp4_plan_create_impl(out, a, sfa, b_stacked, sfb_stacked, d, M_total, N, K, K / 2, K / 2, N, flags,
+                              groups, mtile_group_dev);
 }
 
 extern "C" int smb_fp4_plan_tune(smb_fp4_plan* plan, int group_m, int max_clusters, int prefetch) {

@@ -96,6 +96,7 @@ struct Fp4Launch {
   bool operands_static;  // loads need not wait for the previous kernel on the stream
   bool output_independent;  // with operands_static: stores need not wait either
   PeerCopies peers;
+  const int* mtile_group;  // grouped GEMM (device array, one group id per 256-row tile of A), or null
   bool block16;      // NVFP4 proper: UE4M3 scales per 16 K (256-wide tiles only)
   float alpha;       // factor on every accumulator (block16 only; 1 otherwise)
 };

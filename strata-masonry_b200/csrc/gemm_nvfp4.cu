@@ -92,6 +92,7 @@ struct Params {
   int prefetch;   // L2 prefetch distance in K blocks (0 = off)
   int dynamic;    // 1: tiles come from the hardware work queue (one cluster launched per tile)
   PeerCopies peers;     // extra destinations of every stored box (count 0: none)
+  const int* mtile_group;  // grouped GEMM: group of every 256-row tile of A (device), or null
   float alpha;          // factor on every accumulator (block-16 variant: 1 / (global scale A x B))
   int operands_static;  // 1: operands and scales are not written by the previous kernel on the stream
 };
@@ -205,7 +206,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
         const int col0 = tn * C::kTileN;
         const int band_a = tm * 2 + static_cast<int>(rank);     // 128-row band of SFA
-        const int band_b = col0 / 128;                          // first 128-row band of SFB
+        // Grouped GEMM: B and its scales are stacked [groups * N, ...] (N % 128 == 0); this tile of
+        // A belongs to one group and meets that group's N rows.
+        const int group_row = p.mtile_group != nullptr ? __ldg(p.mtile_group + tm) * p.N : 0;
+        const int band_b = (group_row + col0) / 128;            // first 128-row band of SFB
         const bool has_sub1 = (C::kSubs == 2) && (col0 + W0 < p.N);   // else: right edge of D
         for (int kb = 0; kb < num_kb; ++kb) {
           const long long w0 = prof ? clock64() : 0;
@@ -233,17 +237,17 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tma_load_2d_pair(dst + C::kOffSfb, &tmap_sfb, sf_bar, kb * (kCells * 64), band_b);
           tma_load_2d_pair(dst, &tmap_a, bar, kb * kBlockKBytes, row_a);
           tma_load_2d_pair(dst + C::kOffB0, &tmap_b0, bar, kb * kBlockKBytes,
-                           col0 + static_cast<int>(rank) * (W0 / 2));
+                           group_row + col0 + static_cast<int>(rank) * (W0 / 2));
           if (C::kSubs == 2 && has_sub1) {
             tma_load_2d_pair(dst + C::kOffB1, &tmap_b1, bar, kb * kBlockKBytes,
-                             col0 + W0 + static_cast<int>(rank) * (W1 / 2));
+                             group_row + col0 + W0 + static_cast<int>(rank) * (W1 / 2));
           }
           if (p.prefetch > 0 && kb + p.prefetch < num_kb) {
             const int kp = (kb + p.prefetch) * kBlockKBytes;
             tma_prefetch_l2_2d(&tmap_a, kp, row_a);
-            tma_prefetch_l2_2d(&tmap_b0, kp, col0 + static_cast<int>(rank) * (W0 / 2));
+            tma_prefetch_l2_2d(&tmap_b0, kp, group_row + col0 + static_cast<int>(rank) * (W0 / 2));
             if (C::kSubs == 2 && has_sub1)
-              tma_prefetch_l2_2d(&tmap_b1, kp, col0 + W0 + static_cast<int>(rank) * (W1 / 2));
+              tma_prefetch_l2_2d(&tmap_b1, kp, group_row + col0 + W0 + static_cast<int>(rank) * (W1 / 2));
           }
           }
           __syncwarp();
@@ -511,6 +515,7 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   p.prof = L.prof;
   p.operands_static = L.operands_static ? (L.output_independent ? 2 : 1) : 0;
   p.peers = L.peers;
+  p.mtile_group = L.mtile_group;
   p.alpha = L.alpha;
   p.prefetch = L.prefetch;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;

@@ -234,6 +234,20 @@ class Fp4Plan:
             n if ldd is None else ldd, flags))
 
     @classmethod
+    def grouped(cls, a, sfa, b_stacked, sfb_stacked, d, m_total: int, n: int, k: int, groups: int, mtile_group,
+                flags: int = 0):
+        """Grouped (mixture-of-experts) FP4 GEMM; see Bf16Plan.grouped."""
+        self = cls.__new__(cls)
+        self._lib = capi.lib()
+        self._h = C.c_void_p()
+        self.shape = (m_total, n, k)
+        self._keep = (a, sfa, b_stacked, sfb_stacked, d, mtile_group)
+        capi.check(self._lib.smb_fp4_grouped_plan_create(
+            C.byref(self._h), _ptr(a), _ptr(sfa), _ptr(b_stacked), _ptr(sfb_stacked), _ptr(d), m_total, n, k,
+            groups, _ptr(mtile_group), flags))
+        return self
+
+    @classmethod
     def from_bf16_activations(cls, x, b, sfb, d, m: int, n: int, k: int, ldx: int | None = None,
                               ldb_bytes: int | None = None, ldd: int | None = None, flags: int = 0):
         """Plan whose every run first quantises the BF16 activations `x` [M, K] on the device."""

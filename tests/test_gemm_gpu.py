@@ -750,3 +750,28 @@ def test_bf16_grouped_gemm(smb, oracle, cuda_device, case):
         row0 += r
     lib = smb.capi.lib()
     assert lib.smb_bf16_grouped_plan_create(None, None, None, None, 300, 128, 64, 1, None, 0) == smb.capi.SMB_ERR_INVALID
+
+
+@pytest.mark.parametrize("case", [((512, 0, 256, 768), 384, 512, "FLAG_NONE"), ((256, 1024), 1024, 1024, "FLAG_TILE_N_256"),
+                                  ((256, 256, 512), 128, 256, "FLAG_NONE")])
+def test_fp4_grouped_gemm(smb, cuda_device, case):
+    """FP4 twin of the grouped BF16 test: B and its scales stacked over the groups."""
+    torch = _torch()
+    rows, n, k, name = case
+    groups, m_total = len(rows), sum(rows)
+    a, sfa, sfar = _fp4_operand(smb, m_total, k, 5, 0)
+    b, sfb, sfbr = _fp4_operand(smb, groups * n, k, 5, 1)
+    tile_group = torch.tensor([g for g, r in enumerate(rows) for _ in range(r // 256)], device=cuda_device,
+                              dtype=torch.int32)
+    d = torch.full((m_total, n), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    plan = smb.gemm.Fp4Plan.grouped(a, sfa, b, sfb, d, m_total, n, k, groups, tile_group,
+                                    flags=getattr(smb.capi, name))
+    plan.run(); plan.check(); plan.close()
+    row0 = 0
+    for g, r in enumerate(rows):
+        if r:
+            _check_fp4_full((a[row0:row0 + r], sfar[row0:row0 + r]), (b[g * n:(g + 1) * n], sfbr[g * n:(g + 1) * n]),
+                            d[row0:row0 + r], k)
+        row0 += r
+    with pytest.raises(smb.capi.SmbError):     # N must keep the scale bands of the groups apart
+        smb.gemm.Fp4Plan.grouped(a, sfa, b, sfb, d, m_total, 200, k, groups, tile_group)
