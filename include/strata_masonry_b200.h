@@ -272,6 +272,23 @@ size_t smb_decode_noalloc_scratch_limit(void);
 int smb_bf16_plan_set_peer_copies(smb_bf16_plan* plan, int count, void* const* dst, int64_t ld);
 int smb_fp4_plan_set_peer_copies(smb_fp4_plan* plan, int count, void* const* dst, int64_t ld);
 
+/* Fused scatter of a reduce-scatter: for the K-sharded (row-parallel) form, where every rank
+ * computes a partial product over its slice of K and rank b is to own rows [b R, (b + 1) R) of
+ * the sum.  With a row route set the plan does not write its D: rows of block b go to dst[b]
+ * (<= 8 blocks), at their row inside the block, with plain 16-byte stores, dst[b] normally a
+ * slot reserved for this rank inside rank b's receive buffer, mapped with smb_peer_open().
+ * rows_per_block R % 256 == 0, blocks * R >= M; ld, N, alignment as for peer copies.
+ * blocks = 0 switches the route off.  Once all ranks' kernels have completed, rank b adds its
+ * g slots up with smb_sum_slots_bf16_device (fp32 accumulation in slot order, one bf16
+ * rounding; the partial products themselves were rounded to bf16 when they were stored). */
+int smb_bf16_plan_set_row_route(smb_bf16_plan* plan, int blocks, void* const* dst, int rows_per_block,
+                                int64_t ld);
+int smb_fp4_plan_set_row_route(smb_fp4_plan* plan, int blocks, void* const* dst, int rows_per_block,
+                               int64_t ld);
+/* d[i] = bf16(sum_s slots[s][i]) for `count` consecutive slots of `elems` bf16 each (elems % 8
+ * == 0, 16-byte-aligned buffers).  Stream-ordered. */
+int smb_sum_slots_bf16_device(const void* slots, void* d, int count, int64_t elems, void* stream);
+
 /* Device memory that other processes of the box can map: allocate, export a 64-byte handle
  * (send it to the peers by any host channel), map a peer's handle into this process, unmap,
  * free.  A mapped pointer is valid for kernels and copies of this process; peer access over

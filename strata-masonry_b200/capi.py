@@ -91,6 +91,9 @@ DECLARED = [
     ("smb_decode_noalloc_scratch_limit", C.c_size_t, []),
     ("smb_bf16_plan_set_peer_copies", _i, [_vp, _i, C.POINTER(_vp), _i64]),
     ("smb_fp4_plan_set_peer_copies", _i, [_vp, _i, C.POINTER(_vp), _i64]),
+    ("smb_bf16_plan_set_row_route", _i, [_vp, _i, C.POINTER(_vp), _i, _i64]),
+    ("smb_fp4_plan_set_row_route", _i, [_vp, _i, C.POINTER(_vp), _i, _i64]),
+    ("smb_sum_slots_bf16_device", _i, [_vp, _vp, _i, _i64, _vp]),
     ("smb_peer_alloc", _i, [C.POINTER(_vp), C.c_size_t]),
     ("smb_peer_export", _i, [_vp, C.c_char_p]),
     ("smb_peer_open", _i, [C.c_char_p, C.POINTER(_vp)]),
@@ -101,6 +104,7 @@ DECLARED = [
 
 PEER_HANDLE_BYTES = 64
 MAX_PEER_COPIES = 7
+MAX_ROUTE_BLOCKS = 8
 
 
 class SmbError(RuntimeError):

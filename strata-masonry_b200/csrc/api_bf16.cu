@@ -83,6 +83,7 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
   L.operands_static = (flags & (SMB_FLAG_OPERANDS_STATIC | SMB_FLAG_LAUNCH_INDEPENDENT)) != 0;
   L.output_independent = (flags & SMB_FLAG_LAUNCH_INDEPENDENT) != 0;
   L.peers.count = 0;
+  L.peers.route_rows = 0;
   L.mtile_group = mtile_group;
   L.d = d;
   L.ldd = static_cast<int>(ldd);
@@ -163,6 +164,13 @@ extern "C" int smb_bf16_plan_set_peer_copies(smb_bf16_plan* plan, int count, voi
   if (plan == nullptr) return set_error(SMB_ERR_INVALID, "plan: null handle");
   return set_peer_copies(&plan->launch.peers, plan->launch.tma_store, count, dst, ld,
                          plan->launch.swiglu ? plan->launch.N / 2 : plan->launch.N);
+}
+
+extern "C" int smb_bf16_plan_set_row_route(smb_bf16_plan* plan, int blocks, void* const* dst,
+                                           int rows_per_block, int64_t ld) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "plan: null handle");
+  return set_row_route(&plan->launch.peers, plan->launch.tma_store, blocks, dst, rows_per_block, ld,
+                       plan->launch.M, plan->launch.swiglu ? plan->launch.N / 2 : plan->launch.N);
 }
 
 extern "C" int smb_bf16_plan_set_profile(smb_bf16_plan* plan, long long* counters) {

@@ -94,11 +94,12 @@ __device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, c
     if (kTmaStore) {
       fence_proxy_async_smem();
       __syncwarp();
+      const int n_peers = out.peers->count;
+      const int route_rows = out.peers->route_rows;   // > 0: rows are routed, D itself is not written
       if (lane == 0) {
-        if (row0 < out.M && gcol0 < out.N) tma_store_2d(out.tmap_d, sbuf, gcol0, row0);
+        if (route_rows == 0 && row0 < out.M && gcol0 < out.N) tma_store_2d(out.tmap_d, sbuf, gcol0, row0);
         bulk_commit_group();
       }
-      const int n_peers = out.peers->count;
       if (n_peers > 0) {
         // Lane l copies 16-byte chunk (l % 8) of rows (l / 8) + 4 i: a warp instruction covers
         // four whole 128-byte row segments, read back from the swizzled staging box.
@@ -111,9 +112,17 @@ __device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, c
           ld_shared_v4(sbuf + r * 128 + ((chunk ^ (r & 7)) << 4), x0, x1, x2, x3);
           const int grow = row0 + r;
           if (grow < out.M && gcol < out.N) {
-            const long long off = static_cast<long long>(grow) * out.peers->ld + gcol;
+            if (route_rows > 0) {
+              // Row block b (route_rows rows, a multiple of the tile height, so a warp's 32 rows
+              // share it) goes to destination b, at its row inside the block.
+              const int b = row0 / route_rows;
+              const long long off = static_cast<long long>(grow - b * route_rows) * out.peers->ld + gcol;
+              st_global_v4(out.peers->base[b] + off, x0, x1, x2, x3);
+            } else {
+              const long long off = static_cast<long long>(grow) * out.peers->ld + gcol;
 #pragma unroll 1
-            for (int q = 0; q < n_peers; ++q) st_global_v4(out.peers->base[q] + off, x0, x1, x2, x3);
+              for (int q = 0; q < n_peers; ++q) st_global_v4(out.peers->base[q] + off, x0, x1, x2, x3);
+            }
           }
         }
       }

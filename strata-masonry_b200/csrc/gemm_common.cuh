@@ -44,14 +44,22 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype
 
 // Extra destinations of every stored box of D (see epilogue.cuh): the all-gather of a
 // column-sharded GEMM fused into the epilogue.
-constexpr int kMaxPeerCopies = 7;
+// Two uses.  Replicate (route_rows == 0): every stored box goes to D and to all `count` (<= 7)
+// destinations, the all-gather of a column-sharded GEMM.  Route (route_rows > 0): D is not
+// written; rows [b * route_rows, (b + 1) * route_rows) go to destination b only, at their row
+// inside the block: the scatter half of a reduce-scatter after a K-sharded GEMM, every rank
+// delivering the row block of its partial product that rank b owns.
+constexpr int kMaxPeerCopies = 8;
 struct PeerCopies {
   int count;                        // 0: none
+  int route_rows;                   // 0: replicate; else rows per routed block (multiple of 256)
   long long ld;                     // elements between rows in every destination
-  uint16_t* base[kMaxPeerCopies];   // element (0, 0) of this kernel's D inside destination i
+  uint16_t* base[kMaxPeerCopies];   // replicate: element (0, 0) of D in destination i; route: row 0 of block i
 };
 // Validates and fills `out`; `tma_store` is the plan's store path (peer copies need it).
 int set_peer_copies(PeerCopies* out, bool tma_store, int count, void* const* dst, long long ld, int N);
+int set_row_route(PeerCopies* out, bool tma_store, int blocks, void* const* dst, int rows_per_block, long long ld,
+                  int M, int N);
 
 // --------------------------------------------------------------------------- bf16 launch
 struct Bf16Launch {

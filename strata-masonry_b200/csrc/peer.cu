@@ -73,6 +73,58 @@ __global__ void __launch_bounds__(256) unshard_columns_kernel(const uint4* __res
 
 }  // namespace
 
+namespace {
+
+// D[i] = bf16_rne( sum over the `count` slots, in slot order, of slot[s][i] ), fp32 accumulation.
+// Eight bf16 per thread and step.  HBM-bound: (count + 1) * elems * 2 bytes moved.
+__global__ void __launch_bounds__(256) sum_slots_bf16_kernel(const uint4* __restrict__ slots,
+                                                             uint4* __restrict__ d, int count,
+                                                             long long chunks_per_slot) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks_per_slot;
+       i += stride) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < count; ++s) {
+      const uint4 q = slots[static_cast<long long>(s) * chunks_per_slot + i];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        acc[2 * t] += __uint_as_float(w[t] << 16);
+        acc[2 * t + 1] += __uint_as_float(w[t] & 0xFFFF0000u);
+      }
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[t]) : "f"(acc[2 * t + 1]), "f"(acc[2 * t]));
+    }
+    d[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+}  // namespace
+
+extern "C" int smb_sum_slots_bf16_device(const void* slots, void* d, int count, int64_t elems, void* stream) {
+  if (slots == nullptr || d == nullptr) return set_error(SMB_ERR_INVALID, "sum slots: null pointer");
+  if (count <= 0 || elems <= 0 || elems % 8 != 0)
+    return set_error(SMB_ERR_INVALID, "sum slots: count and elems must be positive, elems a multiple of 8");
+  if (reinterpret_cast<uintptr_t>(slots) % 16 != 0 || reinterpret_cast<uintptr_t>(d) % 16 != 0)
+    return set_error(SMB_ERR_INVALID, "sum slots: buffers must be 16-byte aligned");
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return set_error(SMB_ERR_CUDA, "sum slots: no CUDA device");
+  const long long chunks = elems / 8;
+  long long blocks = (chunks + 255) / 256;
+  const long long cap = static_cast<long long>(sms) * 8;
+  if (blocks > cap) blocks = cap;
+  sum_slots_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(slots), static_cast<uint4*>(d), count, chunks);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_cuda_error(e, "sum slots launch");
+  return SMB_OK;
+}
+
 extern "C" int smb_unshard_columns_device(const void* gathered, void* d, int g, int M, int n_local,
                                           int64_t ldd, void* stream) {
   if (gathered == nullptr || d == nullptr) return set_error(SMB_ERR_INVALID, "unshard: null pointer");

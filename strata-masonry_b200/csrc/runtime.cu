@@ -38,8 +38,9 @@ int device_cluster_slots() {
 }
 
 int set_peer_copies(PeerCopies* out, bool tma_store, int count, void* const* dst, long long ld, int N) {
-  if (count < 0 || count > kMaxPeerCopies)
-    return set_error(SMB_ERR_INVALID, "peer copies: count %d outside 0..%d", count, kMaxPeerCopies);
+  if (count < 0 || count > kMaxPeerCopies - 1)
+    return set_error(SMB_ERR_INVALID, "peer copies: count %d outside 0..%d", count, kMaxPeerCopies - 1);
+  out->route_rows = 0;
   if (count == 0) {
     out->count = 0;
     return SMB_OK;
@@ -59,6 +60,36 @@ int set_peer_copies(PeerCopies* out, bool tma_store, int count, void* const* dst
   out->count = count;
   out->ld = ld;
   for (int i = 0; i < count; ++i) out->base[i] = static_cast<uint16_t*>(dst[i]);
+  return SMB_OK;
+}
+
+int set_row_route(PeerCopies* out, bool tma_store, int blocks, void* const* dst, int rows_per_block, long long ld,
+                  int M, int N) {
+  if (blocks == 0) {
+    out->count = 0;
+    out->route_rows = 0;
+    return SMB_OK;
+  }
+  if (blocks < 0 || blocks > kMaxPeerCopies)
+    return set_error(SMB_ERR_INVALID, "row route: %d blocks outside 1..%d", blocks, kMaxPeerCopies);
+  if (dst == nullptr) return set_error(SMB_ERR_INVALID, "row route: null destination list");
+  if (!tma_store)
+    return set_error(SMB_ERR_UNSUPPORTED,
+                     "row route needs the 16-byte-aligned store path (D 16-byte aligned, ldd %% 8 == 0)");
+  if (rows_per_block <= 0 || rows_per_block % 256 != 0)
+    return set_error(SMB_ERR_UNSUPPORTED, "row route: %d rows per block is not a multiple of 256", rows_per_block);
+  if (static_cast<long long>(blocks) * rows_per_block < M)
+    return set_error(SMB_ERR_INVALID, "row route: %d blocks of %d rows do not cover M=%d", blocks, rows_per_block, M);
+  if (N % 8 != 0 || ld < N || ld % 8 != 0)
+    return set_error(SMB_ERR_INVALID, "row route: N and the row pitch must be multiples of 8, pitch >= N");
+  for (int i = 0; i < blocks; ++i) {
+    if (dst[i] == nullptr || reinterpret_cast<uintptr_t>(dst[i]) % 16 != 0)
+      return set_error(SMB_ERR_INVALID, "row route: destination %d (%p) is null or not 16-byte aligned", i, dst[i]);
+  }
+  out->count = blocks;
+  out->route_rows = rows_per_block;
+  out->ld = ld;
+  for (int i = 0; i < blocks; ++i) out->base[i] = static_cast<uint16_t*>(dst[i]);
   return SMB_OK;
 }
 

@@ -95,6 +95,12 @@ class Bf16Plan:
         self._peer_keep = dst
         capi.check(self._lib.smb_bf16_plan_set_peer_copies(self._h, count, arr, ld))
 
+    def set_row_route(self, dst, rows_per_block: int, ld: int) -> None:
+        """Rows of block b go to dst[b] only (D itself is not written): the fused scatter."""
+        count, arr = _peer_array(dst)
+        self._peer_keep = dst
+        capi.check(self._lib.smb_bf16_plan_set_row_route(self._h, count, arr, rows_per_block, ld))
+
     def run(self, stream=None) -> None:
         capi.check(self._lib.smb_bf16_plan_run(self._h, _stream_ptr(stream)))
 
@@ -272,6 +278,11 @@ class Fp4Plan:
         self._peer_keep = dst
         capi.check(self._lib.smb_fp4_plan_set_peer_copies(self._h, count, arr, ld))
 
+    def set_row_route(self, dst, rows_per_block: int, ld: int) -> None:
+        count, arr = _peer_array(dst)
+        self._peer_keep = dst
+        capi.check(self._lib.smb_fp4_plan_set_row_route(self._h, count, arr, rows_per_block, ld))
+
     def set_alpha(self, alpha: float) -> None:
         """Output factor of a FLAG_SCALE_BLOCK16 plan: 1 / (global scale of A x global scale of B)."""
         capi.check(self._lib.smb_fp4_plan_set_alpha(self._h, alpha))
@@ -292,6 +303,11 @@ class Fp4Plan:
             self.close()
         except Exception:
             pass
+
+
+def sum_slots_bf16_device(slots, d, count: int, elems: int, stream=None) -> None:
+    """d[i] = bf16(sum over `count` consecutive slots of `elems` bf16 each), fp32 accumulation."""
+    capi.check(capi.lib().smb_sum_slots_bf16_device(_ptr(slots), _ptr(d), count, elems, _stream_ptr(stream)))
 
 
 def unshard_columns_device(gathered, d, g: int, m: int, n_local: int, ldd: int | None = None,

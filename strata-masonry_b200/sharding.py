@@ -150,3 +150,48 @@ class SharedOutput:
                 self._mem.close(base)
         self._dist.barrier()
         self._mem.free(self.local)
+
+
+# ------------------------------------------------------------------ fused reduce-scatter plumbing
+def route_targets(bases: list[int], rank: int, slot_bytes: int) -> list[int]:
+    """Where rank `rank` delivers row block b of its partial product: slot `rank` of rank b's
+    receive buffer (`bases[b]` = that buffer as mapped into this process)."""
+    return [base + rank * slot_bytes for base in bases]
+
+
+class ScatterSlots:
+    """Receive side of the fused reduce-scatter of a K-sharded GEMM: on every rank a buffer of g
+    slots [M/g, N] bf16, slot s filled by rank s with the row block this rank owns of rank s's
+    partial product; all buffers mapped into every process.  `dist` and `memory` as for
+    SharedOutput."""
+
+    def __init__(self, m: int, n: int, dist, memory=None, elem_bytes: int = 2):
+        self._dist = dist
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (8 routed row blocks)")
+        if m % self.world != 0 or (m // self.world) % 256 != 0:
+            raise ValueError(f"M/g = {m}/{self.world} must be a multiple of 256 rows")
+        self.m, self.n, self.elem_bytes = m, n, elem_bytes
+        self.rows_per_block = m // self.world
+        self.slot_bytes = self.rows_per_block * n * elem_bytes
+        self._mem = memory if memory is not None else _CudaPeerMemory()
+        self.local = self._mem.alloc(self.world * self.slot_bytes)
+        handles: list = [None] * self.world
+        dist.all_gather_object(handles, self._mem.export(self.local))
+        self.bases = [self.local if r == self.rank else self._mem.open(handles[r]) for r in range(self.world)]
+        self._open = True
+
+    def targets(self) -> list[int]:
+        return route_targets(self.bases, self.rank, self.slot_bytes)
+
+    def close(self) -> None:
+        if not self._open:
+            return
+        self._open = False
+        self._dist.barrier()
+        for r, base in enumerate(self.bases):
+            if r != self.rank:
+                self._mem.close(base)
+        self._dist.barrier()
+        self._mem.free(self.local)

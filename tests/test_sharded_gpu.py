@@ -234,3 +234,129 @@ def test_fused_all_gather_on_two_gpus(smb, cuda_device):
         assert p.exitcode == 0
     results = dict(out.get(timeout=5) for _ in range(2))
     assert results == {0: True, 1: True}
+
+
+# ------------------------------------------------------------------ K-sharded GEMM + fused scatter
+@pytest.mark.parametrize("kind", ["bf16", "fp4"])
+def test_row_route_and_slot_sum_on_one_device(smb, cuda_device, kind):
+    """Two "ranks" on one GPU: each multiplies its half of K and routes row block b of its partial
+    product into slot [rank] of "rank" b's receive buffer; summing the slots gives the full
+    product (to the rounding of the bf16 partials)."""
+    torch = _torch()
+    sys.path.insert(0, str(ROOT / "tests"))
+    from test_gemm_gpu import _fp4_operand, _dequant
+    g, m, n, k = 2, 1024, 384, 1024
+    rows, kl = m // g, k // g
+    recv = [torch.full((g, rows, n), float("nan"), device=cuda_device, dtype=torch.bfloat16) for _ in range(g)]
+    d_unused = torch.full((m, n), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    if kind == "bf16":
+        a = torch.empty(m, k, device=cuda_device, dtype=torch.bfloat16)
+        bt = torch.empty(n, k, device=cuda_device, dtype=torch.bfloat16)
+        smb.gemm.bf16_operands_device(a, bt, m, n, k, 5)
+        ref = a.double() @ bt.double().t()
+    else:
+        a, sfa, sfar = _fp4_operand(smb, m, k, 5, 0)
+        b, sfb, sfbr = _fp4_operand(smb, n, k, 5, 1)
+        ref = _dequant(a, sfar) @ _dequant(b, sfbr).t()
+    for r in range(g):
+        targets = [recv[b][r].data_ptr() for b in range(g)]
+        if kind == "bf16":
+            a_r = a[:, r * kl:(r + 1) * kl].contiguous()
+            bt_r = bt[:, r * kl:(r + 1) * kl].contiguous()
+            plan = smb.gemm.Bf16Plan(a_r, bt_r, d_unused, m, n, kl)
+        else:
+            a_r, sfa_r, _ = _fp4_slice(smb, a, sfar, r, g)
+            b_r, sfb_r, _ = _fp4_slice(smb, b, sfbr, r, g)
+            plan = smb.gemm.Fp4Plan(a_r, sfa_r, b_r, sfb_r, d_unused, m, n, kl)
+        plan.set_row_route(targets, rows, n)
+        plan.run(); plan.check()
+        with pytest.raises(smb.capi.SmbError):
+            plan.set_row_route(targets, rows + 8, n)          # not a multiple of the tile height
+        plan.close()
+    assert bool(torch.isnan(d_unused).all())                   # a routed plan does not write its D
+    out = torch.empty(m, n, device=cuda_device, dtype=torch.bfloat16)
+    for b in range(g):
+        smb.gemm.sum_slots_bf16_device(recv[b], out[b * rows:(b + 1) * rows], g, rows * n)
+    torch.cuda.synchronize()
+    got = out.double()
+    rms = float(ref.pow(2).mean().sqrt())
+    bound = 2.0 ** -6 * ref.abs() + 2.0 ** -9 * (k ** 0.5) * rms     # two bf16 roundings of partials + sum
+    assert int((~torch.isfinite(got) | ((got - ref).abs() > bound)).sum()) == 0
+    # The sum kernel alone: exact against torch on the same slots.
+    want = recv[0].float().sum(dim=0).to(torch.bfloat16)
+    assert torch.equal(out[:rows].view(torch.int16), want.view(torch.int16))
+
+
+def _fp4_slice(smb, codes, sf_rowmajor, r, g):
+    """K slice r of g of a quantised operand: codes, packed scales, row-major scales."""
+    torch = _torch()
+    kb = codes.shape[1] // g
+    sb = sf_rowmajor.shape[1] // g
+    c = codes[:, r * kb:(r + 1) * kb].contiguous()
+    s = sf_rowmajor[:, r * sb:(r + 1) * sb].contiguous()
+    packed = np.zeros(smb.capi.lib().smb_sf_packed_bytes(c.shape[0], sb), dtype=np.uint8)
+    s_host = s.cpu().numpy()
+    smb.capi.check(smb.capi.lib().smb_sf_pack_host(s_host.ctypes.data, c.shape[0], sb, packed.ctypes.data))
+    return c, torch.from_numpy(packed).to(codes.device), s
+
+
+def _two_gpu_scatter_worker(rank, world, port, out):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__ as entry
+    smb = entry.load_package()
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        m, n, k, fill = 1024, 512, 2048, 5
+        kl = k // world
+        slots = smb.sharding.ScatterSlots(m, n, dist)
+        rows = slots.rows_per_block
+        a = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
+        bt = torch.empty(n, k, device=dev, dtype=torch.bfloat16)
+        smb.gemm.bf16_operands_device(a, bt, m, n, k, fill)
+        a_r = a[:, rank * kl:(rank + 1) * kl].contiguous()
+        bt_r = bt[:, rank * kl:(rank + 1) * kl].contiguous()
+        unused = torch.zeros(m, n, device=dev, dtype=torch.bfloat16)
+        plan = smb.gemm.Bf16Plan(a_r, bt_r, unused, m, n, kl)
+        plan.set_row_route(slots.targets(), rows, n)
+        dist.barrier()
+        plan.run()
+        plan.check()            # own deliveries complete
+        dist.barrier()          # everybody's deliveries complete
+        mine = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+        smb.gemm.sum_slots_bf16_device(slots.local, mine, world, rows * n)
+        torch.cuda.synchronize()
+        ref = (a.double() @ bt.double().t())[rank * rows:(rank + 1) * rows]
+        rms = float(ref.pow(2).mean().sqrt())
+        bound = 2.0 ** -6 * ref.abs() + 2.0 ** -9 * (k ** 0.5) * rms
+        got = mine.double()
+        ok = int((~torch.isfinite(got) | ((got - ref).abs() > bound)).sum()) == 0
+        plan.close()
+        slots.close()
+        out.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_fused_scatter_on_two_gpus(smb, cuda_device):
+    torch = _torch()
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_two_gpu_scatter_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    results = dict(out.get(timeout=5) for _ in range(2))
+    assert results == {0: True, 1: True}

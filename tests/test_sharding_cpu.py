@@ -192,3 +192,63 @@ def test_peer_copy_rules(smb):
     assert lib.smb_fp4_plan_set_peer_copies(None, 0, None, 0) == smb.capi.SMB_ERR_INVALID
     assert lib.smb_unshard_columns_device(None, None, 2, 4, 8, 16, None) == smb.capi.SMB_ERR_INVALID
     assert lib.smb_peer_export(None, None) == smb.capi.SMB_ERR_INVALID
+
+
+# ------------------------------------------------------------------ fused reduce-scatter plumbing
+def _scatter_worker(rank, world, port, path, out):
+    import torch.distributed as dist
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__ as entry
+    smb = entry.load_package()
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        m, n = 256 * world, 16
+        rows = m // world
+        region = world * rows * n * 2
+        mem = _FileBackedMemory(path, rank, region)
+        slots = smb.sharding.ScatterSlots(m, n, dist, memory=mem)
+        assert slots.rows_per_block == rows and slots.slot_bytes == rows * n * 2
+        backing = np.memmap(path, dtype=np.uint8, mode="r+", shape=(world * region,))
+        # What the routed epilogue does: row block b of this rank's partial product goes to
+        # targets[b], a [rows, n] block with pitch n.
+        partial = ((rank + 1) * 100 + np.arange(m)[:, None] + np.arange(n)[None, :] * 0).astype(np.uint16)
+        partial = np.broadcast_to(partial, (m, n)).copy()
+        for b, addr in enumerate(slots.targets()):
+            off = addr - mem.BASE
+            backing[off:off + rows * n * 2] = partial[b * rows:(b + 1) * rows].reshape(-1).view(np.uint8)
+        backing.flush()
+        dist.barrier()
+        mine = np.memmap(path, dtype=np.uint16, mode="r", offset=rank * region, shape=(world, rows, n))
+        ok = True
+        for s in range(world):   # slot s holds rank s's partial rows of MY block
+            want = ((s + 1) * 100 + np.arange(rank * rows, (rank + 1) * rows)[:, None]).astype(np.uint16)
+            ok &= np.array_equal(np.asarray(mine[s]), np.broadcast_to(want, (rows, n)))
+        slots.close()
+        out.put(bool(ok))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_scatter_slots_addresses_on_gloo(smb, tmp_path):
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    path = str(tmp_path / "slots.bin")
+    with open(path, "wb") as f:
+        f.write(bytes(world * world * 256 * 16 * 2))
+    procs = [ctx.Process(target=_scatter_worker, args=(r, world, port, path, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert all(out.get(timeout=5) is True for _ in range(world))
+    assert smb.sharding.route_targets([0x1000, 0x9000], 1, 0x100) == [0x1100, 0x9100]
+    lib = smb.capi.lib()
+    assert lib.smb_bf16_plan_set_row_route(None, 0, None, 256, 8) == smb.capi.SMB_ERR_INVALID
+    assert lib.smb_sum_slots_bf16_device(None, None, 2, 8, None) == smb.capi.SMB_ERR_INVALID
