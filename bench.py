@@ -240,6 +240,9 @@ def main():
     ap.add_argument("--allgather", action="store_true", help="also time the all-gather of D (N > 1)")
     ap.add_argument("--fused-allgather", action="store_true",
                     help="also time the GEMM whose epilogue writes D into every GPU's full D (N > 1)")
+    ap.add_argument("--fused-reduce-scatter", action="store_true",
+                    help="also time the K-sharded form: GEMM whose epilogue delivers row blocks to their owners, "
+                         "then a slot sum, against GEMM + NCCL reduce-scatter (BF16 workloads, N > 1)")
     ap.add_argument("--swiglu", action="store_true",
                     help="also time the GEMM with the gated-activation epilogue (D = silu(gate) * up, [M, N/2])")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -630,6 +633,74 @@ def main():
         del d_full
         shared.close()
 
+    # ---------------------------------------------------------------- K-sharded GEMM + reduce-scatter
+    # Row-parallel form of the same problem: rank r multiplies [M, K/g] by [N, K/g]; the sum of the
+    # g partial products is scattered by rows (rank b owns rows [b M/g, (b+1) M/g)).  Fused: the
+    # epilogue stores row block b of the partial product straight into slot r of rank b's receive
+    # buffer (peer-mapped memory, plain stores), a one-element all-reduce on the stream orders
+    # the ranks, and a slot-sum kernel adds the g slots.  Unfused: GEMM into a local [M, N]
+    # buffer, then NCCL reduce_scatter_tensor.
+    reduce_scatter = None
+    if dist is not None and args.fused_reduce_scatter and kind == "bf16" and k % g == 0 and m % (256 * g) == 0:
+        kl = k // g
+        a_r = torch.empty(m, kl, device=dev, dtype=torch.bfloat16)
+        bt_r = torch.empty(n, kl, device=dev, dtype=torch.bfloat16)
+        smb.gemm.fill_bf16_device(a_r, m, kl, fill, 11 + rank, stream=stream)
+        smb.gemm.fill_bf16_device(bt_r, n, kl, fill, 101 + rank, stream=stream)
+        slots = smb.sharding.ScatterSlots(m, n, dist)
+        rows = slots.rows_per_block
+        partial = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        mine = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+        mine_nccl = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+        token = torch.zeros(1, device=dev, dtype=torch.float32)
+        rplan = smb.gemm.Bf16Plan(a_r, bt_r, partial, m, n, kl, flags=smb.capi.FLAG_OPERANDS_STATIC)
+        rplan.set_row_route(slots.targets(), rows, n, slots.first_block())
+        uplan = smb.gemm.Bf16Plan(a_r, bt_r, partial, m, n, kl, flags=smb.capi.FLAG_OPERANDS_STATIC)
+
+        def fused_step():
+            rplan.run(stream)
+            dist.all_reduce(token)          # every rank's deliveries are complete behind this point
+            smb.gemm.sum_slots_bf16_device(slots.local, mine, g, rows * n, stream=stream)
+            dist.all_reduce(token)          # nobody overwrites a slot that is still being summed
+
+        def unfused_step():
+            uplan.run(stream)
+            dist.reduce_scatter_tensor(mine_nccl, partial)
+
+        def timed_rs(fn, reps):
+            for _ in range(2):
+                fn()
+            barrier()
+            t0 = torch.cuda.Event(enable_timing=True)
+            t1 = torch.cuda.Event(enable_timing=True)
+            t0.record(stream)
+            for _ in range(reps):
+                fn()
+            t1.record(stream)
+            barrier()
+            return max_over_ranks(t0.elapsed_time(t1)) / reps
+
+        reps = max(5, min(args.steps, 30))
+        fused_rs_ms = timed_rs(fused_step, reps)
+        rplan.check(stream)
+        unfused_rs_ms = timed_rs(unfused_step, reps)
+        gemm_rs_ms = timed_rs(lambda: uplan.run(stream), reps)
+        # Same sums up to the order of additions and one rounding.
+        diff = (mine.float() - mine_nccl.float()).abs().max()
+        scale = mine_nccl.float().abs().max().clamp_min(1e-30)
+        agree = torch.tensor([float(diff / scale)], device=dev)
+        dist.all_reduce(agree, op=dist.ReduceOp.MAX)
+        sent = (g - 1) * rows * n * 2
+        reduce_scatter = {"fused_ms": fused_rs_ms, "gemm_plus_nccl_reduce_scatter_ms": unfused_rs_ms,
+                          "gemm_only_ms": gemm_rs_ms, "shape_per_rank_mnk": [m, n, kl],
+                          "fused_sent_gb_per_s_per_gpu": sent / (fused_rs_ms * 1e-3) / 1e9,
+                          "max_rel_diff_vs_nccl": float(agree.item()),
+                          "bound_ms": {"nvlink_at_770_gb_s": sent / 770e9 * 1e3, "gemm": gemm_rs_ms}}
+        rplan.close()
+        uplan.close()
+        del partial, mine, mine_nccl, a_r, bt_r
+        slots.close()
+
     # ---------------------------------------------------------------- end to end, host buffers
     e2e = None
     if kind == "bf16":
@@ -685,7 +756,7 @@ def main():
                        "launch": "operands static across steps: consecutive launches may overlap head and tail "
                                  "(programmatic dependent launch); stores to D stay ordered"},
             "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-            "gpu_launches": args.steps, "allgather": allgather, "from_bf16_activations": act_step, "swiglu": swiglu,
+            "gpu_launches": args.steps, "allgather": allgather, "from_bf16_activations": act_step, "swiglu": swiglu, "reduce_scatter": reduce_scatter,
         }
         print(json.dumps(line))
     if dist is not None:

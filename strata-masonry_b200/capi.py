@@ -91,8 +91,8 @@ DECLARED = [
     ("smb_decode_noalloc_scratch_limit", C.c_size_t, []),
     ("smb_bf16_plan_set_peer_copies", _i, [_vp, _i, C.POINTER(_vp), _i64]),
     ("smb_fp4_plan_set_peer_copies", _i, [_vp, _i, C.POINTER(_vp), _i64]),
-    ("smb_bf16_plan_set_row_route", _i, [_vp, _i, C.POINTER(_vp), _i, _i64]),
-    ("smb_fp4_plan_set_row_route", _i, [_vp, _i, C.POINTER(_vp), _i, _i64]),
+    ("smb_bf16_plan_set_row_route", _i, [_vp, _i, C.POINTER(_vp), _i, _i64, _i]),
+    ("smb_fp4_plan_set_row_route", _i, [_vp, _i, C.POINTER(_vp), _i, _i64, _i]),
     ("smb_sum_slots_bf16_device", _i, [_vp, _vp, _i, _i64, _vp]),
     ("smb_peer_alloc", _i, [C.POINTER(_vp), C.c_size_t]),
     ("smb_peer_export", _i, [_vp, C.c_char_p]),

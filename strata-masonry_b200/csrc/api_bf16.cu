@@ -84,6 +84,7 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
   L.output_independent = (flags & SMB_FLAG_LAUNCH_INDEPENDENT) != 0;
   L.peers.count = 0;
   L.peers.route_rows = 0;
+  L.peers.first_block = 0;
   L.mtile_group = mtile_group;
   L.d = d;
   L.ldd = static_cast<int>(ldd);
@@ -167,9 +168,9 @@ extern "C" int smb_bf16_plan_set_peer_copies(smb_bf16_plan* plan, int count, voi
 }
 
 extern "C" int smb_bf16_plan_set_row_route(smb_bf16_plan* plan, int blocks, void* const* dst,
-                                           int rows_per_block, int64_t ld) {
+                                           int rows_per_block, int64_t ld, int first_block) {
   if (plan == nullptr) return set_error(SMB_ERR_INVALID, "plan: null handle");
-  return set_row_route(&plan->launch.peers, plan->launch.tma_store, blocks, dst, rows_per_block, ld,
+  return set_row_route(&plan->launch.peers, plan->launch.tma_store, blocks, dst, rows_per_block, ld, first_block,
                        plan->launch.M, plan->launch.swiglu ? plan->launch.N / 2 : plan->launch.N);
 }
 

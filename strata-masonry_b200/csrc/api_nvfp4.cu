@@ -75,6 +75,7 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
   L.output_independent = (flags & SMB_FLAG_LAUNCH_INDEPENDENT) != 0;
   L.peers.count = 0;
   L.peers.route_rows = 0;
+  L.peers.first_block = 0;
   L.mtile_group = mtile_group;
   L.d = d;
   L.ldd = static_cast<int>(ldd);
@@ -241,11 +242,11 @@ extern "C" int smb_fp4_plan_set_peer_copies(smb_fp4_plan* plan, int count, void*
 }
 
 extern "C" int smb_fp4_plan_set_row_route(smb_fp4_plan* plan, int blocks, void* const* dst,
-                                          int rows_per_block, int64_t ld) {
+                                          int rows_per_block, int64_t ld, int first_block) {
   if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
   if (plan->decode && blocks != 0)
     return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: the decode kernel (M <= 128) has no row route");
-  return set_row_route(&plan->launch.peers, plan->launch.tma_store, blocks, dst, rows_per_block, ld,
+  return set_row_route(&plan->launch.peers, plan->launch.tma_store, blocks, dst, rows_per_block, ld, first_block,
                        plan->launch.M, plan->launch.swiglu ? plan->launch.N / 2 : plan->launch.N);
 }
 

@@ -73,6 +73,7 @@ struct Params {
   long long* prof;    // optional: 8 cycle counters per CTA (see kProf* below), or null
   int dynamic;        // 1: tiles come from the hardware work queue (one cluster launched per tile)
   PeerCopies peers;     // extra destinations of every stored box (count 0: none)
+  int m_rotate;         // the tile walk starts at this 256-row tile (0 unless rows are routed)
   const int* mtile_group;  // grouped GEMM: group of every 256-row tile of A (device), or null
   int operands_static;  // 1: A and BT are not written by the previous kernel on the stream
 };
@@ -175,6 +176,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true)) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+        tm = (tm + p.m_rotate) % p.tiles_m;   // routed stores: ranks start at different row blocks
         const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
         // Grouped GEMM: BT is [groups * N, K]; the rows of this 256-row tile of A belong to one
         // group (every group's row count is a multiple of 256) and meet that group's N rows.
@@ -316,6 +318,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true), ++local) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+        tm = (tm + p.m_rotate) % p.tiles_m;   // routed stores: ranks start at different row blocks
         const int bank = (NB == 1) ? (local & 1) : 0;
         const int slot = (NB == 1) ? bank : group;
         const uint32_t use_parity =
@@ -410,6 +413,7 @@ int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
   p.prof = L.prof;
   p.operands_static = L.operands_static ? (L.output_independent ? 2 : 1) : 0;
   p.peers = L.peers;
+  p.m_rotate = L.peers.route_rows > 0 ? (L.peers.first_block * (L.peers.route_rows / 256)) % p.tiles_m : 0;
   p.mtile_group = L.mtile_group;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);

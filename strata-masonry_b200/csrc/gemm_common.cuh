@@ -53,13 +53,14 @@ constexpr int kMaxPeerCopies = 8;
 struct PeerCopies {
   int count;                        // 0: none
   int route_rows;                   // 0: replicate; else rows per routed block (multiple of 256)
+  int first_block;                  // route: the tile walk starts at this block (spreads the ranks' targets)
   long long ld;                     // elements between rows in every destination
   uint16_t* base[kMaxPeerCopies];   // replicate: element (0, 0) of D in destination i; route: row 0 of block i
 };
 // Validates and fills `out`; `tma_store` is the plan's store path (peer copies need it).
 int set_peer_copies(PeerCopies* out, bool tma_store, int count, void* const* dst, long long ld, int N);
 int set_row_route(PeerCopies* out, bool tma_store, int blocks, void* const* dst, int rows_per_block, long long ld,
-                  int M, int N);
+                  int first_block, int M, int N);
 
 // --------------------------------------------------------------------------- bf16 launch
 struct Bf16Launch {

@@ -92,6 +92,7 @@ struct Params {
   int prefetch;   // L2 prefetch distance in K blocks (0 = off)
   int dynamic;    // 1: tiles come from the hardware work queue (one cluster launched per tile)
   PeerCopies peers;     // extra destinations of every stored box (count 0: none)
+  int m_rotate;         // the tile walk starts at this 256-row tile (0 unless rows are routed)
   const int* mtile_group;  // grouped GEMM: group of every 256-row tile of A (device), or null
   float alpha;          // factor on every accumulator (block-16 variant: 1 / (global scale A x B))
   int operands_static;  // 1: operands and scales are not written by the previous kernel on the stream
@@ -203,6 +204,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true)) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+        tm = (tm + p.m_rotate) % p.tiles_m;   // routed stores: ranks start at different row blocks
         const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
         const int col0 = tn * C::kTileN;
         const int band_a = tm * 2 + static_cast<int>(rank);     // 128-row band of SFA
@@ -277,6 +279,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true), ++local) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+        tm = (tm + p.m_rotate) % p.tiles_m;   // routed stores: ranks start at different row blocks
         const bool has_sub1 = (C::kSubs == 2) && (tn * C::kTileN + W0 < p.N);
         const int bank = C::kTwoBanks ? (local & 1) : 0;
         const uint32_t use_parity =
@@ -430,6 +433,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true), ++local) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+        tm = (tm + p.m_rotate) % p.tiles_m;   // routed stores: ranks start at different row blocks
       const int bank = C::kTwoBanks ? (local & 1) : 0;
       const uint32_t use_parity = static_cast<uint32_t>(C::kTwoBanks ? (local >> 1) : local) & 1u;
       const long long w0 = prof ? clock64() : 0;
@@ -515,6 +519,7 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   p.prof = L.prof;
   p.operands_static = L.operands_static ? (L.output_independent ? 2 : 1) : 0;
   p.peers = L.peers;
+  p.m_rotate = L.peers.route_rows > 0 ? (L.peers.first_block * (L.peers.route_rows / 256)) % p.tiles_m : 0;
   p.mtile_group = L.mtile_group;
   p.alpha = L.alpha;
   p.prefetch = L.prefetch;

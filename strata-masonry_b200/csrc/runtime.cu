@@ -41,6 +41,7 @@ int set_peer_copies(PeerCopies* out, bool tma_store, int count, void* const* dst
   if (count < 0 || count > kMaxPeerCopies - 1)
     return set_error(SMB_ERR_INVALID, "peer copies: count %d outside 0..%d", count, kMaxPeerCopies - 1);
   out->route_rows = 0;
+  out->first_block = 0;
   if (count == 0) {
     out->count = 0;
     return SMB_OK;
@@ -64,10 +65,11 @@ int set_peer_copies(PeerCopies* out, bool tma_store, int count, void* const* dst
 }
 
 int set_row_route(PeerCopies* out, bool tma_store, int blocks, void* const* dst, int rows_per_block, long long ld,
-                  int M, int N) {
+                  int first_block, int M, int N) {
   if (blocks == 0) {
     out->count = 0;
     out->route_rows = 0;
+    out->first_block = 0;
     return SMB_OK;
   }
   if (blocks < 0 || blocks > kMaxPeerCopies)
@@ -86,7 +88,10 @@ int set_row_route(PeerCopies* out, bool tma_store, int blocks, void* const* dst,
     if (dst[i] == nullptr || reinterpret_cast<uintptr_t>(dst[i]) % 16 != 0)
       return set_error(SMB_ERR_INVALID, "row route: destination %d (%p) is null or not 16-byte aligned", i, dst[i]);
   }
+  if (first_block < 0 || first_block >= blocks)
+    return set_error(SMB_ERR_INVALID, "row route: first block %d outside 0..%d", first_block, blocks - 1);
   out->count = blocks;
+  out->first_block = first_block;
   out->route_rows = rows_per_block;
   out->ld = ld;
   for (int i = 0; i < blocks; ++i) out->base[i] = static_cast<uint16_t*>(dst[i]);

@@ -95,11 +95,12 @@ class Bf16Plan:
         self._peer_keep = dst
         capi.check(self._lib.smb_bf16_plan_set_peer_copies(self._h, count, arr, ld))
 
-    def set_row_route(self, dst, rows_per_block: int, ld: int) -> None:
-        """Rows of block b go to dst[b] only (D itself is not written): the fused scatter."""
+    def set_row_route(self, dst, rows_per_block: int, ld: int, first_block: int = 0) -> None:
+        """Rows of block b go to dst[b] only (D itself is not written): the fused scatter.  The tile
+        walk starts at `first_block`; give every rank a different one."""
         count, arr = _peer_array(dst)
         self._peer_keep = dst
-        capi.check(self._lib.smb_bf16_plan_set_row_route(self._h, count, arr, rows_per_block, ld))
+        capi.check(self._lib.smb_bf16_plan_set_row_route(self._h, count, arr, rows_per_block, ld, first_block))
 
     def run(self, stream=None) -> None:
         capi.check(self._lib.smb_bf16_plan_run(self._h, _stream_ptr(stream)))
@@ -278,10 +279,10 @@ class Fp4Plan:
         self._peer_keep = dst
         capi.check(self._lib.smb_fp4_plan_set_peer_copies(self._h, count, arr, ld))
 
-    def set_row_route(self, dst, rows_per_block: int, ld: int) -> None:
+    def set_row_route(self, dst, rows_per_block: int, ld: int, first_block: int = 0) -> None:
         count, arr = _peer_array(dst)
         self._peer_keep = dst
-        capi.check(self._lib.smb_fp4_plan_set_row_route(self._h, count, arr, rows_per_block, ld))
+        capi.check(self._lib.smb_fp4_plan_set_row_route(self._h, count, arr, rows_per_block, ld, first_block))
 
     def set_alpha(self, alpha: float) -> None:
         """Output factor of a FLAG_SCALE_BLOCK16 plan: 1 / (global scale of A x global scale of B)."""

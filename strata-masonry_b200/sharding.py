@@ -185,6 +185,11 @@ class ScatterSlots:
     def targets(self) -> list[int]:
         return route_targets(self.bases, self.rank, self.slot_bytes)
 
+    def first_block(self) -> int:
+        """Row block at which this rank's kernel should start its tile walk: a different one on
+        every rank, so that the ranks do not all deliver to the same owner at the same time."""
+        return (self.rank + 1) % self.world
+
     def close(self) -> None:
         if not self._open:
             return

@@ -268,7 +268,7 @@ def test_row_route_and_slot_sum_on_one_device(smb, cuda_device, kind):
             a_r, sfa_r, _ = _fp4_slice(smb, a, sfar, r, g)
             b_r, sfb_r, _ = _fp4_slice(smb, b, sfbr, r, g)
             plan = smb.gemm.Fp4Plan(a_r, sfa_r, b_r, sfb_r, d_unused, m, n, kl)
-        plan.set_row_route(targets, rows, n)
+        plan.set_row_route(targets, rows, n, (r + 1) % g)
         plan.run(); plan.check()
         with pytest.raises(smb.capi.SmbError):
             plan.set_row_route(targets, rows + 8, n)          # not a multiple of the tile height
@@ -324,7 +324,7 @@ def _two_gpu_scatter_worker(rank, world, port, out):
         bt_r = bt[:, rank * kl:(rank + 1) * kl].contiguous()
         unused = torch.zeros(m, n, device=dev, dtype=torch.bfloat16)
         plan = smb.gemm.Bf16Plan(a_r, bt_r, unused, m, n, kl)
-        plan.set_row_route(slots.targets(), rows, n)
+        plan.set_row_route(slots.targets(), rows, n, slots.first_block())
         dist.barrier()
         plan.run()
         plan.check()            # own deliveries complete

@@ -250,5 +250,5 @@ def test_scatter_slots_addresses_on_gloo(smb, tmp_path):
     assert all(out.get(timeout=5) is True for _ in range(world))
     assert smb.sharding.route_targets([0x1000, 0x9000], 1, 0x100) == [0x1100, 0x9100]
     lib = smb.capi.lib()
-    assert lib.smb_bf16_plan_set_row_route(None, 0, None, 256, 8) == smb.capi.SMB_ERR_INVALID
+    assert lib.smb_bf16_plan_set_row_route(None, 0, None, 256, 8, 0) == smb.capi.SMB_ERR_INVALID
     assert lib.smb_sum_slots_bf16_device(None, None, 2, 8, None) == smb.capi.SMB_ERR_INVALID
