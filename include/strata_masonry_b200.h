@@ -280,8 +280,8 @@ int smb_fp4_plan_set_peer_copies(smb_fp4_plan* plan, int count, void* const* dst
  * rows_per_block R % 256 == 0, blocks * R >= M; ld, N, alignment as for peer copies.
  * The kernel's walk over the tiles starts at row block `first_block`: give every rank a
  * different one (rank + 1, say), or all ranks deliver to the same owner at the same time and
- * its NVLink port is the bottleneck (measured at 8 GPUs: 206 GB/s per GPU against the ... with
- * rotated starts).  blocks = 0 switches the route off.  Once all ranks' kernels have completed, rank b adds its
+ * its NVLink port is the bottleneck (measured at 8 GPUs: 206 GB/s sent per GPU with equal
+ * starts, 526 GB/s with rotated ones).  blocks = 0 switches the route off.  Once all ranks' kernels have completed, rank b adds its
  * g slots up with smb_sum_slots_bf16_device (fp32 accumulation in slot order, one bf16
  * rounding; the partial products themselves were rounded to bf16 when they were stored). */
 int smb_bf16_plan_set_row_route(smb_bf16_plan* plan, int blocks, void* const* dst, int rows_per_block,
