@@ -37,29 +37,40 @@ constexpr int kBlockK = 64;           // K elements per stage (= 128 bytes per r
 constexpr int kThreads = 352;
 constexpr int kEpiWarps = 8;
 constexpr int kABytes = kBlockM * kBlockK * 2;        // 16 KiB
-constexpr int kTmemCols = 512;
 enum { kStorePlain = 0, kStoreTma = 1, kStoreSwiglu = 2 };   // epilogue variants
-constexpr int kRingBudget = 192 * 1024;
 
-template <int TN, int NB>
+// R = CTAs of this kernel that fit on one SM.  Narrow tiles (N <= 128 problems) move 1.5 to 2.5
+// times the operand bytes per flop of a 256-wide tile and are bound by the L2 -> SM path, not by
+// the tensor pipe.  With R = 2 their CTAs take half the shared memory (a 3 or 4 stage ring), half
+// the tensor memory and at most 88 registers, so that prologue, first load, accumulator drain and
+// exit of one cluster overlap the main loop of a neighbour on the same SM pair.  That pays when
+// launches overlap (operands not produced by the previous kernel: measured 6.2 against 9.7 us per
+// launch of 14080 x 128 x 2048).  A launch that runs alone is better off with R = 1: two clusters
+// that start together on one SM pair while other pairs idle take twice as long as one.
+template <int TN, int NB, int R = 1>
 struct Cfg {
   static_assert(TN == 64 || TN == 128 || TN == 256, "tile width");
   static_assert(NB == 1 || (NB == 2 && TN == 256), "two sub-blocks only at full width");
+  static_assert(R == 1 || (R == 2 && TN <= 128), "two resident CTAs only for narrow tiles");
+  static constexpr int kResident = R;
+  static constexpr int kRingBudget = (kResident == 2) ? (TN == 64 ? 92 : 76) * 1024 : 192 * 1024;
+  static constexpr int kTmemCols = (kResident == 2) ? 2 * TN : 512;   // two accumulator slots
   static constexpr int kBBytes = (TN / 2) * kBlockK * 2;         // one sub-block, one CTA
   static constexpr int kStageBytes = kABytes + NB * kBBytes;
-  static constexpr int kStages = kRingBudget / kStageBytes;      // 6, 8, 9 or 4
+  static constexpr int kStages = kRingBudget / kStageBytes;      // R = 1: 9, 8, 6 or 4; R = 2: 4 or 3
   static constexpr int kRingBytes = kStages * kStageBytes;
-  static constexpr int kStoreBytes = kEpiWarps * kStoreBufBytes;
-  static constexpr int kBarrierBytes = 1024;
-  // + 1024 so that the kernel can round the dynamic base up to a 1024-byte boundary.
-  static constexpr int kTotal = 1024 + kRingBytes + kStoreBytes + kBarrierBytes;
   static constexpr int kTileN = TN * NB;
   // Columns of one accumulator slot are split between the two epilogue warp groups when
   // there are at least 128 of them (each group then stores whole 64-column boxes).
   static constexpr int kGroupsPerSlot = (NB == 2) ? 1 : (TN >= 128 ? 2 : 1);
+  static constexpr int kEpiWarpsActive = (NB == 2) ? kEpiWarps : 4 * kGroupsPerSlot;
+  static constexpr int kStoreBytes = kEpiWarpsActive * kStoreBufBytes;   // working warps come first
+  static constexpr int kBarrierBytes = 1024;
+  // + 1024 so that the kernel can round the dynamic base up to a 1024-byte boundary.
+  static constexpr int kTotal = 1024 + kRingBytes + kStoreBytes + kBarrierBytes;
   static constexpr int kColsPerWarp = TN / kGroupsPerSlot;
   static constexpr int kSlotReaders = 2 * 4 * kGroupsPerSlot;    // arrivals per drained slot
-  static_assert(kTotal <= 232448, "shared memory budget");
+  static_assert(kTotal <= (kResident == 2 ? 115712 : 232448), "shared memory budget");
   static_assert(kStages >= 2 && kStages <= 16, "ring depth");
 };
 
@@ -82,12 +93,12 @@ struct Params {
 enum { kProfLoadWait = 0, kProfLoadTotal, kProfMmaWaitFull, kProfMmaWaitAcc, kProfMmaTotal,
        kProfEpiWait, kProfEpiTotal, kProfTiles, kProfCount };
 
-template <int TN, int NB, int kStore>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+template <int TN, int NB, int kStore, int R>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, R)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ Params p) {
-  using C = Cfg<TN, NB>;
+  using C = Cfg<TN, NB, R>;
   constexpr bool kTmaStore = (kStore != kStorePlain);
   constexpr bool kSwiglu = (kStore == kStoreSwiglu);   // D is [M, N/2]: silu(gate) * up
   static_assert(!kSwiglu || C::kColsPerWarp % 128 == 0, "gated epilogue: 64 output columns per box");
@@ -108,7 +119,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   sched.slot_full = bar_base + 528u;
   sched.slot_empty = bar_base + 536u;
   // Consumers of a scheduler response: both load threads, the MMA thread, every working epilogue warp.
-  constexpr int kEpiWarpsActive = (NB == 2) ? 8 : 4 * C::kGroupsPerSlot;
+  constexpr int kEpiWarpsActive = C::kEpiWarpsActive;
   constexpr int kSchedConsumers = 2 + 1 + 2 * kEpiWarpsActive;
 
   const int warp = threadIdx.x >> 5;
@@ -141,7 +152,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (kTmaStore) tma_prefetch_desc(&tmap_d);
   }
   if (warp == 1) {
-    tmem_alloc<2>(tmem_slot, kTmemCols);
+    tmem_alloc<2>(tmem_slot, C::kTmemCols);
     tmem_relinquish<2>();
   }
   tc_fence_before_sync();
@@ -357,7 +368,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc<2>(tmem_base, kTmemCols);
+    tmem_dealloc<2>(tmem_base, C::kTmemCols);
   }
 }
 
@@ -368,10 +379,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // -----------------------------------------------------------------------------------
 namespace {
 
-template <int TN, int NB, int kStore>
+template <int TN, int NB, int kStore, int R = 1>
 int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
-  using C = bf16k::Cfg<TN, NB>;
-  auto kernel = bf16k::gemm_bf16_kernel<TN, NB, kStore>;
+  using C = bf16k::Cfg<TN, NB, R>;
+  auto kernel = bf16k::gemm_bf16_kernel<TN, NB, kStore, R>;
   static thread_local int configured_device = -1;
   static thread_local int max_clusters = 0;
   int dev = 0;
@@ -448,6 +459,13 @@ int launch_bf16_store(const Bf16Launch& L, cudaStream_t stream) {
       return launch_bf16<TN, NB, bf16k::kStoreSwiglu>(L, stream);
     } else {
       return set_error(SMB_ERR_UNSUPPORTED, "bf16: the gated epilogue needs 256-wide tiles");
+    }
+  }
+  if constexpr (TN <= 128) {
+    // Narrow tiles: two CTAs per SM when consecutive launches may overlap (see Cfg).
+    if (L.operands_static) {
+      return L.tma_store ? launch_bf16<TN, NB, bf16k::kStoreTma, 2>(L, stream)
+                         : launch_bf16<TN, NB, bf16k::kStorePlain, 2>(L, stream);
     }
   }
   return L.tma_store ? launch_bf16<TN, NB, bf16k::kStoreTma>(L, stream)

@@ -157,6 +157,40 @@ def test_bf16_every_tile_configuration(smb, oracle, cuda_device, flags_name):
     _check_bf16_full(oracle, a, bt, d, n, k)
 
 
+@pytest.mark.parametrize("tile", ["FLAG_TILE_N_64", "FLAG_TILE_N_128"])
+@pytest.mark.parametrize("overlap", ["FLAG_OPERANDS_STATIC", "FLAG_LAUNCH_INDEPENDENT"])
+@pytest.mark.parametrize("store", ["FLAG_NONE", "FLAG_FORCE_PLAIN_STORE"])
+def test_bf16_narrow_tiles_two_ctas_per_sm(smb, oracle, cuda_device, tile, overlap, store):
+    """Narrow tiles launched with overlapping launches allowed run as the variant whose CTAs share
+    an SM in pairs (short ring, half of tensor memory).  More tiles than cluster slots, a ragged
+    edge in M and N, several launches back to back; results as for every other configuration, and
+    bit-identical to the one-CTA-per-SM variant of the same tile."""
+    torch = _torch()
+    flags = getattr(smb.capi, tile) | getattr(smb.capi, store)
+    m, n, k = 2500, 1088, 2112          # 10 x 9 (or 17) tiles of 256 x 128 (64)
+    a, bt, d1 = _run_bf16(smb, m, n, k, 5, flags=flags)
+    _check_bf16_full(oracle, a, bt, d1, n, k)
+    d2 = torch.full_like(d1, float("nan"))
+    plan = smb.gemm.Bf16Plan(a, bt, d2, m, n, k, flags=flags | getattr(smb.capi, overlap))
+    for _ in range(4):
+        plan.run()
+    plan.check()
+    plan.close()
+    torch.cuda.synchronize()
+    assert torch.equal(d1.view(torch.int16), d2.view(torch.int16))
+    # The shape class the variant is for: N = 128, one tile per cluster, launches overlapping.
+    m, n, k = 14080, 128, 2048
+    a, bt, d1 = _run_bf16(smb, m, n, k, 2)
+    d2 = torch.full_like(d1, float("nan"))
+    plan = smb.gemm.Bf16Plan(a, bt, d2, m, n, k, flags=getattr(smb.capi, overlap) | getattr(smb.capi, store))
+    for _ in range(8):
+        plan.run()
+    plan.check()
+    plan.close()
+    torch.cuda.synchronize()
+    assert torch.equal(d1.view(torch.int16), d2.view(torch.int16))
+
+
 def test_bf16_ragged_edge_case(smb, oracle, cuda_device):
     """BASELINE config 5's ragged case: M=4095, N=12289, K=4160.  D's row pitch (24578 B) is not a
     multiple of 16, so this runs the plain-store epilogue; rows of A/B are 16-byte aligned."""
