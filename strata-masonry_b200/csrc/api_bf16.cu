@@ -17,6 +17,7 @@ struct smb_bf16_plan {
   Bf16Launch launch;
   int* status_dev;
   bool owns_status;
+  int device;   // the device that was current at creation: pointers and status word live there
 };
 
 extern "C" int smb_version(void) { return 1000; }
@@ -62,11 +63,16 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
     return set_error(SMB_ERR_INVALID, "plan: leading dimension smaller than the row length");
   if (lda % 8 != 0 || ldb % 8 != 0)
     return set_error(SMB_ERR_INVALID, "plan: lda and ldb must be multiples of 8 elements");
+  if (ldd > 0x7FFFFFFFLL || lda > 0x7FFFFFFFLL || ldb > 0x7FFFFFFFLL)
+    return set_error(SMB_ERR_UNSUPPORTED, "plan: leading dimensions above 2^31 - 1 elements");
   if (reinterpret_cast<uintptr_t>(d) % 2 != 0)
     return set_error(SMB_ERR_INVALID, "plan: D is not 2-byte aligned");
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return set_error(SMB_ERR_CUDA, "plan: no current CUDA device");
 
   smb_bf16_plan* p = new (std::nothrow) smb_bf16_plan();
   if (p == nullptr) return set_error(SMB_ERR_NOMEM, "plan: out of host memory");
+  p->device = device;
   Bf16Launch& L = p->launch;
   L.M = M;
   L.N = N;
@@ -182,6 +188,10 @@ extern "C" int smb_bf16_plan_set_profile(smb_bf16_plan* plan, long long* counter
 
 extern "C" int smb_bf16_plan_run(smb_bf16_plan* plan, void* stream) {
   if (plan == nullptr) return set_error(SMB_ERR_INVALID, "plan: null handle");
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device != plan->device)
+    return set_error(SMB_ERR_INVALID, "plan: created on device %d, run with device %d current", plan->device,
+                     device);
   return bf16_launch(plan->launch, static_cast<cudaStream_t>(stream));
 }
 
@@ -323,6 +333,17 @@ extern "C" int smb_bf16_host_ctx_create(smb_bf16_host_ctx** out, int M, int N, i
   return SMB_OK;
 }
 
+namespace {
+// An error in the middle of a run: nothing may still be reading or writing the caller's buffers
+// when the call returns.
+int host_ctx_abort(smb_bf16_host_ctx* c, int rc) {
+  cudaStreamSynchronize(c->up);
+  cudaStreamSynchronize(c->compute);
+  cudaStreamSynchronize(c->down);
+  return rc;
+}
+}  // namespace
+
 extern "C" int smb_bf16_host_ctx_run(smb_bf16_host_ctx* c, const uint16_t* a, const uint16_t* bt,
                                      uint16_t* d) {
   if (c == nullptr) return set_error(SMB_ERR_INVALID, "host context: null handle");
@@ -341,9 +362,9 @@ extern "C" int smb_bf16_host_ctx_run(smb_bf16_host_ctx* c, const uint16_t* a, co
                         cudaMemcpyHostToDevice, c->up);
     if (e == cudaSuccess) e = cudaEventRecord(c->uploaded[i], c->up);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(c->compute, c->uploaded[i], 0);
-    if (e != cudaSuccess) return set_cuda_error(e, "host context: upload of A");
+    if (e != cudaSuccess) return host_ctx_abort(c, set_cuda_error(e, "host context: upload of A"));
     int rc = smb_bf16_plan_run(c->plans[i], c->compute);
-    if (rc != SMB_OK) return rc;
+    if (rc != SMB_OK) return host_ctx_abort(c, rc);
     e = cudaEventRecord(c->computed[i], c->compute);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(c->down, c->computed[i], 0);
     if (e == cudaSuccess) {
@@ -358,12 +379,12 @@ extern "C" int smb_bf16_host_ctx_run(smb_bf16_host_ctx* c, const uint16_t* a, co
                               cudaMemcpyDeviceToHost, c->down);
       }
     }
-    if (e != cudaSuccess) return set_cuda_error(e, "host context: download of D");
+    if (e != cudaSuccess) return host_ctx_abort(c, set_cuda_error(e, "host context: download of D"));
   }
   // The download stream has waited for every GEMM: the status word is final when it gets there.
   e = cudaMemcpyAsync(c->status_host, c->status_dev, sizeof(int), cudaMemcpyDeviceToHost, c->down);
   if (e == cudaSuccess) e = cudaStreamSynchronize(c->down);
-  if (e != cudaSuccess) return set_cuda_error(e, "host context: synchronize");
+  if (e != cudaSuccess) return host_ctx_abort(c, set_cuda_error(e, "host context: synchronize"));
   // The next run overwrites A and BT on the upload stream: every GEMM must be done by then (it
   // is: the download stream waited for all of them).
   const int status = *c->status_host;

@@ -16,7 +16,9 @@ using namespace smb;
 struct smb_fp4_plan {
   Fp4Launch launch;
   int* status_dev;
-  // Skinny shapes (M <= 128) run the stream-K decode kernel, which needs scratch memory.
+  int device;   // the device that was current at creation
+  // Skinny shapes (M <= 128) run the decode kernel.  Its scratch (partial-sum slots and tile
+  // counters) is only touched when the CTA count is capped and tiles are split along K.
   bool decode;
   Fp4DecodeLaunch dlaunch;
   void* scratch_dev;      // fp32 slabs followed by the per-tile counters
@@ -55,9 +57,15 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
     return set_error(SMB_ERR_INVALID, "fp4 plan: leading dimension smaller than the row length");
   if (lda_bytes % 16 != 0 || ldb_bytes % 16 != 0)
     return set_error(SMB_ERR_INVALID, "fp4 plan: operand row pitches must be multiples of 16 bytes");
+  if (ldd > 0x7FFFFFFFLL)
+    return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: ldd above 2^31 - 1 elements");
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess)
+    return set_error(SMB_ERR_CUDA, "fp4 plan: no current CUDA device");
 
   smb_fp4_plan* p = new (std::nothrow) smb_fp4_plan();
   if (p == nullptr) return set_error(SMB_ERR_NOMEM, "fp4 plan: out of host memory");
+  p->device = device;
   Fp4Launch& L = p->launch;
   L.M = M;
   L.N = N;
@@ -306,6 +314,10 @@ extern "C" int smb_fp4_plan_create_bf16_activations(smb_fp4_plan** out, const vo
 
 extern "C" int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream) {
   if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device != plan->device)
+    return set_error(SMB_ERR_INVALID, "fp4 plan: created on device %d, run with device %d current",
+                     plan->device, device);
   if (plan->act_src != nullptr) {
     const bool chained = !(plan->decode && plan->dlaunch.no_overlap);
     int rc = quantize_bf16_launch(plan->act_src, plan->act_ld, plan->act_codes, plan->launch.K / 2,

@@ -360,3 +360,26 @@ def test_fused_scatter_on_two_gpus(smb, cuda_device):
         assert p.exitcode == 0
     results = dict(out.get(timeout=5) for _ in range(2))
     assert results == {0: True, 1: True}
+
+
+def test_plan_refuses_to_run_on_another_device(smb, cuda_device):
+    """A plan's pointers, tensor maps and status word belong to the device that was current when it
+    was created; running it with another device current is an error, not a launch."""
+    torch = _torch()
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    m, n, k = 256, 256, 128
+    a = torch.zeros(m, k, device=cuda_device, dtype=torch.bfloat16)
+    bt = torch.zeros(n, k, device=cuda_device, dtype=torch.bfloat16)
+    d = torch.zeros(m, n, device=cuda_device, dtype=torch.bfloat16)
+    with torch.cuda.device(0):
+        plan = smb.gemm.Bf16Plan(a, bt, d, m, n, k)
+    try:
+        with torch.cuda.device(1):
+            with pytest.raises(smb.capi.SmbError, match="created on device 0"):
+                plan.run()
+        with torch.cuda.device(0):
+            plan.run()
+            plan.check()
+    finally:
+        plan.close()
