@@ -153,6 +153,22 @@ def _peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
+def blas_info():
+    """(threads, description) of the BLAS behind NumPy's matmul, the library the reference's CPU path
+    spends its time in; threads falls back to the core count when the pool cannot be inspected."""
+    cores = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_info
+        for pool in threadpool_info():
+            if pool.get("user_api") == "blas":
+                return int(pool.get("num_threads") or cores), (
+                    f"{pool.get('internal_api')} {pool.get('version')} "
+                    f"({pool.get('threading_layer')}, {pool.get('architecture')})")
+    except Exception:
+        pass
+    return cores, "unknown BLAS"
+
+
 def cpu_gemm_rate(oracle, a_bits, bt_bits, budget_s: float):
     """Time the reference's CPU path (bf16 -> fp32, fp32 matmul, round to bf16) on as large a
     square sub-block as fits the time budget.  Returns (TFLOP/s, description, seconds)."""
@@ -180,7 +196,7 @@ def run_reference(args):
         return 0
     kind, m, n, k, fill, desc = WORKLOADS[args.workload]
     oracle = _load_oracle()
-    cores = os.cpu_count() or 1
+    cores, blas = blas_info()
     steps, warmup = args.steps, args.warmup
     # Bounded sample: the whole run must end within a few minutes.
     per_step_budget = max(0.05, min(2.0, 120.0 / max(1, steps + warmup)))
@@ -222,7 +238,8 @@ def run_reference(args):
         "config": {"workload": args.workload, "description": desc, "shape_mnk": [m, n, k],
                    "step": f"reference NumPy CPU path on a {side}x{side}x{k} sub-block"},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                         "sample": f"{side}x{side}x{k} sub-block per step, {steps} steps"},
+                         "sample": f"{side}x{side}x{k} sub-block per step, {steps} steps",
+                         "host_cpus": os.cpu_count(), "blas": blas},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -734,8 +751,9 @@ def main():
         a_np = a_host[:rows].numpy().view(np.uint16)
         bt_np = bt_host[:min(n_local, 4096)].numpy().view(np.uint16)
         rate, sample, secs = cpu_gemm_rate(oracle, a_np, bt_np, budget_s=8.0)
-        cpu_baseline = {"value": rate, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
-                        "sample": sample + f" ({secs:.2f} s)",
+        threads, blas = blas_info()
+        cpu_baseline = {"value": rate, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                        "sample": sample + f" ({secs:.2f} s)", "host_cpus": os.cpu_count(), "blas": blas,
                         "what": "reference NumPy CPU path: bf16 operands -> fp32, a @ b, round to bf16"}
 
     for pl in (plans or [plan]):
