@@ -189,6 +189,34 @@ def cpu_gemm_rate(oracle, a_bits, bt_bits, budget_s: float):
     return 2.0 * side * side * k / best / 1e12, f"{side}x{side}x{k} sub-block of the workload, best of 2", best
 
 
+def cpu_fp4_rate(oracle, m, n, k, budget_s: float):
+    """Time the reference's CPU path for the block-scaled GEMM (codes and scale bytes -> fp32,
+    fp32 matmul, round to bf16) on a rows x cols x K sub-block sized for the time budget.
+    Returns (TFLOP/s, description, seconds)."""
+    rows, cols = min(m, 2048), min(n, 2048)
+    ac, asf = oracle.fp4_operand(min(rows, 256), k, 2, 0)
+    bc, bsf = oracle.fp4_operand(min(cols, 256), k, 2, 1)
+    ra, rb = max(1, rows // ac.shape[0]), max(1, cols // bc.shape[0])
+    # Tiled copies of a small generated block: the timing does not depend on the values.
+    ac, asf, bc, bsf = np.tile(ac, (ra, 1)), np.tile(asf, (ra, 1)), np.tile(bc, (rb, 1)), np.tile(bsf, (rb, 1))
+    probe_r, probe_c = min(128, ac.shape[0]), min(128, bc.shape[0])
+    t0 = time.perf_counter()
+    oracle.gemm_nvfp4_reference(ac[:probe_r], asf[:probe_r], bc[:probe_c], bsf[:probe_c])
+    rate = 2.0 * probe_r * probe_c * k / max(time.perf_counter() - t0, 1e-4)
+    # Keep the M : N proportion of the workload (decode shapes have few rows).
+    area = budget_s * rate / (2.0 * k)
+    r = int(min(ac.shape[0], max(16, (area * m / n) ** 0.5)))
+    c = int(min(bc.shape[0], max(128, area / max(r, 1))))
+    r, c = max(1, r // 16 * 16) if r >= 16 else r, max(128, c // 128 * 128)
+    best = None
+    for _ in range(2):
+        t0 = time.perf_counter()
+        oracle.gemm_nvfp4_reference(ac[:r], asf[:r], bc[:c], bsf[:c])
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return 2.0 * r * c * k / best / 1e12, f"{r}x{c}x{k} sub-block of the workload, best of 2", best
+
+
 def run_reference(args):
     """The reference arm: the reference's NumPy CPU GEMM on this host's cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -745,6 +773,14 @@ def main():
 
     # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1)
     cpu_baseline = None
+    if rank == 0 and g == 1 and not args.no_cpu_baseline and kind != "bf16":
+        oracle = _load_oracle()
+        rate, sample, secs = cpu_fp4_rate(oracle, m, n, k, budget_s=6.0)
+        threads, blas = blas_info()
+        cpu_baseline = {"value": rate, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                        "sample": sample + f" ({secs:.2f} s)", "host_cpus": os.cpu_count(), "blas": blas,
+                        "what": "reference NumPy CPU path: E2M1 codes and UE8M0 scales -> fp32, a @ b, "
+                                "round to bf16"}
     if rank == 0 and g == 1 and not args.no_cpu_baseline and kind == "bf16":
         oracle = _load_oracle()
         rows = min(m, 4096)
