@@ -303,6 +303,11 @@ int smb_peer_open(const unsigned char handle[SMB_PEER_HANDLE_BYTES], void** ptr)
 int smb_peer_close(void* ptr);
 int smb_peer_free(void* ptr);
 
+/* The column slab of rank `rank` of `world`: an equal split of N whose slabs keep 16-byte
+ * aligned bf16 rows (N % world == 0 and (N / world) % 8 == 0, else SMB_ERR_INVALID).  Pure
+ * arithmetic, no device needed; the drivers' --shard=RANK/WORLD uses it. */
+int smb_column_shard(int n_total, int world, int rank, int* n0, int* n_local);
+
 /* Unfused path: an all-gather of the [M, N/g] slabs (NCCL concatenates them rank-major as
  * [g, M, N/g]) followed by this copy into row-major [M, g * n_local] (pitch ldd elements).
  * n_local % 8 == 0, both buffers 16-byte aligned, ldd % 8 == 0.  Stream-ordered. */

@@ -99,6 +99,7 @@ DECLARED = [
     ("smb_peer_open", _i, [C.c_char_p, C.POINTER(_vp)]),
     ("smb_peer_close", _i, [_vp]),
     ("smb_peer_free", _i, [_vp]),
+    ("smb_column_shard", C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     ("smb_unshard_columns_device", _i, [_vp, _vp, _i, _i, _i, _i64, _vp]),
 ]
 

@@ -6,7 +6,8 @@
 // Beyond the reference: any positive M and N, any K that is a multiple of 8, fills 5..7
 // (Gaussian stand-ins), --json=PATH, --ordered-launches (stores of a launch wait for the
 // previous launch; by default the timing loop's launches are independent, as the reference's
-// are).  Operands are generated on the device.
+// are), --shard=RANK/WORLD and --device=INDEX (one process per GPU computes and dumps its column
+// slab of D).  Operands are generated on the device.
 #include "driver_common.h"
 
 namespace {
@@ -50,9 +51,13 @@ struct Options {
   // false (default): launches of the timing loop are independent of one another, as the
   // reference kernels' are; true: every launch orders its stores after the previous launch.
   bool ordered = false;
+  Shard shard;
 };
 
-double run_one(int M, int N, int K, const Options& o) {
+double run_one(int M, int n_total, int K, const Options& o) {
+  Shard shard = o.shard;
+  shard.resolve(n_total);
+  const int N = shard.n_local;   // everything below works on this process's slab
   uint16_t *a = nullptr, *bt = nullptr, *d = nullptr;
   DRV_CUDA(cudaMalloc(&a, static_cast<size_t>(M) * K * 2));
   DRV_CUDA(cudaMalloc(&bt, static_cast<size_t>(N) * K * 2));
@@ -62,7 +67,8 @@ double run_one(int M, int N, int K, const Options& o) {
   DRV_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
   // A: index m*K + k, seed 1.  BT[n][k] = B[k][n]: index k*N + n, seed 2.
   DRV_SMB(smb_fill_bf16_device(a, M, K, K, 0, static_cast<uint64_t>(K), 1, o.fill, 1, stream));
-  DRV_SMB(smb_fill_bf16_device(bt, N, K, K, 0, 1, static_cast<uint64_t>(N), o.fill, 2, stream));
+  DRV_SMB(smb_fill_bf16_device(bt, N, K, K, static_cast<uint64_t>(shard.n0), 1, static_cast<uint64_t>(n_total),
+                               o.fill, 2, stream));
   DRV_CUDA(cudaStreamSynchronize(stream));
 
   smb_bf16_plan* plan = nullptr;
@@ -152,11 +158,13 @@ int main(int argc, char** argv) {
       o.dump = argv[i] + 14;
     } else if (std::strncmp(argv[i], "--json=", 7) == 0) {
       o.json = argv[i] + 7;
+    } else if (o.shard.parse(argv[i])) {
     } else {
       std::fprintf(stderr, "unknown argument: %s\n", argv[i]);
       return 1;
     }
   }
+  DRV_CUDA(cudaSetDevice(o.shard.device));
   DRV_CUDA(cudaFree(0));
   std::printf("K0 dense_gemm_bf16 (Blackwell B200, sm_100a) -- fill=%d %s\n", o.fill,
               fill_label(o.fill));

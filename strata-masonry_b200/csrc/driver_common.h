@@ -87,3 +87,40 @@ inline void write_json(const char* path, const char* kernel, int M, int N, int K
                kernel, M, N, K, fill, timed ? "true" : "false", ms, tflops);
   std::fclose(f);
 }
+
+// --shard=RANK/WORLD and --device=INDEX (beyond the reference, which is single-GPU): the process
+// computes and dumps the column slab D[:, n0 : n0 + n_local) of the logical [M, N] problem, with
+// the operands generated from their global indices, so that the slabs of the WORLD processes of a
+// box, set side by side, are the single-process output bit for bit.
+struct Shard {
+  int rank = 0, world = 1, device = 0;
+  int n0 = 0, n_local = 0;   // set by resolve()
+  bool parse(const char* arg) {
+    if (std::strncmp(arg, "--shard=", 8) == 0) {
+      char tail = 0;
+      if (std::sscanf(arg + 8, "%d/%d%c", &rank, &world, &tail) != 2 || world < 1 || rank < 0 || rank >= world) {
+        std::fprintf(stderr, "--shard must be RANK/WORLD with 0 <= RANK < WORLD\n");
+        std::exit(1);
+      }
+      return true;
+    }
+    if (std::strncmp(arg, "--device=", 9) == 0) {
+      char tail = 0;
+      if (std::sscanf(arg + 9, "%d%c", &device, &tail) != 1 || device < 0) {
+        std::fprintf(stderr, "--device must be a device index\n");
+        std::exit(1);
+      }
+      return true;
+    }
+    return false;
+  }
+  void resolve(int N) {
+    if (smb_column_shard(N, world, rank, &n0, &n_local) != SMB_OK) {
+      std::fprintf(stderr, "unsupported --shard for this shape: %s\n", smb_last_error());
+      std::exit(1);
+    }
+    if (world > 1)
+      std::printf("  shard %d/%d: columns [%d, %d) of N=%d on device %d\n", rank, world, n0, n0 + n_local, N,
+                  device);
+  }
+};

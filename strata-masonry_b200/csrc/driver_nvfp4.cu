@@ -6,7 +6,8 @@
 // against the closed form (exact), the other fills on 2048 hashed samples against a host fp32
 // reference with tolerance max(0.8 % |ref|, 16).  FILL environment variable as default fill.
 // Beyond the reference: any positive M and N, any K that is a multiple of 32, fills 5 and 6
-// (quantised Gaussian stand-ins), --json=PATH, --ordered-launches; no arguments runs a short
+// (quantised Gaussian stand-ins), --json=PATH, --ordered-launches, --shard=RANK/WORLD and
+// --device=INDEX (one process per GPU computes its column slab of D); no arguments runs a short
 // shape list.
 #include <cmath>
 
@@ -34,6 +35,7 @@ struct Options {
   // false (default): launches of the timing loop are independent of one another, as the
   // reference kernels' are; true: every launch orders its stores after the previous launch.
   bool ordered = false;
+  Shard shard;
 };
 
 // One logical row of an operand on the host: values (code * scale) as floats.
@@ -51,7 +53,11 @@ void host_row(std::vector<float>& out, int row, int K, int fill, int which) {
   }
 }
 
-double run_one(int M, int N, int K, const Options& o) {
+double run_one(int M, int n_total, int K, const Options& o) {
+  Shard shard = o.shard;
+  shard.resolve(n_total);
+  const int N = shard.n_local;   // everything below works on this process's slab; global column = n0 + n
+  const int n0 = shard.n0;
   uint8_t *a = nullptr, *b = nullptr, *sfa = nullptr, *sfb = nullptr;
   uint16_t* d = nullptr;
   const size_t sfa_bytes = smb_sf_packed_bytes(M, K / 32), sfb_bytes = smb_sf_packed_bytes(N, K / 32);
@@ -64,7 +70,7 @@ double run_one(int M, int N, int K, const Options& o) {
   cudaStream_t stream;
   DRV_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
   DRV_SMB(smb_fill_fp4_device(a, K / 2, sfa, nullptr, M, K, 0, o.fill, 0, stream));
-  DRV_SMB(smb_fill_fp4_device(b, K / 2, sfb, nullptr, N, K, 0, o.fill, 1, stream));
+  DRV_SMB(smb_fill_fp4_device(b, K / 2, sfb, nullptr, N, K, static_cast<uint64_t>(n0), o.fill, 1, stream));
   DRV_CUDA(cudaStreamSynchronize(stream));
 
   smb_fp4_plan* plan = nullptr;
@@ -103,7 +109,7 @@ double run_one(int M, int N, int K, const Options& o) {
         for (int n = 0; n < N; ++n) {
           const float v = bf16_bits_to_float(host[static_cast<size_t>(m) * N + n]);
           if (std::isnan(v) || std::isinf(v)) { ++nan_count; continue; }
-          const float expected = per_product * K * sa * std::exp2(static_cast<float>(n % 3 - 1));
+          const float expected = per_product * K * sa * std::exp2(static_cast<float>((n0 + n) % 3 - 1));
           const float rel = std::fabs(v - expected) / expected;
           if (rel > max_rel) { max_rel = rel; bad_m = m; bad_n = n; }
         }
@@ -122,7 +128,7 @@ double run_one(int M, int N, int K, const Options& o) {
         const int m = static_cast<int>(hash32(2u * smp + 1u) % static_cast<uint32_t>(M));
         const int n = static_cast<int>(hash32(2u * smp + 2u) % static_cast<uint32_t>(N));
         host_row(ra, m, K, o.fill, 0);
-        host_row(rb, n, K, o.fill, 1);
+        host_row(rb, n0 + n, K, o.fill, 1);
         float acc = 0.0f;
         for (int k = 0; k < K; ++k) acc += ra[k] * rb[k];
         uint32_t bits;
@@ -197,11 +203,13 @@ int main(int argc, char** argv) {
       o.ordered = true;
     } else if (std::strncmp(argv[i], "--dump-output=", 14) == 0 && argv[i][14]) {
       o.dump = argv[i] + 14;
+    } else if (o.shard.parse(argv[i])) {
     } else if (std::strncmp(argv[i], "--json=", 7) == 0 && argv[i][7]) {
       o.json = argv[i] + 7;
     } else if (std::strcmp(argv[i], "--help") == 0) {
       std::printf("Usage: %s [--shape=M,K,N [--fill=1..6] [--no-benchmark]\n"
-                  "       [--no-gpu-verify] [--dump-output=PATH] [--json=PATH]]\n"
+                  "       [--no-gpu-verify] [--dump-output=PATH] [--json=PATH]\n"
+                  "       [--shard=RANK/WORLD] [--device=INDEX]]\n"
                   "No arguments: short sweep (FILL environment variable supported).\n", argv[0]);
       return 0;
     } else {
@@ -215,6 +223,7 @@ int main(int argc, char** argv) {
       return 1;
     }
   }
+  DRV_CUDA(cudaSetDevice(o.shard.device));
   DRV_CUDA(cudaFree(0));
   std::printf("K1 dense_gemm_nvfp4 (sm_100a, B200) -- block32 UE8M0\n\n");
   if (argc > 1) {

@@ -156,3 +156,19 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype
 }
 
 }  // namespace smb
+
+extern "C" int smb_column_shard(int n_total, int world, int rank, int* n0, int* n_local) {
+  using namespace smb;
+  if (n0 == nullptr || n_local == nullptr) return set_error(SMB_ERR_INVALID, "column shard: null output");
+  if (n_total <= 0) return set_error(SMB_ERR_INVALID, "column shard: N=%d must be positive", n_total);
+  if (world < 1 || rank < 0 || rank >= world)
+    return set_error(SMB_ERR_INVALID, "column shard: rank %d outside world of %d", rank, world);
+  if (n_total % world != 0)
+    return set_error(SMB_ERR_INVALID, "column shard: N=%d is not divisible by %d ranks", n_total, world);
+  const int local = n_total / world;
+  if (local % 8 != 0)
+    return set_error(SMB_ERR_INVALID, "column shard: N/g=%d must be a multiple of 8 (16-byte rows of D)", local);
+  *n0 = rank * local;
+  *n_local = local;
+  return SMB_OK;
+}

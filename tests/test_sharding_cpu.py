@@ -252,3 +252,22 @@ def test_scatter_slots_addresses_on_gloo(smb, tmp_path):
     lib = smb.capi.lib()
     assert lib.smb_bf16_plan_set_row_route(None, 0, None, 256, 8, 0) == smb.capi.SMB_ERR_INVALID
     assert lib.smb_sum_slots_bf16_device(None, None, 2, 8, None) == smb.capi.SMB_ERR_INVALID
+
+
+def test_c_abi_column_shard_agrees_with_the_python_helper(smb):
+    """smb_column_shard (what the drivers' --shard uses) and sharding.column_shard state the same
+    split and refuse the same inputs."""
+    import ctypes as C
+    lib = smb.capi.lib()
+    for n_total, world in ((8192, 8), (57344, 8), (768, 3), (64, 2), (8192, 1), (100, 4), (72, 3), (64, 3), (96, 0)):
+        for rank in (0, max(world - 1, 0), world):
+            n0, nl = C.c_int(-1), C.c_int(-1)
+            rc = lib.smb_column_shard(n_total, world, rank, C.byref(n0), C.byref(nl))
+            try:
+                want = smb.sharding.column_shard(n_total, world, rank)
+            except ValueError:
+                assert rc != 0, (n_total, world, rank)
+                assert "column shard" in smb.capi.last_error()
+                continue
+            assert rc == 0 and (n0.value, nl.value) == (want.n0, want.n_local), (n_total, world, rank)
+    assert lib.smb_column_shard(64, 2, 0, None, None) != 0
