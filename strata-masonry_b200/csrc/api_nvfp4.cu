@@ -162,6 +162,8 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
     D.alpha = 1.0f;
     D.dual = fp4_decode_prefers_dual(M);
     if (flags & SMB_FLAG_DECODE_DUAL) D.dual = true;
+    // Asked for by name, the dual form keeps its operands swapped for every M (no wide form).
+    D.narrow = (flags & SMB_FLAG_DECODE_DUAL) != 0;
     if (flags & SMB_FLAG_DECODE_SINGLE) D.dual = false;
     const int m_pad = (M + 15) / 16 * 16;
     rc = encode_tmap_2d(&D.tmap_w, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, ldb_bytes, 128, 128, true);

@@ -116,6 +116,7 @@ int fp4_launch(const Fp4Launch& L, cudaStream_t stream);
 struct Fp4DecodeLaunch {
   CUtensorMap tmap_w, tmap_x, tmap_sfw, tmap_sfx;
   CUtensorMap tmap_d;   // D as [M, N] bf16, boxes of fp4_decode_box_rows(M) x 128, no swizzle (d_tma only)
+  CUtensorMap tmap_d_rows;   // D as [M, N] bf16, boxes of 32 x 64, 128-byte swizzle (wide form, d_tma only)
   int M, N, K;       // M <= 128 activation rows, N weight rows
   void* d;
   int ldd;
@@ -129,6 +130,7 @@ struct Fp4DecodeLaunch {
   bool no_overlap;   // true: plain stream order, no programmatic dependent launch
   bool activations_dynamic;  // X and its scales are written by the previous kernel on the stream
   bool dual;         // two weight tiles per activation box (whole tile pairs; ignored with max_ctas > 0)
+  bool narrow;       // true: never the wide form (activations as the instruction's rows) of the dual kernel
   bool block16;      // E4M3 scales per 16 K (dual form only); tmap_sfw / tmap_sfx boxes are 256 words
   float alpha;       // factor on every accumulator (block16 only)
 };

@@ -20,6 +20,7 @@
 // Warp roles (256 threads): warp 0 TMA producer, warp 1 MMA issue + TMEM owner, warp 2 scale
 // copies (tcgen05.cp, issued apart from the MMAs so that they overlap them), warp 3 idle,
 // warps 4-7 epilogue (warp w reads TMEM lanes 32 (w % 4) .. +31).
+#include "epilogue.cuh"
 #include "gemm_common.cuh"
 #include "ptx.cuh"
 
@@ -28,6 +29,7 @@ namespace smb {
 namespace fp4d {
 
 constexpr int kThreads = 256;
+constexpr int kDualThreads = 384;    // dual-tile form: a second group of four epilogue warps
 constexpr int kBlockKBytes = 128;     // 256 E2M1 values
 constexpr int kBlockK = 256;
 constexpr int kWBytes = 128 * kBlockKBytes;   // 16 KiB weight box
@@ -547,7 +549,18 @@ struct DualParams {
 
 // V4: one E4M3 scale per 16 K (scale_vec::4X): four 4-byte scale cells per band and stage
 // instead of two, 2 KiB of scales per band, 48 instead of 24 tensor-memory columns per slot.
-template <bool V4>
+//
+// kWide (more than 64 activation rows, one tile pair per CTA): the operands are NOT swapped.  The
+// activations are the 128 rows of the instruction and the two weight tiles its 256 columns, one
+// instruction per K = 64 instead of two.  Why: the tensor core reads its operands from shared
+// memory at about 64 bytes per clock, and two 128 x 128 instructions read 2 x (4 + 4) KiB where
+// one 128 x 256 instruction reads 4 + 8 KiB; at M = 128 the swapped form spent 1024 cycles per
+// stage on operand reads (17 us for K = 8192, more than the HBM time), this form 768.  The
+// accumulator is then [m][n] as D is, and the epilogue is the tiled kernels' (32 x 64 boxes,
+// staged in the ring, which is free once the only tile pair of the CTA is complete).
+//   stage:  [W tile 0][W tile 1][X 128 x 128 B (rows >= m_pad never loaded, never stored)][SFW0][SFW1][SFX]
+//   TMEM :  256 accumulator columns, then per stage [SFX cells][cell 0: SFW0 SFW1][cell 1: ...]
+template <bool V4, bool kWide>
 __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x,
                                                  const CUtensorMap& tmap_sfw, const CUtensorMap& tmap_sfx,
                                                  const CUtensorMap& tmap_d, const DualParams& p) {
@@ -580,11 +593,16 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
   const int q_end = min(q_begin + p.pairs_per_cta, pairs);
   const uint32_t w1_off = kWBytes;
   const uint32_t x_off = 2 * kWBytes;
-  const uint32_t sfw0_off = x_off + static_cast<uint32_t>(p.m_pad) * kBlockKBytes;
+  const uint32_t sfw0_off = x_off + static_cast<uint32_t>(kWide ? kMaxPad : p.m_pad) * kBlockKBytes;
   const uint32_t sfw1_off = sfw0_off + kBandBytes;
   const uint32_t sfx_off = sfw1_off + kBandBytes;
-  const uint32_t bank_cols = 2u * static_cast<uint32_t>(p.m_pad);
+  const uint32_t bank_cols = kWide ? 256u : 2u * static_cast<uint32_t>(p.m_pad);
   const uint32_t slot_base = static_cast<uint32_t>(p.banks) * bank_cols;
+  // Epilogue warps 4-7 (group 0) and 8-11 (group 1) share the accumulator columns (= rows of D) of
+  // every tile: group 0 takes the first half in units of 16, group 1 the rest.  With 16 columns
+  // there is nothing to share and group 1 stays out of every barrier.
+  const int epi_groups = p.m_pad >= 32 ? 2 : 1;
+  const int cols_group0 = ((p.m_pad / 16 + 1) / 2) * 16;
 
   griddep_launch_dependents();
   if (threadIdx.x == 0) {
@@ -596,7 +614,7 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full_bar(b), 1);
-      mbar_init(acc_empty_bar(b), 4);
+      mbar_init(acc_empty_bar(b), 4 * epi_groups);   // one arrival per working epilogue warp
     }
     fence_mbar_init_cluster();
   }
@@ -713,8 +731,19 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
           for (int ki = 0; ki < 4; ++ki) {
             const uint32_t sf_id = V4 ? 0u : ((ki & 1) ? 2u : 0u);
             const uint32_t cell = static_cast<uint32_t>(V4 ? ki : (ki >> 1));
-            const uint32_t idesc = make_idesc_mxf4(128, p.m_pad, sf_id, sf_id, !V4);
             const uint32_t accum = (kb > 0 || ki > 0) ? 1u : 0u;
+            if (kWide) {
+              // One instruction over both weight tiles: rows = activations, 256 columns = the 128
+              // rows of W0 followed by those of W1 (adjacent in the stage), scales of cell c at
+              // [SFX cell c] and [cell c: SFW0, SFW1].
+              const uint32_t idesc = make_idesc_mxf4(128, 256, sf_id, sf_id, !V4);
+              const uint32_t sx = sf_t + 4u * cell;
+              const uint32_t sw = sf_t + kOperandCols + 8u * cell;
+              if (V4) mma_nvf4_ss<1>(acc0, desc_x + 2u * ki, desc_w0 + 2u * ki, idesc, sx, sw, accum);
+              else mma_mxf4_ss<1>(acc0, desc_x + 2u * ki, desc_w0 + 2u * ki, idesc, sx, sw, accum);
+              continue;
+            }
+            const uint32_t idesc = make_idesc_mxf4(128, p.m_pad, sf_id, sf_id, !V4);
             const uint32_t s0 = sf_t + 4u * cell, s1 = sf_t + kOperandCols + 4u * cell;
             const uint32_t sx = sf_t + 2u * kOperandCols + 4u * cell;
             if (V4) {
@@ -752,19 +781,32 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
       if (elect_one()) {
 #pragma unroll
         for (int cell = 0; cell < kCells; ++cell) {
-          tmem_cp_32x128b_warpx4<1>(sf_t + 4u * cell, d0 + cell * 32);
-          tmem_cp_32x128b_warpx4<1>(sf_t + kOperandCols + 4u * cell, d1 + cell * 32);
-          tmem_cp_32x128b_warpx4<1>(sf_t + 2u * kOperandCols + 4u * cell, dx + cell * 32);
+          if (kWide) {
+            tmem_cp_32x128b_warpx4<1>(sf_t + 4u * cell, dx + cell * 32);
+            tmem_cp_32x128b_warpx4<1>(sf_t + kOperandCols + 8u * cell, d0 + cell * 32);
+            tmem_cp_32x128b_warpx4<1>(sf_t + kOperandCols + 8u * cell + 4u, d1 + cell * 32);
+          } else {
+            tmem_cp_32x128b_warpx4<1>(sf_t + 4u * cell, d0 + cell * 32);
+            tmem_cp_32x128b_warpx4<1>(sf_t + kOperandCols + 4u * cell, d1 + cell * 32);
+            tmem_cp_32x128b_warpx4<1>(sf_t + 2u * kOperandCols + 4u * cell, dx + cell * 32);
+          }
         }
         mma_commit_1cta(sf_ready_bar(s));
       }
       __syncwarp();
       if (++s == stages) { s = 0; ph ^= 1u; }
     }
-  } else if (warp >= 4) {
-    // ------------------------------------------------------------- epilogue (4 warps)
+  } else if (warp >= 4 && (warp < 8 || epi_groups == 2)) {
+    // ------------------------------------------------------------- epilogue (4 or 8 warps)
+    // Thread (quarter, lane) owns weight row n = quarter * 32 + lane of a tile, i.e. one lane of
+    // tensor memory, whose columns are the rows m of D: the tile comes out transposed and goes
+    // through shared memory ([m][128 n] bf16, 256 bytes per m) to a TMA store.
     const int quarter = warp & 3;
+    const int group = (warp - 4) >> 2;
     const int row = quarter * 32 + lane;
+    const int col_begin = group == 0 ? 0 : cols_group0;
+    const int col_end = (group == 0 && epi_groups == 2) ? cols_group0 : p.m_pad;
+    const int epi_threads = 128 * epi_groups;
     const bool first_thread = (threadIdx.x == 128);
     bool store_pending = false;
     bool waited_for_previous_grid = false;
@@ -781,49 +823,114 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
         griddep_wait();   // first store to D
         waited_for_previous_grid = true;
       }
-      for (int sub = 0; sub < 2; ++sub) {
-        const int tile = 2 * q + sub;
-        if (tile >= tiles) break;
-        const int n = tile * 128 + row;
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                               static_cast<uint32_t>(bank) * bank_cols + static_cast<uint32_t>(sub * p.m_pad);
+      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(bank) * bank_cols;
+      if constexpr (kWide) {
+        // Lanes are rows of D, columns are columns of D: warp group g takes weight tile 2 q + g.
+        // The CTA has this one tile pair, so the ring is free and stages the 32 x 64 boxes.
+        PeerCopies none;
+        none.count = 0;
+        none.route_rows = 0;
+        StoreTarget out;
+        out.tmap_d = &tmap_d;
+        out.d_ptr = p.d;
+        out.ldd = p.ldd;
+        out.M = p.M;
+        out.N = p.N;
+        out.peers = &none;
+        out.alpha = p.alpha;
+        const uint32_t sbuf = ring_base + static_cast<uint32_t>((warp - 4) * kStoreBufBytes);
+        const uint32_t release = mapa_u32(acc_empty_bar(bank), 0);
+        const int col0 = (2 * q + group) * 128;
         if (p.d_tma) {
-          for (int c0 = 0; c0 < p.m_pad; c0 += chunk_rows) {
-            if (first_thread && store_pending) bulk_wait_group_read<0>();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            for (int c = c0; c < c0 + chunk_rows && c < p.m_pad; c += 16) {
+          drain_and_store<128, true, false, V4>(tbase + static_cast<uint32_t>(group * 128), sbuf, out,
+                                                quarter * 32, col0, release, lane);
+          drain_store_groups<true>(lane);
+        } else {
+          drain_and_store<128, false, false, V4>(tbase + static_cast<uint32_t>(group * 128), sbuf, out,
+                                                 quarter * 32, col0, release, lane);
+        }
+        continue;
+      }
+      if (p.d_tma && q == q_end - 1) {
+        // Last tile pair of this CTA: every load has been consumed (the accumulators are
+        // complete), so the whole ring is free and takes both transposed tiles at once,
+        // [sub][m][128 n]; no chunking, one barrier, then all stores.
+        for (int sub = 0; sub < 2; ++sub) {
+          if (2 * q + sub >= tiles) break;
+          for (int c = col_begin; c < col_end; c += 16) {
+            float v[16];
+            ld16(tbase + static_cast<uint32_t>(sub * p.m_pad + c), v);
+            if (V4) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t dst = ring_base + static_cast<uint32_t>((sub * p.m_pad + c + j) * 256 + row * 2);
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst), "h"(to_bf16(v[j])) : "memory");
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
+        if (first_thread) {
+          for (int sub = 0; sub < 2; ++sub) {
+            const int tile = 2 * q + sub;
+            if (tile >= tiles) break;
+            for (int c0 = 0; c0 < p.m_pad; c0 += chunk_rows) {
+              tma_store_2d(&tmap_d, ring_base + static_cast<uint32_t>((sub * p.m_pad + c0) * 256), tile * 128, c0);
+            }
+          }
+          bulk_commit_group();
+          store_pending = true;
+        }
+      } else {
+        for (int sub = 0; sub < 2; ++sub) {
+          const int tile = 2 * q + sub;
+          if (tile >= tiles) break;
+          const int n = tile * 128 + row;
+          const uint32_t taddr = tbase + static_cast<uint32_t>(sub * p.m_pad);
+          if (p.d_tma) {
+            for (int c0 = 0; c0 < p.m_pad; c0 += chunk_rows) {
+              if (first_thread && store_pending) bulk_wait_group_read<0>();
+              asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
+              const int lo = c0 > col_begin ? c0 : col_begin;
+              const int hi = c0 + chunk_rows < col_end ? c0 + chunk_rows : col_end;
+              for (int c = lo; c < hi; c += 16) {
+                float v[16];
+                ld16(taddr + c, v);
+                if (V4) {
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const uint32_t dst = stage_base + static_cast<uint32_t>((c - c0 + j) * 256 + row * 2);
+                  asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst), "h"(to_bf16(v[j])) : "memory");
+                }
+              }
+              fence_proxy_async_smem();
+              asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
+              if (first_thread) {
+                tma_store_2d(&tmap_d, stage_base, tile * 128, c0);
+                bulk_commit_group();
+                store_pending = true;
+              }
+            }
+          } else {
+            for (int c = col_begin; c < col_end; c += 16) {
               float v[16];
               ld16(taddr + c, v);
               if (V4) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
               }
+              if (n < p.N) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const uint32_t dst = stage_base + static_cast<uint32_t>((c - c0 + j) * 256 + row * 2);
-                asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst), "h"(to_bf16(v[j])) : "memory");
-              }
-            }
-            fence_proxy_async_smem();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (first_thread) {
-              tma_store_2d(&tmap_d, stage_base, tile * 128, c0);
-              bulk_commit_group();
-              store_pending = true;
-            }
-          }
-        } else {
-          for (int c = 0; c < p.m_pad; c += 16) {
-            float v[16];
-            ld16(taddr + c, v);
-            if (V4) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
-            }
-            if (n < p.N) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (c + j < p.M) p.d[static_cast<size_t>(c + j) * p.ldd + n] = to_bf16(v[j]);
+                for (int j = 0; j < 16; ++j) {
+                  if (c + j < p.M) p.d[static_cast<size_t>(c + j) * p.ldd + n] = to_bf16(v[j]);
+                }
               }
             }
           }
@@ -844,15 +951,15 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
   }
 }
 
-template <bool V4>
-__global__ void __launch_bounds__(kThreads, 1)
+template <bool V4, bool kWide>
+__global__ void __launch_bounds__(kDualThreads, 1)
 gemm_nvfp4_decode_dual_kernel(const __grid_constant__ CUtensorMap tmap_w,
                               const __grid_constant__ CUtensorMap tmap_x,
                               const __grid_constant__ CUtensorMap tmap_sfw,
                               const __grid_constant__ CUtensorMap tmap_sfx,
                               const __grid_constant__ CUtensorMap tmap_d,
                               const __grid_constant__ DualParams p) {
-  decode_dual_body<V4>(tmap_w, tmap_x, tmap_sfw, tmap_sfx, tmap_d, p);
+  decode_dual_body<V4, kWide>(tmap_w, tmap_x, tmap_sfw, tmap_sfx, tmap_d, p);
 }
 
 }  // namespace fp4d
@@ -872,11 +979,11 @@ int fp4_decode_box_rows(int M) {
 
 namespace {
 
-template <bool V4>
+template <bool V4, bool kWide>
 int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   constexpr int kBandBytes = V4 ? 2048 : 1024;
   constexpr int kSlotCols = V4 ? 48 : 24;
-  auto kernel = fp4d::gemm_nvfp4_decode_dual_kernel<V4>;
+  auto kernel = fp4d::gemm_nvfp4_decode_dual_kernel<V4, kWide>;
   static thread_local int configured_device = -1;
   static thread_local int sm_count = 0;
   constexpr int kSmemBudget = 227 * 1024;
@@ -893,14 +1000,15 @@ int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   p.N = L.N;
   p.K = L.K;
   p.m_pad = (L.M + 15) / 16 * 16;
-  p.stage_bytes = 2 * fp4d::kWBytes + p.m_pad * fp4d::kBlockKBytes + 3 * kBandBytes;
+  // The wide form keeps room for all 128 rows of the instruction's first operand in every stage.
+  p.stage_bytes = 2 * fp4d::kWBytes + (kWide ? fp4d::kMaxPad : p.m_pad) * fp4d::kBlockKBytes + 3 * kBandBytes;
   const int staging = fp4_decode_box_rows(L.M) * 256;
   int stages = (kSmemBudget - 1024 - fp4d::kBarrierBytes - staging) / p.stage_bytes;
   if (stages > fp4d::kMaxStages) stages = fp4d::kMaxStages;
   // Two accumulator banks (a tile pair is drained while the next one is multiplied) when they fit
-  // beside at least three scale slots, else one.
-  p.banks = (4 * p.m_pad + 3 * kSlotCols <= 512) ? 2 : 1;
-  const int max_slots = (512 - p.banks * 2 * p.m_pad) / kSlotCols;
+  // beside at least three scale slots, else one.  The wide form has 256 accumulator columns.
+  p.banks = (!kWide && 4 * p.m_pad + 3 * kSlotCols <= 512) ? 2 : 1;
+  const int max_slots = (512 - (kWide ? 256 : p.banks * 2 * p.m_pad)) / kSlotCols;
   if (stages > max_slots) stages = max_slots;
   if (L.max_stages > 0 && stages > L.max_stages) stages = L.max_stages;
   if (stages < 2) return set_error(SMB_ERR_UNSUPPORTED, "decode (dual): activation tile too large");
@@ -916,7 +1024,7 @@ int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   const int grid = (pairs + p.pairs_per_cta - 1) / p.pairs_per_cta;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(fp4d::kThreads, 1, 1);
+  cfg.blockDim = dim3(fp4d::kDualThreads, 1, 1);
   cfg.dynamicSmemBytes = 1024 + stages * p.stage_bytes + staging + fp4d::kBarrierBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr;
@@ -924,7 +1032,10 @@ int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   attr.val.programmaticStreamSerializationAllowed = L.no_overlap ? 0 : 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L.tmap_w, L.tmap_x, L.tmap_sfw, L.tmap_sfx, L.tmap_d, p);
+  if (kWide && p.pairs_per_cta != 1)
+    return set_error(SMB_ERR_INVALID, "decode (wide): one tile pair per CTA only");
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L.tmap_w, L.tmap_x, L.tmap_sfw, L.tmap_sfx,
+                                     kWide ? L.tmap_d_rows : L.tmap_d, p);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error(e, "nvfp4 decode (dual) launch");
   return SMB_OK;
@@ -934,11 +1045,28 @@ int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
 
 bool fp4_decode_prefers_dual(int M) { return (M + 15) / 16 * 16 >= fp4d::kDualFromPad; }
 
+namespace {
+// More than 64 activation rows and at most one tile pair per SM: the form with the activations as
+// the instruction's rows (see decode_dual_body).
+bool fp4_decode_wide_applies(const Fp4DecodeLaunch& L) {
+  if (L.narrow || (L.M + 15) / 16 * 16 <= 64) return false;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return false;
+  const int pairs = ((L.N + 127) / 128 + 1) / 2;
+  return pairs <= sms;
+}
+}  // namespace
+
 int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   // The dual-tile form has whole tile pairs only: a caller that asks for a CTA count gets the
   // stream-K ranges of the single form.
-  if (L.block16) return fp4_decode_dual_launch<true>(L, stream);   // this format has the dual form only
-  if (L.dual && L.max_ctas == 0) return fp4_decode_dual_launch<false>(L, stream);
+  const bool wide = (L.block16 || (L.dual && L.max_ctas == 0)) && fp4_decode_wide_applies(L);
+  if (L.block16)   // this format has the dual forms only
+    return wide ? fp4_decode_dual_launch<true, true>(L, stream) : fp4_decode_dual_launch<true, false>(L, stream);
+  if (L.dual && L.max_ctas == 0)
+    return wide ? fp4_decode_dual_launch<false, true>(L, stream) : fp4_decode_dual_launch<false, false>(L, stream);
   static thread_local int configured_device = -1;
   static thread_local int sm_count = 0;
   constexpr int kSmemBudget = 227 * 1024;
@@ -1023,10 +1151,15 @@ int fp4_decode_bind_output(Fp4DecodeLaunch* L, void* d, int M, int N, long long 
   L->d = d;
   L->ldd = static_cast<int>(ldd);
   L->d_tma = allow_tma && (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0);
-  if (L->d_tma)
-    return encode_tmap_2d(&L->tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldd * 2,
-                          fp4_decode_box_rows(M), 128, false);
+  if (L->d_tma) {
+    int rc = encode_tmap_2d(&L->tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldd * 2,
+                            fp4_decode_box_rows(M), 128, false);
+    if (rc == SMB_OK)
+      rc = encode_tmap_2d(&L->tmap_d_rows, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldd * 2, 32, 64, true);
+    return rc;
+  }
   L->tmap_d = L->tmap_w;   // never dereferenced
+  L->tmap_d_rows = L->tmap_w;
   return SMB_OK;
 }
 
@@ -1114,6 +1247,7 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
   L.max_stages = 0;
   L.activations_dynamic = false;
   L.dual = fp4_decode_prefers_dual(M);
+  L.narrow = false;
   L.block16 = false;
   L.alpha = 1.0f;
   L.no_overlap = true;   // the memset below must be ordered before every access of this launch

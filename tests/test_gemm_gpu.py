@@ -695,6 +695,26 @@ def test_fp4_decode_forms_agree_bit_for_bit(smb, cuda_device):
         _, _, single = _run_fp4_decode(smb, m, 28672, 8192, flags=smb.capi.FLAG_DECODE_SINGLE)
         _, _, dual = _run_fp4_decode(smb, m, 28672, 8192, flags=smb.capi.FLAG_DECODE_DUAL)
         assert torch.equal(single[0].view(torch.int16), dual[0].view(torch.int16))
+        # The default choice: above 64 rows the dual kernel's wide form (activations as the rows of
+        # the instruction, both weight tiles as its 256 columns), same sums in the same order.
+        _, _, chosen = _run_fp4_decode(smb, m, 28672, 8192)
+        assert torch.equal(single[0].view(torch.int16), chosen[0].view(torch.int16))
+
+
+@pytest.mark.parametrize("shape", [(65, 640, 512), (100, 28672 + 128, 1024), (128, 37888, 512),
+                                   (128, 37888 + 256, 512), (77, 1001, 768), (128, 128, 256), (113, 2000, 8192)])
+def test_fp4_decode_wide_form_edges(smb, cuda_device, shape):
+    """The wide decode form at its edges: ragged M above 64, an odd number of weight tiles, N not a
+    multiple of 128, a D pitch that rules out TMA stores (N = 1001), the largest N it takes (one
+    tile pair per SM) and the first N beyond it (which falls back to the swapped form): inside the
+    north-star bound of the float64 product, bit-identical to the single-tile form, two runs."""
+    torch = _torch()
+    m, n, k = shape
+    A, B, outs = _run_fp4_decode(smb, m, n, k, runs=2)
+    _check_fp4_full(A, B, outs[0], k)
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    _, _, single = _run_fp4_decode(smb, m, n, k, flags=smb.capi.FLAG_DECODE_SINGLE)
+    assert torch.equal(single[0].view(torch.int16), outs[0].view(torch.int16))
 
 
 # ------------------------------------------------------------------------------- NVFP4 proper
