@@ -353,9 +353,11 @@ int smb_unshard_columns_device(const void* gathered, void* d, int g, int M, int 
 #define SMB_FLAG_SCALE_BLOCK16 16384u
 #define SMB_FLAG_NO_DECODE 64u        /* FP4 only: M <= 128 through the tiled kernel, not the decode kernel */
 #define SMB_FLAG_NO_LAUNCH_OVERLAP 128u /* decode kernel: no programmatic dependent launch */
-/* Decode kernel (FP4, M <= 128): force the form in which a CTA multiplies two adjacent weight
- * tiles against one copy of the activations (the default), or the
- * form with one weight tile per activation box. */
+/* Decode kernel (FP4, M <= 128).  By default a CTA multiplies two adjacent weight tiles against
+ * one copy of the activations; up to 64 rows the weights are the rows of the instruction and the
+ * activations its columns, above 64 rows (and N <= 256 x SMs) the other way round.  DECODE_DUAL
+ * forces the two-tile form with the weights as rows for every M, DECODE_SINGLE the form with one
+ * weight tile per activation box.  All forms give the same bits. */
 #define SMB_FLAG_DECODE_DUAL 512u
 #define SMB_FLAG_DECODE_SINGLE 2048u
 
