@@ -164,6 +164,8 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
     if (flags & SMB_FLAG_DECODE_DUAL) D.dual = true;
     // Asked for by name, the dual form keeps its operands swapped for every M (no wide form).
     D.narrow = (flags & SMB_FLAG_DECODE_DUAL) != 0;
+    D.act_src = nullptr;
+    D.act_ld = 0;
     if (flags & SMB_FLAG_DECODE_SINGLE) D.dual = false;
     const int m_pad = (M + 15) / 16 * 16;
     rc = encode_tmap_2d(&D.tmap_w, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, ldb_bytes, 128, 128, true);
@@ -310,6 +312,8 @@ extern "C" int smb_fp4_plan_create_bf16_activations(smb_fp4_plan** out, const vo
   p->act_codes = codes;
   p->act_sf = sf;
   p->dlaunch.activations_dynamic = true;
+  p->dlaunch.act_src = x_bf16;
+  p->dlaunch.act_ld = ldx;
   *out = p;
   return SMB_OK;
 }
@@ -320,7 +324,8 @@ extern "C" int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream) {
   if (cudaGetDevice(&device) != cudaSuccess || device != plan->device)
     return set_error(SMB_ERR_INVALID, "fp4 plan: created on device %d, run with device %d current",
                      plan->device, device);
-  if (plan->act_src != nullptr) {
+  // Where the decode kernel quantises the BF16 activations itself there is nothing to launch first.
+  if (plan->act_src != nullptr && !(plan->decode && fp4_decode_fuses_activations(plan->dlaunch))) {
     const bool chained = !(plan->decode && plan->dlaunch.no_overlap);
     int rc = quantize_bf16_launch(plan->act_src, plan->act_ld, plan->act_codes, plan->launch.K / 2,
                                   plan->act_sf, nullptr, plan->launch.M, plan->launch.K, chained,

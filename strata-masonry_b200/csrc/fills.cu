@@ -101,21 +101,9 @@ SMB_HD void fp4_block(uint32_t grow, uint32_t kb, uint32_t K, int fill, int whic
   *scale_byte = static_cast<uint8_t>(e + 127);
 }
 
-// Quantise one block of 32 fp32 values.
+// Quantise one block of 32 fp32 values (formats.cuh).
 SMB_HD void quantize_block(const float* v, uint8_t* codes16, uint8_t* scale_byte) {
-  float amax = 0.0f;
-  for (int i = 0; i < 32; ++i) {
-    const float a = v[i] < 0.0f ? -v[i] : v[i];
-    amax = a > amax ? a : amax;
-  }
-  const int e = fmt::ue8m0_exponent(amax);
-  const float inv = fmt::exp2i(-e);
-  for (int i = 0; i < 16; ++i) {
-    const uint32_t lo = fmt::e2m1_encode(fmt::mul_rn(v[2 * i], inv));
-    const uint32_t hi = fmt::e2m1_encode(fmt::mul_rn(v[2 * i + 1], inv));
-    codes16[i] = static_cast<uint8_t>(lo | (hi << 4));
-  }
-  *scale_byte = static_cast<uint8_t>(e + 127);
+  fmt::quantize_mx_block(v, codes16, scale_byte);
 }
 
 __global__ void fill_fp4_kernel(uint8_t* data, int64_t ld_bytes, uint8_t* sf_packed,

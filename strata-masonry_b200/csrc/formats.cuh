@@ -174,6 +174,25 @@ SMB_HD float e4m3_decode(uint32_t code) {
   return mul_rn(1.0f + static_cast<float>(m) * 0.125f, exp2i(static_cast<int>(e) - 7));
 }
 
+// FP32 -> E2M1 + UE8M0, one block of 32 values: scale exponent = the smallest e with
+// 6 * 2^e >= max|v|, codes = nearest E2M1 value of v * 2^-e (ties to the even code), two codes per
+// byte with the even element in the low nibble.
+SMB_HD void quantize_mx_block(const float* v, uint8_t* codes16, uint8_t* scale_byte) {
+  float amax = 0.0f;
+  for (int i = 0; i < 32; ++i) {
+    const float a = v[i] < 0.0f ? -v[i] : v[i];
+    amax = a > amax ? a : amax;
+  }
+  const int e = ue8m0_exponent(amax);
+  const float inv = exp2i(-e);
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t lo = e2m1_encode(mul_rn(v[2 * i], inv));
+    const uint32_t hi = e2m1_encode(mul_rn(v[2 * i + 1], inv));
+    codes16[i] = static_cast<uint8_t>(lo | (hi << 4));
+  }
+  *scale_byte = static_cast<uint8_t>(e + 127);
+}
+
 // NVFP4 proper: 16 values share one E4M3 scale; `gs` is the caller's per-tensor factor
 // (typically 448 * 6 / max|tensor|).  scale = e4m3(max|v| * gs / 6); code = e2m1(v * gs / scale).
 // The represented value is e2m1(code) * e4m3(scale) / gs.

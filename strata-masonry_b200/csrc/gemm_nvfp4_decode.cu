@@ -21,6 +21,7 @@
 // copies (tcgen05.cp, issued apart from the MMAs so that they overlap them), warp 3 idle,
 // warps 4-7 epilogue (warp w reads TMEM lanes 32 (w % 4) .. +31).
 #include "epilogue.cuh"
+#include "formats.cuh"
 #include "gemm_common.cuh"
 #include "ptx.cuh"
 
@@ -30,6 +31,8 @@ namespace fp4d {
 
 constexpr int kThreads = 256;
 constexpr int kDualThreads = 384;    // dual-tile form: a second group of four epilogue warps
+constexpr int kQuantWarps = 8;
+constexpr int kFusedThreads = kDualThreads + 32 * kQuantWarps;   // + warps that quantise BF16 activations into the ring
 constexpr int kBlockKBytes = 128;     // 256 E2M1 values
 constexpr int kBlockK = 256;
 constexpr int kWBytes = 128 * kBlockKBytes;   // 16 KiB weight box
@@ -531,6 +534,59 @@ gemm_nvfp4_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
 //   TMEM :  banks of 2 x m_pad accumulator columns (two banks when they fit beside the scale
 //           slots, else one), then per stage 24 scale columns (SFW0 | SFW1 | SFX).
 // -----------------------------------------------------------------------------------
+// Eight fp32 values -> eight E2M1 codes in one word (value 0 in the low nibble of byte 0), by the
+// hardware conversion: round to nearest, ties to the even code, saturating at 6 -- what
+// fmt::e2m1_encode computes with comparisons.  The first source of the instruction lands in the
+// high nibble.
+__device__ __forceinline__ uint32_t e2m1x8_from_f32(float f0, float f1, float f2, float f3, float f4,
+                                                    float f5, float f6, float f7) {
+  uint32_t out;
+  asm("{\n\t"
+      ".reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t"
+      "}"
+      : "=r"(out)
+      : "f"(f0), "f"(f1), "f"(f2), "f"(f3), "f"(f4), "f"(f5), "f"(f6), "f"(f7));
+  return out;
+}
+
+// One block of 32 BF16 values (sixteen words, even element in the low half) -> sixteen code bytes
+// and the UE8M0 scale byte; the same result as fmt::quantize_mx_block on the widened values for
+// finite inputs, in about four instructions per value instead of twenty-five: every CTA of the
+// decode kernel quantises all activations again, so the conversion has to be cheap.
+__device__ __forceinline__ void quantize_mx_block_bf16(const uint4 (&raw)[4], uint4* codes, uint32_t* scale_byte) {
+  const uint32_t w[16] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w,
+                          raw[2].x, raw[2].y, raw[2].z, raw[2].w, raw[3].x, raw[3].y, raw[3].z, raw[3].w};
+  uint32_t m = 0u;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t a = w[i] & 0x7FFF7FFFu;   // |x| of both halves
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(m) : "r"(m), "r"(a));
+  }
+  const float hi = __uint_as_float(m & 0xFFFF0000u), lo = __uint_as_float(m << 16);
+  const int e = fmt::ue8m0_exponent(hi > lo ? hi : lo);
+  const float inv = fmt::exp2i(-e);
+  uint32_t out[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float f[8];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      // + 0 in the same rounding turns a negative zero into the positive one, as the comparison
+      // form does; every other product is unchanged.
+      f[2 * t] = __fmaf_rn(__uint_as_float(w[4 * q + t] << 16), inv, 0.0f);
+      f[2 * t + 1] = __fmaf_rn(__uint_as_float(w[4 * q + t] & 0xFFFF0000u), inv, 0.0f);
+    }
+    out[q] = e2m1x8_from_f32(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7]);
+  }
+  *codes = make_uint4(out[0], out[1], out[2], out[3]);
+  *scale_byte = static_cast<uint32_t>(e + 127);
+}
+
 struct DualParams {
   int M, N, K;
   int m_pad;
@@ -544,6 +600,8 @@ struct DualParams {
   int d_tma;
   int activations_dynamic;
   float alpha;          // factor on every accumulator (block-16 scales: 1 / (global scale X x W))
+  const uint16_t* x_src;   // kFused: BF16 activations [M, K], quantised by the kernel itself
+  long long ldx;           // elements between their rows
 };
 
 
@@ -560,7 +618,15 @@ struct DualParams {
 // staged in the ring, which is free once the only tile pair of the CTA is complete).
 //   stage:  [W tile 0][W tile 1][X 128 x 128 B (rows >= m_pad never loaded, never stored)][SFW0][SFW1][SFX]
 //   TMEM :  256 accumulator columns, then per stage [SFX cells][cell 0: SFW0 SFW1][cell 1: ...]
-template <bool V4, bool kWide>
+//
+// kFused (swapped form, UE8M0 scales): the activations arrive as BF16 and eight extra warps
+// quantise them straight into the ring: for every stage one warp reads the stage's 256 K values of
+// all rows from global memory (L2-resident after the first CTA), computes scale and codes per 32
+// values exactly as quantize_mx_bf16_kernel does, and writes the codes in the 128-byte-swizzled
+// layout a TMA load would have produced and the scale bytes in the packed cell layout, then
+// arrives on the stage's barriers beside the TMA producer.  Saves the separate quantiser launch
+// of a decode step (M = 16, N = 28672, K = 8192: 21.9 us per step against 23.2 us chained).
+template <bool V4, bool kWide, bool kFused>
 __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x,
                                                  const CUtensorMap& tmap_sfw, const CUtensorMap& tmap_sfx,
                                                  const CUtensorMap& tmap_d, const DualParams& p) {
@@ -607,9 +673,9 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
   griddep_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), kFused ? 2 : 1);      // TMA producer (+ the quantising warp of the stage)
       mbar_init(empty_bar(s), 1);
-      mbar_init(sf_full_bar(s), 1);
+      mbar_init(sf_full_bar(s), kFused ? 2 : 1);
       mbar_init(sf_ready_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -639,10 +705,10 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
     // ------------------------------------------------------------- TMA producer
     const uint64_t stream_once = l2_policy_evict_first();
     const uint64_t keep = l2_policy_evict_last();
-    const uint32_t op_bytes = 2 * kWBytes + static_cast<uint32_t>(p.m_pad) * kBlockKBytes;
+    const uint32_t op_bytes = 2 * kWBytes + (kFused ? 0u : static_cast<uint32_t>(p.m_pad) * kBlockKBytes);
     int s = 0;
     uint32_t ph = 0;
-    bool waited = !p.activations_dynamic;
+    bool waited = kFused || !p.activations_dynamic;
     int issued = 0;
     for (int q = q_begin; q < q_end; ++q) {
       for (int kb = 0; kb < num_kb; ++kb, ++issued) {
@@ -669,14 +735,14 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
         }
         const uint32_t dst = ring_base + static_cast<uint32_t>(s * p.stage_bytes);
         if (elect_one()) {
-          mbar_arrive_expect_tx(sf_full_bar(s), 3 * kBandBytes);
+          mbar_arrive_expect_tx(sf_full_bar(s), (kFused ? 2 : 3) * kBandBytes);
           tma_load_2d_cta_hint(dst + sfw0_off, &tmap_sfw, sf_full_bar(s), kb * kSfBox, 2 * q, stream_once);
           tma_load_2d_cta_hint(dst + sfw1_off, &tmap_sfw, sf_full_bar(s), kb * kSfBox, 2 * q + 1, stream_once);
           mbar_arrive_expect_tx(full_bar(s), op_bytes);
           tma_load_2d_cta_hint(dst, &tmap_w, full_bar(s), kb * kBlockKBytes, (2 * q) * 128, stream_once);
           tma_load_2d_cta_hint(dst + w1_off, &tmap_w, full_bar(s), kb * kBlockKBytes, (2 * q + 1) * 128,
                                stream_once);
-          if (waited) {
+          if (waited && !kFused) {
             tma_load_2d_cta_hint(dst + sfx_off, &tmap_sfx, sf_full_bar(s), kb * kSfBox, 0, keep);
             tma_load_2d_cta_hint(dst + x_off, &tmap_x, full_bar(s), kb * kBlockKBytes, 0, keep);
           }
@@ -796,7 +862,7 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
       __syncwarp();
       if (++s == stages) { s = 0; ph ^= 1u; }
     }
-  } else if (warp >= 4 && (warp < 8 || epi_groups == 2)) {
+  } else if (warp >= 4 && (warp < 8 || (warp < 12 && epi_groups == 2))) {
     // ------------------------------------------------------------- epilogue (4 or 8 warps)
     // Thread (quarter, lane) owns weight row n = quarter * 32 + lane of a tile, i.e. one lane of
     // tensor memory, whose columns are the rows m of D: the tile comes out transposed and goes
@@ -941,6 +1007,69 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
       if (lane == 0) mbar_arrive(acc_empty_bar(bank));
     }
     if (first_thread && store_pending) bulk_wait_group_read<0>();
+  } else if (kFused && warp >= 12) {
+    // ------------------------------------------------------------- activation quantiser (kQuantWarps warps)
+    // Warp w takes the stages w, w + kQuantWarps, ...: a stage visit costs an L2 round trip, and
+    // that many visits in flight keep up with the weight stream.  Lane l of a pass holds blocks l, l + 32, l + 64,
+    // l + 96 of the stage (block = row * 8 + k-block: eight lanes read 512 contiguous bytes of a row).
+    // No more warps than ring slots take part: a warp whose consecutive visits lay more than one
+    // ring cycle apart could be two barrier phases ahead of a slot, and a parity wait cannot tell
+    // "two phases ago" from "now" (it would pass early and arrive on a barrier that is still in
+    // use).
+    const int qw = warp - 12;
+    const int q_active = stages < kQuantWarps ? stages : kQuantWarps;
+    const int total = qw < q_active ? (q_end - q_begin) * num_kb : 0;
+    const int kblocks = p.K / 32;
+    const int stage_blocks = p.m_pad * 8;
+    griddep_wait();   // the activations are the previous kernel's output
+    for (int g = qw; g < total; g += q_active) {
+      const int s = g % stages;
+      const uint32_t ph = static_cast<uint32_t>(g / stages) & 1u;
+      const int kb = g % num_kb;
+      if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
+        if (lane == 0) report_status(p.status, kDevTimeoutProducer);
+        break;
+      }
+      const uint32_t dst = ring_base + static_cast<uint32_t>(s * p.stage_bytes);
+      for (int b0 = 0; b0 < stage_blocks; b0 += 128) {
+        uint4 raw[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int b = b0 + i * 32 + lane;
+          const int r = b >> 3, gk = kb * 8 + (b & 7);
+          if (b < stage_blocks && r < p.M && gk < kblocks) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.x_src + static_cast<long long>(r) * p.ldx + gk * 32);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) raw[i][j] = __ldg(src + j);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) raw[i][j] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int b = b0 + i * 32 + lane;
+          if (b >= stage_blocks) continue;
+          const int r = b >> 3, j8 = b & 7;
+          uint4 packed;
+          uint32_t sb;
+          quantize_mx_block_bf16(raw[i], &packed, &sb);   // an all-zero block (padding): codes 0, scale 127
+          // Codes: row r, 16-byte chunk j8 of its 128 bytes, at chunk j8 ^ (r % 8) (128-byte swizzle).
+          st_shared_v4(dst + x_off + static_cast<uint32_t>(r * 128 + ((j8 ^ (r & 7)) << 4)), packed.x, packed.y,
+                       packed.z, packed.w);
+          // Scale: cell j8 / 4, line r % 32, 4-byte group r / 32, byte j8 % 4.
+          const uint32_t sf_dst = dst + sfx_off +
+                                  static_cast<uint32_t>((j8 >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (j8 & 3));
+          asm volatile("st.shared.u8 [%0], %1;" ::"r"(sf_dst), "r"(sb) : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(sf_full_bar(s));
+        mbar_arrive(full_bar(s));
+      }
+    }
   }
   __syncwarp();
   tc_fence_before_sync();
@@ -951,15 +1080,16 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
   }
 }
 
-template <bool V4, bool kWide>
-__global__ void __launch_bounds__(kDualThreads, 1)
+template <bool V4, bool kWide, bool kFused>
+__global__ void __launch_bounds__(kFused ? kFusedThreads : kDualThreads, 1)
 gemm_nvfp4_decode_dual_kernel(const __grid_constant__ CUtensorMap tmap_w,
                               const __grid_constant__ CUtensorMap tmap_x,
                               const __grid_constant__ CUtensorMap tmap_sfw,
                               const __grid_constant__ CUtensorMap tmap_sfx,
                               const __grid_constant__ CUtensorMap tmap_d,
                               const __grid_constant__ DualParams p) {
-  decode_dual_body<V4, kWide>(tmap_w, tmap_x, tmap_sfw, tmap_sfx, tmap_d, p);
+  static_assert(!kFused || (!V4 && !kWide), "the fused quantiser exists for the swapped UE8M0 form");
+  decode_dual_body<V4, kWide, kFused>(tmap_w, tmap_x, tmap_sfw, tmap_sfx, tmap_d, p);
 }
 
 }  // namespace fp4d
@@ -979,11 +1109,11 @@ int fp4_decode_box_rows(int M) {
 
 namespace {
 
-template <bool V4, bool kWide>
+template <bool V4, bool kWide, bool kFused = false>
 int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   constexpr int kBandBytes = V4 ? 2048 : 1024;
   constexpr int kSlotCols = V4 ? 48 : 24;
-  auto kernel = fp4d::gemm_nvfp4_decode_dual_kernel<V4, kWide>;
+  auto kernel = fp4d::gemm_nvfp4_decode_dual_kernel<V4, kWide, kFused>;
   static thread_local int configured_device = -1;
   static thread_local int sm_count = 0;
   constexpr int kSmemBudget = 227 * 1024;
@@ -1019,12 +1149,14 @@ int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   p.d_tma = L.d_tma ? 1 : 0;
   p.activations_dynamic = L.activations_dynamic ? 1 : 0;
   p.alpha = L.alpha;
+  p.x_src = static_cast<const uint16_t*>(L.act_src);
+  p.ldx = L.act_ld;
   const int pairs = ((L.N + 127) / 128 + 1) / 2;
   p.pairs_per_cta = (pairs + sm_count - 1) / sm_count;
   const int grid = (pairs + p.pairs_per_cta - 1) / p.pairs_per_cta;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(fp4d::kDualThreads, 1, 1);
+  cfg.blockDim = dim3(kFused ? fp4d::kFusedThreads : fp4d::kDualThreads, 1, 1);
   cfg.dynamicSmemBytes = 1024 + stages * p.stage_bytes + staging + fp4d::kBarrierBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr;
@@ -1045,6 +1177,16 @@ int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
 
 bool fp4_decode_prefers_dual(int M) { return (M + 15) / 16 * 16 >= fp4d::kDualFromPad; }
 
+// BF16 activations are quantised inside the GEMM kernel by the swapped dual form with UE8M0 scales
+// and whole tile pairs, for at most 16 rows: every CTA quantises all activations again, one
+// stage visit of a warp takes about 1.3 us per 16 rows, and with more rows the visits no longer
+// keep up with the weight stream (N = 28672, K = 8192, us per step, fused / quantiser kernel
+// chained in front: M = 1 20.6 / 22.8, 16 21.9 / 23.2, 32 30.2 / 23.8, 64 49.1 / 26.4).  Elsewhere
+// the caller quantises first.
+bool fp4_decode_fuses_activations(const Fp4DecodeLaunch& L) {
+  return L.act_src != nullptr && !L.block16 && L.dual && !L.narrow && L.max_ctas == 0 && L.M <= 16;
+}
+
 namespace {
 // More than 64 activation rows and at most one tile pair per SM: the form with the activations as
 // the instruction's rows (see decode_dual_body).
@@ -1063,6 +1205,7 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   // The dual-tile form has whole tile pairs only: a caller that asks for a CTA count gets the
   // stream-K ranges of the single form.
   const bool wide = (L.block16 || (L.dual && L.max_ctas == 0)) && fp4_decode_wide_applies(L);
+  if (fp4_decode_fuses_activations(L)) return fp4_decode_dual_launch<false, false, true>(L, stream);
   if (L.block16)   // this format has the dual forms only
     return wide ? fp4_decode_dual_launch<true, true>(L, stream) : fp4_decode_dual_launch<true, false>(L, stream);
   if (L.dual && L.max_ctas == 0)
@@ -1248,6 +1391,8 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
   L.activations_dynamic = false;
   L.dual = fp4_decode_prefers_dual(M);
   L.narrow = false;
+  L.act_src = nullptr;
+  L.act_ld = 0;
   L.block16 = false;
   L.alpha = 1.0f;
   L.no_overlap = true;   // the memset below must be ordered before every access of this launch

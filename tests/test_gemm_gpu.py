@@ -245,6 +245,45 @@ def test_bf16_8192_cubed_properties(smb, oracle, cuda_device):
     assert bool((d3 == 8192.0).all())
 
 
+def test_bf16_large_config_slab_of_one_rank(smb, oracle, cuda_device):
+    """BASELINE config 5 as one GPU of eight sees it: M = 32768, K = 8192 and the 7168 columns of
+    rank 3 (rows 21504.. of BT, generated with their global indices, fill 6 = N(0,1) x 0.05
+    stand-in).  Sampled fp64 check against operands generated independently on the host for the
+    sampled rows, every edge tile in full, and the constant fill (every element written once)."""
+    torch = _torch()
+    m, n_total, k, world, rank = 32768, 57344, 8192, 8, 3
+    sh = smb.sharding.column_shard(n_total, world, rank)
+    n = sh.n_local
+    dev = cuda_device
+    a = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
+    bt = torch.empty(n, k, device=dev, dtype=torch.bfloat16)
+    d = torch.full((m, n), float("nan"), device=dev, dtype=torch.bfloat16)
+    smb.gemm.bf16_operands_device(a, bt, m, n, k, 6, n0=sh.n0, n_total=n_total)
+    plan = smb.gemm.Bf16Plan(a, bt, d, m, n, k)
+    plan.run(); plan.check(); plan.close()
+    # The slab's rows of BT are the global rows n0.. of the logical operand: compare a few with the
+    # host generator (index k * N_total + n_global, seed 2).
+    for local in (0, 1, 4097, n - 1):
+        want = smb.gemm.fill_bf16_host(1, k, 6, 2, sh.n0 + local, 1, n_total)
+        assert np.array_equal(want.reshape(-1), bt[local].view(torch.int16).cpu().numpy().view(np.uint16))
+    rows, cols = oracle.sample_coordinates(m, n, 8192)
+    ra = torch.from_numpy(rows).to(dev)
+    ca = torch.from_numpy(cols).to(dev)
+    ref = (a[ra].double() * bt[ca].double()).sum(1)
+    rms = float((a[:256].double() @ bt.double().t()).pow(2).mean().sqrt())
+    bound = 2.0 ** -7 * ref.abs() + 2.0 ** -10 * (k ** 0.5) * rms
+    assert int(((d[ra, ca].double() - ref).abs() > bound).sum()) == 0
+    last = a[-256:].double() @ bt.double().t()
+    bound = 2.0 ** -7 * last.abs() + 2.0 ** -10 * (k ** 0.5) * rms
+    assert int(((d[-256:].double() - last).abs() > bound).sum()) == 0
+    right = a[:2048].double() @ bt[-256:].double().t()
+    bound = 2.0 ** -7 * right.abs() + 2.0 ** -10 * (k ** 0.5) * rms
+    assert int(((d[:2048, -256:].double() - right).abs() > bound).sum()) == 0
+    del a, bt, d
+    _, _, d3 = _run_bf16(smb, m, n, k, 3)
+    assert bool((d3 == 8192.0).all())
+
+
 def test_bf16_argument_errors_on_device(smb, cuda_device):
     torch = _torch()
     t = torch.zeros(1024, device=cuda_device, dtype=torch.bfloat16)
@@ -545,10 +584,12 @@ def test_bf16_quantizer_is_bit_identical_to_oracle(smb, oracle, cuda_device):
 
 
 @pytest.mark.parametrize("shape", [(16, 1024, 2048), (64, 2560, 1024), (128, 1152, 512), (7, 300, 96),
-                                   (300, 512, 256)])
+                                   (300, 512, 256), (1, 256, 8192), (16, 28672, 8192), (48, 3000, 2048),
+                                   (33, 1000, 1056), (64, 38400, 512)])
 def test_fp4_plan_fed_with_bf16_activations(smb, cuda_device, shape):
-    """The plan that quantises BF16 activations before every run (decode kernel for M <= 128, tiled
-    kernel above) equals quantise-then-multiply done as two separate calls, and follows the
+    """The plan that takes BF16 activations (up to 16 rows: quantised inside the decode kernel by
+    its own warps; up to 128: by a kernel chained in front of the decode kernel; above: in front of
+    the tiled kernel) equals quantise-then-multiply done as two separate calls, and follows the
     activations when they change between runs."""
     torch = _torch()
     m, n, k = shape
@@ -563,6 +604,10 @@ def test_fp4_plan_fed_with_bf16_activations(smb, cuda_device, shape):
     ref_plan = smb.gemm.Fp4Plan(codes, sfp, w, sfw, d_ref, m, n, k)
     for step in range(3):
         x.copy_((torch.randn(m, k, generator=g) * (0.5 + step)).to(torch.bfloat16))
+        x[0, :32] = 0                      # an all-zero block: neutral scale, zero codes
+        x[0, 32:36] = -0.0                 # negative zeros and values that round to zero
+        x[0, 36:40] = -1e-3
+        x[m - 1, k - 32:] *= 2.0 ** 20     # and a large one in the last block of the last row
         d.fill_(float("nan"))
         plan.run()
         plan.run()     # back to back: the second quantiser must not disturb the first GEMM
@@ -572,6 +617,14 @@ def test_fp4_plan_fed_with_bf16_activations(smb, cuda_device, shape):
         ref_plan.run()
         ref_plan.check()
         assert torch.equal(d.view(torch.int16), d_ref.view(torch.int16)), f"step {step}"
+    if m <= 16:
+        # A ring shallower than the number of quantising warps: only as many warps as ring slots
+        # may take part (a warp further ahead would pass a parity wait two phases early).
+        for depth in (2, 3):
+            plan.tune(depth, 0, -1)
+            d.fill_(float("nan"))
+            plan.run(); plan.run(); plan.check()
+            assert torch.equal(d.view(torch.int16), d_ref.view(torch.int16)), f"ring depth {depth}"
     plan.close()
     ref_plan.close()
 
