@@ -292,6 +292,9 @@ def main():
     ap.add_argument("--swiglu", action="store_true",
                     help="also time the GEMM with the gated-activation epilogue (D = silu(gate) * up, [M, N/2])")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra-warmup", action="store_true",
+                    help="decode workloads: skip the 0.3 s warm-up (for profiler captures, where few "
+                         "launches should precede the captured one)")
     ap.add_argument("--e2e-steps", type=int, default=8)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -448,7 +451,8 @@ def main():
     warm_t0 = time.perf_counter()
     extra_warm = 0
     burst = None
-    while kind == "decode" and time.perf_counter() - warm_t0 < MIN_WARM_S and extra_warm < 100000:
+    while (kind == "decode" and not args.no_extra_warmup and time.perf_counter() - warm_t0 < MIN_WARM_S
+           and extra_warm < 100000):
         for i in range(20):
             run_step(extra_warm + i)
         extra_warm += 20
