@@ -56,7 +56,8 @@ DECODE_WEIGHT_SETS = 4   # rotate weight buffers so that every step streams from
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the
 # dominant kernel on this workload at 1 GPU; the summaries are under profiles/).
-NCU_TRAFFIC_BYTES = {"bf16_8192": 970_156_544, "nvfp4_8192": 255_423_744, "decode_m16": 128_616_448}
+NCU_TRAFFIC_BYTES = {"bf16_8192": 970_156_544, "nvfp4_8192": 255_423_744, "decode_m16": 128_138_240,
+                     "decode_m128": 128_483_072}
 
 MIN_WARM_S = 0.3
 BURST_AFTER_S = 0.03   # decode workloads: a first, short timing this long into the warm-up
