@@ -585,7 +585,7 @@ def test_bf16_quantizer_is_bit_identical_to_oracle(smb, oracle, cuda_device):
 
 @pytest.mark.parametrize("shape", [(16, 1024, 2048), (64, 2560, 1024), (128, 1152, 512), (7, 300, 96),
                                    (300, 512, 256), (1, 256, 8192), (16, 28672, 8192), (48, 3000, 2048),
-                                   (33, 1000, 1056), (64, 38400, 512)])
+                                   (33, 1000, 1056), (64, 38400, 512), (16, 38400, 512), (9, 1001, 352)])
 def test_fp4_plan_fed_with_bf16_activations(smb, cuda_device, shape):
     """The plan that takes BF16 activations (up to 16 rows: quantised inside the decode kernel by
     its own warps; up to 128: by a kernel chained in front of the decode kernel; above: in front of
