@@ -38,20 +38,28 @@ constexpr int kThreads = 384;
 constexpr int kEpiWarps = 8;
 constexpr int kABytes = kBlockM * kBlockKBytes;   // 16 KiB
 constexpr int kSfCellBytes = 512;     // 128 rows x 4 scale bytes (K = 128)
-constexpr int kTmemCols = 512;
 enum { kStorePlain = 0, kStoreTma = 1, kStoreSwiglu = 2 };   // epilogue variants
-constexpr int kRingBudget = 192 * 1024;
 
 // V4: NVFP4 proper, one UE4M3 scale per 16 K (scale_vec::4X): a 4-byte scale cell per K=64
 // instruction, four cells per stage instead of two (the layout the reference sketches but does
 // not build, nvfp4/dense_gemm_nvfp4.cu:109-129).
-template <int W0, int W1, bool V4 = false>
+// R = CTAs of the kernel that fit on one SM.  R = 2 exists for the 128-wide tile (N <= 128
+// problems, bound by the L2 -> SM path): half the shared memory (3 stages), 256 tensor-memory
+// columns with a single accumulator bank, at most 80 registers, so that two clusters share an SM
+// pair and one's prologue, drain and exit overlap the other's main loop.  Used when consecutive
+// launches may overlap (as for the BF16 kernel's narrow tiles); a launch that runs alone keeps
+// R = 1 and its two accumulator banks.
+template <int W0, int W1, bool V4 = false, int R = 1>
 struct Cfg {
   static_assert(W0 == 128 || W0 == 256, "first sub-block width");
   static_assert(W1 == 0 || W1 == 128 || W1 == 256, "second sub-block width");
+  static_assert(R == 1 || (R == 2 && W0 == 128 && W1 == 0 && !V4), "two resident CTAs: 128-wide tile only");
+  static constexpr int kResident = R;
+  static constexpr int kTmemCols = (R == 2) ? 256 : 512;
+  static constexpr int kRingBudget = (R == 2) ? 78 * 1024 : 192 * 1024;
   static constexpr int kSubs = (W1 == 0) ? 1 : 2;
   static constexpr int kTileN = W0 + W1;
-  static constexpr bool kTwoBanks = (kTileN == 128);              // epilogue overlaps next main loop
+  static constexpr bool kTwoBanks = (kTileN == 128) && R == 1;    // epilogue overlaps next main loop
   static constexpr int kB0Bytes = (W0 / 2) * kBlockKBytes;
   static constexpr int kB1Bytes = (W1 / 2) * kBlockKBytes;
   static constexpr int kCells = V4 ? 4 : 2;                       // 4-byte scale cells per row and stage
@@ -77,7 +85,7 @@ struct Cfg {
   static_assert(kStageBytes % 1024 == 0, "stage bases must stay 1024-byte aligned");
   static_assert(kColsPerWarp % kStoreCols == 0, "epilogue split");
   static_assert(kAccCols + kStages * kSlotCols <= kTmemCols, "tensor memory budget");
-  static_assert(kTotal <= 232448, "shared memory budget");
+  static_assert(kTotal <= (R == 2 ? 115712 : 232448), "shared memory budget");
   static_assert(kStages >= 2, "ring depth");
 };
 
@@ -101,15 +109,15 @@ struct Params {
 enum { kProfLoadWait = 0, kProfLoadTotal, kProfMmaWaitFull, kProfMmaWaitAcc, kProfMmaTotal,
        kProfEpiWait, kProfEpiTotal, kProfTiles, kProfCount };
 
-template <int W0, int W1, int kStore, bool V4 = false>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+template <int W0, int W1, int kStore, bool V4 = false, int R = 1>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, R)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b0,
                   const __grid_constant__ CUtensorMap tmap_b1,
                   const __grid_constant__ CUtensorMap tmap_sfa,
                   const __grid_constant__ CUtensorMap tmap_sfb,
                   const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ Params p) {
-  using C = Cfg<W0, W1, V4>;
+  using C = Cfg<W0, W1, V4, R>;
   constexpr int kCells = C::kCells;
   constexpr bool kTmaStore = (kStore != kStorePlain);
   constexpr bool kSwiglu = (kStore == kStoreSwiglu);   // D is [M, N/2]: silu(gate) * up
@@ -169,7 +177,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (kTmaStore) tma_prefetch_desc(&tmap_d);
   }
   if (warp == 1) {
-    tmem_alloc<2>(tmem_slot, kTmemCols);
+    tmem_alloc<2>(tmem_slot, C::kTmemCols);
     tmem_relinquish<2>();
   }
   tc_fence_before_sync();
@@ -465,7 +473,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
   cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc<2>(tmem_base, kTmemCols);
+    tmem_dealloc<2>(tmem_base, C::kTmemCols);
   }
 }
 
@@ -476,10 +484,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // -----------------------------------------------------------------------------------
 namespace {
 
-template <int W0, int W1, int kStore, bool V4 = false>
+template <int W0, int W1, int kStore, bool V4 = false, int R = 1>
 int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
-  using C = fp4k::Cfg<W0, W1, V4>;
-  auto kernel = fp4k::gemm_nvfp4_kernel<W0, W1, kStore, V4>;
+  using C = fp4k::Cfg<W0, W1, V4, R>;
+  auto kernel = fp4k::gemm_nvfp4_kernel<W0, W1, kStore, V4, R>;
   static thread_local int configured_device = -1;
   static thread_local int max_clusters = 0;
   int dev = 0;
@@ -564,6 +572,13 @@ int launch_fp4_store(const Fp4Launch& L, cudaStream_t stream) {
       return launch_fp4<W0, W1, fp4k::kStoreSwiglu>(L, stream);
     } else {
       return set_error(SMB_ERR_UNSUPPORTED, "nvfp4: the gated epilogue needs 256-wide tiles");
+    }
+  }
+  if constexpr (W0 == 128 && W1 == 0) {
+    // Narrow tile: two CTAs per SM when consecutive launches may overlap (see Cfg).
+    if (L.operands_static) {
+      return L.tma_store ? launch_fp4<W0, W1, fp4k::kStoreTma, false, 2>(L, stream)
+                         : launch_fp4<W0, W1, fp4k::kStorePlain, false, 2>(L, stream);
     }
   }
   return L.tma_store ? launch_fp4<W0, W1, fp4k::kStoreTma>(L, stream)

@@ -340,6 +340,33 @@ def _check_fp4_full(A, B, d, k):
     assert int(bad.sum()) == 0, f"{int(bad.sum())} elements outside the north-star bound"
 
 
+@pytest.mark.parametrize("overlap", ["FLAG_OPERANDS_STATIC", "FLAG_LAUNCH_INDEPENDENT"])
+@pytest.mark.parametrize("store", ["FLAG_NONE", "FLAG_FORCE_PLAIN_STORE"])
+def test_fp4_narrow_tile_two_ctas_per_sm(smb, cuda_device, overlap, store):
+    """The 128-wide FP4 tile launched with overlapping launches allowed runs as the variant whose
+    CTAs share an SM in pairs (3-stage ring, one accumulator bank, 256 tensor-memory columns):
+    more tiles than cluster slots with ragged edges, then the N = 128 one-wave shape it is for,
+    several launches back to back; bit-identical to the one-CTA-per-SM variant."""
+    torch = _torch()
+    capi = smb.capi
+    for (m, n, k), tile in (((2500, 1100, 2304), capi.FLAG_TILE_N_128 | capi.FLAG_NO_DECODE),
+                            ((14080, 128, 2048), 0), ((300, 100, 512), 0)):
+        flags = tile | getattr(capi, store)
+        A, B, d1 = _run_fp4(smb, m, n, k, 5, flags=flags)
+        _check_fp4_full(A, B, d1, k)
+        (a, _), (b, _) = A, B
+        sfa = _fp4_operand(smb, m, k, 5, 0)[1]
+        sfb = _fp4_operand(smb, n, k, 5, 1)[1]
+        d2 = torch.full_like(d1, float("nan"))
+        plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, d2, m, n, k, flags=flags | getattr(capi, overlap))
+        for _ in range(6):
+            plan.run()
+        plan.check()
+        plan.close()
+        torch.cuda.synchronize()
+        assert torch.equal(d1.view(torch.int16), d2.view(torch.int16)), (m, n, k)
+
+
 @pytest.mark.parametrize("fill", [1, 2, 3, 4])
 def test_fp4_smoke_against_reference_golden(smb, oracle, golden, cuda_device, fill):
     """The reference's smoke case (--shape=256,256,128): output vs the reference CPU path."""
