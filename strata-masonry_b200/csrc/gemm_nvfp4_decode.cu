@@ -20,6 +20,12 @@
 // Warp roles (256 threads): warp 0 TMA producer, warp 1 MMA issue + TMEM owner, warp 2 scale
 // copies (tcgen05.cp, issued apart from the MMAs so that they overlap them), warp 3 idle,
 // warps 4-7 epilogue (warp w reads TMEM lanes 32 (w % 4) .. +31).
+//
+// That is the single-tile form, kept for callers that ask for a CTA count.  The default is the
+// dual-tile form further down (two weight tiles per activation box, whole tile pairs per CTA, no
+// scratch; 384 threads: a second group of epilogue warps), with two variants of its own: above 64
+// activation rows the operands are not swapped (one 128 x 256 instruction per K step), and up to
+// 16 rows BF16 activations are quantised by extra warps of the kernel itself (640 threads).
 #include "epilogue.cuh"
 #include "formats.cuh"
 #include "gemm_common.cuh"
