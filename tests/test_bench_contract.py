@@ -48,3 +48,28 @@ def test_gpu_arm_prints_one_contract_line():
     assert line["e2e"]["h2d_bytes_per_step"] > 0 and line["e2e"]["d2h_bytes_per_step"] > 0
     assert line["e2e"]["matches_device_path"] is True
     assert set(line["clocks"]) >= {"sm_mhz", "sm_max_mhz", "reasons"}
+
+
+def test_cpu_baseline_helpers():
+    """The pieces of the CPU baseline that need no GPU: the BLAS description, and the block-scaled
+    sample (codes and scale bytes -> fp32 -> matmul) on a budget small enough for a unit test, with
+    the few-row proportion of a decode workload kept."""
+    sys.path.insert(0, str(ROOT))
+    import bench
+    threads, blas = bench.blas_info()
+    assert threads >= 1 and isinstance(blas, str) and blas
+    oracle = bench._load_oracle()
+    rate, sample, secs = bench.cpu_fp4_rate(oracle, 16, 28672, 512, budget_s=0.05)
+    assert rate > 0 and secs > 0 and sample.startswith("16x") and sample.split("x")[2].startswith("512")
+    rate, sample, secs = bench.cpu_fp4_rate(oracle, 8192, 8192, 256, budget_s=0.05)
+    rows, cols = int(sample.split("x")[0]), int(sample.split("x")[1])
+    assert rate > 0 and rows >= 16 and cols >= 128
+
+
+def test_reference_arm_of_a_block_scaled_workload():
+    r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1",
+                        "--warmup", "0", "--workload", "decode_m16"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    line = _last_json_line(r.stdout)
+    assert line["impl"] == "reference" and line["dtype"] == "e2m1" and line["value"] > 0
+    assert "blas" in line["cpu_baseline"] and line["cpu_baseline"]["cores"] >= 1
