@@ -143,6 +143,13 @@ int smb_bf16_plan_run(smb_bf16_plan* plan, void* stream);
  * the role that gave up in smb_last_error(). */
 int smb_bf16_plan_check(smb_bf16_plan* plan, void* stream);
 int smb_bf16_plan_destroy(smb_bf16_plan* plan);
+/* Self test of the bounded device waits: launches one CTA that waits `budget_cycles` SM clocks
+ * (1 .. 2 000 000, i.e. at most about a millisecond) on an mbarrier nobody arrives at, gives up,
+ * writes the "bounded-wait probe" status into the plan's status word and returns normally.  The
+ * next smb_bf16_plan_check() therefore returns SMB_ERR_DEVICE with that message and clears the
+ * word; the plan, the stream and the context stay usable.  The reference's wait helper spins
+ * without a limit (src/primitives/33_mbarrier_try_wait.cuh:90-114) and has no such path. */
+int smb_bf16_plan_wait_probe(smb_bf16_plan* plan, long long budget_cycles, void* stream);
 /* Grouped GEMM for mixture-of-experts layers ("shared N and K, varying M", the case of the
  * reference's tile map composites/83_grouped_gemm_tile_map.cuh:71-101, which no kernel of its
  * tree uses): A [M_total, K] holds the rows of all groups back to back, every group padded to a
@@ -191,8 +198,10 @@ int smb_bf16_host_ctx_destroy(smb_bf16_host_ctx* ctx);
  * bytes (multiples of 16); SFA / SFB: UE8M0 bytes in the packed layout of
  * smb_sf_packed_bytes(); D: bf16 row-major.  Any M, N >= 1; K a multiple of 32.
  * Shapes with M <= 128 (decode: few activation rows against a large weight matrix B) run a
- * separate HBM-bound kernel that streams B once, split evenly over the SMs along N and K; the
- * plan owns its scratch memory (fp32 partial sums of the tiles shared by two SMs).
+ * separate HBM-bound kernel that streams B once.  By default every CTA owns whole pairs of
+ * 128-row weight tiles and needs no scratch memory; when a CTA count is forced
+ * (smb_fp4_plan_tune) the (tile, K block) pairs are cut into equal ranges over those CTAs and
+ * the fp32 partial sums of tiles shared between CTAs travel through plan-owned scratch.
  * ---------------------------------------------------------------------------------- */
 typedef struct smb_fp4_plan smb_fp4_plan;
 int smb_fp4_plan_create(smb_fp4_plan** plan, const void* a, const void* sfa, const void* b,
@@ -220,6 +229,8 @@ int smb_fp4_grouped_plan_create(smb_fp4_plan** plan, const void* a, const void* 
 int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_destroy(smb_fp4_plan* plan);
+/* The bounded-wait self test on an FP4 plan's status word; see smb_bf16_plan_wait_probe. */
+int smb_fp4_plan_wait_probe(smb_fp4_plan* plan, long long budget_cycles, void* stream);
 /* Tuning: raster group height (0 = default), cluster cap (0 = all), L2 prefetch distance in
  * 256-wide K blocks (0 = off, negative = keep). */
 int smb_fp4_plan_tune(smb_fp4_plan* plan, int group_m, int max_clusters, int prefetch);
@@ -234,25 +245,47 @@ int smb_dense_gemm_nvfp4(const void* a, const void* sfa, const void* b, const vo
 int smb_dense_gemm_nvfp4_host(const uint8_t* a, const uint8_t* sfa_rowmajor, const uint8_t* b,
                               const uint8_t* sfb_rowmajor, uint16_t* d, int M, int N, int K);
 
+/* Host-buffer context, the FP4 twin of smb_bf16_host_ctx (the reference driver does these steps
+ * inline: nvfp4/dense_gemm_nvfp4.cu:2418-2468 sf_pack and uploads, :2594-2610 download): create
+ * once for a shape; every run uploads the E2M1 codes of A [M, K/2] and B [N, K/2] and their UE8M0
+ * scales in logical form ([rows, K/32] bytes row-major), packs the scales on the device,
+ * multiplies and downloads D [M, N] (bf16).  Uploads, GEMMs and downloads of row chunks of A
+ * overlap.  With b == NULL and sfb_rowmajor == NULL a run reuses the B of the previous run on this
+ * context (a decode step: weights stay on the device, activations travel).  Pass pinned host
+ * memory for full copy bandwidth.  Synchronises before it returns. */
+typedef struct smb_fp4_host_ctx smb_fp4_host_ctx;
+int smb_fp4_host_ctx_create(smb_fp4_host_ctx** ctx, int M, int N, int K);
+int smb_fp4_host_ctx_run(smb_fp4_host_ctx* ctx, const uint8_t* a, const uint8_t* sfa_rowmajor,
+                         const uint8_t* b, const uint8_t* sfb_rowmajor, uint16_t* d);
+int smb_fp4_host_ctx_destroy(smb_fp4_host_ctx* ctx);
+
 /* Decode-shape FP4 GEMM (M <= 128) for callers that cannot allocate device memory where the
- * GEMM runs: a server whose start-up pool owns all of HBM, a plugin living inside another
- * framework's allocator, a call made while a stream is being captured.  It has no counterpart
- * in the reference.  Same operands and result as smb_dense_gemm_nvfp4 (packed scales, lda =
+ * GEMM runs: a server whose start-up pool owns all of HBM, or a plugin living inside another
+ * framework's allocator, where a cudaMalloc on the request path either fails or stalls every
+ * stream of the device.  It has no counterpart in the reference.  Same operands and result as smb_dense_gemm_nvfp4 (packed scales, lda =
  * ldb = K/2 bytes, ldd = N); what the kernel needs besides its operands (a status word, and for
  * its stream-K work split tile counters and partial-sum slots) lives in a 2 MiB array built
  * into the library, so the call performs no cudaMalloc / cudaFree of any kind.
- *   - The array must hold one 4-byte counter per 128 columns of N and two fp32 partial-tile
- *     slots (round_up(M,16) * 512 bytes each) for at least one CTA within
- *     smb_decode_noalloc_scratch_limit() bytes (2 MiB - 256); a shape that does not fit
- *     returns SMB_ERR_UNSUPPORTED.  The default work split (whole tile pairs per CTA) uses
- *     only the status word.
+ *   - Work split: by default every CTA owns whole pairs of weight tiles and only the status
+ *     word is used.  After smb_decode_noalloc_set_split(ctas > 0) the (tile, K block) pairs are
+ *     cut into equal ranges over `ctas` CTAs (at most one per SM); the array must then hold one
+ *     4-byte counter per 128 columns of N and two fp32 partial-tile slots (round_up(M,16) * 512
+ *     bytes each) per CTA within smb_decode_noalloc_scratch_limit() bytes (2 MiB - 256): the CTA
+ *     count is lowered to what fits, and a shape whose counters leave room for no CTA returns
+ *     SMB_ERR_UNSUPPORTED.  The setting is process-wide, like the array.  The splits agree up
+ *     to the order of a few fp32 additions.
  *   - The first call on a device looks up the array's device address; make that call outside
  *     any stream capture.
- *   - All calls share the one array: it is cleared on `stream` before each launch, and two
- *     calls that overlap on the GPU (different streams) corrupt each other.
- *   - Enqueues and returns; a kernel that gives up a bounded wait is not reported here. */
+ *   - All calls share the one array and it keeps the previous call's contents: what must start
+ *     at zero (status word; counters for the stream-K split) is cleared on `stream` before each
+ *     launch, and two calls that overlap on the GPU (different streams) corrupt each other.
+ *   - Enqueues and returns.  smb_decode_noalloc_check(stream) synchronises `stream`, reads the
+ *     status word into a host variable (no allocation) and returns SMB_ERR_DEVICE if the last
+ *     call's kernel gave up a bounded wait. */
 int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sfa, const void* b,
                                         const void* sfb, void* d, int M, int N, int K, void* stream);
+int smb_decode_noalloc_set_split(int ctas);
+int smb_decode_noalloc_check(void* stream);
 size_t smb_decode_noalloc_scratch_limit(void);
 
 /* ----------------------------------------------------------------------------------
@@ -313,6 +346,31 @@ int smb_column_shard(int n_total, int world, int rank, int* n0, int* n_local);
  * n_local % 8 == 0, both buffers 16-byte aligned, ldd % 8 == 0.  Stream-ordered. */
 int smb_unshard_columns_device(const void* gathered, void* d, int g, int M, int n_local, int64_t ldd,
                                void* stream);
+
+/* The all-gather itself behind the C ABI: NCCL over NVLink, resolved at run time (libnccl.so.2;
+ * SMB_ERR_UNSUPPORTED when it cannot be loaded).  A communicator is either one rank of a
+ * one-process-per-GPU job (rank 0 makes an id with smb_comm_unique_id, hands it to the others by
+ * any host channel, every rank calls smb_comm_create with its device current), or one of `ndev`
+ * communicators of a single process that drives several devices (smb_comm_create_all; devices
+ * == NULL means 0 .. ndev - 1), which is what the drivers' --gpus=G --allgather uses.
+ * smb_allgather_columns: `slab` is this rank's [M, n_local] bf16 result, `gathered` receives
+ * all ranks' slabs rank-major as [world, M, n_local]; if d_full is not NULL the unshard copy
+ * into row-major [M, world * n_local] (pitch ldd) follows on the same stream.  The _multi form
+ * makes the calls of all devices of one process inside one NCCL group.  Stream-ordered; same
+ * alignment rules as smb_unshard_columns_device.  smb_allgather_check applies the shape rules
+ * only (no device or NCCL needed). */
+#define SMB_COMM_ID_BYTES 128
+typedef struct smb_comm smb_comm;
+int smb_comm_unique_id(unsigned char id[SMB_COMM_ID_BYTES]);
+int smb_comm_create(smb_comm** comm, const unsigned char id[SMB_COMM_ID_BYTES], int world, int rank);
+int smb_comm_create_all(smb_comm** comms, int ndev, const int* devices);
+int smb_comm_destroy(smb_comm* comm);
+int smb_allgather_check(int world, int M, int n_local, int64_t ldd);
+int smb_allgather_columns(smb_comm* comm, const void* slab, void* gathered, void* d_full, int M,
+                          int n_local, int64_t ldd, void* stream);
+int smb_allgather_columns_multi(smb_comm* const* comms, int ndev, const void* const* slabs,
+                                void* const* gathered, void* const* d_full, int M, int n_local,
+                                int64_t ldd, void* const* streams);
 
 #define SMB_FLAG_NONE 0u
 #define SMB_FLAG_FORCE_PLAIN_STORE 1u /* use the non-TMA epilogue even when D is aligned */

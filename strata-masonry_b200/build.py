@@ -30,7 +30,7 @@ COMMON = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-
           "--expt-relaxed-constexpr"]
 
 LIB_SOURCES = ["runtime.cu", "fills.cu", "gemm_bf16.cu", "api_bf16.cu", "gemm_nvfp4.cu",
-               "gemm_nvfp4_decode.cu", "api_nvfp4.cu", "peer.cu"]
+               "gemm_nvfp4_decode.cu", "api_nvfp4.cu", "peer.cu", "gather.cu", "selftest.cu"]
 DRIVERS = {"kernel_sm100a_dense_gemm_bf16": "driver_bf16.cu",
            "kernel_sm100a_dense_gemm_nvfp4": "driver_nvfp4.cu"}
 
@@ -57,7 +57,8 @@ def _stale(out: Path, src: Path, dep_mtime: float) -> bool:
 def _run(cmd, log: Path | None = None, verbose=False):
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if log is not None:
-        with open(log, "a") as f:
+        # One resource report per source file, rewritten whenever that file is compiled.
+        with open(log, "w") as f:
             f.write("$ " + " ".join(map(str, cmd)) + "\n" + proc.stderr + proc.stdout + "\n")
     if verbose or proc.returncode != 0:
         sys.stderr.write(proc.stderr)
@@ -72,8 +73,6 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     LIB.parent.mkdir(exist_ok=True)
     BIN.mkdir(exist_ok=True)
     dep_mtime = _deps_mtime()
-    log = BUILD / "ptxas.log"
-
     jobs = []
     objects = []
     for name in LIB_SOURCES:
@@ -81,12 +80,17 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         obj = BUILD / (src.stem + ".o")
         objects.append(obj)
         if force or _stale(obj, src, dep_mtime):
-            jobs.append([nvcc, *ARCH_FLAGS, *COMMON, "-c", str(src), "-o", str(obj)])
+            jobs.append(([nvcc, *ARCH_FLAGS, *COMMON, "-c", str(src), "-o", str(obj)],
+                         BUILD / f"ptxas_{src.stem}.log"))
     if jobs:
-        if log.exists():
-            log.unlink()
         with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
-            list(pool.map(lambda c: _run(c, log, verbose), jobs))
+            list(pool.map(lambda job: _run(job[0], job[1], verbose), jobs))
+        # The complete -Xptxas -v record of the library: every source's latest report, in build order.
+        with open(BUILD / "ptxas.log", "w") as full:
+            for name in LIB_SOURCES:
+                part = BUILD / f"ptxas_{Path(name).stem}.log"
+                if part.exists():
+                    full.write(part.read_text())
     if jobs or not LIB.exists():
         _run([nvcc, *ARCH_FLAGS, "-shared", "-o", str(LIB), *map(str, objects), "-lcudart_static",
               "-ldl", "-lpthread", "-lrt"], None, verbose)

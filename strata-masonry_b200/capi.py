@@ -67,6 +67,7 @@ DECLARED = [
     ("smb_bf16_plan_run", _i, [_vp, _vp]),
     ("smb_bf16_plan_check", _i, [_vp, _vp]),
     ("smb_bf16_plan_destroy", _i, [_vp]),
+    ("smb_bf16_plan_wait_probe", _i, [_vp, C.c_longlong, _vp]),
     ("smb_bf16_plan_tune", _i, [_vp, _i, _i]),
     ("smb_bf16_plan_set_profile", _i, [_vp, _vp]),
     ("smb_dense_gemm_bf16", _i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
@@ -83,11 +84,17 @@ DECLARED = [
     ("smb_fp4_plan_run", _i, [_vp, _vp]),
     ("smb_fp4_plan_check", _i, [_vp, _vp]),
     ("smb_fp4_plan_destroy", _i, [_vp]),
+    ("smb_fp4_plan_wait_probe", _i, [_vp, C.c_longlong, _vp]),
     ("smb_fp4_plan_tune", _i, [_vp, _i, _i, _i]),
     ("smb_fp4_plan_set_profile", _i, [_vp, _vp]),
     ("smb_dense_gemm_nvfp4", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     ("smb_dense_gemm_nvfp4_host", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
+    ("smb_fp4_host_ctx_create", _i, [C.POINTER(_vp), _i, _i, _i]),
+    ("smb_fp4_host_ctx_run", _i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    ("smb_fp4_host_ctx_destroy", _i, [_vp]),
     ("smb_dense_gemm_nvfp4_decode_noalloc", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    ("smb_decode_noalloc_set_split", _i, [_i]),
+    ("smb_decode_noalloc_check", _i, [_vp]),
     ("smb_decode_noalloc_scratch_limit", C.c_size_t, []),
     ("smb_bf16_plan_set_peer_copies", _i, [_vp, _i, C.POINTER(_vp), _i64]),
     ("smb_fp4_plan_set_peer_copies", _i, [_vp, _i, C.POINTER(_vp), _i64]),
@@ -101,9 +108,18 @@ DECLARED = [
     ("smb_peer_free", _i, [_vp]),
     ("smb_column_shard", C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     ("smb_unshard_columns_device", _i, [_vp, _vp, _i, _i, _i, _i64, _vp]),
+    ("smb_comm_unique_id", _i, [C.c_char_p]),
+    ("smb_comm_create", _i, [C.POINTER(_vp), C.c_char_p, _i, _i]),
+    ("smb_comm_create_all", _i, [C.POINTER(_vp), _i, C.POINTER(_i)]),
+    ("smb_comm_destroy", _i, [_vp]),
+    ("smb_allgather_check", _i, [_i, _i, _i, _i64]),
+    ("smb_allgather_columns", _i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _vp]),
+    ("smb_allgather_columns_multi", _i,
+     [C.POINTER(_vp), _i, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _i, _i, _i64, C.POINTER(_vp)]),
 ]
 
 PEER_HANDLE_BYTES = 64
+COMM_ID_BYTES = 128
 MAX_PEER_COPIES = 7
 MAX_ROUTE_BLOCKS = 8
 

@@ -210,6 +210,11 @@ extern "C" int smb_bf16_plan_check(smb_bf16_plan* plan, void* stream) {
   return SMB_OK;
 }
 
+extern "C" int smb_bf16_plan_wait_probe(smb_bf16_plan* plan, long long budget_cycles, void* stream) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "plan: null handle");
+  return wait_probe_launch(plan->status_dev, budget_cycles, nullptr, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int smb_bf16_plan_destroy(smb_bf16_plan* plan) {
   if (plan == nullptr) return SMB_OK;
   if (plan->status_dev && plan->owns_status) cudaFree(plan->status_dev);

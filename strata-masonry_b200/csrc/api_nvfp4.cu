@@ -16,6 +16,7 @@ using namespace smb;
 struct smb_fp4_plan {
   Fp4Launch launch;
   int* status_dev;
+  bool owns_status;   // false: the word belongs to a host context that several plans report into
   int device;   // the device that was current at creation
   // Skinny shapes (M <= 128) run the decode kernel.  Its scratch (partial-sum slots and tile
   // counters) is only touched when the CTA count is capped and tiles are split along K.
@@ -34,7 +35,7 @@ namespace {
 
 int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, const void* b, const void* sfb,
                          void* d, int M, int N, int K, int64_t lda_bytes, int64_t ldb_bytes, int64_t ldd,
-                         unsigned flags, int groups, const int* mtile_group) {
+                         unsigned flags, int groups, const int* mtile_group, int* shared_status = nullptr) {
   if (out == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null output handle");
   *out = nullptr;
   if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || d == nullptr)
@@ -142,10 +143,13 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
     else
       L.tmap_d = L.tmap_a;
   }
-  if (rc == SMB_OK) {
+  p->owns_status = (shared_status == nullptr);
+  if (rc == SMB_OK && p->owns_status) {
     cudaError_t e = cudaMalloc(&p->status_dev, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(p->status_dev, 0, sizeof(int));
     if (e != cudaSuccess) rc = set_cuda_error(e, "fp4 plan: status word allocation");
+  } else if (rc == SMB_OK) {
+    p->status_dev = shared_status;
   }
   if (rc == SMB_OK && p->decode) {
     // Operands swap roles: the weights (B, N rows) fill the 128 rows of the MMA, the
@@ -193,7 +197,7 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
     }
   }
   if (rc != SMB_OK) {
-    if (p->status_dev) cudaFree(p->status_dev);
+    if (p->status_dev && p->owns_status) cudaFree(p->status_dev);
     if (p->scratch_dev) cudaFree(p->scratch_dev);
     delete p;
     return rc;
@@ -353,9 +357,14 @@ extern "C" int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream) {
   return SMB_OK;
 }
 
+extern "C" int smb_fp4_plan_wait_probe(smb_fp4_plan* plan, long long budget_cycles, void* stream) {
+  if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
+  return wait_probe_launch(plan->status_dev, budget_cycles, nullptr, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int smb_fp4_plan_destroy(smb_fp4_plan* plan) {
   if (plan == nullptr) return SMB_OK;
-  if (plan->status_dev) cudaFree(plan->status_dev);
+  if (plan->status_dev && plan->owns_status) cudaFree(plan->status_dev);
   if (plan->scratch_dev) cudaFree(plan->scratch_dev);
   if (plan->act_codes) cudaFree(plan->act_codes);
   if (plan->act_sf) cudaFree(plan->act_sf);
@@ -418,4 +427,227 @@ extern "C" int smb_dense_gemm_nvfp4_host(const uint8_t* a, const uint8_t* sfa_ro
   cudaFree(dsb);
   cudaFree(dd);
   return rc;
+}
+
+// ------------------------------------------------------------------------------------
+// Host-buffer context, the FP4 twin of smb_bf16_host_ctx: device buffers, plans, streams and
+// events are created once for a shape; a run uploads codes and row-major scales, packs the
+// scales on the device, multiplies and downloads D.  The rows of A are cut into chunks (whole
+// 128-row scale bands) so that the upload of chunk i + 1, the GEMM of chunk i and the download
+// of chunk i - 1 overlap; the chunks shrink towards the end so that the last GEMM and download,
+// which nothing overlaps, are short.  M <= 128 is one chunk (the decode kernel).  B and its
+// scales go up first; a run given b == NULL keeps the weights of the previous run (a decode
+// step: the weights stay resident, only the activations travel).
+// ------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kFp4HostChunkRows = 1024;
+constexpr int kFp4HostChunkMinRows = 256;
+
+int fp4_next_chunk_rows(int rows_left) {
+  if (rows_left <= 128) return rows_left;
+  if (rows_left >= 4 * kFp4HostChunkRows) return kFp4HostChunkRows;
+  int rows = (rows_left / 4 + kFp4HostChunkMinRows - 1) / kFp4HostChunkMinRows * kFp4HostChunkMinRows;
+  if (rows < kFp4HostChunkMinRows) rows = kFp4HostChunkMinRows;
+  return rows < rows_left ? rows : rows_left;
+}
+
+// Row-major scale bytes [rows, kblocks] (rows row0 .. row0 + rows of the operand) into the packed
+// layout of the whole operand.  Padding rows of the last band keep the neutral byte they were
+// initialised with.
+__global__ void sf_pack_kernel(const uint8_t* __restrict__ rowmajor, uint8_t* __restrict__ packed,
+                               int64_t row0, int64_t rows, uint32_t kblocks) {
+  const int64_t total = rows * kblocks;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t r = i / kblocks;
+    const uint32_t j = static_cast<uint32_t>(i - r * kblocks);
+    packed[fmt::sf_packed_offset(static_cast<uint32_t>(row0 + r), j, kblocks)] = rowmajor[(row0 + r) * kblocks + j];
+  }
+}
+
+int sf_pack_launch(const void* rowmajor, void* packed, int64_t row0, int64_t rows, uint32_t kblocks,
+                   cudaStream_t st) {
+  const int64_t total = rows * kblocks;
+  if (total <= 0) return SMB_OK;
+  const int64_t want = (total + 255) / 256;
+  const int blocks = static_cast<int>(want < 148 * 8 ? want : 148 * 8);
+  sf_pack_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint8_t*>(rowmajor), static_cast<uint8_t*>(packed), row0,
+                                         rows, kblocks);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_cuda_error(e, "scale pack launch");
+  return SMB_OK;
+}
+
+}  // namespace
+
+struct smb_fp4_host_ctx {
+  int M, N, K;
+  int64_t ldd;
+  void *da, *db, *dsa_rm, *dsb_rm, *dsa, *dsb, *dd;
+  int* status_dev;
+  int* status_host;   // pinned
+  bool weights_loaded;
+  std::vector<smb_fp4_plan*> plans;   // one per row chunk
+  std::vector<int> chunk_row0, chunk_rows;
+  std::vector<cudaEvent_t> uploaded, computed;
+  cudaStream_t up, compute, down;
+};
+
+extern "C" int smb_fp4_host_ctx_destroy(smb_fp4_host_ctx* ctx) {
+  if (ctx == nullptr) return SMB_OK;
+  for (smb_fp4_plan* p : ctx->plans) smb_fp4_plan_destroy(p);
+  for (cudaEvent_t e : ctx->uploaded) cudaEventDestroy(e);
+  for (cudaEvent_t e : ctx->computed) cudaEventDestroy(e);
+  void* bufs[] = {ctx->da, ctx->db, ctx->dsa_rm, ctx->dsb_rm, ctx->dsa, ctx->dsb, ctx->dd, ctx->status_dev};
+  for (void* b : bufs)
+    if (b) cudaFree(b);
+  if (ctx->status_host) cudaFreeHost(ctx->status_host);
+  if (ctx->up) cudaStreamDestroy(ctx->up);
+  if (ctx->compute) cudaStreamDestroy(ctx->compute);
+  if (ctx->down) cudaStreamDestroy(ctx->down);
+  delete ctx;
+  return SMB_OK;
+}
+
+extern "C" int smb_fp4_host_ctx_create(smb_fp4_host_ctx** out, int M, int N, int K) {
+  if (out == nullptr) return set_error(SMB_ERR_INVALID, "fp4 host context: null output handle");
+  *out = nullptr;
+  if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0)
+    return set_error(SMB_ERR_INVALID, "fp4 host context: bad dimensions (K must be a multiple of 32)");
+  smb_fp4_host_ctx* c = new (std::nothrow) smb_fp4_host_ctx();
+  if (c == nullptr) return set_error(SMB_ERR_NOMEM, "fp4 host context: out of host memory");
+  c->M = M;
+  c->N = N;
+  c->K = K;
+  c->ldd = (static_cast<int64_t>(N) + 7) / 8 * 8;   // the aligned store path is always usable
+  c->da = c->db = c->dsa_rm = c->dsb_rm = c->dsa = c->dsb = c->dd = nullptr;
+  c->status_dev = c->status_host = nullptr;
+  c->up = c->compute = c->down = nullptr;
+  c->weights_loaded = false;
+  const int64_t kblocks = K / 32;
+  const size_t sfa_bytes = smb_sf_packed_bytes(M, kblocks), sfb_bytes = smb_sf_packed_bytes(N, kblocks);
+  int rc = SMB_OK;
+  cudaError_t e = cudaStreamCreateWithFlags(&c->up, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->compute, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->down, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMalloc(&c->da, static_cast<size_t>(M) * K / 2);
+  if (e == cudaSuccess) e = cudaMalloc(&c->db, static_cast<size_t>(N) * K / 2);
+  if (e == cudaSuccess) e = cudaMalloc(&c->dsa_rm, static_cast<size_t>(M) * kblocks);
+  if (e == cudaSuccess) e = cudaMalloc(&c->dsb_rm, static_cast<size_t>(N) * kblocks);
+  if (e == cudaSuccess) e = cudaMalloc(&c->dsa, sfa_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&c->dsb, sfb_bytes);
+  if (e == cudaSuccess) e = cudaMemset(c->dsa, 127, sfa_bytes);
+  if (e == cudaSuccess) e = cudaMemset(c->dsb, 127, sfb_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&c->dd, static_cast<size_t>(M) * c->ldd * 2);
+  if (e == cudaSuccess) e = cudaMalloc(&c->status_dev, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(c->status_dev, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaMallocHost(&c->status_host, sizeof(int));
+  if (e != cudaSuccess) rc = set_cuda_error(e, "fp4 host context: allocation");
+  const size_t band_bytes = static_cast<size_t>((kblocks + 3) / 4) * 512;
+  for (int row0 = 0; rc == SMB_OK && row0 < M;) {
+    const int rows = fp4_next_chunk_rows(M - row0);
+    smb_fp4_plan* plan = nullptr;
+    // A chunk's operands arrive by host copies ordered with events, never from the GEMM launched
+    // before it on the stream, so consecutive chunk GEMMs may overlap.
+    rc = fp4_plan_create_impl(&plan, static_cast<char*>(c->da) + static_cast<size_t>(row0) * K / 2,
+                              static_cast<char*>(c->dsa) + static_cast<size_t>(row0 / 128) * band_bytes, c->db, c->dsb,
+                              static_cast<char*>(c->dd) + static_cast<size_t>(row0) * c->ldd * 2, rows, N, K, K / 2,
+                              K / 2, c->ldd, SMB_FLAG_OPERANDS_STATIC, 1, nullptr, c->status_dev);
+    if (rc != SMB_OK) break;
+    c->plans.push_back(plan);
+    c->chunk_row0.push_back(row0);
+    c->chunk_rows.push_back(rows);
+    cudaEvent_t ev_up = nullptr, ev_done = nullptr;
+    e = cudaEventCreateWithFlags(&ev_up, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ev_done, cudaEventDisableTiming);
+    if (ev_up) c->uploaded.push_back(ev_up);
+    if (ev_done) c->computed.push_back(ev_done);
+    if (e != cudaSuccess) rc = set_cuda_error(e, "fp4 host context: event creation");
+    row0 += rows;
+  }
+  if (rc != SMB_OK) {
+    smb_fp4_host_ctx_destroy(c);
+    return rc;
+  }
+  *out = c;
+  return SMB_OK;
+}
+
+namespace {
+// An error in the middle of a run: nothing may still read or write the caller's buffers when the
+// call returns.
+int fp4_host_ctx_abort(smb_fp4_host_ctx* c, int rc) {
+  cudaStreamSynchronize(c->up);
+  cudaStreamSynchronize(c->compute);
+  cudaStreamSynchronize(c->down);
+  return rc;
+}
+}  // namespace
+
+extern "C" int smb_fp4_host_ctx_run(smb_fp4_host_ctx* c, const uint8_t* a, const uint8_t* sfa_rowmajor,
+                                    const uint8_t* b, const uint8_t* sfb_rowmajor, uint16_t* d) {
+  if (c == nullptr) return set_error(SMB_ERR_INVALID, "fp4 host context: null handle");
+  if (a == nullptr || sfa_rowmajor == nullptr || d == nullptr)
+    return set_error(SMB_ERR_INVALID, "fp4 host context: null operand pointer");
+  if ((b == nullptr) != (sfb_rowmajor == nullptr))
+    return set_error(SMB_ERR_INVALID, "fp4 host context: B and its scales come together or not at all");
+  if (b == nullptr && !c->weights_loaded)
+    return set_error(SMB_ERR_INVALID, "fp4 host context: no weights from an earlier run to reuse");
+  const int64_t kblocks = c->K / 32;
+  const size_t row_bytes = static_cast<size_t>(c->K) / 2;
+  cudaError_t e = cudaSuccess;
+  int rc = SMB_OK;
+  if (b != nullptr) {
+    e = cudaMemcpyAsync(c->db, b, static_cast<size_t>(c->N) * row_bytes, cudaMemcpyHostToDevice, c->up);
+    if (e == cudaSuccess)
+      e = cudaMemcpyAsync(c->dsb_rm, sfb_rowmajor, static_cast<size_t>(c->N) * kblocks, cudaMemcpyHostToDevice, c->up);
+    if (e != cudaSuccess) return fp4_host_ctx_abort(c, set_cuda_error(e, "fp4 host context: upload of B"));
+    rc = sf_pack_launch(c->dsb_rm, c->dsb, 0, c->N, static_cast<uint32_t>(kblocks), c->up);
+    if (rc != SMB_OK) return fp4_host_ctx_abort(c, rc);
+    c->weights_loaded = true;
+  }
+  const size_t chunks = c->plans.size();
+  for (size_t i = 0; i < chunks; ++i) {
+    const size_t row0 = static_cast<size_t>(c->chunk_row0[i]);
+    const size_t rows = static_cast<size_t>(c->chunk_rows[i]);
+    e = cudaMemcpyAsync(static_cast<char*>(c->da) + row0 * row_bytes, a + row0 * row_bytes, rows * row_bytes,
+                        cudaMemcpyHostToDevice, c->up);
+    if (e == cudaSuccess)
+      e = cudaMemcpyAsync(static_cast<char*>(c->dsa_rm) + row0 * kblocks, sfa_rowmajor + row0 * kblocks,
+                          rows * kblocks, cudaMemcpyHostToDevice, c->up);
+    if (e != cudaSuccess) return fp4_host_ctx_abort(c, set_cuda_error(e, "fp4 host context: upload of A"));
+    rc = sf_pack_launch(c->dsa_rm, c->dsa, static_cast<int64_t>(row0), static_cast<int64_t>(rows),
+                        static_cast<uint32_t>(kblocks), c->up);
+    if (rc != SMB_OK) return fp4_host_ctx_abort(c, rc);
+    e = cudaEventRecord(c->uploaded[i], c->up);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->compute, c->uploaded[i], 0);
+    if (e != cudaSuccess) return fp4_host_ctx_abort(c, set_cuda_error(e, "fp4 host context: upload order"));
+    rc = smb_fp4_plan_run(c->plans[i], c->compute);
+    if (rc != SMB_OK) return fp4_host_ctx_abort(c, rc);
+    e = cudaEventRecord(c->computed[i], c->compute);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->down, c->computed[i], 0);
+    if (e == cudaSuccess) {
+      char* dst = reinterpret_cast<char*>(d) + row0 * static_cast<size_t>(c->N) * 2;
+      const char* src = static_cast<char*>(c->dd) + row0 * static_cast<size_t>(c->ldd) * 2;
+      if (c->ldd == c->N) {
+        e = cudaMemcpyAsync(dst, src, rows * static_cast<size_t>(c->N) * 2, cudaMemcpyDeviceToHost, c->down);
+      } else {
+        e = cudaMemcpy2DAsync(dst, static_cast<size_t>(c->N) * 2, src, static_cast<size_t>(c->ldd) * 2,
+                              static_cast<size_t>(c->N) * 2, rows, cudaMemcpyDeviceToHost, c->down);
+      }
+    }
+    if (e != cudaSuccess) return fp4_host_ctx_abort(c, set_cuda_error(e, "fp4 host context: download of D"));
+  }
+  // The download stream has waited for every GEMM: the status word is final when it gets there,
+  // and the next run may overwrite the operand buffers.
+  e = cudaMemcpyAsync(c->status_host, c->status_dev, sizeof(int), cudaMemcpyDeviceToHost, c->down);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(c->down);
+  if (e != cudaSuccess) return fp4_host_ctx_abort(c, set_cuda_error(e, "fp4 host context: synchronize"));
+  const int status = *c->status_host;
+  if (status != 0) {
+    cudaMemset(c->status_dev, 0, sizeof(int));
+    return set_error(SMB_ERR_DEVICE, "nvfp4 GEMM kernel reported status %d: %s", status, device_status_name(status));
+  }
+  return SMB_OK;
 }

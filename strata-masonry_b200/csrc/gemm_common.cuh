@@ -15,6 +15,14 @@ namespace smb {
 // Record a message for smb_last_error() (thread-local) and return `code`.
 int set_error(int code, const char* fmt, ...);
 int set_cuda_error(cudaError_t e, const char* what);
+// Text for a kernel's status word (ptx.cuh: DeviceStatus).
+const char* device_status_name(int code);
+
+// --------------------------------------------------------------------------- self test
+// One CTA waits `budget_cycles` on an mbarrier nobody arrives at and then records
+// kDevTimeoutProbe in `status` (device memory); `waited_cycles` (device, optional) receives how
+// long it waited.  Stream-ordered.  selftest.cu.
+int wait_probe_launch(int* status, long long budget_cycles, long long* waited_cycles, cudaStream_t stream);
 
 // --------------------------------------------------------------------------- raster
 // Map a flat tile index onto (tile_m, tile_n).  Tiles are walked in groups of `group_m`

@@ -1318,15 +1318,17 @@ int fp4_decode_bind_output(Fp4DecodeLaunch* L, void* d, int M, int N, long long 
 // Decode GEMM for callers that must not allocate
 // -----------------------------------------------------------------------------------
 // Some hosts of this library cannot call cudaMalloc on the path that runs the GEMM: an
-// inference server that has handed all device memory to its own pool at start-up, a
-// plugin running inside another framework's allocator, code between a stream capture's
-// begin and end.  For them the status word, the tile counters and the fp32 partial-sum slots
+// inference server that has handed all device memory to its own pool at start-up, or a
+// plugin running inside another framework's allocator: there a cudaMalloc on the request path
+// fails, or succeeds and stalls every stream of the device while it runs.  For them the status word, the tile counters and the fp32 partial-sum slots
 // of the decode kernel live in the fixed array below instead of in a plan-owned allocation.
-// The default work split (whole tile pairs per CTA) shares no tile between CTAs and touches
-// only the status word; counters and slots are what the stream-K split needs, and the array
-// has room for the counters of 500 000 columns and a few CTAs' slots.  The array is part of
-// the library image: every GPU that loads the library carries these 2 MiB until the process
-// exits.
+// Which of them a call uses depends on the work split (smb_decode_noalloc_set_split): whole
+// tile pairs per CTA share no tile between CTAs and use the status word only; the stream-K
+// split over a fixed number of CTAs uses the counters of all tiles and two slots per CTA.  The
+// array is part of the library image: every GPU that loads the library carries these 2 MiB until
+// the process exits.
+#include <atomic>
+
 namespace {
 
 constexpr size_t kStaticScratchBytes = size_t(2) << 20;
@@ -1334,7 +1336,11 @@ constexpr size_t kStaticStatusOffset = kStaticScratchBytes - 256;   // last 256 
 static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+// Device address of the array per device ordinal, published once it is known.  Two host threads
+// that race here both look the same address up and store the same value.
+std::atomic<void*> g_static_scratch_addr[kMaxDevices];
+// CTAs of the stream-K split; 0 = whole tile pairs per CTA.  Process-wide, like the array.
+std::atomic<int> g_noalloc_split_ctas{0};
 
 // The array's name is only a host-side handle here; the kernel needs its device address,
 // which differs per device.  Looked up once per device, with that device current.
@@ -1344,21 +1350,45 @@ int static_scratch_address(void** out) {
   if (e != cudaSuccess) return smb::set_cuda_error(e, "no-alloc decode: cudaGetDevice");
   if (dev < 0 || dev >= kMaxDevices)
     return smb::set_error(SMB_ERR_UNSUPPORTED, "no-alloc decode: device ordinal %d out of range", dev);
-  if (g_static_scratch_addr[dev] == nullptr) {
-    void* ptr = nullptr;
+  void* ptr = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
     e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
     if (e != cudaSuccess) return smb::set_cuda_error(e, "no-alloc decode: cudaGetSymbolAddress");
     if (ptr == nullptr)
       return smb::set_error(SMB_ERR_CUDA, "no-alloc decode: cudaGetSymbolAddress returned null");
-    g_static_scratch_addr[dev] = ptr;
+    g_static_scratch_addr[dev].store(ptr, std::memory_order_release);
   }
-  *out = g_static_scratch_addr[dev];
+  *out = ptr;
   return SMB_OK;
 }
 
 }  // namespace
 
 extern "C" size_t smb_decode_noalloc_scratch_limit(void) { return kStaticStatusOffset; }
+
+extern "C" int smb_decode_noalloc_set_split(int ctas) {
+  if (ctas < 0 || ctas > 4096)
+    return smb::set_error(SMB_ERR_INVALID, "no-alloc decode: split of %d CTAs outside 0..4096", ctas);
+  g_noalloc_split_ctas.store(ctas, std::memory_order_relaxed);
+  return SMB_OK;
+}
+
+extern "C" int smb_decode_noalloc_check(void* stream) {
+  using namespace smb;
+  void* base = nullptr;
+  if (int rc = static_scratch_address(&base)) return rc;
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return set_cuda_error(e, "no-alloc decode check: stream synchronize");
+  int status = 0;   // host stack: the copy below allocates nothing
+  e = cudaMemcpy(&status, static_cast<char*>(base) + kStaticStatusOffset, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return set_cuda_error(e, "no-alloc decode check: status read");
+  if (status != 0) {
+    // The next call clears the word (and, for the stream-K split, the counters) before it launches.
+    return set_error(SMB_ERR_DEVICE, "nvfp4 decode kernel reported status %d: %s", status,
+                     device_status_name(status));
+  }
+  return SMB_OK;
+}
 
 extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sfa, const void* b,
                                                    const void* sfb, void* d, int M, int N, int K,
@@ -1373,17 +1403,21 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
   if (K % 32 != 0)
     return set_error(SMB_ERR_UNSUPPORTED, "no-alloc decode: K=%d must be a multiple of 32", K);
   const int m_pad = (M + 15) / 16 * 16;
-  // Two slots per CTA plus one counter per tile.  As many CTAs as the array has slots for (and
-  // the device has SMs); a shape whose counters alone leave room for none is refused.
+  // Stream-K split: one counter per tile and two slots per CTA must fit below the status word.
+  // Whole tile pairs need neither, so any N is served.
+  const int split = g_noalloc_split_ctas.load(std::memory_order_relaxed);
   const size_t counter_bytes = (static_cast<size_t>(N) + 127) / 128 * sizeof(int);
   const size_t per_cta = 2 * fp4_decode_slot_bytes(M);
-  if (counter_bytes + per_cta > kStaticStatusOffset)
-    return set_error(SMB_ERR_UNSUPPORTED,
-                     "no-alloc decode: M=%d N=%d needs %zu bytes of scratch for its tile counters and "
-                     "one CTA, the built-in array holds %zu",
-                     M, N, counter_bytes + per_cta, kStaticStatusOffset);
-  const size_t fit = (kStaticStatusOffset - counter_bytes) / per_cta;
-  const int ctas = fit > 4096 ? 4096 : static_cast<int>(fit);
+  int ctas = 0;
+  if (split > 0) {
+    if (counter_bytes + per_cta > kStaticStatusOffset)
+      return set_error(SMB_ERR_UNSUPPORTED,
+                       "no-alloc decode: M=%d N=%d needs %zu bytes of scratch for its tile counters and "
+                       "one CTA, the built-in array holds %zu",
+                       M, N, counter_bytes + per_cta, kStaticStatusOffset);
+    const size_t fit = (kStaticStatusOffset - counter_bytes) / per_cta;
+    ctas = fit < static_cast<size_t>(split) ? static_cast<int>(fit) : split;
+  }
   const size_t slot_bytes = static_cast<size_t>(ctas) * per_cta;
   void* base = nullptr;
   if (int rc = static_scratch_address(&base)) return rc;
@@ -1392,7 +1426,7 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
   L.M = M;
   L.N = N;
   L.K = K;
-  L.max_ctas = 0;
+  L.max_ctas = ctas;     // 0: whole tile pairs; else stream-K ranges over this many CTAs
   L.max_stages = 0;
   L.activations_dynamic = false;
   L.dual = fp4_decode_prefers_dual(M);
@@ -1401,7 +1435,7 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
   L.act_ld = 0;
   L.block16 = false;
   L.alpha = 1.0f;
-  L.no_overlap = true;   // the memset below must be ordered before every access of this launch
+  L.no_overlap = true;   // the clears below must be ordered before every access of this launch
   L.scratch = static_cast<float*>(base);
   L.scratch_ctas = ctas;
   L.counters = reinterpret_cast<int*>(static_cast<char*>(base) + slot_bytes);
@@ -1420,12 +1454,13 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
                         kchunks * 512, 1, 128, false);
   if (rc == SMB_OK) rc = fp4_decode_bind_output(&L, d, M, N, N, true);
   if (rc != SMB_OK) return rc;
-  // The counters keep whatever the last call left in them (all zero after a call that ran to
-  // the end, anything after one that was cut short): clear them, and the status.  The slots
+  // The array keeps whatever the last call left in it.  The status word always starts at zero.
+  // The counters (used by the stream-K split only) are all zero after a call that ran to the
+  // end and anything after one that was cut short, so that split clears them too.  The slots
   // need no clearing: a slot is read only after its writer has counted itself in.
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e = cudaMemsetAsync(L.counters, 0, counter_bytes, st);
-  if (e == cudaSuccess) e = cudaMemsetAsync(L.status, 0, sizeof(int), st);
+  cudaError_t e = cudaMemsetAsync(L.status, 0, sizeof(int), st);
+  if (e == cudaSuccess && ctas > 0) e = cudaMemsetAsync(L.counters, 0, counter_bytes, st);
   if (e != cudaSuccess) return set_cuda_error(e, "no-alloc decode: scratch clear");
   return fp4_decode_launch(L, st);
 }

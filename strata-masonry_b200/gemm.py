@@ -105,6 +105,10 @@ class Bf16Plan:
     def run(self, stream=None) -> None:
         capi.check(self._lib.smb_bf16_plan_run(self._h, _stream_ptr(stream)))
 
+    def wait_probe(self, budget_cycles: int = 200_000, stream=None) -> None:
+        """Self test of the bounded device waits: the next check() raises SMB_ERR_DEVICE."""
+        capi.check(self._lib.smb_bf16_plan_wait_probe(self._h, budget_cycles, _stream_ptr(stream)))
+
     def check(self, stream=None) -> None:
         capi.check(self._lib.smb_bf16_plan_check(self._h, _stream_ptr(stream)))
 
@@ -291,12 +295,79 @@ class Fp4Plan:
     def run(self, stream=None) -> None:
         capi.check(self._lib.smb_fp4_plan_run(self._h, _stream_ptr(stream)))
 
+    def wait_probe(self, budget_cycles: int = 200_000, stream=None) -> None:
+        """Self test of the bounded device waits: the next check() raises SMB_ERR_DEVICE."""
+        capi.check(self._lib.smb_fp4_plan_wait_probe(self._h, budget_cycles, _stream_ptr(stream)))
+
     def check(self, stream=None) -> None:
         capi.check(self._lib.smb_fp4_plan_check(self._h, _stream_ptr(stream)))
 
     def close(self) -> None:
         if self._h:
             self._lib.smb_fp4_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Fp4HostContext:
+    """Host-buffer FP4 GEMM with device buffers, plans and streams kept between calls: codes and
+    row-major scale bytes go up, the scales are packed on the device, D comes back."""
+
+    def __init__(self, m: int, n: int, k: int):
+        self._lib = capi.lib()
+        self._h = C.c_void_p()
+        self.shape = (m, n, k)
+        capi.check(self._lib.smb_fp4_host_ctx_create(C.byref(self._h), m, n, k))
+
+    def run(self, a, sfa, b, sfb, d) -> None:
+        """a [M,K/2] u8, sfa [M,K/32] u8, b [N,K/2] u8, sfb [N,K/32] u8, d [M,N] bf16 bits: host
+        buffers (NumPy arrays, pinned torch tensors or raw addresses).  b = sfb = None keeps the
+        weights of the previous run on the device."""
+        capi.check(self._lib.smb_fp4_host_ctx_run(self._h, _ptr(a), _ptr(sfa), _ptr(b), _ptr(sfb), _ptr(d)))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.smb_fp4_host_ctx_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Comm:
+    """One rank's NCCL communicator behind the C ABI (one process per GPU)."""
+
+    def __init__(self, comm_id: bytes, world: int, rank: int):
+        self._lib = capi.lib()
+        self._h = C.c_void_p()
+        self.world, self.rank = world, rank
+        capi.check(self._lib.smb_comm_create(C.byref(self._h), comm_id, world, rank))
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(capi.COMM_ID_BYTES)
+        capi.check(capi.lib().smb_comm_unique_id(buf))
+        return buf.raw
+
+    def allgather_columns(self, slab, gathered, d_full, m: int, n_local: int, ldd: int | None = None,
+                          stream=None) -> None:
+        """[M, n_local] slabs of all ranks -> `gathered` [world, M, n_local]; with d_full also the
+        row-major [M, world * n_local] copy."""
+        capi.check(self._lib.smb_allgather_columns(
+            self._h, _ptr(slab), _ptr(gathered), _ptr(d_full), m, n_local,
+            self.world * n_local if ldd is None else ldd, _stream_ptr(stream)))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.smb_comm_destroy(self._h)
             self._h = C.c_void_p()
 
     def __del__(self):

@@ -909,3 +909,70 @@ def test_fp4_grouped_gemm(smb, cuda_device, case):
         row0 += r
     with pytest.raises(smb.capi.SmbError):     # N must keep the scale bands of the groups apart
         smb.gemm.Fp4Plan.grouped(a, sfa, b, sfb, d, m_total, 200, k, groups, tile_group)
+
+
+# ------------------------------------------------------------------------------- bounded waits
+@pytest.mark.parametrize("kind", ["bf16", "fp4"])
+def test_bounded_wait_probe_reports_and_recovers(smb, oracle, cuda_device, kind):
+    """A wait that runs out of budget comes back as SMB_ERR_DEVICE through the plan's status word,
+    the word is cleared by the check, and the same plan on the same stream then works.  The probe
+    kernel waits about 100 us on an mbarrier nobody arrives at and returns normally: nothing
+    faults, traps or hangs."""
+    torch = _torch()
+    m, n, k = 512, 512, 512
+    if kind == "bf16":
+        a = torch.empty(m, k, device=cuda_device, dtype=torch.bfloat16)
+        bt = torch.empty(n, k, device=cuda_device, dtype=torch.bfloat16)
+        d = torch.full((m, n), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+        smb.gemm.bf16_operands_device(a, bt, m, n, k, 5)
+        plan = smb.gemm.Bf16Plan(a, bt, d, m, n, k)
+    else:
+        a, sfa, sfar = _fp4_operand(smb, m, k, 5, 0)
+        b, sfb, sfbr = _fp4_operand(smb, n, k, 5, 1)
+        d = torch.full((m, n), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+        plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k)
+    plan.run()
+    plan.check()
+    plan.wait_probe(200_000)
+    with pytest.raises(smb.capi.SmbError) as err:
+        plan.check()
+    assert err.value.code == smb.capi.SMB_ERR_DEVICE
+    assert "status 107" in err.value.message and "bounded-wait probe" in err.value.message
+    plan.check()                      # the word was cleared: no stale error
+    d.fill_(float("nan"))
+    plan.run()                        # and the context, stream and plan still work
+    plan.check()
+    if kind == "bf16":
+        _check_bf16_full(oracle, a, bt, d, n, k)
+    else:
+        _check_fp4_full((a, sfar), (b, sfbr), d, k)
+    # Budgets outside 1 .. 2 000 000 cycles are refused on the host.
+    lib = smb.capi.lib()
+    fn = lib.smb_bf16_plan_wait_probe if kind == "bf16" else lib.smb_fp4_plan_wait_probe
+    assert fn(plan._h, 0, None) == smb.capi.SMB_ERR_INVALID
+    assert fn(plan._h, 10 ** 9, None) == smb.capi.SMB_ERR_INVALID
+    plan.close()
+
+
+# ------------------------------------------------------------------------------- FP4 host context
+@pytest.mark.parametrize("shape", [(2500, 1000, 512), (300, 520, 256), (100, 1024, 1024), (16, 4096, 2048)])
+def test_fp4_host_context(smb, cuda_device, shape):
+    """Host-buffer FP4 context (what the FP4 `e2e` figures of bench.py time): codes and row-major
+    scales go up, scales are packed on the device, row chunks pipeline, D comes back.  Identical
+    to the device-resident plan; a second run that keeps the weights on the device agrees too."""
+    torch = _torch()
+    m, n, k = shape
+    A, B, d = _run_fp4(smb, m, n, k, 5, fill_a=6)
+    a_host, sfa_host = A[0].cpu().numpy(), A[1].cpu().numpy()
+    b_host, sfb_host = B[0].cpu().numpy(), B[1].cpu().numpy()
+    ctx = smb.gemm.Fp4HostContext(m, n, k)
+    with pytest.raises(smb.capi.SmbError):
+        ctx.run(a_host, sfa_host, None, None, np.zeros((m, n), dtype=np.uint16))   # no weights yet
+    out = np.zeros((m, n), dtype=np.uint16)
+    ctx.run(a_host, sfa_host, b_host, sfb_host, out)
+    np.testing.assert_array_equal(out, _bits(d))
+    out2 = np.zeros((m, n), dtype=np.uint16)
+    ctx.run(a_host, sfa_host, None, None, out2)
+    np.testing.assert_array_equal(out2, _bits(d))
+    ctx.close()
+    _check_fp4_full(A, B, d, k)
