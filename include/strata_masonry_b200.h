@@ -143,6 +143,9 @@ int smb_bf16_plan_run(smb_bf16_plan* plan, void* stream);
  * the role that gave up in smb_last_error(). */
 int smb_bf16_plan_check(smb_bf16_plan* plan, void* stream);
 int smb_bf16_plan_destroy(smb_bf16_plan* plan);
+/* One line naming the kernel configuration the plan launches (tile shape, store path, CTAs per
+ * SM), e.g. "bf16 tile 256x512 store=tma resident=1": what measurements are keyed by. */
+int smb_bf16_plan_describe(smb_bf16_plan* plan, char* out, size_t capacity);
 /* Self test of the bounded device waits: launches one CTA that waits `budget_cycles` SM clocks
  * (1 .. 2 000 000, i.e. at most about a millisecond) on an mbarrier nobody arrives at, gives up,
  * writes the "bounded-wait probe" status into the plan's status word and returns normally.  The
@@ -229,6 +232,7 @@ int smb_fp4_grouped_plan_create(smb_fp4_plan** plan, const void* a, const void* 
 int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_destroy(smb_fp4_plan* plan);
+int smb_fp4_plan_describe(smb_fp4_plan* plan, char* out, size_t capacity);
 /* The bounded-wait self test on an FP4 plan's status word; see smb_bf16_plan_wait_probe. */
 int smb_fp4_plan_wait_probe(smb_fp4_plan* plan, long long budget_cycles, void* stream);
 /* Tuning: raster group height (0 = default), cluster cap (0 = all), L2 prefetch distance in
@@ -335,6 +339,10 @@ int smb_peer_export(void* ptr, unsigned char handle[SMB_PEER_HANDLE_BYTES]);
 int smb_peer_open(const unsigned char handle[SMB_PEER_HANDLE_BYTES], void** ptr);
 int smb_peer_close(void* ptr);
 int smb_peer_free(void* ptr);
+/* Waits for all work this process has queued on the current device.  Call it before telling the
+ * other ranks that a peer-mapped buffer may be unmapped or freed: a GEMM with peer copies or a
+ * row route may still be storing into it. */
+int smb_device_synchronize(void);
 
 /* The column slab of rank `rank` of `world`: an equal split of N whose slabs keep 16-byte
  * aligned bf16 rows (N % world == 0 and (N / world) % 8 == 0, else SMB_ERR_INVALID).  Pure
@@ -371,6 +379,16 @@ int smb_allgather_columns(smb_comm* comm, const void* slab, void* gathered, void
 int smb_allgather_columns_multi(smb_comm* const* comms, int ndev, const void* const* slabs,
                                 void* const* gathered, void* const* d_full, int M, int n_local,
                                 int64_t ldd, void* const* streams);
+
+/* Host-buffer contexts of a column-sharded job (one process per GPU, `comm` from
+ * smb_comm_create, kept by the caller for the life of the context): the context's N is this
+ * rank's n_local columns, and every run takes only this rank's M / world rows of A (rows
+ * [rank M / world, (rank + 1) M / world); for FP4 also of its row-major scales), its own shard
+ * of BT / B, and returns its [M, n_local] slab of D.  The ranks complete A on every GPU with an
+ * NCCL all-gather over NVLink inside the run, so the host sends every byte of A once per step
+ * instead of once per GPU.  M % world == 0.  All ranks must call run together. */
+int smb_bf16_host_ctx_create_sharded(smb_bf16_host_ctx** ctx, int M, int n_local, int K, smb_comm* comm);
+int smb_fp4_host_ctx_create_sharded(smb_fp4_host_ctx** ctx, int M, int n_local, int K, smb_comm* comm);
 
 #define SMB_FLAG_NONE 0u
 #define SMB_FLAG_FORCE_PLAIN_STORE 1u /* use the non-TMA epilogue even when D is aligned */

@@ -67,6 +67,8 @@ DECLARED = [
     ("smb_bf16_plan_run", _i, [_vp, _vp]),
     ("smb_bf16_plan_check", _i, [_vp, _vp]),
     ("smb_bf16_plan_destroy", _i, [_vp]),
+    ("smb_bf16_plan_describe", _i, [_vp, C.c_char_p, C.c_size_t]),
+    ("smb_fp4_plan_describe", _i, [_vp, C.c_char_p, C.c_size_t]),
     ("smb_bf16_plan_wait_probe", _i, [_vp, C.c_longlong, _vp]),
     ("smb_bf16_plan_tune", _i, [_vp, _i, _i]),
     ("smb_bf16_plan_set_profile", _i, [_vp, _vp]),
@@ -106,12 +108,15 @@ DECLARED = [
     ("smb_peer_open", _i, [C.c_char_p, C.POINTER(_vp)]),
     ("smb_peer_close", _i, [_vp]),
     ("smb_peer_free", _i, [_vp]),
+    ("smb_device_synchronize", _i, []),
     ("smb_column_shard", C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     ("smb_unshard_columns_device", _i, [_vp, _vp, _i, _i, _i, _i64, _vp]),
     ("smb_comm_unique_id", _i, [C.c_char_p]),
     ("smb_comm_create", _i, [C.POINTER(_vp), C.c_char_p, _i, _i]),
     ("smb_comm_create_all", _i, [C.POINTER(_vp), _i, C.POINTER(_i)]),
     ("smb_comm_destroy", _i, [_vp]),
+    ("smb_bf16_host_ctx_create_sharded", _i, [C.POINTER(_vp), _i, _i, _i, _vp]),
+    ("smb_fp4_host_ctx_create_sharded", _i, [C.POINTER(_vp), _i, _i, _i, _vp]),
     ("smb_allgather_check", _i, [_i, _i, _i, _i64]),
     ("smb_allgather_columns", _i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _vp]),
     ("smb_allgather_columns_multi", _i,

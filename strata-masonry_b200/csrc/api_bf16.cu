@@ -1,6 +1,8 @@
 // C-ABI of the BF16 GEMM: plans (tensor maps + tile choice), launch, status check, and the
 // host-buffer convenience path.  Host-side counterpart of run_one_impl in the reference
 // (src/kernels/gemm/sm100a/dense_gemm_bf16.cu:281-445).
+#include <cstdio>
+#include <cstdlib>
 #include <new>
 
 #include "gemm_common.cuh"
@@ -84,6 +86,13 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
   if (flags & SMB_FLAG_TILE_N_64) { L.tile_n = 64; L.sub_blocks = 1; }
   L.group_m = 0;
   L.max_clusters = 0;
+  L.l2_a = L.l2_b = 0;
+  if (const char* env = getenv("SMB_TUNE_BF16_L2")) {   // tuning sweeps: "<a><b>", digits 0..2
+    if (env[0] >= '0' && env[0] <= '2' && env[1] >= '0' && env[1] <= '2') {
+      L.l2_a = env[0] - '0';
+      L.l2_b = env[1] - '0';
+    }
+  }
   L.prof = nullptr;
   L.dynamic = (flags & SMB_FLAG_DYNAMIC_TILES) != 0;
   L.operands_static = (flags & (SMB_FLAG_OPERANDS_STATIC | SMB_FLAG_LAUNCH_INDEPENDENT)) != 0;
@@ -210,6 +219,16 @@ extern "C" int smb_bf16_plan_check(smb_bf16_plan* plan, void* stream) {
   return SMB_OK;
 }
 
+extern "C" int smb_bf16_plan_describe(smb_bf16_plan* plan, char* out, size_t capacity) {
+  if (plan == nullptr || out == nullptr || capacity == 0)
+    return set_error(SMB_ERR_INVALID, "plan describe: null argument");
+  const Bf16Launch& L = plan->launch;
+  const bool narrow_pair = L.tile_n <= 128 && L.operands_static && !L.swiglu;
+  snprintf(out, capacity, "bf16 tile 256x%d store=%s resident=%d", L.tile_n * L.sub_blocks,
+           L.swiglu ? "swiglu" : (L.tma_store ? "tma" : "plain"), narrow_pair ? 2 : 1);
+  return SMB_OK;
+}
+
 extern "C" int smb_bf16_plan_wait_probe(smb_bf16_plan* plan, long long budget_cycles, void* stream) {
   if (plan == nullptr) return set_error(SMB_ERR_INVALID, "plan: null handle");
   return wait_probe_launch(plan->status_dev, budget_cycles, nullptr, static_cast<cudaStream_t>(stream));
@@ -266,6 +285,10 @@ struct smb_bf16_host_ctx {
   std::vector<int> chunk_row0, chunk_rows;
   std::vector<cudaEvent_t> uploaded, computed;
   cudaStream_t up, compute, down;
+  // Sharded form: this rank uploads only its M / world rows of A; the ranks complete A over
+  // NVLink with an all-gather on the compute stream.
+  smb_comm* comm;
+  cudaEvent_t a_block_up, operands_up;
 };
 
 extern "C" int smb_bf16_host_ctx_destroy(smb_bf16_host_ctx* ctx) {
@@ -273,6 +296,8 @@ extern "C" int smb_bf16_host_ctx_destroy(smb_bf16_host_ctx* ctx) {
   for (smb_bf16_plan* p : ctx->plans) smb_bf16_plan_destroy(p);
   for (cudaEvent_t e : ctx->uploaded) cudaEventDestroy(e);
   for (cudaEvent_t e : ctx->computed) cudaEventDestroy(e);
+  if (ctx->a_block_up) cudaEventDestroy(ctx->a_block_up);
+  if (ctx->operands_up) cudaEventDestroy(ctx->operands_up);
   if (ctx->da) cudaFree(ctx->da);
   if (ctx->db) cudaFree(ctx->db);
   if (ctx->dd) cudaFree(ctx->dd);
@@ -285,12 +310,32 @@ extern "C" int smb_bf16_host_ctx_destroy(smb_bf16_host_ctx* ctx) {
   return SMB_OK;
 }
 
+namespace {
+int bf16_host_ctx_create_impl(smb_bf16_host_ctx** out, int M, int N, int K, smb_comm* comm);
+}
+
 extern "C" int smb_bf16_host_ctx_create(smb_bf16_host_ctx** out, int M, int N, int K) {
+  return bf16_host_ctx_create_impl(out, M, N, K, nullptr);
+}
+
+extern "C" int smb_bf16_host_ctx_create_sharded(smb_bf16_host_ctx** out, int M, int n_local, int K,
+                                                smb_comm* comm) {
+  if (comm == nullptr) return set_error(SMB_ERR_INVALID, "sharded host context: null communicator");
+  if (M <= 0 || M % comm_world(comm) != 0)
+    return set_error(SMB_ERR_INVALID, "sharded host context: M=%d is not divisible by %d ranks", M,
+                     comm_world(comm));
+  return bf16_host_ctx_create_impl(out, M, n_local, K, comm);
+}
+
+namespace {
+int bf16_host_ctx_create_impl(smb_bf16_host_ctx** out, int M, int N, int K, smb_comm* comm) {
   if (out == nullptr) return set_error(SMB_ERR_INVALID, "host context: null output handle");
   *out = nullptr;
   if (M <= 0 || N <= 0 || K <= 0) return set_error(SMB_ERR_INVALID, "host context: bad dimensions");
   smb_bf16_host_ctx* c = new (std::nothrow) smb_bf16_host_ctx();
   if (c == nullptr) return set_error(SMB_ERR_NOMEM, "host context: out of host memory");
+  c->comm = comm;
+  c->a_block_up = c->operands_up = nullptr;
   c->M = M;
   c->N = N;
   c->K = K;
@@ -309,6 +354,8 @@ extern "C" int smb_bf16_host_ctx_create(smb_bf16_host_ctx** out, int M, int N, i
   if (e == cudaSuccess) e = cudaMalloc(&c->status_dev, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(c->status_dev, 0, sizeof(int));
   if (e == cudaSuccess) e = cudaMallocHost(&c->status_host, sizeof(int));
+  if (e == cudaSuccess && comm != nullptr) e = cudaEventCreateWithFlags(&c->a_block_up, cudaEventDisableTiming);
+  if (e == cudaSuccess && comm != nullptr) e = cudaEventCreateWithFlags(&c->operands_up, cudaEventDisableTiming);
   if (e != cudaSuccess) rc = set_cuda_error(e, "host context: allocation");
   for (int row0 = 0; rc == SMB_OK && row0 < M;) {
     const int rows = next_chunk_rows(M - row0);
@@ -337,6 +384,7 @@ extern "C" int smb_bf16_host_ctx_create(smb_bf16_host_ctx** out, int M, int N, i
   *out = c;
   return SMB_OK;
 }
+}  // namespace
 
 namespace {
 // An error in the middle of a run: nothing may still be reading or writing the caller's buffers
@@ -355,18 +403,38 @@ extern "C" int smb_bf16_host_ctx_run(smb_bf16_host_ctx* c, const uint16_t* a, co
   if (a == nullptr || bt == nullptr || d == nullptr)
     return set_error(SMB_ERR_INVALID, "host context: null operand pointer");
   const size_t row_bytes_a = static_cast<size_t>(c->K) * 2;
-  cudaError_t e = cudaMemcpyAsync(c->db, bt, static_cast<size_t>(c->N) * c->K * 2,
-                                  cudaMemcpyHostToDevice, c->up);
-  if (e != cudaSuccess) return set_cuda_error(e, "host context: upload of BT");
+  cudaError_t e = cudaSuccess;
+  const bool sharded = c->comm != nullptr;
+  if (sharded) {
+    // `a` holds this rank's M / world rows.  They go up first so that the all-gather over NVLink
+    // runs while BT is still crossing PCIe; the GEMMs wait for both.
+    const size_t block_bytes = static_cast<size_t>(c->M / comm_world(c->comm)) * row_bytes_a;
+    e = cudaMemcpyAsync(static_cast<char*>(c->da) + static_cast<size_t>(comm_rank(c->comm)) * block_bytes, a,
+                        block_bytes, cudaMemcpyHostToDevice, c->up);
+    if (e == cudaSuccess) e = cudaEventRecord(c->a_block_up, c->up);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->compute, c->a_block_up, 0);
+    if (e != cudaSuccess) return host_ctx_abort(c, set_cuda_error(e, "host context: upload of the A block"));
+    int rc = comm_allgather_inplace(c->comm, c->da, block_bytes, c->compute);
+    if (rc != SMB_OK) return host_ctx_abort(c, rc);
+  }
+  e = cudaMemcpyAsync(c->db, bt, static_cast<size_t>(c->N) * c->K * 2, cudaMemcpyHostToDevice, c->up);
+  if (e != cudaSuccess) return host_ctx_abort(c, set_cuda_error(e, "host context: upload of BT"));
+  if (sharded) {
+    e = cudaEventRecord(c->operands_up, c->up);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->compute, c->operands_up, 0);
+    if (e != cudaSuccess) return host_ctx_abort(c, set_cuda_error(e, "host context: upload order"));
+  }
   const size_t chunks = c->plans.size();
   for (size_t i = 0; i < chunks; ++i) {
     const size_t row0 = static_cast<size_t>(c->chunk_row0[i]);
     const size_t rows = static_cast<size_t>(c->chunk_rows[i]);
-    e = cudaMemcpyAsync(static_cast<char*>(c->da) + row0 * row_bytes_a,
-                        reinterpret_cast<const char*>(a) + row0 * row_bytes_a, rows * row_bytes_a,
-                        cudaMemcpyHostToDevice, c->up);
-    if (e == cudaSuccess) e = cudaEventRecord(c->uploaded[i], c->up);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->compute, c->uploaded[i], 0);
+    if (!sharded) {
+      e = cudaMemcpyAsync(static_cast<char*>(c->da) + row0 * row_bytes_a,
+                          reinterpret_cast<const char*>(a) + row0 * row_bytes_a, rows * row_bytes_a,
+                          cudaMemcpyHostToDevice, c->up);
+      if (e == cudaSuccess) e = cudaEventRecord(c->uploaded[i], c->up);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(c->compute, c->uploaded[i], 0);
+    }
     if (e != cudaSuccess) return host_ctx_abort(c, set_cuda_error(e, "host context: upload of A"));
     int rc = smb_bf16_plan_run(c->plans[i], c->compute);
     if (rc != SMB_OK) return host_ctx_abort(c, rc);

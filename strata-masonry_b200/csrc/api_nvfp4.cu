@@ -1,6 +1,7 @@
 // C-ABI of the block-scaled FP4 GEMM: plans, launch, status check, host-buffer path.
 // Host-side counterpart of run_one_k1 in the reference
 // (src/kernels/gemm/sm100a/nvfp4/dense_gemm_nvfp4.cu:2353-2700).
+#include <cstdio>
 #include <new>
 #include <vector>
 
@@ -357,6 +358,22 @@ extern "C" int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream) {
   return SMB_OK;
 }
 
+extern "C" int smb_fp4_plan_describe(smb_fp4_plan* plan, char* out, size_t capacity) {
+  if (plan == nullptr || out == nullptr || capacity == 0)
+    return set_error(SMB_ERR_INVALID, "fp4 plan describe: null argument");
+  if (plan->decode) {
+    const Fp4DecodeLaunch& D = plan->dlaunch;
+    snprintf(out, capacity, "fp4 decode m_pad=%d %s%s%s", (D.M + 15) / 16 * 16,
+             D.max_ctas > 0 ? "stream-k" : (D.dual ? "tile-pairs" : "single-tiles"), D.block16 ? " block16" : "",
+             D.act_src != nullptr ? " bf16-activations" : "");
+  } else {
+    const Fp4Launch& L = plan->launch;
+    snprintf(out, capacity, "fp4 tile 256x%d store=%s%s", L.w0 + L.w1,
+             L.swiglu ? "swiglu" : (L.tma_store ? "tma" : "plain"), L.block16 ? " block16" : "");
+  }
+  return SMB_OK;
+}
+
 extern "C" int smb_fp4_plan_wait_probe(smb_fp4_plan* plan, long long budget_cycles, void* stream) {
   if (plan == nullptr) return set_error(SMB_ERR_INVALID, "fp4 plan: null handle");
   return wait_probe_launch(plan->status_dev, budget_cycles, nullptr, static_cast<cudaStream_t>(stream));
@@ -492,6 +509,10 @@ struct smb_fp4_host_ctx {
   std::vector<int> chunk_row0, chunk_rows;
   std::vector<cudaEvent_t> uploaded, computed;
   cudaStream_t up, compute, down;
+  // Sharded form: this rank uploads only its M / world rows of A (codes and scales); the ranks
+  // complete A over NVLink with all-gathers on the compute stream.
+  smb_comm* comm;
+  cudaEvent_t a_block_up, operands_up;
 };
 
 extern "C" int smb_fp4_host_ctx_destroy(smb_fp4_host_ctx* ctx) {
@@ -499,6 +520,8 @@ extern "C" int smb_fp4_host_ctx_destroy(smb_fp4_host_ctx* ctx) {
   for (smb_fp4_plan* p : ctx->plans) smb_fp4_plan_destroy(p);
   for (cudaEvent_t e : ctx->uploaded) cudaEventDestroy(e);
   for (cudaEvent_t e : ctx->computed) cudaEventDestroy(e);
+  if (ctx->a_block_up) cudaEventDestroy(ctx->a_block_up);
+  if (ctx->operands_up) cudaEventDestroy(ctx->operands_up);
   void* bufs[] = {ctx->da, ctx->db, ctx->dsa_rm, ctx->dsb_rm, ctx->dsa, ctx->dsb, ctx->dd, ctx->status_dev};
   for (void* b : bufs)
     if (b) cudaFree(b);
@@ -510,13 +533,33 @@ extern "C" int smb_fp4_host_ctx_destroy(smb_fp4_host_ctx* ctx) {
   return SMB_OK;
 }
 
+namespace {
+int fp4_host_ctx_create_impl(smb_fp4_host_ctx** out, int M, int N, int K, smb_comm* comm);
+}
+
 extern "C" int smb_fp4_host_ctx_create(smb_fp4_host_ctx** out, int M, int N, int K) {
+  return fp4_host_ctx_create_impl(out, M, N, K, nullptr);
+}
+
+extern "C" int smb_fp4_host_ctx_create_sharded(smb_fp4_host_ctx** out, int M, int n_local, int K,
+                                               smb_comm* comm) {
+  if (comm == nullptr) return set_error(SMB_ERR_INVALID, "sharded fp4 host context: null communicator");
+  if (M <= 0 || M % comm_world(comm) != 0)
+    return set_error(SMB_ERR_INVALID, "sharded fp4 host context: M=%d is not divisible by %d ranks", M,
+                     comm_world(comm));
+  return fp4_host_ctx_create_impl(out, M, n_local, K, comm);
+}
+
+namespace {
+int fp4_host_ctx_create_impl(smb_fp4_host_ctx** out, int M, int N, int K, smb_comm* comm) {
   if (out == nullptr) return set_error(SMB_ERR_INVALID, "fp4 host context: null output handle");
   *out = nullptr;
   if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0)
     return set_error(SMB_ERR_INVALID, "fp4 host context: bad dimensions (K must be a multiple of 32)");
   smb_fp4_host_ctx* c = new (std::nothrow) smb_fp4_host_ctx();
   if (c == nullptr) return set_error(SMB_ERR_NOMEM, "fp4 host context: out of host memory");
+  c->comm = comm;
+  c->a_block_up = c->operands_up = nullptr;
   c->M = M;
   c->N = N;
   c->K = K;
@@ -543,6 +586,8 @@ extern "C" int smb_fp4_host_ctx_create(smb_fp4_host_ctx** out, int M, int N, int
   if (e == cudaSuccess) e = cudaMalloc(&c->status_dev, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(c->status_dev, 0, sizeof(int));
   if (e == cudaSuccess) e = cudaMallocHost(&c->status_host, sizeof(int));
+  if (e == cudaSuccess && comm != nullptr) e = cudaEventCreateWithFlags(&c->a_block_up, cudaEventDisableTiming);
+  if (e == cudaSuccess && comm != nullptr) e = cudaEventCreateWithFlags(&c->operands_up, cudaEventDisableTiming);
   if (e != cudaSuccess) rc = set_cuda_error(e, "fp4 host context: allocation");
   const size_t band_bytes = static_cast<size_t>((kblocks + 3) / 4) * 512;
   for (int row0 = 0; rc == SMB_OK && row0 < M;) {
@@ -573,6 +618,7 @@ extern "C" int smb_fp4_host_ctx_create(smb_fp4_host_ctx** out, int M, int N, int
   *out = c;
   return SMB_OK;
 }
+}  // namespace
 
 namespace {
 // An error in the middle of a run: nothing may still read or write the caller's buffers when the
@@ -598,6 +644,25 @@ extern "C" int smb_fp4_host_ctx_run(smb_fp4_host_ctx* c, const uint8_t* a, const
   const size_t row_bytes = static_cast<size_t>(c->K) / 2;
   cudaError_t e = cudaSuccess;
   int rc = SMB_OK;
+  const bool sharded = c->comm != nullptr;
+  if (sharded) {
+    // `a` and `sfa_rowmajor` hold this rank's M / world rows.  They go up first so that the
+    // all-gathers over NVLink run while B is still crossing PCIe; then all of SFA is packed.
+    const size_t block_rows = static_cast<size_t>(c->M / comm_world(c->comm));
+    const size_t r = static_cast<size_t>(comm_rank(c->comm));
+    e = cudaMemcpyAsync(static_cast<char*>(c->da) + r * block_rows * row_bytes, a, block_rows * row_bytes,
+                        cudaMemcpyHostToDevice, c->up);
+    if (e == cudaSuccess)
+      e = cudaMemcpyAsync(static_cast<char*>(c->dsa_rm) + r * block_rows * kblocks, sfa_rowmajor,
+                          block_rows * kblocks, cudaMemcpyHostToDevice, c->up);
+    if (e == cudaSuccess) e = cudaEventRecord(c->a_block_up, c->up);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->compute, c->a_block_up, 0);
+    if (e != cudaSuccess) return fp4_host_ctx_abort(c, set_cuda_error(e, "fp4 host context: upload of the A block"));
+    rc = comm_allgather_inplace(c->comm, c->da, block_rows * row_bytes, c->compute);
+    if (rc == SMB_OK) rc = comm_allgather_inplace(c->comm, c->dsa_rm, block_rows * kblocks, c->compute);
+    if (rc == SMB_OK) rc = sf_pack_launch(c->dsa_rm, c->dsa, 0, c->M, static_cast<uint32_t>(kblocks), c->compute);
+    if (rc != SMB_OK) return fp4_host_ctx_abort(c, rc);
+  }
   if (b != nullptr) {
     e = cudaMemcpyAsync(c->db, b, static_cast<size_t>(c->N) * row_bytes, cudaMemcpyHostToDevice, c->up);
     if (e == cudaSuccess)
@@ -607,22 +672,29 @@ extern "C" int smb_fp4_host_ctx_run(smb_fp4_host_ctx* c, const uint8_t* a, const
     if (rc != SMB_OK) return fp4_host_ctx_abort(c, rc);
     c->weights_loaded = true;
   }
+  if (sharded) {
+    e = cudaEventRecord(c->operands_up, c->up);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->compute, c->operands_up, 0);
+    if (e != cudaSuccess) return fp4_host_ctx_abort(c, set_cuda_error(e, "fp4 host context: upload order"));
+  }
   const size_t chunks = c->plans.size();
   for (size_t i = 0; i < chunks; ++i) {
     const size_t row0 = static_cast<size_t>(c->chunk_row0[i]);
     const size_t rows = static_cast<size_t>(c->chunk_rows[i]);
-    e = cudaMemcpyAsync(static_cast<char*>(c->da) + row0 * row_bytes, a + row0 * row_bytes, rows * row_bytes,
-                        cudaMemcpyHostToDevice, c->up);
-    if (e == cudaSuccess)
-      e = cudaMemcpyAsync(static_cast<char*>(c->dsa_rm) + row0 * kblocks, sfa_rowmajor + row0 * kblocks,
-                          rows * kblocks, cudaMemcpyHostToDevice, c->up);
-    if (e != cudaSuccess) return fp4_host_ctx_abort(c, set_cuda_error(e, "fp4 host context: upload of A"));
-    rc = sf_pack_launch(c->dsa_rm, c->dsa, static_cast<int64_t>(row0), static_cast<int64_t>(rows),
-                        static_cast<uint32_t>(kblocks), c->up);
-    if (rc != SMB_OK) return fp4_host_ctx_abort(c, rc);
-    e = cudaEventRecord(c->uploaded[i], c->up);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->compute, c->uploaded[i], 0);
-    if (e != cudaSuccess) return fp4_host_ctx_abort(c, set_cuda_error(e, "fp4 host context: upload order"));
+    if (!sharded) {
+      e = cudaMemcpyAsync(static_cast<char*>(c->da) + row0 * row_bytes, a + row0 * row_bytes, rows * row_bytes,
+                          cudaMemcpyHostToDevice, c->up);
+      if (e == cudaSuccess)
+        e = cudaMemcpyAsync(static_cast<char*>(c->dsa_rm) + row0 * kblocks, sfa_rowmajor + row0 * kblocks,
+                            rows * kblocks, cudaMemcpyHostToDevice, c->up);
+      if (e != cudaSuccess) return fp4_host_ctx_abort(c, set_cuda_error(e, "fp4 host context: upload of A"));
+      rc = sf_pack_launch(c->dsa_rm, c->dsa, static_cast<int64_t>(row0), static_cast<int64_t>(rows),
+                          static_cast<uint32_t>(kblocks), c->up);
+      if (rc != SMB_OK) return fp4_host_ctx_abort(c, rc);
+      e = cudaEventRecord(c->uploaded[i], c->up);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(c->compute, c->uploaded[i], 0);
+      if (e != cudaSuccess) return fp4_host_ctx_abort(c, set_cuda_error(e, "fp4 host context: upload order"));
+    }
     rc = smb_fp4_plan_run(c->plans[i], c->compute);
     if (rc != SMB_OK) return fp4_host_ctx_abort(c, rc);
     e = cudaEventRecord(c->computed[i], c->compute);

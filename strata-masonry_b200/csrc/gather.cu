@@ -75,6 +75,25 @@ struct smb_comm {
   int world, rank, device;
 };
 
+namespace smb {
+
+int comm_world(const smb_comm* comm) { return comm->world; }
+int comm_rank(const smb_comm* comm) { return comm->rank; }
+int comm_device(const smb_comm* comm) { return comm->device; }
+
+int comm_allgather_inplace(smb_comm* comm, void* buf, size_t block_bytes, cudaStream_t stream) {
+  if (comm == nullptr || buf == nullptr) return set_error(SMB_ERR_INVALID, "all-gather: null argument");
+  const NcclApi* api = nccl();
+  if (api == nullptr) return nccl_missing();
+  // NCCL's in-place form: the send buffer is this rank's block inside the receive buffer.
+  const char* send = static_cast<const char*>(buf) + static_cast<size_t>(comm->rank) * block_bytes;
+  ncclResult_t r = api->AllGather(send, buf, block_bytes, ncclUint8, comm->comm, stream);
+  if (r != ncclSuccess) return nccl_error(api, r, "ncclAllGather");
+  return SMB_OK;
+}
+
+}  // namespace smb
+
 // Shape rules shared by both all-gather entry points; no device needed.
 extern "C" int smb_allgather_check(int world, int M, int n_local, int64_t ldd) {
   if (world < 1 || world > 64) return set_error(SMB_ERR_INVALID, "all-gather: world of %d ranks outside 1..64", world);

@@ -87,6 +87,7 @@ struct Params {
   int m_rotate;         // the tile walk starts at this 256-row tile (0 unless rows are routed)
   const int* mtile_group;  // grouped GEMM: group of every 256-row tile of A (device), or null
   int operands_static;  // 1: A and BT are not written by the previous kernel on the stream
+  int l2_a, l2_b;       // L2 eviction hint of the A / BT loads: 0 none, 1 evict-last, 2 evict-first
 };
 
 // Per-CTA role timers (cycles), written when Params::prof is set.
@@ -178,6 +179,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const long long t_begin = prof ? clock64() : 0;
       TileCursor cursor;
       cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
+      const uint64_t pol_a = p.l2_a == 2 ? l2_policy_evict_first() : l2_policy_evict_last();
+      const uint64_t pol_b = p.l2_b == 2 ? l2_policy_evict_first() : l2_policy_evict_last();
       // Everything before this point overlapped the tail of the previous kernel on the stream;
       // its results (possibly this kernel's operands, certainly the old contents of D) are
       // complete and visible once this returns.  Unless the caller vouches that the operands are
@@ -207,11 +210,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // same barrier and may land before or after the arming, which mbarrier tolerates.
           if (elect_one()) {
             if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * C::kStageBytes);
-            tma_load_2d_pair(dst_a, &tmap_a, bar, kb * kBlockK, row_a);
+            if (p.l2_a != 0) tma_load_2d_pair_hint(dst_a, &tmap_a, bar, kb * kBlockK, row_a, pol_a);
+            else tma_load_2d_pair(dst_a, &tmap_a, bar, kb * kBlockK, row_a);
 #pragma unroll
             for (int h = 0; h < NB; ++h) {
-              tma_load_2d_pair(dst_a + kABytes + h * C::kBBytes, &tmap_b, bar, kb * kBlockK,
-                               row_b + h * TN);
+              if (p.l2_b != 0)
+                tma_load_2d_pair_hint(dst_a + kABytes + h * C::kBBytes, &tmap_b, bar, kb * kBlockK,
+                                      row_b + h * TN, pol_b);
+              else
+                tma_load_2d_pair(dst_a + kABytes + h * C::kBBytes, &tmap_b, bar, kb * kBlockK,
+                                 row_b + h * TN);
             }
           }
           __syncwarp();
@@ -426,6 +434,8 @@ int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
   p.peers = L.peers;
   p.m_rotate = L.peers.route_rows > 0 ? (L.peers.first_block * (L.peers.route_rows / 256)) % p.tiles_m : 0;
   p.mtile_group = L.mtile_group;
+  p.l2_a = L.l2_a;
+  p.l2_b = L.l2_b;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (L.max_clusters > 0 && clusters > L.max_clusters) clusters = L.max_clusters;

@@ -18,6 +18,14 @@ int set_cuda_error(cudaError_t e, const char* what);
 // Text for a kernel's status word (ptx.cuh: DeviceStatus).
 const char* device_status_name(int code);
 
+// --------------------------------------------------------------------------- communicator (gather.cu)
+// In-place NCCL all-gather of equal byte blocks: rank r's block already sits at
+// buf + r * block_bytes; afterwards every rank holds all blocks.  Stream-ordered.
+int comm_allgather_inplace(smb_comm* comm, void* buf, size_t block_bytes, cudaStream_t stream);
+int comm_world(const smb_comm* comm);
+int comm_rank(const smb_comm* comm);
+int comm_device(const smb_comm* comm);
+
 // --------------------------------------------------------------------------- self test
 // One CTA waits `budget_cycles` on an mbarrier nobody arrives at and then records
 // kDevTimeoutProbe in `status` (device memory); `waited_cycles` (device, optional) receives how
@@ -89,6 +97,7 @@ struct Bf16Launch {
   bool output_independent;  // with operands_static: stores need not wait either
   PeerCopies peers;
   const int* mtile_group;  // grouped GEMM (device array, one group id per 256-row tile of A), or null
+  int l2_a, l2_b;    // L2 eviction hints of the A / BT loads: 0 none, 1 evict-last, 2 evict-first
 };
 void bf16_pick_tile(int M, int N, int K, int clusters, int* tile_n, int* sub_blocks);
 // Number of 2-CTA clusters that can run at once on the current device (SM count / 2), 0 if unknown.

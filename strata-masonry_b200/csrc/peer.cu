@@ -51,6 +51,12 @@ extern "C" int smb_peer_free(void* ptr) {
   return SMB_OK;
 }
 
+extern "C" int smb_device_synchronize(void) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return set_cuda_error(e, "device synchronize");
+  return SMB_OK;
+}
+
 namespace {
 
 // One 16-byte chunk per thread and step: chunk c of output row m comes from slab c / chunks_local.

@@ -105,6 +105,11 @@ class Bf16Plan:
     def run(self, stream=None) -> None:
         capi.check(self._lib.smb_bf16_plan_run(self._h, _stream_ptr(stream)))
 
+    def describe(self) -> str:
+        buf = C.create_string_buffer(160)
+        capi.check(self._lib.smb_bf16_plan_describe(self._h, buf, 160))
+        return buf.value.decode()
+
     def wait_probe(self, budget_cycles: int = 200_000, stream=None) -> None:
         """Self test of the bounded device waits: the next check() raises SMB_ERR_DEVICE."""
         capi.check(self._lib.smb_bf16_plan_wait_probe(self._h, budget_cycles, _stream_ptr(stream)))
@@ -127,11 +132,17 @@ class Bf16Plan:
 class Bf16HostContext:
     """Host-buffer GEMM with device buffers, plan and stream kept between calls."""
 
-    def __init__(self, m: int, n: int, k: int):
+    def __init__(self, m: int, n: int, k: int, comm=None):
+        """With `comm` (a Comm): the sharded form, n = this rank's columns, run() takes this
+        rank's M / world rows of A and all ranks call it together."""
         self._lib = capi.lib()
         self._h = C.c_void_p()
         self.shape = (m, n, k)
-        capi.check(self._lib.smb_bf16_host_ctx_create(C.byref(self._h), m, n, k))
+        self._comm = comm
+        if comm is None:
+            capi.check(self._lib.smb_bf16_host_ctx_create(C.byref(self._h), m, n, k))
+        else:
+            capi.check(self._lib.smb_bf16_host_ctx_create_sharded(C.byref(self._h), m, n, k, comm._h))
 
     def run(self, a, bt, d) -> None:
         """a [M,K], bt [N,K], d [M,N]: host buffers of bf16 bit patterns (NumPy arrays, pinned
@@ -295,6 +306,11 @@ class Fp4Plan:
     def run(self, stream=None) -> None:
         capi.check(self._lib.smb_fp4_plan_run(self._h, _stream_ptr(stream)))
 
+    def describe(self) -> str:
+        buf = C.create_string_buffer(160)
+        capi.check(self._lib.smb_fp4_plan_describe(self._h, buf, 160))
+        return buf.value.decode()
+
     def wait_probe(self, budget_cycles: int = 200_000, stream=None) -> None:
         """Self test of the bounded device waits: the next check() raises SMB_ERR_DEVICE."""
         capi.check(self._lib.smb_fp4_plan_wait_probe(self._h, budget_cycles, _stream_ptr(stream)))
@@ -318,11 +334,17 @@ class Fp4HostContext:
     """Host-buffer FP4 GEMM with device buffers, plans and streams kept between calls: codes and
     row-major scale bytes go up, the scales are packed on the device, D comes back."""
 
-    def __init__(self, m: int, n: int, k: int):
+    def __init__(self, m: int, n: int, k: int, comm=None):
+        """With `comm` (a Comm): the sharded form, n = this rank's columns, run() takes this
+        rank's M / world rows of A and of its scales, and all ranks call it together."""
         self._lib = capi.lib()
         self._h = C.c_void_p()
         self.shape = (m, n, k)
-        capi.check(self._lib.smb_fp4_host_ctx_create(C.byref(self._h), m, n, k))
+        self._comm = comm
+        if comm is None:
+            capi.check(self._lib.smb_fp4_host_ctx_create(C.byref(self._h), m, n, k))
+        else:
+            capi.check(self._lib.smb_fp4_host_ctx_create_sharded(C.byref(self._h), m, n, k, comm._h))
 
     def run(self, a, sfa, b, sfb, d) -> None:
         """a [M,K/2] u8, sfa [M,K/32] u8, b [N,K/2] u8, sfb [N,K/32] u8, d [M,N] bf16 bits: host

@@ -90,8 +90,27 @@ class _CudaPeerMemory:
     def close(self, ptr: int) -> None:
         self._capi.check(self._lib.smb_peer_close(ptr))
 
+    def synchronize(self) -> None:
+        """Wait for all work of this process on the current device (kernels whose epilogues may
+        still be storing into peers' buffers)."""
+        self._capi.check(self._lib.smb_device_synchronize())
+
     def free(self, ptr: int) -> None:
         self._capi.check(self._lib.smb_peer_free(ptr))
+
+
+def _close_shared(dist, mem, bases, rank, local) -> None:
+    """Tear-down order of peer-mapped buffers.  A kernel of this rank may still be storing into the
+    other ranks' buffers (its epilogue writes them with plain stores), and the host barrier below
+    says nothing about the device: so every rank first drains its own device, then all meet (now
+    nobody writes into anybody's buffer), unmap, meet again (nobody still has a mapping), free."""
+    mem.synchronize()
+    dist.barrier()
+    for r, base in enumerate(bases):
+        if r != rank:
+            mem.close(base)
+    dist.barrier()
+    mem.free(local)
 
 
 class SharedOutput:
@@ -140,16 +159,11 @@ class SharedOutput:
         return flat.view(torch.bfloat16).view(self.m, self.n_total)
 
     def close(self) -> None:
-        """Collective: nobody may still be writing into a buffer that is about to be freed."""
+        """Collective: device synchronize, barrier, unmap, barrier, free (see _close_shared)."""
         if not self._open:
             return
         self._open = False
-        self._dist.barrier()
-        for r, base in enumerate(self.bases):
-            if r != self.rank:
-                self._mem.close(base)
-        self._dist.barrier()
-        self._mem.free(self.local)
+        _close_shared(self._dist, self._mem, self.bases, self.rank, self.local)
 
 
 # ------------------------------------------------------------------ fused reduce-scatter plumbing
@@ -194,9 +208,4 @@ class ScatterSlots:
         if not self._open:
             return
         self._open = False
-        self._dist.barrier()
-        for r, base in enumerate(self.bases):
-            if r != self.rank:
-                self._mem.close(base)
-        self._dist.barrier()
-        self._mem.free(self.local)
+        _close_shared(self._dist, self._mem, self.bases, self.rank, self.local)

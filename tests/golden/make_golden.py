@@ -13,6 +13,7 @@ this file, which travels with the repository; the reference tree does not.
 from __future__ import annotations
 
 import importlib.util
+import os
 import sys
 from pathlib import Path
 
@@ -29,7 +30,7 @@ def _load(path: Path, name: str):
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SMB_REFERENCE_DIR", "/root/reference"))
     gemm_dir = ref_root / "src" / "kernels" / "gemm" / "sm100a"
     vb = _load(gemm_dir / "dense_gemm_bf16_cpu_verifier.py", "ref_bf16_verifier")
     vf = _load(gemm_dir / "nvfp4" / "dense_gemm_nvfp4_cpu_verifier.py", "ref_nvfp4_verifier")

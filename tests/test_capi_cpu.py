@@ -209,3 +209,35 @@ def test_nvf4_host_quantizer_matches_oracle(smb, oracle):
     assert np.all(np.abs(back - x) <= 0.26 * np.maximum(amax, 1e-30) + 2.0 ** -9 / gs * 6)
     assert lib.smb_quantize_nvf4_host(None, 0, C.c_float(1.0), None, 0, None, None, 1, 32) == smb.capi.SMB_ERR_INVALID
     assert lib.smb_fp4_plan_set_alpha(None, C.c_float(1.0)) == smb.capi.SMB_ERR_INVALID
+
+
+def test_new_entry_points_validate_their_arguments(smb):
+    """Host-side rules of the entry points added for the sharded path, the self test and the
+    allocation-free decode call: all of them answer with status codes before touching a device."""
+    lib, capi = smb.capi.lib(), smb.capi
+    # All-gather shape rules (no device, no NCCL needed).
+    assert lib.smb_allgather_check(8, 32768, 7168, 57344) == capi.SMB_OK
+    assert lib.smb_allgather_check(8, 32768, 7168, 0) == capi.SMB_OK          # no full-D copy asked for
+    assert lib.smb_allgather_check(0, 16, 8, 8) == capi.SMB_ERR_INVALID
+    assert lib.smb_allgather_check(2, 16, 12, 24) == capi.SMB_ERR_INVALID     # slab rows not 16-byte multiples
+    assert "multiple of 8" in capi.last_error()
+    assert lib.smb_allgather_check(2, 16, 8, 8) == capi.SMB_ERR_INVALID       # pitch below world * n_local
+    assert lib.smb_allgather_check(2, 0, 8, 16) == capi.SMB_ERR_INVALID
+    assert lib.smb_allgather_columns(None, None, None, None, 16, 8, 16, None) == capi.SMB_ERR_INVALID
+    assert lib.smb_comm_create(None, None, 2, 0) == capi.SMB_ERR_INVALID
+    assert lib.smb_comm_destroy(None) == capi.SMB_OK
+    # Contexts and probes.
+    ctx = C.c_void_p()
+    assert lib.smb_fp4_host_ctx_create(C.byref(ctx), 16, 128, 48) == capi.SMB_ERR_INVALID   # K % 32
+    assert lib.smb_fp4_host_ctx_run(None, None, None, None, None, None) == capi.SMB_ERR_INVALID
+    assert lib.smb_fp4_host_ctx_destroy(None) == capi.SMB_OK
+    assert lib.smb_bf16_host_ctx_create_sharded(C.byref(ctx), 16, 128, 64, None) == capi.SMB_ERR_INVALID
+    assert lib.smb_fp4_host_ctx_create_sharded(C.byref(ctx), 16, 128, 64, None) == capi.SMB_ERR_INVALID
+    assert lib.smb_bf16_plan_wait_probe(None, 1000, None) == capi.SMB_ERR_INVALID
+    assert lib.smb_fp4_plan_wait_probe(None, 1000, None) == capi.SMB_ERR_INVALID
+    assert lib.smb_bf16_plan_describe(None, None, 0) == capi.SMB_ERR_INVALID
+    # Allocation-free decode call: the split is a process-wide setting with a range.
+    assert lib.smb_decode_noalloc_set_split(-1) == capi.SMB_ERR_INVALID
+    assert lib.smb_decode_noalloc_set_split(4097) == capi.SMB_ERR_INVALID
+    assert lib.smb_decode_noalloc_set_split(0) == capi.SMB_OK
+    assert lib.smb_decode_noalloc_scratch_limit() == (2 << 20) - 256

@@ -1,8 +1,8 @@
 """Output files of this repository's drivers against output files of the reference's own GPU
 drivers (built unchanged from the reference sources into oracle/_ref by oracle/Makefile), same
 shape, same fill, on the same GPU.  Skipped where oracle/_ref has not been built.  Timings of both
-sides are written to a JSON file (SMB_AB_RECORD, default reference_ab.json in the run's output
-folder) for the record; only parity is asserted."""
+sides are written to a JSON file for the record (SMB_AB_RECORD if set, else reference_ab.json
+in the test's temporary folder); only parity is asserted."""
 import json
 import os
 import re
@@ -43,8 +43,8 @@ def _pair(kind, m, k, n, fill, tmp_path, benchmark):
         RESULTS[f"{kind} M={m} N={n} K={k} fill={fill}"] = {
             "reference_ms": times[0][0], "reference_tflops": times[0][1],
             "ours_ms": times[1][0], "ours_tflops": times[1][1]}
-        record = Path(os.environ.get("SMB_AB_RECORD", str(ROOT / "gpurun_out" / "reference_ab.json")))
-        record.parent.mkdir(exist_ok=True)
+        record = Path(os.environ.get("SMB_AB_RECORD", str(tmp_path.parent / "reference_ab.json")))
+        record.parent.mkdir(parents=True, exist_ok=True)
         record.write_text(json.dumps(RESULTS, indent=1))
     return outs
 

@@ -1,6 +1,7 @@
 """The reference's own verifier command lines, unchanged, on output files this repository's drivers
 wrote on a B200 (tests/golden/gpu_dumps).  Runs only where the reference tree is mounted."""
 import json
+import os
 import subprocess
 import sys
 from pathlib import Path
@@ -9,7 +10,7 @@ import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
 DUMPS = ROOT / "tests" / "golden" / "gpu_dumps"
-GEMM = Path("/root/reference/src/kernels/gemm/sm100a")
+GEMM = Path(os.environ.get("SMB_REFERENCE_DIR", "/root/reference")) / "src" / "kernels" / "gemm" / "sm100a"
 VERIFIERS = {"bf16": GEMM / "dense_gemm_bf16_cpu_verifier.py",
              "nvfp4": GEMM / "nvfp4" / "dense_gemm_nvfp4_cpu_verifier.py"}
 

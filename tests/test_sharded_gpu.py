@@ -175,6 +175,39 @@ def _free_port():
         return s.getsockname()[1]
 
 
+_PG_TIMEOUT = __import__("datetime").timedelta(seconds=120)
+
+
+def _run_ranks(ctx, target, world, args, out, timeout=300):
+    """Start one child per rank, wait, and never leave one behind: a child that is still alive at
+    the deadline is terminated (then killed) so that it does not keep its GPU, and the test fails
+    with what the children reported."""
+    procs = [ctx.Process(target=target, args=(r, world, *args)) for r in range(world)]
+    for p in procs:
+        p.start()
+    deadline = __import__("time").time() + timeout
+    for p in procs:
+        p.join(timeout=max(1.0, deadline - __import__("time").time()))
+    stuck = [p for p in procs if p.is_alive()]
+    for p in stuck:
+        p.terminate()
+    for p in stuck:
+        p.join(timeout=10)
+        if p.is_alive():
+            p.kill()
+            p.join(timeout=10)
+    results = {}
+    while len(results) < world:
+        try:
+            rank, ok = out.get(timeout=2)
+        except Exception:
+            break
+        results[rank] = ok
+    assert not stuck, f"{len(stuck)} rank(s) did not finish within {timeout} s; reports so far: {results}"
+    assert all(p.exitcode == 0 for p in procs), f"exit codes {[p.exitcode for p in procs]}; reports: {results}"
+    assert results == {r: True for r in range(world)}, results
+
+
 def _two_gpu_worker(rank, world, port, out):
     import torch
     import torch.distributed as dist
@@ -186,7 +219,7 @@ def _two_gpu_worker(rank, world, port, out):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=_PG_TIMEOUT)
     try:
         m, n, k, fill = 1000, 2048, 512, 5
         shared = smb.sharding.SharedOutput(m, n, dist)
@@ -214,6 +247,10 @@ def _two_gpu_worker(rank, world, port, out):
         del d_full
         shared.close()
         out.put((rank, bool(ok)))
+    except BaseException:
+        import traceback
+        out.put((rank, traceback.format_exc()))
+        raise
     finally:
         dist.destroy_process_group()
 
@@ -226,14 +263,7 @@ def test_fused_all_gather_on_two_gpus(smb, cuda_device):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_two_gpu_worker, args=(r, 2, port, out)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-        assert p.exitcode == 0
-    results = dict(out.get(timeout=5) for _ in range(2))
-    assert results == {0: True, 1: True}
+    _run_ranks(ctx, _two_gpu_worker, 2, (port, out), out)
 
 
 # ------------------------------------------------------------------ K-sharded GEMM + fused scatter
@@ -311,7 +341,7 @@ def _two_gpu_scatter_worker(rank, world, port, out):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=_PG_TIMEOUT)
     try:
         m, n, k, fill = 1024, 512, 2048, 5
         kl = k // world
@@ -340,6 +370,10 @@ def _two_gpu_scatter_worker(rank, world, port, out):
         plan.close()
         slots.close()
         out.put((rank, bool(ok)))
+    except BaseException:
+        import traceback
+        out.put((rank, traceback.format_exc()))
+        raise
     finally:
         dist.destroy_process_group()
 
@@ -352,14 +386,7 @@ def test_fused_scatter_on_two_gpus(smb, cuda_device):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_two_gpu_scatter_worker, args=(r, 2, port, out)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-        assert p.exitcode == 0
-    results = dict(out.get(timeout=5) for _ in range(2))
-    assert results == {0: True, 1: True}
+    _run_ranks(ctx, _two_gpu_scatter_worker, 2, (port, out), out)
 
 
 def test_plan_refuses_to_run_on_another_device(smb, cuda_device):
@@ -383,3 +410,111 @@ def test_plan_refuses_to_run_on_another_device(smb, cuda_device):
             plan.check()
     finally:
         plan.close()
+
+
+# ------------------------------------------------------------------ all-gather and sharded host contexts behind the C ABI
+def _capi_gather_worker(rank, world, port, out):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__ as entry
+    smb = entry.load_package()
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=_PG_TIMEOUT)
+    try:
+        # The library's own communicator: rank 0 makes the id, the others get it over the host channel.
+        ident = [smb.gemm.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ident, 0)
+        comm = smb.gemm.Comm(ident[0], world, rank)
+        m, n, k, fill = 1024, 1536, 512, 5
+        sh = smb.sharding.column_shard(n, world, rank)
+        a = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
+        bt = torch.empty(sh.n_local, k, device=dev, dtype=torch.bfloat16)
+        slab = torch.empty(m, sh.n_local, device=dev, dtype=torch.bfloat16)
+        smb.gemm.bf16_operands_device(a, bt, m, sh.n_local, k, fill, n0=sh.n0, n_total=n)
+        plan = smb.gemm.Bf16Plan(a, bt, slab, m, sh.n_local, k)
+        plan.run(); plan.check(); plan.close()
+        # Single-GPU result of the whole problem, computed locally.
+        bt_all = torch.empty(n, k, device=dev, dtype=torch.bfloat16)
+        smb.gemm.bf16_operands_device(a, bt_all, m, n, k, fill)
+        ref = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        p1 = smb.gemm.Bf16Plan(a, bt_all, ref, m, n, k)
+        p1.run(); p1.check(); p1.close()
+        gathered = torch.full((world, m, sh.n_local), float("nan"), device=dev, dtype=torch.bfloat16)
+        full = torch.full((m, n), float("nan"), device=dev, dtype=torch.bfloat16)
+        comm.allgather_columns(slab, gathered, full, m, sh.n_local)
+        torch.cuda.synchronize()
+        ok = torch.equal(full.view(torch.int16), ref.view(torch.int16))
+        ok &= torch.equal(gathered[rank].view(torch.int16), slab.view(torch.int16))
+        # Sharded host context: this rank sends its M / world rows of A and its shard of BT; the
+        # GPUs complete A over NVLink inside the run.
+        rows = m // world
+        a_host = a[rank * rows:(rank + 1) * rows].view(torch.int16).cpu().numpy().view(np.uint16)
+        bt_host = bt.view(torch.int16).cpu().numpy().view(np.uint16)
+        ctx = smb.gemm.Bf16HostContext(m, sh.n_local, k, comm=comm)
+        for _ in range(2):
+            d_host = np.zeros((m, sh.n_local), dtype=np.uint16)
+            ctx.run(a_host, bt_host, d_host)
+            ok &= np.array_equal(d_host, slab.view(torch.int16).cpu().numpy().view(np.uint16))
+        ctx.close()
+        # The same for the block-scaled GEMM (codes and row-major scales of A travel in blocks).
+        def fp4_operand(rows_, fill_, which, row0):
+            data = torch.empty(rows_, k // 2, device=dev, dtype=torch.uint8)
+            sfp = torch.empty(smb.gemm.sf_packed_bytes(rows_, k), device=dev, dtype=torch.uint8)
+            sfr = torch.empty(rows_, k // 32, device=dev, dtype=torch.uint8)
+            smb.gemm.fill_fp4_device(data, sfp, sfr, rows_, k, fill_, which, row0)
+            return data, sfp, sfr
+
+        fa, fsfa, fsfar = fp4_operand(m, 6, 0, 0)
+        fb, fsfb, fsfbr = fp4_operand(sh.n_local, 5, 1, sh.n0)
+        fd = torch.empty(m, sh.n_local, device=dev, dtype=torch.bfloat16)
+        fplan = smb.gemm.Fp4Plan(fa, fsfa, fb, fsfb, fd, m, sh.n_local, k)
+        fplan.run(); fplan.check(); fplan.close()
+        fctx = smb.gemm.Fp4HostContext(m, sh.n_local, k, comm=comm)
+        d_host = np.zeros((m, sh.n_local), dtype=np.uint16)
+        fctx.run(fa[rank * rows:(rank + 1) * rows].cpu().numpy(), fsfar[rank * rows:(rank + 1) * rows].cpu().numpy(),
+                 fb.cpu().numpy(), fsfbr.cpu().numpy(), d_host)
+        ok &= np.array_equal(d_host, fd.view(torch.int16).cpu().numpy().view(np.uint16))
+        fctx.close()
+        dist.barrier()
+        comm.close()
+        out.put((rank, bool(ok)))
+    except BaseException:
+        import traceback
+        out.put((rank, traceback.format_exc()))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def test_capi_allgather_and_sharded_host_contexts_on_two_gpus(smb, cuda_device):
+    """smb_comm_* + smb_allgather_columns (NCCL resolved at run time) give every rank the
+    single-GPU result bit for bit; the sharded host contexts give each rank its slab while the host
+    sends every row of A once."""
+    torch = _torch()
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    _run_ranks(ctx, _capi_gather_worker, 2, (_free_port(), out), out)
+
+
+def test_capi_allgather_single_rank(smb, cuda_device):
+    """A world of one: the all-gather is a copy and the unshard copy the identity.  Exercises the
+    run-time NCCL binding on a 1-GPU box."""
+    torch = _torch()
+    m, nl = 512, 256
+    comm = smb.gemm.Comm(smb.gemm.Comm.unique_id(), 1, 0)
+    slab = torch.randn(m, nl, device=cuda_device).to(torch.bfloat16)
+    gathered = torch.zeros(1, m, nl, device=cuda_device, dtype=torch.bfloat16)
+    full = torch.zeros(m, nl, device=cuda_device, dtype=torch.bfloat16)
+    comm.allgather_columns(slab, gathered, full, m, nl)
+    torch.cuda.synchronize()
+    assert torch.equal(gathered[0], slab) and torch.equal(full, slab)
+    with pytest.raises(smb.capi.SmbError):
+        comm.allgather_columns(slab, gathered, full, m, 100)      # slab width not a multiple of 8
+    comm.close()

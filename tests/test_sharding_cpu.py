@@ -117,6 +117,9 @@ class _FileBackedMemory:
     def free(self, ptr):
         self.freed.append(ptr)
 
+    def synchronize(self):
+        self.synced = getattr(self, "synced", 0) + 1
+
 
 def _fused_worker(rank, world, port, path, out):
     import torch.distributed as dist
@@ -152,7 +155,7 @@ def _fused_worker(rank, world, port, path, out):
         ok &= order == [(rank + i) % world for i in range(1, world)]
         ok &= sorted(mem.opened) == sorted(mem.BASE + r * region for r in range(world) if r != rank)
         shared.close()
-        ok &= sorted(mem.closed) == sorted(mem.opened) and mem.freed == [shared.local]
+        ok &= sorted(mem.closed) == sorted(mem.opened) and mem.freed == [shared.local] and mem.synced == 1
         out.put(bool(ok))
         dist.barrier()
     finally:
@@ -178,6 +181,60 @@ def test_shared_output_addresses_on_gloo(smb, tmp_path, world):
         p.join(timeout=120)
         assert p.exitcode == 0
     assert all(out.get(timeout=5) is True for _ in range(world))
+
+
+class _Recorder:
+    """Stand-ins for `dist` and the peer memory that log the order of what close() does."""
+
+    def __init__(self):
+        self.log = []
+
+    # torch.distributed face
+    def get_rank(self):
+        return 0
+
+    def get_world_size(self):
+        return 2
+
+    def barrier(self):
+        self.log.append("barrier")
+
+    def all_gather_object(self, handles, mine):
+        handles[0] = mine
+        handles[1] = (0x9000).to_bytes(8, "little") + bytes(56)
+
+    # memory face
+    def alloc(self, nbytes):
+        return 0x5000
+
+    def export(self, ptr):
+        return int(ptr).to_bytes(8, "little") + bytes(56)
+
+    def open(self, handle):
+        return int.from_bytes(handle[:8], "little")
+
+    def close(self, ptr):
+        self.log.append("unmap")
+
+    def free(self, ptr):
+        self.log.append("free")
+
+    def synchronize(self):
+        self.log.append("sync")
+
+
+@pytest.mark.parametrize("kind", ["SharedOutput", "ScatterSlots"])
+def test_close_drains_the_device_before_peers_may_free(smb, kind):
+    """A rank's GEMM epilogue may still be storing into the other ranks' buffers when close() is
+    called; a host barrier alone does not wait for it.  Order: device synchronize, barrier, unmap,
+    barrier, free."""
+    rec = _Recorder()
+    obj = (smb.sharding.SharedOutput(16, 32, rec, memory=rec) if kind == "SharedOutput"
+           else smb.sharding.ScatterSlots(512, 32, rec, memory=rec))
+    obj.close()
+    assert rec.log == ["sync", "barrier", "unmap", "barrier", "free"]
+    obj.close()                       # idempotent
+    assert len(rec.log) == 5
 
 
 def test_peer_copy_rules(smb):
