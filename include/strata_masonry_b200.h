@@ -118,6 +118,13 @@ uint32_t smb_debug_idesc_bf16(int mma_m, int mma_n);
 uint32_t smb_debug_idesc_mxf4(int mma_m, int mma_n, uint32_t sf_id_a, uint32_t sf_id_b, int ue8m0);
 void smb_debug_tile_coords(int t, int tiles_m, int tiles_n, int group_m, int* tm, int* tn);
 uint64_t smb_debug_sf_offset(uint32_t row, uint32_t kblock, uint32_t kblocks);
+/* The tile list of the FP4 kernel with 256 x 384 tiles: `wide_tiles_n` full tiles per 256-row tile
+ * row followed by `narrow_tiles_n` tiles of 256 columns (chosen so that the round-robin walk of
+ * `clusters` clusters ends soonest), and tile t of that list (first column, full width or not).
+ * Counterpart of the reference's static tile orders (nvfp4/dense_gemm_nvfp4.cu:380-434). */
+void smb_debug_fp4_phases(int M, int N, int K, int clusters, int* wide_tiles_n, int* narrow_tiles_n);
+void smb_debug_fp4_tile(int t, int tiles_m, int wide_tiles_n, int narrow_tiles_n, int group_m, int* tm,
+                        int* col0, int* full_width);
 
 /* ------------------------------------------------------------------------------------
  * Dense BF16 GEMM:  D[M,N] = bf16_rne( sum_k A[M,K] * BT[N,K] ), FP32 accumulate.

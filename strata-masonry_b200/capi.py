@@ -62,6 +62,8 @@ DECLARED = [
     ("smb_debug_idesc_mxf4", _u32, [_i, _i, _u32, _u32, _i]),
     ("smb_debug_tile_coords", None, [_i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
     ("smb_debug_sf_offset", _u64, [_u32, _u32, _u32]),
+    ("smb_debug_fp4_phases", None, [_i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
+    ("smb_debug_fp4_tile", None, [_i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     ("smb_bf16_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, C.c_uint]),
     ("smb_bf16_grouped_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, _i, _vp, C.c_uint]),
     ("smb_bf16_plan_run", _i, [_vp, _vp]),

@@ -86,7 +86,7 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
   if (flags & SMB_FLAG_TILE_N_64) { L.tile_n = 64; L.sub_blocks = 1; }
   L.group_m = 0;
   L.max_clusters = 0;
-  L.l2_a = L.l2_b = 0;
+  L.l2_a = L.l2_b = 1;   // evict-last on both operands: +1-2 % sustained on 8192^3 over no hint
   if (const char* env = getenv("SMB_TUNE_BF16_L2")) {   // tuning sweeps: "<a><b>", digits 0..2
     if (env[0] >= '0' && env[0] <= '2' && env[1] >= '0' && env[1] <= '2') {
       L.l2_a = env[0] - '0';

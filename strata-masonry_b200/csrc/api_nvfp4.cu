@@ -2,6 +2,7 @@
 // Host-side counterpart of run_one_k1 in the reference
 // (src/kernels/gemm/sm100a/nvfp4/dense_gemm_nvfp4.cu:2353-2700).
 #include <cstdio>
+#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -80,6 +81,15 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
   L.max_clusters = 0;
   L.prof = nullptr;
   L.prefetch = 0;
+  L.uniform_tiles = false;
+  L.l2_a = L.l2_b = 0;
+  if (const char* env = getenv("SMB_TUNE_FP4_L2")) {   // tuning sweeps: "<a><b>", digits 0..2
+    if (env[0] >= '0' && env[0] <= '2' && env[1] >= '0' && env[1] <= '2') {
+      L.l2_a = env[0] - '0';
+      L.l2_b = env[1] - '0';
+    }
+  }
+  if (getenv("SMB_TUNE_FP4_UNIFORM")) L.uniform_tiles = true;
   L.dynamic = (flags & SMB_FLAG_DYNAMIC_TILES) != 0;
   L.operands_static = (flags & (SMB_FLAG_OPERANDS_STATIC | SMB_FLAG_LAUNCH_INDEPENDENT)) != 0;
   L.output_independent = (flags & SMB_FLAG_LAUNCH_INDEPENDENT) != 0;

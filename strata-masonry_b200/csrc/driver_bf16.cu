@@ -7,7 +7,9 @@
 // (Gaussian stand-ins), --json=PATH, --ordered-launches (stores of a launch wait for the
 // previous launch; by default the timing loop's launches are independent, as the reference's
 // are), --shard=RANK/WORLD and --device=INDEX (one process per GPU computes and dumps its column
-// slab of D).  Operands are generated on the device.
+// slab of D), --gpus=G [--allgather] (one process drives G devices, times the box, optionally
+// exchanges the slabs with an NCCL all-gather timed apart, and dumps the full D).  Operands are
+// generated on the device.
 #include "driver_common.h"
 
 namespace {
@@ -52,31 +54,116 @@ struct Options {
   // reference kernels' are; true: every launch orders its stores after the previous launch.
   bool ordered = false;
   Shard shard;
+  BoxOptions box;
 };
 
+// Operands, output and plan of one device's share: columns [n0, n0 + N) of the logical problem.
+struct Case {
+  int M = 0, N = 0, K = 0, n0 = 0, n_total = 0;
+  uint16_t *a = nullptr, *bt = nullptr, *d = nullptr;
+  cudaStream_t stream = nullptr;
+  smb_bf16_plan* plan = nullptr;
+};
+
+// On the current device.
+Case make_case(int M, int n_total, int K, int n0, int n_local, const Options& o) {
+  Case c;
+  c.M = M;
+  c.N = n_local;
+  c.K = K;
+  c.n0 = n0;
+  c.n_total = n_total;
+  const int N = n_local;
+  DRV_CUDA(cudaMalloc(&c.a, static_cast<size_t>(M) * K * 2));
+  DRV_CUDA(cudaMalloc(&c.bt, static_cast<size_t>(N) * K * 2));
+  DRV_CUDA(cudaMalloc(&c.d, static_cast<size_t>(M) * N * 2));
+  DRV_CUDA(cudaMemset(c.d, 0, static_cast<size_t>(M) * N * 2));
+  DRV_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+  // A: index m*K + k, seed 1.  BT[n][k] = B[k][n]: index k*N + n, seed 2.
+  DRV_SMB(smb_fill_bf16_device(c.a, M, K, K, 0, static_cast<uint64_t>(K), 1, o.fill, 1, c.stream));
+  DRV_SMB(smb_fill_bf16_device(c.bt, N, K, K, static_cast<uint64_t>(n0), 1, static_cast<uint64_t>(n_total),
+                               o.fill, 2, c.stream));
+  DRV_CUDA(cudaStreamSynchronize(c.stream));
+  DRV_SMB(smb_bf16_plan_create(&c.plan, c.a, c.bt, c.d, M, N, K, K, K, N,
+                               o.ordered ? SMB_FLAG_OPERANDS_STATIC : SMB_FLAG_LAUNCH_INDEPENDENT));
+  if (o.raster == 1) DRV_SMB(smb_bf16_plan_tune(c.plan, 1, 0));
+  if (o.raster == 2) DRV_SMB(smb_bf16_plan_tune(c.plan, (M + 255) / 256, 0));
+  return c;
+}
+
+// The driver's self-check of one slab against the CUDA-core reference; 0 = passed.
+int verify_case(const Case& c) {
+  const int M = c.M, N = c.N, K = c.K;
+  uint16_t* ref = nullptr;
+  DRV_CUDA(cudaMalloc(&ref, static_cast<size_t>(M) * N * 2));
+  reference_gemm_bf16<<<M, 256>>>(c.a, c.bt, ref, M, N, K);
+  DRV_CUDA(cudaDeviceSynchronize());
+  std::vector<uint16_t> got(static_cast<size_t>(M) * N), want(got.size());
+  DRV_CUDA(cudaMemcpy(got.data(), c.d, got.size() * 2, cudaMemcpyDeviceToHost));
+  DRV_CUDA(cudaMemcpy(want.data(), ref, want.size() * 2, cudaMemcpyDeviceToHost));
+  float max_diff = 0.0f;
+  bool ok = true;
+  for (size_t i = 0; i < got.size(); ++i) {
+    const float g = bf16_bits_to_float(got[i]), w = bf16_bits_to_float(want[i]);
+    const float diff = fabsf(g - w);
+    if (!(diff <= max_diff)) max_diff = diff;
+    if (!(diff <= 0.05f + 0.05f * fabsf(w))) ok = false;
+  }
+  std::printf("  verify (M=%d,N=%d,K=%d): max_diff=%.3f tight=%s\n", M, N, K, max_diff, ok ? "OK" : "FAIL");
+  cudaFree(ref);
+  return ok ? 0 : 1;
+}
+
+void free_case(Case& c) {
+  smb_bf16_plan_destroy(c.plan);
+  cudaStreamDestroy(c.stream);
+  cudaFree(c.a);
+  cudaFree(c.bt);
+  cudaFree(c.d);
+}
+
 double run_one(int M, int n_total, int K, const Options& o) {
+  if (o.box.gpus > 0) {
+    // One process, several devices: device g holds the slab of rank g.
+    int have = 0;
+    DRV_CUDA(cudaGetDeviceCount(&have));
+    if (o.box.gpus > have) {
+      std::fprintf(stderr, "--gpus=%d but only %d device(s) are visible\n", o.box.gpus, have);
+      std::exit(1);
+    }
+    std::vector<Case> cases(o.box.gpus);
+    std::vector<BoxSlab> slabs(o.box.gpus);
+    for (int g = 0; g < o.box.gpus; ++g) {
+      int n0 = 0, n_local = 0;
+      if (smb_column_shard(n_total, o.box.gpus, g, &n0, &n_local) != SMB_OK) {
+        std::fprintf(stderr, "unsupported --gpus for this shape: %s\n", smb_last_error());
+        std::exit(1);
+      }
+      DRV_CUDA(cudaSetDevice(g));
+      cases[g] = make_case(M, n_total, K, n0, n_local, o);
+      Case* c = &cases[g];
+      BoxSlab& s = slabs[g];
+      s.device = g;
+      s.n0 = n0;
+      s.n_local = n_local;
+      s.stream = c->stream;
+      s.d = c->d;
+      s.launch = [c]() { return smb_bf16_plan_run(c->plan, c->stream); };
+      s.check = [c]() { return smb_bf16_plan_check(c->plan, c->stream); };
+      if (o.verify) s.verify = [c]() { return verify_case(*c); };
+      s.destroy = [c]() { free_case(*c); };
+    }
+    const double tflops = run_box(slabs, M, n_total, K, o.benchmark, o.box.allgather, o.dump,
+                                  "  shape (%6d, %6d, %4d): %.6f ms  %7.1f TFLOPS\n");
+    DRV_CUDA(cudaSetDevice(0));
+    return tflops;
+  }
   Shard shard = o.shard;
   shard.resolve(n_total);
   const int N = shard.n_local;   // everything below works on this process's slab
-  uint16_t *a = nullptr, *bt = nullptr, *d = nullptr;
-  DRV_CUDA(cudaMalloc(&a, static_cast<size_t>(M) * K * 2));
-  DRV_CUDA(cudaMalloc(&bt, static_cast<size_t>(N) * K * 2));
-  DRV_CUDA(cudaMalloc(&d, static_cast<size_t>(M) * N * 2));
-  DRV_CUDA(cudaMemset(d, 0, static_cast<size_t>(M) * N * 2));
-  cudaStream_t stream;
-  DRV_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
-  // A: index m*K + k, seed 1.  BT[n][k] = B[k][n]: index k*N + n, seed 2.
-  DRV_SMB(smb_fill_bf16_device(a, M, K, K, 0, static_cast<uint64_t>(K), 1, o.fill, 1, stream));
-  DRV_SMB(smb_fill_bf16_device(bt, N, K, K, static_cast<uint64_t>(shard.n0), 1, static_cast<uint64_t>(n_total),
-                               o.fill, 2, stream));
-  DRV_CUDA(cudaStreamSynchronize(stream));
-
-  smb_bf16_plan* plan = nullptr;
-  DRV_SMB(smb_bf16_plan_create(&plan, a, bt, d, M, N, K, K, K, N,
-                               o.ordered ? SMB_FLAG_OPERANDS_STATIC : SMB_FLAG_LAUNCH_INDEPENDENT));
-  if (o.raster == 1) DRV_SMB(smb_bf16_plan_tune(plan, 1, 0));
-  if (o.raster == 2) DRV_SMB(smb_bf16_plan_tune(plan, (M + 255) / 256, 0));
-  auto launch = [&]() { return smb_bf16_plan_run(plan, stream); };
+  Case c = make_case(M, n_total, K, shard.n0, N, o);
+  cudaStream_t stream = c.stream;
+  auto launch = [&]() { return smb_bf16_plan_run(c.plan, stream); };
   double ms = 0.0;
   if (o.benchmark) {
     ms = measure_mean_ms(stream, launch);
@@ -85,7 +172,7 @@ double run_one(int M, int n_total, int K, const Options& o) {
   }
   // The dumped output comes from one more launch, as in the reference driver.
   DRV_SMB(launch());
-  DRV_SMB(smb_bf16_plan_check(plan, stream));
+  DRV_SMB(smb_bf16_plan_check(c.plan, stream));
   double tflops = 0.0;
   if (o.benchmark) {
     tflops = 2.0 * M * N * K / (ms * 1e-3) / 1e12;
@@ -94,35 +181,9 @@ double run_one(int M, int n_total, int K, const Options& o) {
     std::printf("  shape (%6d, %6d, %4d): untimed\n", M, N, K);
   }
   write_json(o.json, "dense_gemm_bf16", M, N, K, o.fill, ms, tflops, o.benchmark);
-  if (o.dump) dump_bf16(d, static_cast<size_t>(M) * N, o.dump);
-
-  int rc = 0;
-  if (o.verify) {
-    uint16_t* ref = nullptr;
-    DRV_CUDA(cudaMalloc(&ref, static_cast<size_t>(M) * N * 2));
-    reference_gemm_bf16<<<M, 256>>>(a, bt, ref, M, N, K);
-    DRV_CUDA(cudaDeviceSynchronize());
-    std::vector<uint16_t> got(static_cast<size_t>(M) * N), want(got.size());
-    DRV_CUDA(cudaMemcpy(got.data(), d, got.size() * 2, cudaMemcpyDeviceToHost));
-    DRV_CUDA(cudaMemcpy(want.data(), ref, want.size() * 2, cudaMemcpyDeviceToHost));
-    float max_diff = 0.0f;
-    bool ok = true;
-    for (size_t i = 0; i < got.size(); ++i) {
-      const float g = bf16_bits_to_float(got[i]), w = bf16_bits_to_float(want[i]);
-      const float diff = fabsf(g - w);
-      if (!(diff <= max_diff)) max_diff = diff;
-      if (!(diff <= 0.05f + 0.05f * fabsf(w))) ok = false;
-    }
-    std::printf("  verify (M=%d,N=%d,K=%d): max_diff=%.3f tight=%s\n", M, N, K, max_diff,
-                ok ? "OK" : "FAIL");
-    if (!ok) rc = 1;
-    cudaFree(ref);
-  }
-  smb_bf16_plan_destroy(plan);
-  cudaStreamDestroy(stream);
-  cudaFree(a);
-  cudaFree(bt);
-  cudaFree(d);
+  if (o.dump) dump_bf16(c.d, static_cast<size_t>(M) * N, o.dump);
+  const int rc = o.verify ? verify_case(c) : 0;
+  free_case(c);
   if (rc != 0) std::exit(rc);
   return tflops;
 }
@@ -159,10 +220,19 @@ int main(int argc, char** argv) {
     } else if (std::strncmp(argv[i], "--json=", 7) == 0) {
       o.json = argv[i] + 7;
     } else if (o.shard.parse(argv[i])) {
+    } else if (o.box.parse(argv[i])) {
     } else {
       std::fprintf(stderr, "unknown argument: %s\n", argv[i]);
       return 1;
     }
+  }
+  if (o.box.allgather && o.box.gpus < 1) {
+    std::fprintf(stderr, "--allgather requires --gpus=G\n");
+    return 1;
+  }
+  if (o.box.gpus > 0 && o.shard.world > 1) {
+    std::fprintf(stderr, "--gpus and --shard exclude each other\n");
+    return 1;
   }
   DRV_CUDA(cudaSetDevice(o.shard.device));
   DRV_CUDA(cudaFree(0));

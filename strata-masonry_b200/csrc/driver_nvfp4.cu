@@ -7,8 +7,9 @@
 // reference with tolerance max(0.8 % |ref|, 16).  FILL environment variable as default fill.
 // Beyond the reference: any positive M and N, any K that is a multiple of 32, fills 5 and 6
 // (quantised Gaussian stand-ins), --json=PATH, --ordered-launches, --shard=RANK/WORLD and
-// --device=INDEX (one process per GPU computes its column slab of D); no arguments runs a short
-// shape list.
+// --device=INDEX (one process per GPU computes its column slab of D), --gpus=G [--allgather] (one
+// process drives G devices, times the box, optionally exchanges the slabs with an NCCL all-gather
+// timed apart, and dumps the full D); no arguments runs a short shape list.
 #include <cmath>
 
 #include "driver_common.h"
@@ -36,6 +37,7 @@ struct Options {
   // reference kernels' are; true: every launch orders its stores after the previous launch.
   bool ordered = false;
   Shard shard;
+  BoxOptions box;
 };
 
 // One logical row of an operand on the host: values (code * scale) as floats.
@@ -53,30 +55,153 @@ void host_row(std::vector<float>& out, int row, int K, int fill, int which) {
   }
 }
 
+// Operands, output and plan of one device's share: columns [n0, n0 + N) of the logical problem.
+struct Case {
+  int M = 0, N = 0, K = 0, n0 = 0, fill = 1;
+  uint8_t *a = nullptr, *b = nullptr, *sfa = nullptr, *sfb = nullptr;
+  uint16_t* d = nullptr;
+  cudaStream_t stream = nullptr;
+  smb_fp4_plan* plan = nullptr;
+};
+
+// On the current device.
+Case make_case(int M, int K, int n0, int n_local, const Options& o) {
+  Case c;
+  c.M = M;
+  c.N = n_local;
+  c.K = K;
+  c.n0 = n0;
+  c.fill = o.fill;
+  const int N = n_local;
+  const size_t sfa_bytes = smb_sf_packed_bytes(M, K / 32), sfb_bytes = smb_sf_packed_bytes(N, K / 32);
+  DRV_CUDA(cudaMalloc(&c.a, static_cast<size_t>(M) * K / 2));
+  DRV_CUDA(cudaMalloc(&c.b, static_cast<size_t>(N) * K / 2));
+  DRV_CUDA(cudaMalloc(&c.sfa, sfa_bytes));
+  DRV_CUDA(cudaMalloc(&c.sfb, sfb_bytes));
+  DRV_CUDA(cudaMalloc(&c.d, static_cast<size_t>(M) * N * 2));
+  DRV_CUDA(cudaMemset(c.d, 0, static_cast<size_t>(M) * N * 2));
+  DRV_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+  DRV_SMB(smb_fill_fp4_device(c.a, K / 2, c.sfa, nullptr, M, K, 0, o.fill, 0, c.stream));
+  DRV_SMB(smb_fill_fp4_device(c.b, K / 2, c.sfb, nullptr, N, K, static_cast<uint64_t>(n0), o.fill, 1, c.stream));
+  DRV_CUDA(cudaStreamSynchronize(c.stream));
+  DRV_SMB(smb_fp4_plan_create(&c.plan, c.a, c.sfa, c.b, c.sfb, c.d, M, N, K, K / 2, K / 2, N,
+                              o.ordered ? SMB_FLAG_OPERANDS_STATIC : SMB_FLAG_LAUNCH_INDEPENDENT));
+  return c;
+}
+
+void free_case(Case& c) {
+  smb_fp4_plan_destroy(c.plan);
+  cudaStreamDestroy(c.stream);
+  cudaFree(c.a);
+  cudaFree(c.b);
+  cudaFree(c.sfa);
+  cudaFree(c.sfb);
+  cudaFree(c.d);
+}
+
+// The driver's self-check of one slab (global column = n0 + n); 0 = passed.
+int verify_case(const Case& c) {
+  const int M = c.M, N = c.N, K = c.K, n0 = c.n0, fill = c.fill;
+  int rc = 0;
+  std::vector<uint16_t> host(static_cast<size_t>(M) * N);
+  DRV_CUDA(cudaMemcpy(host.data(), c.d, host.size() * 2, cudaMemcpyDeviceToHost));
+  if (fill == 1 || fill == 3) {
+    // D[m][n] = p K 2^((m % 5) - 2) 2^((n % 3) - 1), p = 16 (fill 1) or 1 (fill 3): exact.
+    const float per_product = (fill == 3) ? 1.0f : 16.0f;
+    float max_rel = 0.0f;
+    int nan_count = 0, bad_m = -1, bad_n = -1;
+    for (int m = 0; m < M; ++m) {
+      const float sa = std::exp2(static_cast<float>(m % 5 - 2));
+      for (int n = 0; n < N; ++n) {
+        const float v = bf16_bits_to_float(host[static_cast<size_t>(m) * N + n]);
+        if (std::isnan(v) || std::isinf(v)) { ++nan_count; continue; }
+        const float expected = per_product * K * sa * std::exp2(static_cast<float>((n0 + n) % 3 - 1));
+        const float rel = std::fabs(v - expected) / expected;
+        if (rel > max_rel) { max_rel = rel; bad_m = m; bad_n = n; }
+      }
+    }
+    const bool ok = nan_count == 0 && max_rel < 1e-3f;
+    std::printf("  verify M=%d,N=%d,K=%d (real scales): max_rel=%.2e nan=%d %s", M, N, K, max_rel,
+                nan_count, ok ? "OK" : "FAIL");
+    if (!ok && bad_m >= 0) std::printf(" [worst at m=%d n=%d]", bad_m, bad_n);
+    std::printf("\n");
+    if (!ok) rc = 1;
+  } else {
+    int fail = 0, nan_count = 0, bad_m = -1, bad_n = -1;
+    float max_err = 0.0f, max_ref = 0.0f, max_got = 0.0f;
+    std::vector<float> ra, rb;
+    for (int smp = 0; smp < 2048; ++smp) {
+      const int m = static_cast<int>(hash32(2u * smp + 1u) % static_cast<uint32_t>(M));
+      const int n = static_cast<int>(hash32(2u * smp + 2u) % static_cast<uint32_t>(N));
+      host_row(ra, m, K, fill, 0);
+      host_row(rb, n0 + n, K, fill, 1);
+      float acc = 0.0f;
+      for (int k = 0; k < K; ++k) acc += ra[k] * rb[k];
+      uint32_t bits;
+      std::memcpy(&bits, &acc, 4);
+      const float ref = bf16_bits_to_float(static_cast<uint16_t>((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16));
+      const float got = bf16_bits_to_float(host[static_cast<size_t>(m) * N + n]);
+      if (std::isnan(got) || std::isinf(got)) { ++nan_count; continue; }
+      const float err = std::fabs(got - ref);
+      const float floor_abs = (fill <= 4) ? 16.0f : 0.25f;
+      if (err > std::fmax(0.008f * std::fabs(ref), floor_abs)) {
+        ++fail;
+        if (err > max_err) { max_err = err; bad_m = m; bad_n = n; max_ref = ref; max_got = got; }
+      }
+    }
+    const bool ok = nan_count == 0 && fail == 0;
+    std::printf("  verify M=%d,N=%d,K=%d (FILL=%d sampled ref x2048): fail=%d nan=%d %s", M, N, K,
+                fill, fail, nan_count, ok ? "OK" : "FAIL");
+    if (!ok && bad_m >= 0)
+      std::printf(" [worst at m=%d n=%d: got %.3f ref %.3f]", bad_m, bad_n, max_got, max_ref);
+    std::printf("\n");
+    if (!ok) rc = 1;
+  }
+  return rc;
+}
+
 double run_one(int M, int n_total, int K, const Options& o) {
+  if (o.box.gpus > 0) {
+    // One process, several devices: device g holds the slab of rank g.
+    int have = 0;
+    DRV_CUDA(cudaGetDeviceCount(&have));
+    if (o.box.gpus > have) {
+      std::fprintf(stderr, "--gpus=%d but only %d device(s) are visible\n", o.box.gpus, have);
+      std::exit(1);
+    }
+    std::vector<Case> cases(o.box.gpus);
+    std::vector<BoxSlab> slabs(o.box.gpus);
+    for (int g = 0; g < o.box.gpus; ++g) {
+      int n0 = 0, n_local = 0;
+      if (smb_column_shard(n_total, o.box.gpus, g, &n0, &n_local) != SMB_OK) {
+        std::fprintf(stderr, "unsupported --gpus for this shape: %s\n", smb_last_error());
+        std::exit(1);
+      }
+      DRV_CUDA(cudaSetDevice(g));
+      cases[g] = make_case(M, K, n0, n_local, o);
+      Case* c = &cases[g];
+      BoxSlab& s = slabs[g];
+      s.device = g;
+      s.n0 = n0;
+      s.n_local = n_local;
+      s.stream = c->stream;
+      s.d = c->d;
+      s.launch = [c]() { return smb_fp4_plan_run(c->plan, c->stream); };
+      s.check = [c]() { return smb_fp4_plan_check(c->plan, c->stream); };
+      if (o.verify) s.verify = [c]() { return verify_case(*c); };
+      s.destroy = [c]() { free_case(*c); };
+    }
+    const double tflops = run_box(slabs, M, n_total, K, o.benchmark, o.box.allgather, o.dump,
+                                  "  shape (%6d, %6d, %4d): mean=%.6f ms  %7.1f NVFP4_TFLOPS\n");
+    DRV_CUDA(cudaSetDevice(0));
+    return tflops;
+  }
   Shard shard = o.shard;
   shard.resolve(n_total);
   const int N = shard.n_local;   // everything below works on this process's slab; global column = n0 + n
-  const int n0 = shard.n0;
-  uint8_t *a = nullptr, *b = nullptr, *sfa = nullptr, *sfb = nullptr;
-  uint16_t* d = nullptr;
-  const size_t sfa_bytes = smb_sf_packed_bytes(M, K / 32), sfb_bytes = smb_sf_packed_bytes(N, K / 32);
-  DRV_CUDA(cudaMalloc(&a, static_cast<size_t>(M) * K / 2));
-  DRV_CUDA(cudaMalloc(&b, static_cast<size_t>(N) * K / 2));
-  DRV_CUDA(cudaMalloc(&sfa, sfa_bytes));
-  DRV_CUDA(cudaMalloc(&sfb, sfb_bytes));
-  DRV_CUDA(cudaMalloc(&d, static_cast<size_t>(M) * N * 2));
-  DRV_CUDA(cudaMemset(d, 0, static_cast<size_t>(M) * N * 2));
-  cudaStream_t stream;
-  DRV_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
-  DRV_SMB(smb_fill_fp4_device(a, K / 2, sfa, nullptr, M, K, 0, o.fill, 0, stream));
-  DRV_SMB(smb_fill_fp4_device(b, K / 2, sfb, nullptr, N, K, static_cast<uint64_t>(n0), o.fill, 1, stream));
-  DRV_CUDA(cudaStreamSynchronize(stream));
-
-  smb_fp4_plan* plan = nullptr;
-  DRV_SMB(smb_fp4_plan_create(&plan, a, sfa, b, sfb, d, M, N, K, K / 2, K / 2, N,
-                              o.ordered ? SMB_FLAG_OPERANDS_STATIC : SMB_FLAG_LAUNCH_INDEPENDENT));
-  auto launch = [&]() { return smb_fp4_plan_run(plan, stream); };
+  Case c = make_case(M, K, shard.n0, N, o);
+  cudaStream_t stream = c.stream;
+  auto launch = [&]() { return smb_fp4_plan_run(c.plan, stream); };
   double ms = 0.0;
   if (o.benchmark) {
     ms = measure_mean_ms(stream, launch);
@@ -84,7 +209,7 @@ double run_one(int M, int n_total, int K, const Options& o) {
     DRV_SMB(launch());
   }
   DRV_SMB(launch());
-  DRV_SMB(smb_fp4_plan_check(plan, stream));
+  DRV_SMB(smb_fp4_plan_check(c.plan, stream));
   double tflops = 0.0;
   if (o.benchmark) {
     tflops = 2.0 * M * N * K / (ms * 1e-3) / 1e12;
@@ -93,72 +218,9 @@ double run_one(int M, int n_total, int K, const Options& o) {
     std::printf("  shape (%6d, %6d, %4d): untimed\n", M, N, K);
   }
   write_json(o.json, "dense_gemm_nvfp4", M, N, K, o.fill, ms, tflops, o.benchmark);
-  if (o.dump) dump_bf16(d, static_cast<size_t>(M) * N, o.dump);
-
-  int rc = 0;
-  if (o.verify) {
-    std::vector<uint16_t> host(static_cast<size_t>(M) * N);
-    DRV_CUDA(cudaMemcpy(host.data(), d, host.size() * 2, cudaMemcpyDeviceToHost));
-    if (o.fill == 1 || o.fill == 3) {
-      // D[m][n] = p K 2^((m % 5) - 2) 2^((n % 3) - 1), p = 16 (fill 1) or 1 (fill 3): exact.
-      const float per_product = (o.fill == 3) ? 1.0f : 16.0f;
-      float max_rel = 0.0f;
-      int nan_count = 0, bad_m = -1, bad_n = -1;
-      for (int m = 0; m < M; ++m) {
-        const float sa = std::exp2(static_cast<float>(m % 5 - 2));
-        for (int n = 0; n < N; ++n) {
-          const float v = bf16_bits_to_float(host[static_cast<size_t>(m) * N + n]);
-          if (std::isnan(v) || std::isinf(v)) { ++nan_count; continue; }
-          const float expected = per_product * K * sa * std::exp2(static_cast<float>((n0 + n) % 3 - 1));
-          const float rel = std::fabs(v - expected) / expected;
-          if (rel > max_rel) { max_rel = rel; bad_m = m; bad_n = n; }
-        }
-      }
-      const bool ok = nan_count == 0 && max_rel < 1e-3f;
-      std::printf("  verify M=%d,N=%d,K=%d (real scales): max_rel=%.2e nan=%d %s", M, N, K, max_rel,
-                  nan_count, ok ? "OK" : "FAIL");
-      if (!ok && bad_m >= 0) std::printf(" [worst at m=%d n=%d]", bad_m, bad_n);
-      std::printf("\n");
-      if (!ok) rc = 1;
-    } else {
-      int fail = 0, nan_count = 0, bad_m = -1, bad_n = -1;
-      float max_err = 0.0f, max_ref = 0.0f, max_got = 0.0f;
-      std::vector<float> ra, rb;
-      for (int smp = 0; smp < 2048; ++smp) {
-        const int m = static_cast<int>(hash32(2u * smp + 1u) % static_cast<uint32_t>(M));
-        const int n = static_cast<int>(hash32(2u * smp + 2u) % static_cast<uint32_t>(N));
-        host_row(ra, m, K, o.fill, 0);
-        host_row(rb, n0 + n, K, o.fill, 1);
-        float acc = 0.0f;
-        for (int k = 0; k < K; ++k) acc += ra[k] * rb[k];
-        uint32_t bits;
-        std::memcpy(&bits, &acc, 4);
-        const float ref = bf16_bits_to_float(static_cast<uint16_t>((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16));
-        const float got = bf16_bits_to_float(host[static_cast<size_t>(m) * N + n]);
-        if (std::isnan(got) || std::isinf(got)) { ++nan_count; continue; }
-        const float err = std::fabs(got - ref);
-        const float floor_abs = (o.fill <= 4) ? 16.0f : 0.25f;
-        if (err > std::fmax(0.008f * std::fabs(ref), floor_abs)) {
-          ++fail;
-          if (err > max_err) { max_err = err; bad_m = m; bad_n = n; max_ref = ref; max_got = got; }
-        }
-      }
-      const bool ok = nan_count == 0 && fail == 0;
-      std::printf("  verify M=%d,N=%d,K=%d (FILL=%d sampled ref x2048): fail=%d nan=%d %s", M, N, K,
-                  o.fill, fail, nan_count, ok ? "OK" : "FAIL");
-      if (!ok && bad_m >= 0)
-        std::printf(" [worst at m=%d n=%d: got %.3f ref %.3f]", bad_m, bad_n, max_got, max_ref);
-      std::printf("\n");
-      if (!ok) rc = 1;
-    }
-  }
-  smb_fp4_plan_destroy(plan);
-  cudaStreamDestroy(stream);
-  cudaFree(a);
-  cudaFree(b);
-  cudaFree(sfa);
-  cudaFree(sfb);
-  cudaFree(d);
+  if (o.dump) dump_bf16(c.d, static_cast<size_t>(M) * N, o.dump);
+  const int rc = o.verify ? verify_case(c) : 0;
+  free_case(c);
   if (rc != 0) std::exit(EXIT_FAILURE);
   return tflops;
 }
@@ -204,12 +266,13 @@ int main(int argc, char** argv) {
     } else if (std::strncmp(argv[i], "--dump-output=", 14) == 0 && argv[i][14]) {
       o.dump = argv[i] + 14;
     } else if (o.shard.parse(argv[i])) {
+    } else if (o.box.parse(argv[i])) {
     } else if (std::strncmp(argv[i], "--json=", 7) == 0 && argv[i][7]) {
       o.json = argv[i] + 7;
     } else if (std::strcmp(argv[i], "--help") == 0) {
       std::printf("Usage: %s [--shape=M,K,N [--fill=1..6] [--no-benchmark]\n"
                   "       [--no-gpu-verify] [--dump-output=PATH] [--json=PATH]\n"
-                  "       [--shard=RANK/WORLD] [--device=INDEX]]\n"
+                  "       [--shard=RANK/WORLD] [--device=INDEX] [--gpus=G [--allgather]]]\n"
                   "No arguments: short sweep (FILL environment variable supported).\n", argv[0]);
       return 0;
     } else {
@@ -222,6 +285,14 @@ int main(int argc, char** argv) {
       std::fprintf(stderr, "require --shape=M,K,N: positive M and N, K a multiple of 32\n");
       return 1;
     }
+  }
+  if (o.box.allgather && o.box.gpus < 1) {
+    std::fprintf(stderr, "--allgather requires --gpus=G\n");
+    return 1;
+  }
+  if (o.box.gpus > 0 && o.shard.world > 1) {
+    std::fprintf(stderr, "--gpus and --shard exclude each other\n");
+    return 1;
   }
   DRV_CUDA(cudaSetDevice(o.shard.device));
   DRV_CUDA(cudaFree(0));

@@ -423,9 +423,7 @@ int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
   p.K = L.K;
   p.tiles_m = (L.M + 255) / 256;
   p.tiles_n = (L.N + C::kTileN - 1) / C::kTileN;
-  // Default raster group: about sqrt(clusters * tile_n / tile_m) tile rows, so that one wave
-  // touches as few distinct operand rows as possible.
-  p.group_m = L.group_m > 0 ? L.group_m : (NB == 2 ? 16 : 8);
+  p.group_m = L.group_m > 0 ? L.group_m : raster_group_rows(p.tiles_m, static_cast<long long>(L.K) * 2);
   p.ldd = L.ldd;
   p.d_ptr = static_cast<uint16_t*>(L.d);
   p.status = L.status;

@@ -49,6 +49,19 @@ __host__ __device__ inline void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / rows;
 }
 
+// Default raster group height: as many 256-row tile rows of A as stay resident in L2 while the B
+// panels stream past them, taken as 32 MB of A (a quarter of the 126 MB L2: the two dies each
+// cache what their SMs read).  `row_bytes` = bytes of one row of A (K elements).  Measured on
+// BF16 8192^3 (sustained, TFLOP/s): 4 rows 1320-1346, 8 rows 1345-1370, 16 rows 1330-1351, 32 rows
+// 1239-1287; block-scaled 8192^3 with 384-wide tiles: 8 rows 5660, 16 rows 5750-5860, 32 rows
+// 5850-5960 (A is a quarter the size there).
+inline int raster_group_rows(int tiles_m, long long row_bytes) {
+  long long rows = (32ll << 20) / (256 * (row_bytes > 0 ? row_bytes : 1));
+  if (rows < 1) rows = 1;
+  if (rows > tiles_m) rows = tiles_m;
+  return static_cast<int>(rows);
+}
+
 // --------------------------------------------------------------------------- tensor maps
 // 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements, `ld_bytes` between rows,
 // copied in boxes of [box_rows, box_cols].  `swizzle128`: 128-byte shared-memory swizzle
@@ -125,8 +138,11 @@ struct Fp4Launch {
   const int* mtile_group;  // grouped GEMM (device array, one group id per 256-row tile of A), or null
   bool block16;      // NVFP4 proper: UE4M3 scales per 16 K (256-wide tiles only)
   float alpha;       // factor on every accumulator (block16 only; 1 otherwise)
+  bool uniform_tiles;  // true: full-width tiles only (no narrower tiles at the end of the tile list)
+  int l2_a, l2_b;    // L2 eviction hints of the A / B loads: 0 none, 1 evict-last, 2 evict-first
 };
 void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1);
+void fp4_split_phases(int M, int N, int K, int w0, int w1, int clusters, int* wide_tiles_n, int* narrow_tiles_n);
 int fp4_launch(const Fp4Launch& L, cudaStream_t stream);
 
 // --------------------------------------------------------------------------- nvfp4 decode launch

@@ -92,6 +92,12 @@ struct Cfg {
 struct Params {
   int M, N, K;
   int tiles_m, tiles_n;
+  // Tiles are handed out in two phases: first `tiles_n` full-width tiles per tile row over the
+  // columns [0, tiles_n * kTileN), then `narrow_tiles_n` tiles of the first sub-block's width (W0)
+  // over [narrow_col0, N).  With equal tiles the last wave leaves clusters idle (8192^3 with
+  // 256 x 384 tiles: 10 tile times per cluster where 9.5 would be balanced); a few narrower tiles
+  // at the end of the list even the clusters out.  narrow_tiles_n = 0: one phase, as before.
+  int narrow_tiles_n, narrow_col0;
   int group_m;
   int ldd;
   uint16_t* d_ptr;
@@ -104,10 +110,28 @@ struct Params {
   const int* mtile_group;  // grouped GEMM: group of every 256-row tile of A (device), or null
   float alpha;          // factor on every accumulator (block-16 variant: 1 / (global scale A x B))
   int operands_static;  // 1: operands and scales are not written by the previous kernel on the stream
+  int l2_a, l2_b;       // L2 eviction hint of the A / B loads: 0 none, 1 evict-last, 2 evict-first
 };
 
 enum { kProfLoadWait = 0, kProfLoadTotal, kProfMmaWaitFull, kProfMmaWaitAcc, kProfMmaTotal,
        kProfEpiWait, kProfEpiTotal, kProfTiles, kProfCount };
+
+// Tile index -> tile row, first column, and whether the tile has its second sub-block.
+template <int kTileN, int W0>
+__host__ __device__ inline void fp4_tile(int t, int tiles_m, int tiles_n, int narrow_tiles_n, int narrow_col0,
+                                         int group_m, int& tm, int& col0, bool& full_width) {
+  const int wide_tiles = tiles_m * tiles_n;
+  int tn;
+  if (t < wide_tiles) {
+    tile_coords(t, tiles_m, tiles_n, group_m, tm, tn);
+    col0 = tn * kTileN;
+    full_width = true;
+  } else {
+    tile_coords(t - wide_tiles, tiles_m, narrow_tiles_n, group_m, tm, tn);
+    col0 = narrow_col0 + tn * W0;
+    full_width = false;
+  }
+}
 
 template <int W0, int W1, int kStore, bool V4 = false, int R = 1>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, R)
@@ -147,7 +171,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t rank = cluster_ctarank();
   const int cluster = static_cast<int>(cluster_id_x());
   const int n_clusters = static_cast<int>(num_clusters_x());
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = p.tiles_m * (p.tiles_n + p.narrow_tiles_n);
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
 
   // Programmatic dependent launch: the next kernel on the stream may begin its prologue while
@@ -203,6 +227,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const long long t_begin = prof ? clock64() : 0;
       TileCursor cursor;
       cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
+      const uint64_t pol_a = p.l2_a == 2 ? l2_policy_evict_first() : l2_policy_evict_last();
+      const uint64_t pol_b = p.l2_b == 2 ? l2_policy_evict_first() : l2_policy_evict_last();
       // Everything before this point overlapped the tail of the previous kernel on the stream;
       // its results (possibly this kernel's operands, certainly the old contents of D) are
       // complete and visible once this returns.  Unless the caller vouches that the operands are
@@ -210,17 +236,19 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // epilogue waits (before it overwrites D) and loads and MMAs overlap the previous tail.
       if (!p.operands_static) griddep_wait();
       for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true)) {
-        int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+        int tm, col0;
+        bool full_width;
+        fp4_tile<C::kTileN, W0>(t, p.tiles_m, p.tiles_n, p.narrow_tiles_n, p.narrow_col0, p.group_m, tm, col0,
+                                full_width);
         tm = (tm + p.m_rotate) % p.tiles_m;   // routed stores: ranks start at different row blocks
         const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
-        const int col0 = tn * C::kTileN;
         const int band_a = tm * 2 + static_cast<int>(rank);     // 128-row band of SFA
         // Grouped GEMM: B and its scales are stacked [groups * N, ...] (N % 128 == 0); this tile of
         // A belongs to one group and meets that group's N rows.
         const int group_row = p.mtile_group != nullptr ? __ldg(p.mtile_group + tm) * p.N : 0;
         const int band_b = (group_row + col0) / 128;            // first 128-row band of SFB
-        const bool has_sub1 = (C::kSubs == 2) && (col0 + W0 < p.N);   // else: right edge of D
+        // No second sub-block in a narrow tile, nor where it would lie beyond the right edge of D.
+        const bool has_sub1 = (C::kSubs == 2) && full_width && (col0 + W0 < p.N);
         for (int kb = 0; kb < num_kb; ++kb) {
           const long long w0 = prof ? clock64() : 0;
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
@@ -245,12 +273,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // words (two 512-byte cells) of each band.
           tma_load_2d_pair(dst + C::kOffSfa, &tmap_sfa, sf_bar, kb * (kCells * 64), band_a);
           tma_load_2d_pair(dst + C::kOffSfb, &tmap_sfb, sf_bar, kb * (kCells * 64), band_b);
-          tma_load_2d_pair(dst, &tmap_a, bar, kb * kBlockKBytes, row_a);
-          tma_load_2d_pair(dst + C::kOffB0, &tmap_b0, bar, kb * kBlockKBytes,
-                           group_row + col0 + static_cast<int>(rank) * (W0 / 2));
+          if (p.l2_a != 0) tma_load_2d_pair_hint(dst, &tmap_a, bar, kb * kBlockKBytes, row_a, pol_a);
+          else tma_load_2d_pair(dst, &tmap_a, bar, kb * kBlockKBytes, row_a);
+          const int row_b0 = group_row + col0 + static_cast<int>(rank) * (W0 / 2);
+          if (p.l2_b != 0) tma_load_2d_pair_hint(dst + C::kOffB0, &tmap_b0, bar, kb * kBlockKBytes, row_b0, pol_b);
+          else tma_load_2d_pair(dst + C::kOffB0, &tmap_b0, bar, kb * kBlockKBytes, row_b0);
           if (C::kSubs == 2 && has_sub1) {
-            tma_load_2d_pair(dst + C::kOffB1, &tmap_b1, bar, kb * kBlockKBytes,
-                             group_row + col0 + W0 + static_cast<int>(rank) * (W1 / 2));
+            const int row_b1 = group_row + col0 + W0 + static_cast<int>(rank) * (W1 / 2);
+            if (p.l2_b != 0) tma_load_2d_pair_hint(dst + C::kOffB1, &tmap_b1, bar, kb * kBlockKBytes, row_b1, pol_b);
+            else tma_load_2d_pair(dst + C::kOffB1, &tmap_b1, bar, kb * kBlockKBytes, row_b1);
           }
           if (p.prefetch > 0 && kb + p.prefetch < num_kb) {
             const int kp = (kb + p.prefetch) * kBlockKBytes;
@@ -285,10 +316,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       TileCursor cursor;
       cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
       for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true), ++local) {
-        int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
-        tm = (tm + p.m_rotate) % p.tiles_m;   // routed stores: ranks start at different row blocks
-        const bool has_sub1 = (C::kSubs == 2) && (tn * C::kTileN + W0 < p.N);
+        int tm, col0;
+        bool full_width;
+        fp4_tile<C::kTileN, W0>(t, p.tiles_m, p.tiles_n, p.narrow_tiles_n, p.narrow_col0, p.group_m, tm, col0,
+                                full_width);
+        const bool has_sub1 = (C::kSubs == 2) && full_width && (col0 + W0 < p.N);
         const int bank = C::kTwoBanks ? (local & 1) : 0;
         const uint32_t use_parity =
             static_cast<uint32_t>(C::kTwoBanks ? (local >> 1) : local) & 1u;
@@ -427,7 +459,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     out.d_ptr = p.d_ptr;
     out.ldd = p.ldd;
     out.M = p.M;
-    out.N = kSwiglu ? p.N / 2 : p.N;
+    const int n_out = kSwiglu ? p.N / 2 : p.N;
+    out.N = n_out;
     out.peers = &p.peers;
     out.alpha = p.alpha;
     int local = 0;
@@ -439,9 +472,17 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     TileCursor cursor;
     cursor.init(p.dynamic != 0, n_clusters, num_tiles, sched);
     for (int t = cluster; t >= 0 && ok; t = cursor.next(t, lane == 0, true), ++local) {
-      int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
-        tm = (tm + p.m_rotate) % p.tiles_m;   // routed stores: ranks start at different row blocks
+      int tm, tile_col0;
+      bool full_width;
+      fp4_tile<C::kTileN, W0>(t, p.tiles_m, p.tiles_n, p.narrow_tiles_n, p.narrow_col0, p.group_m, tm, tile_col0,
+                              full_width);
+      tm = (tm + p.m_rotate) % p.tiles_m;   // routed stores: ranks start at different row blocks
+      // A narrow tile has no second sub-block: its accumulator columns beyond W0 hold nothing and
+      // the columns of D there belong to the next tile.
+      if (C::kSubs == 2) {
+        const int limit = tile_col0 + (full_width ? C::kTileN : W0);
+        out.N = limit < n_out ? limit : n_out;
+      }
       const int bank = C::kTwoBanks ? (local & 1) : 0;
       const uint32_t use_parity = static_cast<uint32_t>(C::kTwoBanks ? (local >> 1) : local) & 1u;
       const long long w0 = prof ? clock64() : 0;
@@ -454,7 +495,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_after_sync();
       const int row0 = tm * 256 + static_cast<int>(rank) * kBlockM + quarter * 32;
       const int tile_col = group * C::kColsPerWarp;
-      const int col0 = tn * C::kTileN + tile_col;
+      const int col0 = tile_col0 + tile_col;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(bank * 128 + tile_col);
       drain_and_store<C::kColsPerWarp, kTmaStore, kSwiglu, V4>(taddr, sbuf, out, row0, col0,
@@ -520,7 +561,15 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   p.K = L.K;
   p.tiles_m = (L.M + 255) / 256;
   p.tiles_n = (L.N + C::kTileN - 1) / C::kTileN;
-  p.group_m = L.group_m > 0 ? L.group_m : (C::kTileN >= 384 ? 12 : 8);
+  p.narrow_tiles_n = 0;
+  p.narrow_col0 = 0;
+  if (C::kSubs == 2 && !L.uniform_tiles) {
+    int clusters_now = max_clusters;
+    if (L.max_clusters > 0 && clusters_now > L.max_clusters) clusters_now = L.max_clusters;
+    fp4_split_phases(L.M, L.N, L.K, W0, W1, clusters_now, &p.tiles_n, &p.narrow_tiles_n);
+    p.narrow_col0 = p.tiles_n * C::kTileN;
+  }
+  p.group_m = L.group_m > 0 ? L.group_m : raster_group_rows(p.tiles_m, static_cast<long long>(L.K) / 2);
   p.ldd = L.ldd;
   p.d_ptr = static_cast<uint16_t*>(L.d);
   p.status = L.status;
@@ -531,7 +580,9 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   p.mtile_group = L.mtile_group;
   p.alpha = L.alpha;
   p.prefetch = L.prefetch;
-  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  p.l2_a = L.l2_a;
+  p.l2_b = L.l2_b;
+  const long long tiles = static_cast<long long>(p.tiles_m) * (p.tiles_n + p.narrow_tiles_n);
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (L.max_clusters > 0 && clusters > L.max_clusters) clusters = L.max_clusters;
   p.dynamic = (L.dynamic && tiles > clusters && L.max_clusters == 0) ? 1 : 0;
@@ -587,6 +638,66 @@ int launch_fp4_store(const Fp4Launch& L, cudaStream_t stream) {
 
 }  // namespace
 
+// How many full-width (w0 + w1) tiles per tile row, and how many w0-wide tiles after them, make
+// the round-robin walk of `clusters` clusters over the tile list end soonest.  Cost of a tile in
+// tensor-pipe cycles: 2 cycles per column and 256-wide K block, plus ~2000 cycles of exposed
+// accumulator drain.  Tile t goes to cluster t % clusters; the walk ends when the busiest cluster does.
+namespace {
+thread_local double g_last_phase_cost = 0.0;   // written by fp4_split_phases for fp4_pick_tile (same thread, same call)
+}
+
+void fp4_split_phases(int M, int N, int K, int w0, int w1, int clusters, int* wide_tiles_n, int* narrow_tiles_n) {
+  const int tile_n = w0 + w1;
+  const int tiles_m = (M + 255) / 256;
+  const int max_wide = (N + tile_n - 1) / tile_n;
+  *wide_tiles_n = max_wide;
+  *narrow_tiles_n = 0;
+  if (w1 == 0 || clusters < 1) return;
+  const double kb = (K + 255) / 256;
+  const double cost_wide = kb * 2.0 * tile_n + 2000.0, cost_narrow = kb * 2.0 * w0 + 2000.0;
+  double best = -1.0;
+  // Only the last few wide tiles of a row are worth trading: beyond that the narrow tiles'
+  // extra drains and operand traffic outweigh any balance gained.
+  const int lowest = max_wide - 8 > 0 ? max_wide - 8 : 0;
+  for (int a = max_wide; a >= lowest; --a) {
+    const long long rest = static_cast<long long>(N) - static_cast<long long>(a) * tile_n;
+    const int b = rest > 0 ? static_cast<int>((rest + w0 - 1) / w0) : 0;
+    const long long wide = static_cast<long long>(tiles_m) * a, narrow = static_cast<long long>(tiles_m) * b;
+    // Cluster c gets the tiles t = c, c + clusters, ...: the busiest one is either cluster 0 or the
+    // one that takes the first narrow tile.
+    double worst = 0.0;
+    const long long probes[3] = {0, wide % clusters, (wide + narrow - 1) % clusters};
+    for (long long c : probes) {
+      const long long nw = wide > c ? (wide - c + clusters - 1) / clusters : 0;
+      const long long total = wide + narrow > c ? (wide + narrow - c + clusters - 1) / clusters : 0;
+      const double cost = nw * cost_wide + (total - nw) * cost_narrow;
+      if (cost > worst) worst = cost;
+    }
+    if (best < 0.0 || worst < best * 0.995) {   // a change of plan must buy at least half a percent
+      best = worst;
+      *wide_tiles_n = a;
+      *narrow_tiles_n = b;
+    }
+  }
+  g_last_phase_cost = best;
+}
+
+}  // namespace smb
+
+// Host-side views of the tile list, for known-answer tests (no device needed).
+extern "C" void smb_debug_fp4_phases(int M, int N, int K, int clusters, int* wide_tiles_n, int* narrow_tiles_n) {
+  smb::fp4_split_phases(M, N, K, 256, 128, clusters, wide_tiles_n, narrow_tiles_n);
+}
+extern "C" void smb_debug_fp4_tile(int t, int tiles_m, int wide_tiles_n, int narrow_tiles_n, int group_m, int* tm,
+                                   int* col0, int* full_width) {
+  bool full = false;
+  smb::fp4k::fp4_tile<384, 256>(t, tiles_m, wide_tiles_n, narrow_tiles_n, wide_tiles_n * 384, group_m, *tm, *col0,
+                                full);
+  *full_width = full ? 1 : 0;
+}
+
+namespace smb {
+
 void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1) {
   *w1 = 0;
   if (N <= 128) {
@@ -604,7 +715,11 @@ void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1) {
   const long long waves256 = (tiles_m * ((N + 255) / 256) + clusters - 1) / clusters;
   const long long waves384 = (tiles_m * ((N + 383) / 384) + clusters - 1) / clusters;
   const double cost256 = static_cast<double>(waves256) * (kb * 512.0 + 2000.0) / 0.985;
-  const double cost384 = static_cast<double>(waves384) * (kb * 768.0 + 2000.0);
+  double cost384 = static_cast<double>(waves384) * (kb * 768.0 + 2000.0);
+  // The 384-wide kernel ends its tile list with 256-wide tiles where that evens the clusters out.
+  int wide = 0, narrow = 0;
+  fp4_split_phases(M, N, K, 256, 128, clusters, &wide, &narrow);
+  if (g_last_phase_cost > 0.0 && g_last_phase_cost < cost384) cost384 = g_last_phase_cost;
   if (cost384 <= cost256) *w1 = 128;
 }
 

@@ -1,6 +1,7 @@
 // Error plumbing and tensor-map encoding shared by every entry point.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "gemm_common.cuh"
@@ -146,10 +147,17 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype
   const cuuint64_t strides[1] = {ld_bytes};
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t estr[2] = {1, 1};
+  CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+  if (const char* env = getenv("SMB_TUNE_L2_PROMO")) {   // tuning sweeps: 0, 64, 128 or 256 bytes
+    const int v = atoi(env);
+    promo = v == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                   : (v == 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                              : (v == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+  }
   CUresult r = fn(out, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, promo,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return set_error(SMB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
   return SMB_OK;

@@ -241,3 +241,36 @@ def test_new_entry_points_validate_their_arguments(smb):
     assert lib.smb_decode_noalloc_set_split(4097) == capi.SMB_ERR_INVALID
     assert lib.smb_decode_noalloc_set_split(0) == capi.SMB_OK
     assert lib.smb_decode_noalloc_scratch_limit() == (2 << 20) - 256
+
+
+@pytest.mark.parametrize("shape", [(8192, 8192, 8192), (14080, 5120, 2048), (30720, 2048, 4096), (300, 1000, 256),
+                                   (256, 384, 256), (8192, 1024, 8192), (512, 130, 512)])
+def test_fp4_tile_list_covers_every_column_once(smb, shape):
+    """The FP4 kernel with 256 x 384 tiles hands out full tiles first and 256-wide tiles after them;
+    together they must cover every 128-column unit of every tile row exactly once, whatever the
+    split, and the split must never be worse than uniform tiles under its own cost model."""
+    lib = smb.capi.lib()
+    m, n, k = shape
+    tiles_m = (m + 255) // 256
+    units = (n + 127) // 128
+    for clusters in (74, 66, 1):
+        wide, narrow = C.c_int(), C.c_int()
+        lib.smb_debug_fp4_phases(m, n, k, clusters, C.byref(wide), C.byref(narrow))
+        a, b = wide.value, narrow.value
+        assert a >= 0 and b >= 0 and a * 384 + b * 256 >= n
+        assert a * 384 < n + 384 and (b == 0 or a * 384 + (b - 1) * 256 < n)
+        seen = np.zeros((tiles_m, units), dtype=np.int32)
+        tm, col0, full = C.c_int(), C.c_int(), C.c_int()
+        for t in range(tiles_m * (a + b)):
+            lib.smb_debug_fp4_tile(t, tiles_m, a, b, 12, C.byref(tm), C.byref(col0), C.byref(full))
+            assert 0 <= tm.value < tiles_m and col0.value % 128 == 0 and col0.value < n
+            assert full.value == (1 if t < tiles_m * a else 0)
+            width = 384 if full.value else 256
+            u0 = col0.value // 128
+            seen[tm.value, u0:min(units, u0 + width // 128)] += 1
+        assert (seen == 1).all(), (a, b)
+    # 8192^3 on 74 clusters: 18 full tiles and 5 narrow ones per tile row end sooner than 22 full
+    # tiles (10 tile times per cluster against 8 wide + 2 narrow).
+    wide, narrow = C.c_int(), C.c_int()
+    lib.smb_debug_fp4_phases(8192, 8192, 8192, 74, C.byref(wide), C.byref(narrow))
+    assert (wide.value, narrow.value) == (18, 5)

@@ -137,3 +137,39 @@ def test_sharded_driver_slabs_make_up_the_unsharded_output(cuda_device, tmp_path
     assert np.array_equal(np.concatenate(slabs, axis=1), want)
     r = _run(exe, f"--shape={m},{k},{n}", "--shard=0/5")
     assert r.returncode == 1 and "unsupported --shard" in r.stderr
+
+
+def test_drivers_reject_bad_box_options():
+    r = _run(BF16, "--allgather", "--shape=256,64,128")
+    assert r.returncode == 1 and "--allgather requires --gpus" in r.stderr
+    r = _run(FP4, "--gpus=0", "--shape=256,256,128")
+    assert r.returncode == 1 and "--gpus must be" in r.stderr
+    r = _run(BF16, "--gpus=2", "--shard=0/2", "--shape=256,64,128")
+    assert r.returncode == 1 and "exclude each other" in r.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("which", ["bf16", "fp4"])
+@pytest.mark.parametrize("gpus", [1, 2])
+def test_box_mode_gathers_the_unsharded_output(cuda_device, tmp_path, which, gpus):
+    """--gpus=G --allgather: one process drives G devices, every device computes its column slab,
+    the slabs are exchanged with the library's NCCL all-gather and unshard copy, and the dump of
+    the gathered D is the single-GPU dump bit for bit.  Without --allgather the dump is assembled
+    from the slabs on the host and must be the same file."""
+    import torch
+    if torch.cuda.device_count() < gpus:
+        pytest.skip(f"needs {gpus} GPUs")
+    exe = BF16 if which == "bf16" else FP4
+    m, k, n = 512, 256, 768
+    whole = tmp_path / "whole.bf16"
+    r = _run(exe, f"--shape={m},{k},{n}", "--fill=2", "--no-benchmark", f"--dump-output={whole}")
+    assert r.returncode == 0, r.stderr + r.stdout
+    want = np.fromfile(whole, dtype="<u2")
+    for extra in (["--allgather"], []):
+        out = tmp_path / f"box{len(extra)}.bf16"
+        r = _run(exe, f"--shape={m},{k},{n}", "--fill=2", f"--gpus={gpus}", *extra, f"--dump-output={out}")
+        assert r.returncode == 0, r.stderr + r.stdout
+        assert f"box of {gpus} GPUs" in r.stdout and "OK" in r.stdout
+        if extra:
+            assert f"all-gather of D over {gpus} GPUs" in r.stdout
+        assert np.array_equal(np.fromfile(out, dtype="<u2"), want)

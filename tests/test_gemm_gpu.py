@@ -976,3 +976,41 @@ def test_fp4_host_context(smb, cuda_device, shape):
     np.testing.assert_array_equal(out2, _bits(d))
     ctx.close()
     _check_fp4_full(A, B, d, k)
+
+
+# ------------------------------------------------------------------------------- mixed tile widths
+@pytest.mark.parametrize("shape", [(1024, 1920, 512), (2048, 2432, 256), (512, 1000, 288), (8192, 8192, 256)])
+@pytest.mark.parametrize("clusters", [0, 7, 3])
+def test_fp4_full_and_narrow_tiles_in_one_launch(smb, cuda_device, shape, clusters):
+    """The 256 x 384 kernel ends its tile list with 256-wide tiles where that evens the clusters
+    out; which tiles are narrow depends on the shape and on the number of clusters.  Whatever the
+    split: full fp64 check, exact constant fill (every element written exactly once, no narrow
+    tile spills into its neighbour's columns), padding columns of D untouched."""
+    torch = _torch()
+    lib = smb.capi.lib()
+    m, n, k = shape
+    import ctypes as C
+    wide, narrow = C.c_int(), C.c_int()
+    lib.smb_debug_fp4_phases(m, n, k, clusters or 74, C.byref(wide), C.byref(narrow))
+    ldd = n + 24
+    for fill in (5, 3):
+        a, sfa, sfar = _fp4_operand(smb, m, k, fill, 0)
+        b, sfb, sfbr = _fp4_operand(smb, n, k, fill, 1)
+        d = torch.full((m, ldd), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+        plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k, ldd=ldd,
+                                flags=smb.capi.FLAG_TILE_N_384 | smb.capi.FLAG_NO_DECODE)
+        plan.tune(0, clusters, -1)
+        assert plan.describe().startswith("fp4 tile 256x384")
+        plan.run()
+        plan.check()
+        plan.close()
+        assert bool(torch.isnan(d[:, n:].float()).all()), "padding columns were written"
+        if fill == 5:
+            _check_fp4_full((a, sfar), (b, sfbr), d[:, :n].contiguous(), k)
+        else:
+            mm = torch.arange(m, device=d.device).view(-1, 1)
+            nn = torch.arange(n, device=d.device).view(1, -1)
+            exact = (k * torch.exp2((mm % 5) - 2.0) * torch.exp2((nn % 3) - 1.0)).to(torch.bfloat16)
+            assert torch.equal(d[:, :n], exact)
+    if shape == (8192, 8192, 256) and clusters == 0:
+        assert narrow.value > 0       # this shape does get narrow tiles on a full GPU
