@@ -36,6 +36,8 @@ FLAG_DECODE_SINGLE = 2048
 FLAG_LAUNCH_INDEPENDENT = 4096
 FLAG_EPILOGUE_SWIGLU = 8192
 FLAG_SCALE_BLOCK16 = 16384
+FLAG_ACT_QUANT_PER_CTA = 32768
+FLAG_ACT_QUANT_CHAINED = 65536
 
 _vp = C.c_void_p
 _i = C.c_int

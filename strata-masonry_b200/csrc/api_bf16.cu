@@ -37,6 +37,7 @@ const char* device_status_name(int code) {
     case 105: return "a role timed out waiting for the tile scheduler";
     case 106: return "split-K fix-up timed out";
     case 107: return "bounded-wait probe ran out of budget";
+    case 108: return "decode kernel timed out waiting for the activation quantiser of its grid";
     default: return "unknown device status";
   }
 }

@@ -31,6 +31,7 @@ struct smb_fp4_plan {
   int64_t act_ld;
   void* act_codes;
   void* act_sf;
+  void* act_counter;   // 8 bytes: CTAs counted in by the in-kernel quantiser
 };
 
 namespace {
@@ -123,7 +124,7 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
   p->scratch_bytes = 0;
   p->act_src = nullptr;
   p->act_ld = 0;
-  p->act_codes = p->act_sf = nullptr;
+  p->act_codes = p->act_sf = p->act_counter = nullptr;
 
   // Packed scales: chunks of 4 scale bytes per row, i.e. K = 128 (one scale per 32) or K = 64
   // (one per 16); a stage (K = 256) reads 2 or 4 chunks of 64 words.
@@ -181,6 +182,9 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
     D.narrow = (flags & SMB_FLAG_DECODE_DUAL) != 0;
     D.act_src = nullptr;
     D.act_ld = 0;
+    D.act_mode = 0;
+    D.act_codes = D.act_sf = nullptr;
+    D.act_counter = nullptr;
     if (flags & SMB_FLAG_DECODE_SINGLE) D.dual = false;
     const int m_pad = (M + 15) / 16 * 16;
     rc = encode_tmap_2d(&D.tmap_w, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, ldb_bytes, 128, 128, true);
@@ -305,10 +309,12 @@ extern "C" int smb_fp4_plan_create_bf16_activations(smb_fp4_plan** out, const vo
     return set_error(SMB_ERR_INVALID, "fp4 plan: bad activation shape (K must be a multiple of 32)");
   if (ldx < K || ldx % 8 != 0 || reinterpret_cast<uintptr_t>(x_bf16) % 16 != 0)
     return set_error(SMB_ERR_INVALID, "fp4 plan: activation rows must be 16-byte aligned, pitch >= K");
-  void *codes = nullptr, *sf = nullptr;
+  void *codes = nullptr, *sf = nullptr, *counter = nullptr;
   const size_t sf_bytes = smb_sf_packed_bytes(M, K / 32);
   cudaError_t e = cudaMalloc(&codes, static_cast<size_t>(M) * K / 2);
   if (e == cudaSuccess) e = cudaMalloc(&sf, sf_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&counter, 8);
+  if (e == cudaSuccess) e = cudaMemset(counter, 0, 8);
   // Rows of the last 128-row band that no activation row fills keep the neutral scale byte.
   if (e == cudaSuccess) e = cudaMemset(sf, 127, sf_bytes);
   int rc = e == cudaSuccess ? SMB_OK : set_cuda_error(e, "fp4 plan: activation buffers");
@@ -320,15 +326,21 @@ extern "C" int smb_fp4_plan_create_bf16_activations(smb_fp4_plan** out, const vo
   if (rc != SMB_OK) {
     if (codes) cudaFree(codes);
     if (sf) cudaFree(sf);
+    if (counter) cudaFree(counter);
     return rc;
   }
   p->act_src = x_bf16;
   p->act_ld = ldx;
   p->act_codes = codes;
   p->act_sf = sf;
+  p->act_counter = counter;
   p->dlaunch.activations_dynamic = true;
   p->dlaunch.act_src = x_bf16;
   p->dlaunch.act_ld = ldx;
+  p->dlaunch.act_codes = codes;
+  p->dlaunch.act_sf = sf;
+  p->dlaunch.act_counter = static_cast<unsigned long long*>(counter);
+  p->dlaunch.act_mode = (flags & SMB_FLAG_ACT_QUANT_PER_CTA) ? 1 : ((flags & SMB_FLAG_ACT_QUANT_CHAINED) ? 2 : 0);
   *out = p;
   return SMB_OK;
 }
@@ -340,7 +352,8 @@ extern "C" int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream) {
     return set_error(SMB_ERR_INVALID, "fp4 plan: created on device %d, run with device %d current",
                      plan->device, device);
   // Where the decode kernel quantises the BF16 activations itself there is nothing to launch first.
-  if (plan->act_src != nullptr && !(plan->decode && fp4_decode_fuses_activations(plan->dlaunch))) {
+  if (plan->act_src != nullptr &&
+      !(plan->decode && (fp4_decode_fuses_activations(plan->dlaunch) || fp4_decode_spreads_activations(plan->dlaunch)))) {
     const bool chained = !(plan->decode && plan->dlaunch.no_overlap);
     int rc = quantize_bf16_launch(plan->act_src, plan->act_ld, plan->act_codes, plan->launch.K / 2,
                                   plan->act_sf, nullptr, plan->launch.M, plan->launch.K, chained,
@@ -362,6 +375,7 @@ extern "C" int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream) {
     cudaMemset(plan->status_dev, 0, sizeof(int));
     // A decode launch that gave up may have left partial sums behind.
     if (plan->scratch_dev) cudaMemset(plan->scratch_dev, 0, plan->scratch_bytes);
+    if (plan->act_counter) cudaMemset(plan->act_counter, 0, 8);
     return set_error(SMB_ERR_DEVICE, "nvfp4 GEMM kernel reported status %d: %s", status,
                      device_status_name(status));
   }
@@ -395,6 +409,7 @@ extern "C" int smb_fp4_plan_destroy(smb_fp4_plan* plan) {
   if (plan->scratch_dev) cudaFree(plan->scratch_dev);
   if (plan->act_codes) cudaFree(plan->act_codes);
   if (plan->act_sf) cudaFree(plan->act_sf);
+  if (plan->act_counter) cudaFree(plan->act_counter);
   delete plan;
   return SMB_OK;
 }

@@ -165,13 +165,21 @@ struct Fp4DecodeLaunch {
   bool dual;         // two weight tiles per activation box (whole tile pairs; ignored with max_ctas > 0)
   const void* act_src;  // BF16 activations [M, K] behind X (plans created from BF16 activations), or null
   long long act_ld;     // elements between their rows
+  // How such a plan quantises: 0 = once per launch, shared by the CTAs of the decode kernel
+  // (needs act_codes / act_sf / act_counter); 1 = inside every CTA for up to 16 rows, else a
+  // kernel chained in front; 2 = always the kernel chained in front.
+  int act_mode;
+  void* act_codes;      // [M, K/2] codes and packed scales the kernel's tensor maps of X read
+  void* act_sf;
+  unsigned long long* act_counter;   // device, zero at plan creation
   bool narrow;       // true: never the wide form (activations as the instruction's rows) of the dual kernel
   bool block16;      // E4M3 scales per 16 K (dual form only); tmap_sfw / tmap_sfx boxes are 256 words
   float alpha;       // factor on every accumulator (block16 only)
 };
 int fp4_decode_stage_bytes(int m_pad);
 bool fp4_decode_prefers_dual(int M);   // default choice of Fp4DecodeLaunch::dual for M activation rows
-bool fp4_decode_fuses_activations(const Fp4DecodeLaunch& L);   // the launch quantises L.act_src itself
+bool fp4_decode_fuses_activations(const Fp4DecodeLaunch& L);   // the launch quantises L.act_src itself, per CTA
+bool fp4_decode_spreads_activations(const Fp4DecodeLaunch& L); // ... itself, once per launch across the grid
 size_t fp4_decode_slot_bytes(int M);                       // one fp32 partial tile
 size_t fp4_decode_scratch_bytes(int M, int N, int ctas);   // slots for `ctas` CTAs + tile counters
 int fp4_decode_box_rows(int M);

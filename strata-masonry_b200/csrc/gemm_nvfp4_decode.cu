@@ -606,10 +606,39 @@ struct DualParams {
   int d_tma;
   int activations_dynamic;
   float alpha;          // factor on every accumulator (block-16 scales: 1 / (global scale X x W))
-  const uint16_t* x_src;   // kFused: BF16 activations [M, K], quantised by the kernel itself
+  const uint16_t* x_src;   // kFused / act_spread: BF16 activations [M, K], quantised by the kernel itself
   long long ldx;           // elements between their rows
+  // act_spread: the CTAs of the grid share the quantisation of x_src into act_codes / act_sf
+  // (the buffers tmap_x / tmap_sfx read) and meet on act_counter before any of them loads
+  // activations; see the comment at the top of decode_dual_body.
+  int act_spread;
+  uint8_t* act_codes;                 // [M, K/2] E2M1 codes
+  uint8_t* act_sf;                    // packed UE8M0 scales of X
+  unsigned long long* act_counter;    // arrivals of all launches so far (never reset)
 };
 
+
+// act_spread: thread `t` of `threads` in this CTA converts its share of the M * K / 32 blocks
+// of the BF16 activations; the grid's threads walk the blocks with a grid-wide stride, so that
+// consecutive threads read consecutive 64-byte blocks of a row and write consecutive 16-byte
+// code groups.
+__device__ __forceinline__ void spread_quantize(const DualParams& p, int t, int threads) {
+  const long long kblocks = p.K / 32;
+  const long long total = static_cast<long long>(p.M) * kblocks;
+  const long long stride = static_cast<long long>(gridDim.x) * threads;
+  for (long long i = static_cast<long long>(blockIdx.x) * threads + t; i < total; i += stride) {
+    const long long r = i / kblocks;
+    const long long j = i - r * kblocks;
+    const uint4* src = reinterpret_cast<const uint4*>(p.x_src + r * p.ldx + j * 32);
+    uint4 raw[4] = {__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3)};
+    uint4 codes;
+    uint32_t sb;
+    quantize_mx_block_bf16(raw, &codes, &sb);
+    *reinterpret_cast<uint4*>(p.act_codes + r * (p.K / 2) + j * 16) = codes;
+    p.act_sf[fmt::sf_packed_offset(static_cast<uint32_t>(r), static_cast<uint32_t>(j),
+                                   static_cast<uint32_t>(kblocks))] = static_cast<uint8_t>(sb);
+  }
+}
 
 // V4: one E4M3 scale per 16 K (scale_vec::4X): four 4-byte scale cells per band and stage
 // instead of two, 2 KiB of scales per band, 48 instead of 24 tensor-memory columns per slot.
@@ -632,6 +661,20 @@ struct DualParams {
 // layout a TMA load would have produced and the scale bytes in the packed cell layout, then
 // arrives on the stage's barriers beside the TMA producer.  Saves the separate quantiser launch
 // of a decode step (M = 16, N = 28672, K = 8192: 21.9 us per step against 23.2 us chained).
+//
+// act_spread (any form with UE8M0 scales, run-time switch): the activations arrive as BF16 and
+// the grid quantises them ONCE, every CTA a 1 / gridDim share, instead of once per CTA (kFused) or
+// in a kernel of its own chained in front: the eight epilogue warps, idle until the first
+// accumulator is complete, wait for the previous kernel on the stream (which may have written
+// x_src, and whose CTAs may still be reading the code buffer), convert their share of the
+// 32-value blocks into the plan's code and scale buffers, fence, and count the CTA in on a global
+// counter.  The TMA producer, which has meanwhile filled the ring with weights, waits until all
+// CTAs of this launch are counted in (bounded), orders the async proxy behind that, and loads the
+// activation boxes like any others.  The counter only grows: a CTA that arrives as number `old`
+// waits for (old / gridDim + 1) * gridDim, which every CTA of one launch computes alike because
+// the arrivals of consecutive launches never mix (each waits for its predecessor's completion).
+// All CTAs of the grid are resident at once (one per SM, grid <= SM count), so nobody waits for
+// a CTA that cannot start.
 template <bool V4, bool kWide, bool kFused>
 __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x,
                                                  const CUtensorMap& tmap_sfw, const CUtensorMap& tmap_sfx,
@@ -655,6 +698,8 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (4 * kMaxStages + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (4 * kMaxStages + 2 + b); };
   const uint32_t tmem_slot = bar_base + 8u * (4 * kMaxStages + 4);
+  const uint32_t quant_bar = bar_base + 8u * (4 * kMaxStages + 6);      // act_spread: this CTA's share is done
+  const uint32_t quant_target = bar_base + 8u * (4 * kMaxStages + 7);   // counter value to wait for (u64)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -688,6 +733,7 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
       mbar_init(acc_full_bar(b), 1);
       mbar_init(acc_empty_bar(b), 4 * epi_groups);   // one arrival per working epilogue warp
     }
+    mbar_init(quant_bar, 1);
     fence_mbar_init_cluster();
   }
   if (warp == 0 && lane == 0) {
@@ -716,12 +762,40 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
     uint32_t ph = 0;
     bool waited = kFused || !p.activations_dynamic;
     int issued = 0;
-    for (int q = q_begin; q < q_end; ++q) {
+    // Until the activations exist: the quantiser kernel launched just before this one has
+    // completed, or (act_spread) every CTA of this grid has converted its share.
+    auto wait_activations = [&]() -> bool {
+      if (!p.act_spread) {
+        griddep_wait();
+        return true;
+      }
+      if (!mbar_wait(quant_bar, 0u)) return false;
+      unsigned long long target;
+      asm volatile("ld.shared.u64 %0, [%1];" : "=l"(target) : "r"(quant_target) : "memory");
+      const long long t0 = clock64();
+      while (true) {
+        unsigned long long seen;
+        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(p.act_counter) : "memory");
+        if (seen >= target) break;
+        if (clock64() - t0 > SMB_WAIT_BUDGET_CYCLES) return false;
+        __nanosleep(40);
+      }
+      // The codes and scales were written with ordinary stores by other CTAs; the loads below
+      // go through the async proxy.
+      asm volatile("fence.proxy.async;" ::: "memory");
+      return true;
+    };
+    bool acts_ok = true;
+    for (int q = q_begin; q < q_end && acts_ok; ++q) {
       for (int kb = 0; kb < num_kb; ++kb, ++issued) {
         // Activations written by the kernel launched just before this one (the quantiser): the
         // first ring of weight boxes goes out before the wait, the activation boxes after it.
         if (!waited && issued == stages) {
-          griddep_wait();
+          if (!wait_activations()) {
+            report_status(p.status, kDevTimeoutActivations);
+            acts_ok = false;
+            break;
+          }
           waited = true;
           for (int j = 0; j < stages; ++j) {
             const int kbj = (j) % num_kb;
@@ -757,9 +831,12 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
         if (++s == stages) { s = 0; ph ^= 1u; }
       }
     }
-    if (!waited) {
+    if (!waited && acts_ok && !wait_activations()) {
+      report_status(p.status, kDevTimeoutActivations);
+      acts_ok = false;
+    }
+    if (!waited && acts_ok) {
       // Fewer units than ring slots: the activation boxes of everything issued are still owed.
-      griddep_wait();
       for (int j = 0; j < issued; ++j) {
         const int kbj = j % num_kb;
         const uint32_t dstj = ring_base + static_cast<uint32_t>(j * p.stage_bytes);
@@ -883,6 +960,21 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
     bool store_pending = false;
     bool waited_for_previous_grid = false;
     int seg = 0;
+    if (p.act_spread) {
+      // This CTA's share of the activation quantiser (see the top of this function); the four
+      // warps 8-11 take part even where they have no accumulator columns to drain.
+      griddep_wait();
+      waited_for_previous_grid = true;
+      spread_quantize(p, static_cast<int>(threadIdx.x) - 128, 128 * epi_groups);
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
+      if (first_thread) {
+        const unsigned long long old = atomicAdd(p.act_counter, 1ull);
+        const unsigned long long target = (old / gridDim.x + 1ull) * gridDim.x;
+        asm volatile("st.shared.u64 [%0], %1;" ::"r"(quant_target), "l"(target) : "memory");
+        mbar_arrive(quant_bar);
+      }
+    }
     for (int q = q_begin; q < q_end; ++q, ++seg) {
       const int bank = p.banks == 2 ? (seg & 1) : 0;
       const uint32_t use = static_cast<uint32_t>(p.banks == 2 ? (seg >> 1) : seg) & 1u;
@@ -1157,6 +1249,10 @@ int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   p.alpha = L.alpha;
   p.x_src = static_cast<const uint16_t*>(L.act_src);
   p.ldx = L.act_ld;
+  p.act_spread = (!kFused && fp4_decode_spreads_activations(L)) ? 1 : 0;
+  p.act_codes = static_cast<uint8_t*>(L.act_codes);
+  p.act_sf = static_cast<uint8_t*>(L.act_sf);
+  p.act_counter = L.act_counter;
   const int pairs = ((L.N + 127) / 128 + 1) / 2;
   p.pairs_per_cta = (pairs + sm_count - 1) / sm_count;
   const int grid = (pairs + p.pairs_per_cta - 1) / p.pairs_per_cta;
@@ -1190,7 +1286,16 @@ bool fp4_decode_prefers_dual(int M) { return (M + 15) / 16 * 16 >= fp4d::kDualFr
 // chained in front: M = 1 20.6 / 22.8, 16 21.9 / 23.2, 32 30.2 / 23.8, 64 49.1 / 26.4).  Elsewhere
 // the caller quantises first.
 bool fp4_decode_fuses_activations(const Fp4DecodeLaunch& L) {
-  return L.act_src != nullptr && !L.block16 && L.dual && !L.narrow && L.max_ctas == 0 && L.M <= 16;
+  return L.act_src != nullptr && L.act_mode == 1 && !L.block16 && L.dual && !L.narrow && L.max_ctas == 0 &&
+         L.M <= 16;
+}
+
+// BF16 activations quantised once per launch by the grid as a whole (act_spread in
+// decode_dual_body): any number of rows, the dual forms with UE8M0 scales and whole tile pairs,
+// plans that own a code buffer and a counter.
+bool fp4_decode_spreads_activations(const Fp4DecodeLaunch& L) {
+  return L.act_src != nullptr && L.act_mode == 0 && L.act_counter != nullptr && L.act_codes != nullptr &&
+         !L.block16 && L.dual && L.max_ctas == 0;
 }
 
 namespace {

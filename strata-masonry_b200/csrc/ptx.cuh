@@ -28,6 +28,7 @@ enum DeviceStatus : int {
   kDevTimeoutSched = 105,      // a role gave up waiting for the tile scheduler
   kDevTimeoutFixup = 106,      // split-K fix-up wait gave up
   kDevTimeoutProbe = 107,      // the bounded-wait self test (expected outcome)
+  kDevTimeoutActivations = 108,  // decode kernel gave up waiting for the grid's activation quantiser
 };
 
 // Wait budget in SM clock cycles (~2 s at 2 GHz).  The longest legitimate wait on this

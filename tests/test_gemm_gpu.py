@@ -613,18 +613,22 @@ def test_bf16_quantizer_is_bit_identical_to_oracle(smb, oracle, cuda_device):
 @pytest.mark.parametrize("shape", [(16, 1024, 2048), (64, 2560, 1024), (128, 1152, 512), (7, 300, 96),
                                    (300, 512, 256), (1, 256, 8192), (16, 28672, 8192), (48, 3000, 2048),
                                    (33, 1000, 1056), (64, 38400, 512), (16, 38400, 512), (9, 1001, 352)])
-def test_fp4_plan_fed_with_bf16_activations(smb, cuda_device, shape):
-    """The plan that takes BF16 activations (up to 16 rows: quantised inside the decode kernel by
-    its own warps; up to 128: by a kernel chained in front of the decode kernel; above: in front of
-    the tiled kernel) equals quantise-then-multiply done as two separate calls, and follows the
-    activations when they change between runs."""
+@pytest.mark.parametrize("mode", ["FLAG_NONE", "FLAG_ACT_QUANT_PER_CTA", "FLAG_ACT_QUANT_CHAINED"])
+def test_fp4_plan_fed_with_bf16_activations(smb, cuda_device, shape, mode):
+    """The plan that takes BF16 activations equals quantise-then-multiply done as two separate
+    calls, and follows the activations when they change between runs, in each of its forms: the
+    default (up to 128 rows the CTAs of the decode kernel share the quantisation and meet on a
+    counter; above, a quantiser kernel in front of the tiled kernel), every CTA quantising all
+    activations into its own ring (up to 16 rows), and the quantiser kernel chained in front."""
     torch = _torch()
     m, n, k = shape
     g = torch.Generator(device="cpu").manual_seed(m * 7 + n)
     w, sfw, _ = _fp4_operand(smb, n, k, 5, 1)
     d = torch.empty(m, n, device=cuda_device, dtype=torch.bfloat16)
     x = torch.empty(m, k, device=cuda_device, dtype=torch.bfloat16)
-    plan = smb.gemm.Fp4Plan.from_bf16_activations(x, w, sfw, d, m, n, k)
+    plan = smb.gemm.Fp4Plan.from_bf16_activations(x, w, sfw, d, m, n, k, flags=getattr(smb.capi, mode))
+    if m <= 128:
+        assert "bf16-activations" in plan.describe()
     codes = torch.empty(m, k // 2, device=cuda_device, dtype=torch.uint8)
     sfp = torch.empty(smb.gemm.sf_packed_bytes(m, k), device=cuda_device, dtype=torch.uint8)
     d_ref = torch.empty(m, n, device=cuda_device, dtype=torch.bfloat16)
@@ -637,7 +641,8 @@ def test_fp4_plan_fed_with_bf16_activations(smb, cuda_device, shape):
         x[m - 1, k - 32:] *= 2.0 ** 20     # and a large one in the last block of the last row
         d.fill_(float("nan"))
         plan.run()
-        plan.run()     # back to back: the second quantiser must not disturb the first GEMM
+        plan.run()     # back to back: the second launch's quantiser must not disturb the first GEMM
+        plan.run()
         plan.check()
         smb.capi.check(smb.capi.lib().smb_quantize_mx_bf16_device(
             x.data_ptr(), k, codes.data_ptr(), k // 2, sfp.data_ptr(), None, m, k, None))
