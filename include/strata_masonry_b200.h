@@ -220,13 +220,14 @@ int smb_fp4_plan_create(smb_fp4_plan** plan, const void* a, const void* sfa, con
 /* The same GEMM fed with BF16 activations [M, K] (row pitch ldx elements), as a model hands them
  * to a decode step: the plan owns the E2M1 codes and packed scales of A, and every
  * smb_fp4_plan_run first quantises `x_bf16` into them (the rule of smb_quantize_mx_*) and then
- * multiplies.  For M <= 128 this is ONE kernel: the decode kernel starts streaming its weights at
- * once, its CTAs share the quantisation of the activations between them (each converts
- * 1 / grid of the blocks after the previous kernel on the stream has completed), meet on a
- * counter, and only then load activations.  SMB_FLAG_ACT_QUANT_PER_CTA selects the older
- * in-kernel form (every CTA converts all activations straight into its ring, at most 16 rows),
- * SMB_FLAG_ACT_QUANT_CHAINED a quantiser kernel chained in front; above 128 rows it is always the
- * chained kernel.  All forms give the same bits.  The reference has no quantiser; its drivers generate codes and
+ * multiplies.  For M <= 128 this is ONE kernel.  From 17 rows up the decode kernel starts
+ * streaming its weights at once, its CTAs share the quantisation of the activations between them
+ * (each converts 1 / grid of the blocks after the previous kernel on the stream has completed),
+ * meet on a counter, and only then load activations (SMB_FLAG_ACT_QUANT_SHARED forces this form
+ * for fewer rows too).  Up to 16 rows every CTA converts all activations straight into its own
+ * ring instead (SMB_FLAG_ACT_QUANT_PER_CTA; cheaper than the meeting for so few rows).
+ * SMB_FLAG_ACT_QUANT_CHAINED selects a quantiser kernel chained in front, which is also what
+ * runs above 128 rows.  All forms give the same bits.  The reference has no quantiser; its drivers generate codes and
  * scales directly (nvfp4/dense_gemm_nvfp4.cu:2279-2290). */
 int smb_fp4_plan_create_bf16_activations(smb_fp4_plan** plan, const void* x_bf16, int64_t ldx,
                                          const void* b, const void* sfb, void* d, int M, int N, int K,
@@ -451,6 +452,7 @@ int smb_fp4_host_ctx_create_sharded(smb_fp4_host_ctx** ctx, int M, int n_local, 
  * per launch, shared by the CTAs of the decode kernel); see smb_fp4_plan_create_bf16_activations. */
 #define SMB_FLAG_ACT_QUANT_PER_CTA 32768u
 #define SMB_FLAG_ACT_QUANT_CHAINED 65536u
+#define SMB_FLAG_ACT_QUANT_SHARED 131072u
 
 #ifdef __cplusplus
 }

@@ -38,6 +38,7 @@ FLAG_EPILOGUE_SWIGLU = 8192
 FLAG_SCALE_BLOCK16 = 16384
 FLAG_ACT_QUANT_PER_CTA = 32768
 FLAG_ACT_QUANT_CHAINED = 65536
+FLAG_ACT_QUANT_SHARED = 131072
 
 _vp = C.c_void_p
 _i = C.c_int

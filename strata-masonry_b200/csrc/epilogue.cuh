@@ -42,14 +42,11 @@ struct StoreTarget {
 // the output is D[m, n] = bf16(silu(gate_n) * up_n), half as wide as the accumulator.  col0 is
 // then the accumulator column; out.N and the tensor map describe the [M, N/2] output.
 // kScaled: every accumulator is multiplied by out.alpha first (the per-tensor scales of NVFP4).
-template <int kCols, bool kTmaStore, bool kSwiglu = false, bool kScaled = false>
-__device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, const StoreTarget& out,
-                                                int row0, int col0, uint32_t release_bar, int lane) {
-  constexpr int kOutCols = kSwiglu ? kCols / 2 : kCols;
-  static_assert(kOutCols % kStoreCols == 0, "whole store boxes only");
-  static_assert(!kSwiglu || kTmaStore, "the gated epilogue uses the aligned store path");
-  if (kSwiglu) col0 /= 2;
-  uint32_t packed[kOutCols / 2];
+// Phase 1 alone: kCols fp32 columns of this warp's 32 lanes, starting at `taddr`, into
+// `packed` (two bf16 per register; kSwiglu: one output pair per four accumulator columns).
+template <int kCols, bool kSwiglu = false, bool kScaled = false>
+__device__ __forceinline__ void drain_columns(uint32_t taddr, float alpha,
+                                              uint32_t (&packed)[(kSwiglu ? kCols / 2 : kCols) / 2]) {
 #pragma unroll
   for (int g = 0; g < kCols / 32; ++g) {
     uint32_t v[32];
@@ -57,7 +54,7 @@ __device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, c
     tmem_ld_wait();
     if (kScaled) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * out.alpha);
+      for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
     }
     if (kSwiglu) {
 #pragma unroll
@@ -71,10 +68,22 @@ __device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, c
       for (int i = 0; i < 16; ++i) packed[g * 16 + i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
     }
   }
+}
+
+// Hand the drained accumulator columns back to the MMA role: one arrival on `release_bar` (a
+// cluster-mapped mbarrier address) per warp.
+__device__ __forceinline__ void release_columns(uint32_t release_bar, int lane) {
   tc_fence_before_sync();
   __syncwarp();
   if (lane == 0) mbar_arrive_cluster(release_bar);
+}
 
+// Phase 2 alone: kOutCols packed columns to D rows [row0, row0 + 32), columns [col0, col0 + kOutCols),
+// in 64-column boxes through the warp's staging buffer.
+template <int kOutCols, bool kTmaStore>
+__device__ __forceinline__ void store_columns(const uint32_t (&packed)[kOutCols / 2], uint32_t sbuf,
+                                              const StoreTarget& out, int row0, int col0, int lane) {
+  static_assert(kOutCols % kStoreCols == 0, "whole store boxes only");
 #pragma unroll
   for (int c = 0; c < kOutCols / kStoreCols; ++c) {
     // The TMA store that last read the staging buffer must have finished reading it.
@@ -145,6 +154,19 @@ __device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, c
       __syncwarp();
     }
   }
+}
+
+template <int kCols, bool kTmaStore, bool kSwiglu = false, bool kScaled = false>
+__device__ __forceinline__ void drain_and_store(uint32_t taddr, uint32_t sbuf, const StoreTarget& out,
+                                                int row0, int col0, uint32_t release_bar, int lane) {
+  constexpr int kOutCols = kSwiglu ? kCols / 2 : kCols;
+  static_assert(kOutCols % kStoreCols == 0, "whole store boxes only");
+  static_assert(!kSwiglu || kTmaStore, "the gated epilogue uses the aligned store path");
+  if (kSwiglu) col0 /= 2;
+  uint32_t packed[kOutCols / 2];
+  drain_columns<kCols, kSwiglu, kScaled>(taddr, out.alpha, packed);
+  release_columns(release_bar, lane);
+  store_columns<kOutCols, kTmaStore>(packed, sbuf, out, row0, col0, lane);
 }
 
 // Call once per warp after its last tile: the CTA's shared memory must outlive the reads of its

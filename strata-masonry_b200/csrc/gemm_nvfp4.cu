@@ -651,8 +651,14 @@ int launch_fp4_store(const Fp4Launch& L, cudaStream_t stream) {
 
 // How many full-width (w0 + w1) tiles per tile row, and how many w0-wide tiles after them, make
 // the round-robin walk of `clusters` clusters over the tile list end soonest.  Cost of a tile in
-// tensor-pipe cycles: 2 cycles per column and 256-wide K block, plus ~2000 cycles of exposed
-// accumulator drain.  Tile t goes to cluster t % clusters; the walk ends when the busiest cluster does.
+// SM cycles, fitted to measurements (8192^3, 14080 x 5120 x 2048, 14080 x 2048 x 4096 at the
+// ~1.57 GHz the kernels run at): a 256-wide K block costs 811 cycles on a 384-wide tile and 556
+// on a 256-wide one (768 and 512 would be the tensor pipe's own time), and every tile pays about
+// 3100-3200 cycles between its last instruction and the first of the next tile (accumulator
+// drain, barrier round trips).
+constexpr double kFp4CyclesPerColumnAndKBlock384 = 811.0 / 384.0;
+constexpr double kFp4CyclesPerColumnAndKBlock256 = 556.0 / 256.0;
+constexpr double kFp4TileOverhead384 = 3200.0, kFp4TileOverhead256 = 3100.0;
 namespace {
 thread_local double g_last_phase_cost = 0.0;   // written by fp4_split_phases for fp4_pick_tile (same thread, same call)
 }
@@ -665,7 +671,8 @@ void fp4_split_phases(int M, int N, int K, int w0, int w1, int clusters, int* wi
   *narrow_tiles_n = 0;
   if (w1 == 0 || clusters < 1) return;
   const double kb = (K + 255) / 256;
-  const double cost_wide = kb * 2.0 * tile_n + 2000.0, cost_narrow = kb * 2.0 * w0 + 2000.0;
+  const double cost_wide = kb * kFp4CyclesPerColumnAndKBlock384 * tile_n + kFp4TileOverhead384;
+  const double cost_narrow = kb * kFp4CyclesPerColumnAndKBlock256 * w0 + kFp4TileOverhead256;
   double best = -1.0;
   // Only the last few wide tiles of a row are worth trading: beyond that the narrow tiles'
   // extra drains and operand traffic outweigh any balance gained.
@@ -716,16 +723,16 @@ void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1) {
   }
   *w0 = 256;
   if (N <= 256) return;
-  // 256 x 384 against 256 x 256 tiles (one accumulator set each, ~2000 cycles of drain per
-  // tile): the wider tile moves less data per flop, the narrower one spreads better over the
-  // clusters.  Estimated cycles, 768 / 512 MMA cycles per 256-wide K block:
+  // 256 x 384 against 256 x 256 tiles (one accumulator set each): the wider tile moves less data
+  // per flop and pays the per-tile overhead less often, the narrower one spreads better over the
+  // clusters.  Estimated cycles with the fitted costs above:
   if (clusters < 1) clusters = 74;
   const long long tiles_m = (M + 255) / 256;
   const long long kb = (K + 255) / 256;
   const long long waves256 = (tiles_m * ((N + 255) / 256) + clusters - 1) / clusters;
   const long long waves384 = (tiles_m * ((N + 383) / 384) + clusters - 1) / clusters;
-  const double cost256 = static_cast<double>(waves256) * (kb * 512.0 + 2000.0) / 0.985;
-  double cost384 = static_cast<double>(waves384) * (kb * 768.0 + 2000.0);
+  const double cost256 = static_cast<double>(waves256) * (kb * 556.0 + kFp4TileOverhead256);
+  double cost384 = static_cast<double>(waves384) * (kb * 811.0 + kFp4TileOverhead384);
   // The 384-wide kernel ends its tile list with 256-wide tiles where that evens the clusters out.
   int wide = 0, narrow = 0;
   fp4_split_phases(M, N, K, 256, 128, clusters, &wide, &narrow);

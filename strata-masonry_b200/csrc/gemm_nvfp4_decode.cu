@@ -778,7 +778,7 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
         asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(p.act_counter) : "memory");
         if (seen >= target) break;
         if (clock64() - t0 > SMB_WAIT_BUDGET_CYCLES) return false;
-        __nanosleep(40);
+        __nanosleep(20);
       }
       // The codes and scales were written with ordinary stores by other CTAs; the loads below
       // go through the async proxy.

@@ -117,6 +117,35 @@ def main() -> None:
             [vf.reference_value(int(m), int(n), c["k"], mode) for m, n in zip(rows, cols)],
             dtype=np.float32)
 
+    # ---- every benchmark configuration through the verifiers' own sampling and reference code.
+    # The verifiers only know their built-in CASES; a shape outside them is added to the imported
+    # module's CASES at run time (the files on disk are never edited) and then served by the same
+    # sample_coordinates / references / reference_value functions verify() itself calls.  The GPU
+    # tests hold the CUDA output at these coordinates to these values under verify()'s mismatch rule.
+    config_samples = 256
+    bf16_configs = {"bf16_8192": (8192, 8192, 8192), "bf16_ragged": (4095, 4160, 12289),
+                    "bf16_large": (32768, 8192, 57344)}
+    for name, (m, k, n) in bf16_configs.items():
+        vb.CASES[name] = {"m": m, "k": k, "n": n, "production_m": m}
+        c = vb.CASES[name]
+        rows, cols = vb.sample_coordinates(c["m"], c["n"], config_samples, 20260827)
+        out[f"cfg_{name}_rows"] = rows.astype(np.int64)
+        out[f"cfg_{name}_cols"] = cols.astype(np.int64)
+        out[f"cfg_{name}_shape"] = np.array([m, k, n], dtype=np.int64)
+        out[f"cfg_{name}_ref_m2"] = vb.references(c, rows, cols, 2).astype(np.float32)
+    fp4_configs = {"nvfp4_8192": (8192, 8192, 8192), "decode_m16": (16, 8192, 28672),
+                   "decode_m64": (64, 8192, 28672), "decode_m128": (128, 8192, 28672)}
+    for name, (m, k, n) in fp4_configs.items():
+        vf.CASES[name] = {"m": m, "k": k, "n": n, "production_m": m}
+        c = vf.CASES[name]
+        rows, cols = vf.sample_coordinates(c["m"], c["n"], config_samples, 20260827)
+        out[f"cfg_{name}_rows"] = rows.astype(np.int64)
+        out[f"cfg_{name}_cols"] = cols.astype(np.int64)
+        out[f"cfg_{name}_shape"] = np.array([m, k, n], dtype=np.int64)
+        out[f"cfg_{name}_ref_m2"] = np.array(
+            [vf.reference_value(int(r), int(cc), c["k"], 2) for r, cc in zip(rows, cols)], dtype=np.float32)
+    out["cfg_tolerances"] = np.array([0.05, 0.05, 16.0, 0.008], dtype=np.float64)   # bf16 atol, rtol; nvfp4 atol, rtol
+
     np.savez_compressed(HERE / "reference_vectors.npz", **out)
     total = sum(v.nbytes for v in out.values())
     print(f"wrote {len(out)} arrays, {total / 1024:.0f} KiB raw, "

@@ -613,7 +613,7 @@ def test_bf16_quantizer_is_bit_identical_to_oracle(smb, oracle, cuda_device):
 @pytest.mark.parametrize("shape", [(16, 1024, 2048), (64, 2560, 1024), (128, 1152, 512), (7, 300, 96),
                                    (300, 512, 256), (1, 256, 8192), (16, 28672, 8192), (48, 3000, 2048),
                                    (33, 1000, 1056), (64, 38400, 512), (16, 38400, 512), (9, 1001, 352)])
-@pytest.mark.parametrize("mode", ["FLAG_NONE", "FLAG_ACT_QUANT_PER_CTA", "FLAG_ACT_QUANT_CHAINED"])
+@pytest.mark.parametrize("mode", ["FLAG_NONE", "FLAG_ACT_QUANT_SHARED", "FLAG_ACT_QUANT_PER_CTA", "FLAG_ACT_QUANT_CHAINED"])
 def test_fp4_plan_fed_with_bf16_activations(smb, cuda_device, shape, mode):
     """The plan that takes BF16 activations equals quantise-then-multiply done as two separate
     calls, and follows the activations when they change between runs, in each of its forms: the
@@ -1017,5 +1017,42 @@ def test_fp4_full_and_narrow_tiles_in_one_launch(smb, cuda_device, shape, cluste
             nn = torch.arange(n, device=d.device).view(1, -1)
             exact = (k * torch.exp2((mm % 5) - 2.0) * torch.exp2((nn % 3) - 1.0)).to(torch.bfloat16)
             assert torch.equal(d[:, :n], exact)
-    if shape == (8192, 8192, 256) and clusters == 0:
-        assert narrow.value > 0       # this shape does get narrow tiles on a full GPU
+    if shape == (2048, 2432, 256):
+        assert narrow.value > 0       # this shape does get narrow tiles
+
+
+# ------------------------------------------------------------------------------- every configuration under the verifiers' rule
+def _verifier_mismatches(observed_bits, reference, atol, rtol):
+    """The mismatch rule of the reference verifiers' verify() (dense_gemm_bf16_cpu_verifier.py:82-83,
+    nvfp4/dense_gemm_nvfp4_cpu_verifier.py:119-122): not finite, or off by more than atol AND by more
+    than rtol |reference|."""
+    observed = (observed_bits.astype(np.uint32) << 16).view(np.float32)
+    error = np.abs(observed - reference)
+    return int(np.count_nonzero(~np.isfinite(observed) | ((error > atol) & (error > rtol * np.abs(reference)))))
+
+
+@pytest.mark.parametrize("name", ["bf16_8192", "bf16_ragged", "bf16_large"])
+def test_bf16_configurations_under_the_reference_verifier_rule(smb, golden, cuda_device, name):
+    """Each BF16 benchmark configuration once with the reference's fill 2: the CUDA output at the
+    verifier's own sample coordinates against the verifier's own reference values (made by its
+    code with CASES extended at run time), under its own tolerance."""
+    torch = _torch()
+    m, k, n = (int(x) for x in golden[f"cfg_{name}_shape"])
+    a, bt, d = _run_bf16(smb, m, n, k, 2)
+    rows = torch.from_numpy(golden[f"cfg_{name}_rows"]).to(d.device)
+    cols = torch.from_numpy(golden[f"cfg_{name}_cols"]).to(d.device)
+    atol, rtol = golden["cfg_tolerances"][:2]
+    assert _verifier_mismatches(_bits(d[rows, cols]), golden[f"cfg_{name}_ref_m2"], atol, rtol) == 0
+    del a, bt, d
+    torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("name", ["nvfp4_8192", "decode_m16", "decode_m64", "decode_m128"])
+def test_fp4_configurations_under_the_reference_verifier_rule(smb, golden, cuda_device, name):
+    torch = _torch()
+    m, k, n = (int(x) for x in golden[f"cfg_{name}_shape"])
+    A, B, d = _run_fp4(smb, m, n, k, 2)
+    rows = torch.from_numpy(golden[f"cfg_{name}_rows"]).to(d.device)
+    cols = torch.from_numpy(golden[f"cfg_{name}_cols"]).to(d.device)
+    atol, rtol = golden["cfg_tolerances"][2:]
+    assert _verifier_mismatches(_bits(d[rows, cols]), golden[f"cfg_{name}_ref_m2"], atol, rtol) == 0

@@ -55,6 +55,38 @@ def test_bf16_sampled_references_match(oracle, golden, name, mode):
     np.testing.assert_allclose(ref64, want, rtol=2e-5, atol=2e-4)
 
 
+@pytest.mark.parametrize("name", ["bf16_8192", "bf16_ragged", "bf16_large"])
+def test_bf16_config_references_match(oracle, golden, name):
+    """Every BF16 benchmark configuration, fill 2, at the reference verifier's own sample
+    coordinates (its CASES extended at run time when the vectors were made): the oracle's operands
+    and float64 product against the reference's sampled fp32 dot products."""
+    m, k, n = (int(x) for x in golden[f"cfg_{name}_shape"])
+    rows, cols = golden[f"cfg_{name}_rows"], golden[f"cfg_{name}_cols"]
+    assert rows.size >= 200 and rows.max() < m and cols.max() < n
+    ks = np.arange(k, dtype=np.uint64)
+    a = oracle.bf16_to_f32(oracle.bf16_fill(rows.astype(np.uint64)[:, None] * np.uint64(k) + ks, 2, 1))
+    b = oracle.bf16_to_f32(oracle.bf16_fill(ks[None, :] * np.uint64(n) + cols.astype(np.uint64)[:, None], 2, 2))
+    ref64 = np.einsum("ik,ik->i", a.astype(np.float64), b.astype(np.float64))
+    np.testing.assert_allclose(ref64, golden[f"cfg_{name}_ref_m2"], rtol=5e-5, atol=2e-3)
+
+
+@pytest.mark.parametrize("name", ["nvfp4_8192", "decode_m16", "decode_m64", "decode_m128"])
+def test_fp4_config_references_match(oracle, golden, name):
+    m, k, n = (int(x) for x in golden[f"cfg_{name}_shape"])
+    rows, cols = golden[f"cfg_{name}_rows"], golden[f"cfg_{name}_cols"]
+    want = golden[f"cfg_{name}_ref_m2"]
+    ks = np.arange(k, dtype=np.uint64)
+    kb = np.arange(k // 32, dtype=np.uint64)
+    for i in range(0, rows.size, 4):     # every fourth sample keeps the CPU suite short
+        r, c = rows[i], cols[i]
+        a = oracle.e2m1_decode(oracle.fp4_fill_codes(np.uint64(r) * np.uint64(k) + ks, 2, oracle.SEED_FP4_A))
+        b = oracle.e2m1_decode(oracle.fp4_fill_codes(np.uint64(c) * np.uint64(k) + ks, 2, oracle.SEED_FP4_B))
+        sa = np.exp2(oracle.fp4_fill_scale_exp(np.uint64(r), kb, 2, 0).astype(np.float64))
+        sb = np.exp2(oracle.fp4_fill_scale_exp(np.uint64(c), kb, 2, 1).astype(np.float64))
+        ref = float(np.sum(a.astype(np.float64) * np.repeat(sa, 32) * b * np.repeat(sb, 32)))
+        assert abs(ref - float(want[i])) <= max(16.0, 0.008 * abs(ref))
+
+
 def test_hash_matches_reference(oracle, golden):
     np.testing.assert_array_equal(oracle.hash32(golden["hash_inputs"]), golden["hash32"])
 
