@@ -49,17 +49,32 @@ __host__ __device__ inline void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / rows;
 }
 
-// Default raster group height: as many 256-row tile rows of A as stay resident in L2 while the B
-// panels stream past them, taken as 32 MB of A (a quarter of the 126 MB L2: the two dies each
-// cache what their SMs read).  `row_bytes` = bytes of one row of A (K elements).  Measured on
-// BF16 8192^3 (sustained, TFLOP/s): 4 rows 1320-1346, 8 rows 1345-1370, 16 rows 1330-1351, 32 rows
-// 1239-1287; block-scaled 8192^3 with 384-wide tiles: 8 rows 5660, 16 rows 5750-5860, 32 rows
-// 5850-5960 (A is a quarter the size there).
+// Default raster group height (tile rows walked M-fastest before the walk moves on along N).
+// Two things pull on it.  A wave of ~74 clusters that spans g tile rows and 74 / g tile columns
+// touches g A panels and 74 / g B panels, least for g around 8 to 12; and tiles of one row should
+// run close together in time so that its A panel is still in L2.  Measured (sustained TFLOP/s):
+//   BF16 8192^3 (256 x 512 tiles): g = 4 1320-1346, 8 1345-1370, 16 1330-1351, 32 1239-1287;
+//   BF16 8192 x 8192 x 4096: 8 1600, 16 1614, 32 1572;  30720 x 2048 x 4096 (256 x 256 tiles): 8 1565,
+//   16 1557, 32 1390;  14080 x 5120 x 2048: 8 1552, 16 1542, 32 1537.
+// `row_bytes` = bytes of one row of A.  BF16: 32 MB of A per group, kept between 8 and 16 rows.
 inline int raster_group_rows(int tiles_m, long long row_bytes) {
   long long rows = (32ll << 20) / (256 * (row_bytes > 0 ? row_bytes : 1));
-  if (rows < 1) rows = 1;
+  if (rows < 8) rows = 8;
+  if (rows > 16) rows = 16;
   if (rows > tiles_m) rows = tiles_m;
   return static_cast<int>(rows);
+}
+// Block-scaled kernel (A is a quarter the size, and the tile list ends every group with narrower
+// tiles): all rows in one group when they are fewer than the clusters and A as a whole stays in
+// L2 (32 MB) - the narrow tiles then all come last, which also evens out the last wave - else 8.
+// Measured (TFLOP/s, group of 4 / 8 / 16 / 32 / all rows): 8192^3 (32 rows) 6150 / 6007 / 6110 /
+// 6200 / 6200;  14080 x 2048 x 4096 (55 rows) 5213 / 5217 / 5247 / 5293 / 5337;  14080 x 5120 x 2048
+// 4700 / 4698 / 4635 / 4551 / 4672;  30720 x 2048 x 4096 (120 rows) 5352 / 5352 / 5363 / 5353 / 5250;
+// 30720 x 5120 x 2048 4814 / 4782 / 4740 / 4662 / 4490;  30720 x 4096 x 8192 6230 / 6238 / 6145 / 6136 / -.
+inline int raster_group_rows_fp4(int tiles_m, long long row_bytes) {
+  const long long a_bytes = static_cast<long long>(tiles_m) * 256 * row_bytes;
+  if (tiles_m <= 64 && a_bytes <= (32ll << 20)) return tiles_m;
+  return tiles_m < 8 ? tiles_m : 8;
 }
 
 // --------------------------------------------------------------------------- tensor maps

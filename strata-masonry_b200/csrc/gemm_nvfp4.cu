@@ -320,6 +320,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int s = 0;
       uint32_t ph = 0;
       int local = 0;
+      int sub1_tiles = 0;   // tiles so far that had a second sub-block (its barriers' phase count)
       bool ok = true;
       const bool prof = p.prof != nullptr;
       long long wait_full = 0, wait_acc = 0;
@@ -335,16 +336,18 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int bank = C::kTwoBanks ? (local & 1) : 0;
         const uint32_t use_parity =
             static_cast<uint32_t>(C::kTwoBanks ? (local >> 1) : local) & 1u;
-        const long long a0 = prof ? clock64() : 0;
-        if (!mbar_wait(acc_empty_bar(bank), use_parity ^ 1u)) {
-          report_status(p.status, kDevTimeoutMmaAcc);
-          ok = false;
-          break;
+        if constexpr (C::kSubs == 1) {
+          const long long a0 = prof ? clock64() : 0;
+          if (!mbar_wait(acc_empty_bar(bank), use_parity ^ 1u)) {
+            report_status(p.status, kDevTimeoutMmaAcc);
+            ok = false;
+            break;
+          }
+          if (prof) wait_acc += clock64() - a0;
+          tc_fence_after_sync();
         }
-        if (prof) wait_acc += clock64() - a0;
-        tc_fence_after_sync();
         const uint32_t acc_base = tmem_base + static_cast<uint32_t>(bank * 128);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
           // Operands in shared memory (full) and scales in tensor memory (sf_ready, committed by
           // the scale warp).
           const long long w0 = prof ? clock64() : 0;
@@ -358,41 +361,71 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t stage = ring_base + s * C::kStageBytes;
           const uint32_t sf_t = tmem_base + static_cast<uint32_t>(C::kAccCols + s * C::kSlotCols);
           const uint64_t desc_a = make_smem_desc(stage, 1024, 16, kSwizzle128B);
-          if (elect_one()) {
-#pragma unroll
-          for (int ki = 0; ki < 4; ++ki) {
-            // K = 64 per instruction = 32 bytes along the swizzled row.  Atoms 2c and 2c + 1 share
-            // scale cell c: the first reads bytes 0-1 of each cell (scale id 0), the second bytes
-            // 2-3 (scale id 2).
+          // One K = 64 instruction of sub-block h.  K = 64 per instruction = 32 bytes along the
+          // swizzled row.  Atoms 2c and 2c + 1 share scale cell c: the first reads bytes 0-1 of
+          // each cell (scale id 0), the second bytes 2-3 (scale id 2).
+          auto issue = [&](int h, int ki) {
             const uint32_t sf_id = V4 ? 0u : ((ki & 1) ? 2u : 0u);
             const uint32_t cell = static_cast<uint32_t>(V4 ? ki : (ki >> 1));
-            uint32_t sfb_col = C::kSfaCols;
-            uint32_t acc_col = 0;
+            const int width = (h == 0) ? W0 : W1;
+            const int bands = width / 128;
+            const uint32_t sfb_col = C::kSfaCols + (h == 0 ? 0u : static_cast<uint32_t>((W0 / 128) * kCells * 4));
+            const uint32_t acc_col = (h == 0) ? 0u : static_cast<uint32_t>(W0);
+            const uint64_t desc_b = make_smem_desc(stage + (h == 0 ? C::kOffB0 : C::kOffB1), 1024, 16, kSwizzle128B);
+            const uint32_t idesc = make_idesc_mxf4(256, width, sf_id, sf_id, !V4);
+            const uint32_t sfa_t = sf_t + 4u * cell;
+            const uint32_t sfb_t = sf_t + sfb_col + cell * static_cast<uint32_t>(bands * 4);
+            const uint32_t accum = (kb > 0 || ki > 0) ? 1u : 0u;
+            if (V4) mma_nvf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc, sfa_t, sfb_t, accum);
+            else mma_mxf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc, sfa_t, sfb_t, accum);
+          };
+          if (C::kSubs == 2 && (kb == 0 || kb == num_kb - 1)) {
+            // First and last K block of a two-sub-block tile: sub-block by sub-block, so that each
+            // is taken over from the epilogue (first block) and handed to it (last block) on its
+            // own.  The epilogue drains sub-block 0 first; its columns are multiplied again while
+            // sub-block 1 is still being read out, and sub-block 0 of the finished tile is on its
+            // way out while the last instructions of sub-block 1 run.
 #pragma unroll
-            for (int h = 0; h < C::kSubs; ++h) {
-              const int width = (h == 0) ? W0 : W1;
-              const int bands = width / 128;
-              if (h == 0 || has_sub1) {
-                const uint64_t desc_b = make_smem_desc(stage + (h == 0 ? C::kOffB0 : C::kOffB1),
-                                                       1024, 16, kSwizzle128B);
-                const uint32_t idesc = make_idesc_mxf4(256, width, sf_id, sf_id, !V4);
-                const uint32_t sfa_t = sf_t + 4u * cell;
-                const uint32_t sfb_t = sf_t + sfb_col + cell * static_cast<uint32_t>(bands * 4);
-                const uint32_t accum = (kb > 0 || ki > 0) ? 1u : 0u;
-                if (V4) mma_nvf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc, sfa_t, sfb_t, accum);
-                else mma_mxf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc, sfa_t, sfb_t, accum);
+            for (int h = 0; h < 2; ++h) {
+              if (h == 1 && !has_sub1) break;
+              if (kb == 0) {
+                const uint32_t use = static_cast<uint32_t>(h == 0 ? local : sub1_tiles) & 1u;
+                const long long a0 = prof ? clock64() : 0;
+                if (!mbar_wait(acc_empty_bar(h), use ^ 1u)) {
+                  report_status(p.status, kDevTimeoutMmaAcc);
+                  ok = false;
+                  break;
+                }
+                if (prof) wait_acc += clock64() - a0;
+                tc_fence_after_sync();
               }
-              sfb_col += static_cast<uint32_t>(bands * kCells * 4);
-              acc_col += static_cast<uint32_t>(width);
+              if (elect_one()) {
+#pragma unroll
+                for (int ki = 0; ki < 4; ++ki) issue(h, ki);
+                if (kb == num_kb - 1) mma_commit_pair(acc_full_bar(h), 0x3);
+              }
+              __syncwarp();
             }
-          }
-          mma_commit_pair(empty_bar(s), 0x3);
+            if (!ok) break;
+            if (elect_one()) mma_commit_pair(empty_bar(s), 0x3);
+          } else if (elect_one()) {
+#pragma unroll
+            for (int ki = 0; ki < 4; ++ki) {
+#pragma unroll
+              for (int h = 0; h < C::kSubs; ++h) {
+                if (h == 0 || has_sub1) issue(h, ki);
+              }
+            }
+            mma_commit_pair(empty_bar(s), 0x3);
           }
           __syncwarp();
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
-        if (ok && elect_one()) mma_commit_pair(acc_full_bar(bank), 0x3);
-        __syncwarp();
+        if (C::kSubs == 1) {
+          if (ok && elect_one()) mma_commit_pair(acc_full_bar(bank), 0x3);
+          __syncwarp();
+        }
+        if (has_sub1) ++sub1_tiles;
       }
       if (prof && lane == 0) {
         p.prof[blockIdx.x * kProfCount + kProfMmaWaitFull] = wait_full;
@@ -475,6 +508,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     out.peers = &p.peers;
     out.alpha = p.alpha;
     int local = 0;
+    int sub1_tiles = 0;   // tiles so far that had a second sub-block
     bool ok = true;
     if (p.operands_static == 1) griddep_wait();   // 2: D is independent too, no wait at all
     const bool prof = p.prof != nullptr && warp == 2 && lane == 0;
@@ -496,21 +530,54 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       const int bank = C::kTwoBanks ? (local & 1) : 0;
       const uint32_t use_parity = static_cast<uint32_t>(C::kTwoBanks ? (local >> 1) : local) & 1u;
-      const long long w0 = prof ? clock64() : 0;
-      if (!mbar_wait(acc_full_bar(bank), use_parity)) {
-        if (lane == 0) report_status(p.status, kDevTimeoutEpilogue);
-        ok = false;
-        break;
-      }
-      if (prof) waited += clock64() - w0;
-      tc_fence_after_sync();
       const int row0 = tm * 256 + static_cast<int>(rank) * kBlockM + quarter * 32;
-      const int tile_col = group * C::kColsPerWarp;
-      const int col0 = tile_col0 + tile_col;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                             static_cast<uint32_t>(bank * 128 + tile_col);
-      drain_and_store<C::kColsPerWarp, kTmaStore, kSwiglu, V4>(taddr, sbuf, out, row0, col0,
-                                                                leader_acc_empty0 + 8u * bank, lane);
+      const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      if constexpr (C::kSubs == 2) {
+        // Sub-block by sub-block (see the MMA role): both warp groups read their half of
+        // sub-block 0 and hand it back, then their half of sub-block 1, and only then store.
+        static_assert(W0 == 256 && W1 == 128 && !kSwiglu, "two sub-blocks: the 256 + 128 tile");
+        const bool has_sub1 = full_width && (tile_col0 + W0 < p.N);
+        uint32_t packed0[64], packed1[32];
+        const long long w0 = prof ? clock64() : 0;
+        if (!mbar_wait(acc_full_bar(0), static_cast<uint32_t>(local) & 1u)) {
+          if (lane == 0) report_status(p.status, kDevTimeoutEpilogue);
+          ok = false;
+          break;
+        }
+        if (prof) waited += clock64() - w0;
+        tc_fence_after_sync();
+        drain_columns<128, false, V4>(lane_base + static_cast<uint32_t>(group * 128), out.alpha, packed0);
+        release_columns(leader_acc_empty0, lane);
+        if (has_sub1) {
+          const long long w1 = prof ? clock64() : 0;
+          if (!mbar_wait(acc_full_bar(1), static_cast<uint32_t>(sub1_tiles) & 1u)) {
+            if (lane == 0) report_status(p.status, kDevTimeoutEpilogue);
+            ok = false;
+            break;
+          }
+          if (prof) waited += clock64() - w1;
+          tc_fence_after_sync();
+          drain_columns<64, false, V4>(lane_base + static_cast<uint32_t>(W0 + group * 64), out.alpha, packed1);
+          release_columns(leader_acc_empty0 + 8u, lane);
+          ++sub1_tiles;
+        }
+        store_columns<128, kTmaStore>(packed0, sbuf, out, row0, tile_col0 + group * 128, lane);
+        if (has_sub1) store_columns<64, kTmaStore>(packed1, sbuf, out, row0, tile_col0 + W0 + group * 64, lane);
+      } else {
+        const long long w0 = prof ? clock64() : 0;
+        if (!mbar_wait(acc_full_bar(bank), use_parity)) {
+          if (lane == 0) report_status(p.status, kDevTimeoutEpilogue);
+          ok = false;
+          break;
+        }
+        if (prof) waited += clock64() - w0;
+        tc_fence_after_sync();
+        const int tile_col = group * C::kColsPerWarp;
+        const int col0 = tile_col0 + tile_col;
+        const uint32_t taddr = lane_base + static_cast<uint32_t>(bank * 128 + tile_col);
+        drain_and_store<C::kColsPerWarp, kTmaStore, kSwiglu, V4>(taddr, sbuf, out, row0, col0,
+                                                                  leader_acc_empty0 + 8u * bank, lane);
+      }
     }
     drain_store_groups<kTmaStore>(lane);
     if (prof) {
@@ -580,7 +647,7 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
     fp4_split_phases(L.M, L.N, L.K, W0, W1, clusters_now, &p.tiles_n, &p.narrow_tiles_n);
     p.narrow_col0 = p.tiles_n * C::kTileN;
   }
-  p.group_m = L.group_m > 0 ? L.group_m : raster_group_rows(p.tiles_m, static_cast<long long>(L.K) / 2);
+  p.group_m = L.group_m > 0 ? L.group_m : raster_group_rows_fp4(p.tiles_m, static_cast<long long>(L.K) / 2);
   p.ldd = L.ldd;
   p.d_ptr = static_cast<uint16_t*>(L.d);
   p.status = L.status;
