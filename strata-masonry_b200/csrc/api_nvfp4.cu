@@ -53,9 +53,10 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
   if (block16 && (flags & SMB_FLAG_EPILOGUE_SWIGLU))
     return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: no gated epilogue for block-16 scales");
   const bool swiglu = (flags & SMB_FLAG_EPILOGUE_SWIGLU) != 0;
-  if (swiglu && (N % 2 != 0 || (M <= 128 && !(flags & SMB_FLAG_NO_DECODE))))
-    return set_error(SMB_ERR_UNSUPPORTED,
-                     "fp4 plan: the gated epilogue needs an even N and the tiled kernel (M > 128)");
+  if (swiglu && N % 2 != 0)
+    return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: the gated epilogue needs an even N (up/gate row pairs of B)");
+  if (swiglu && M <= 128 && !(flags & SMB_FLAG_NO_DECODE) && (flags & SMB_FLAG_DECODE_SINGLE))
+    return set_error(SMB_ERR_UNSUPPORTED, "fp4 plan: the decode kernel's single-tile form has no gated epilogue");
   const int n_out = swiglu ? N / 2 : N;
   if (lda_bytes < K / 2 || ldb_bytes < K / 2 || ldd < n_out)
     return set_error(SMB_ERR_INVALID, "fp4 plan: leading dimension smaller than the row length");
@@ -91,6 +92,8 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
     }
   }
   if (getenv("SMB_TUNE_FP4_UNIFORM")) L.uniform_tiles = true;
+  L.handover = true;
+  if (const char* env = getenv("SMB_TUNE_FP4_HANDOVER")) L.handover = env[0] != '0';
   L.dynamic = (flags & SMB_FLAG_DYNAMIC_TILES) != 0;
   L.operands_static = (flags & (SMB_FLAG_OPERANDS_STATIC | SMB_FLAG_LAUNCH_INDEPENDENT)) != 0;
   L.output_independent = (flags & SMB_FLAG_LAUNCH_INDEPENDENT) != 0;
@@ -115,8 +118,10 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
       return set_error(SMB_ERR_UNSUPPORTED,
                        "fp4 plan: the gated epilogue needs a 16-byte-aligned D with ldd %% 8 == 0");
     }
-    L.w0 = 256;
-    L.w1 = 0;
+    if (L.w0 < 256) {   // four accumulator columns make two outputs: at least 128 columns per warp
+      L.w0 = 256;
+      L.w1 = 0;
+    }
   }
   p->status_dev = nullptr;
   p->decode = (M <= 128) && !(flags & SMB_FLAG_NO_DECODE) && mtile_group == nullptr;
@@ -176,7 +181,8 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
     D.activations_dynamic = false;
     D.block16 = block16;
     D.alpha = 1.0f;
-    D.dual = fp4_decode_prefers_dual(M);
+    D.swiglu = swiglu;
+    D.dual = swiglu ? true : fp4_decode_prefers_dual(M);
     if (flags & SMB_FLAG_DECODE_DUAL) D.dual = true;
     // Asked for by name, the dual form keeps its operands swapped for every M (no wide form).
     D.narrow = (flags & SMB_FLAG_DECODE_DUAL) != 0;

@@ -155,6 +155,7 @@ struct Fp4Launch {
   float alpha;       // factor on every accumulator (block16 only; 1 otherwise)
   bool uniform_tiles;  // true: full-width tiles only (no narrower tiles at the end of the tile list)
   int l2_a, l2_b;    // L2 eviction hints of the A / B loads: 0 none, 1 evict-last, 2 evict-first
+  bool handover;     // 256 + 128 tile: accumulator handed over per sub-block (default) or as a whole
 };
 void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1);
 void fp4_split_phases(int M, int N, int K, int w0, int w1, int clusters, int* wide_tiles_n, int* narrow_tiles_n);
@@ -190,6 +191,7 @@ struct Fp4DecodeLaunch {
   bool narrow;       // true: never the wide form (activations as the instruction's rows) of the dual kernel
   bool block16;      // E4M3 scales per 16 K (dual form only); tmap_sfw / tmap_sfx boxes are 256 words
   float alpha;       // factor on every accumulator (block16 only)
+  bool swiglu;       // gated epilogue: D is [M, N/2] = silu(acc[:, 1::2]) * acc[:, 0::2]; set before binding D
 };
 int fp4_decode_stage_bytes(int m_pad);
 bool fp4_decode_prefers_dual(int M);   // default choice of Fp4DecodeLaunch::dual for M activation rows

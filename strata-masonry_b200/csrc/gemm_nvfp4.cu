@@ -111,6 +111,7 @@ struct Params {
   float alpha;          // factor on every accumulator (block-16 variant: 1 / (global scale A x B))
   int operands_static;  // 1: operands and scales are not written by the previous kernel on the stream
   int l2_a, l2_b;       // L2 eviction hint of the A / B loads: 0 none, 1 evict-last, 2 evict-first
+  int handover;         // two-sub-block tiles: 1 = accumulator handed over sub-block by sub-block
 };
 
 enum { kProfLoadWait = 0, kProfLoadTotal, kProfMmaWaitFull, kProfMmaWaitAcc, kProfMmaTotal,
@@ -156,7 +157,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr int kCells = C::kCells;
   constexpr bool kTmaStore = (kStore != kStorePlain);
   constexpr bool kSwiglu = (kStore == kStoreSwiglu);   // D is [M, N/2]: silu(gate) * up
-  static_assert(!kSwiglu || C::kColsPerWarp % 128 == 0, "gated epilogue: 64 output columns per box");
+  static_assert(!kSwiglu || C::kSubs == 2 || C::kColsPerWarp % 128 == 0, "gated epilogue: 64 output columns per box");
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -379,7 +380,35 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (V4) mma_nvf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc, sfa_t, sfb_t, accum);
             else mma_mxf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc, sfa_t, sfb_t, accum);
           };
-          if (C::kSubs == 2 && (kb == 0 || kb == num_kb - 1)) {
+          if (C::kSubs == 2 && p.handover == 0 && (kb == 0 || kb == num_kb - 1)) {
+            // Both sub-blocks taken over before the first instruction and handed back after the last.
+            if (kb == 0) {
+              for (int h = 0; h < 2 && ok; ++h) {
+                if (h == 1 && !has_sub1) break;
+                const uint32_t use = static_cast<uint32_t>(h == 0 ? local : sub1_tiles) & 1u;
+                if (!mbar_wait(acc_empty_bar(h), use ^ 1u)) {
+                  report_status(p.status, kDevTimeoutMmaAcc);
+                  ok = false;
+                }
+              }
+              if (!ok) break;
+              tc_fence_after_sync();
+            }
+            if (elect_one()) {
+#pragma unroll
+              for (int ki = 0; ki < 4; ++ki) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  if (h == 0 || has_sub1) issue(h, ki);
+                }
+              }
+              mma_commit_pair(empty_bar(s), 0x3);
+              if (kb == num_kb - 1) {
+                mma_commit_pair(acc_full_bar(0), 0x3);
+                if (has_sub1) mma_commit_pair(acc_full_bar(1), 0x3);
+              }
+            }
+          } else if (C::kSubs == 2 && (kb == 0 || kb == num_kb - 1)) {
             // First and last K block of a two-sub-block tile: sub-block by sub-block, so that each
             // is taken over from the epilogue (first block) and handed to it (last block) on its
             // own.  The epilogue drains sub-block 0 first; its columns are multiplied again while
@@ -525,7 +554,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // A narrow tile has no second sub-block: its accumulator columns beyond W0 hold nothing and
       // the columns of D there belong to the next tile.
       if (C::kSubs == 2) {
-        const int limit = tile_col0 + (full_width ? C::kTileN : W0);
+        const int limit = (tile_col0 + (full_width ? C::kTileN : W0)) / (kSwiglu ? 2 : 1);
         out.N = limit < n_out ? limit : n_out;
       }
       const int bank = C::kTwoBanks ? (local & 1) : 0;
@@ -535,9 +564,16 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if constexpr (C::kSubs == 2) {
         // Sub-block by sub-block (see the MMA role): both warp groups read their half of
         // sub-block 0 and hand it back, then their half of sub-block 1, and only then store.
-        static_assert(W0 == 256 && W1 == 128 && !kSwiglu, "two sub-blocks: the 256 + 128 tile");
+        static_assert(W0 == 256 && W1 == 128, "two sub-blocks: the 256 + 128 tile");
         const bool has_sub1 = full_width && (tile_col0 + W0 < p.N);
-        uint32_t packed0[64], packed1[32];
+        // Plain: group g takes 128 columns of sub-block 0 and 64 of sub-block 1.  Gated: four
+        // accumulator columns make two outputs, so 128 columns fill one 64-column store box: group g
+        // takes 128 columns of sub-block 0, group 0 all 128 of sub-block 1.
+        constexpr int kOut0 = kSwiglu ? 64 : 128;
+        constexpr int kCols1 = kSwiglu ? 128 : 64;
+        constexpr int kOut1 = 64;
+        uint32_t packed0[kOut0 / 2], packed1[kOut1 / 2];
+        const bool reads_sub1 = !kSwiglu || group == 0;
         const long long w0 = prof ? clock64() : 0;
         if (!mbar_wait(acc_full_bar(0), static_cast<uint32_t>(local) & 1u)) {
           if (lane == 0) report_status(p.status, kDevTimeoutEpilogue);
@@ -546,7 +582,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         if (prof) waited += clock64() - w0;
         tc_fence_after_sync();
-        drain_columns<128, false, V4>(lane_base + static_cast<uint32_t>(group * 128), out.alpha, packed0);
+        drain_columns<128, kSwiglu, V4>(lane_base + static_cast<uint32_t>(group * 128), out.alpha, packed0);
         release_columns(leader_acc_empty0, lane);
         if (has_sub1) {
           const long long w1 = prof ? clock64() : 0;
@@ -557,12 +593,16 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           if (prof) waited += clock64() - w1;
           tc_fence_after_sync();
-          drain_columns<64, false, V4>(lane_base + static_cast<uint32_t>(W0 + group * 64), out.alpha, packed1);
+          if (reads_sub1)
+            drain_columns<kCols1, kSwiglu, V4>(lane_base + static_cast<uint32_t>(W0 + (kSwiglu ? 0 : group * 64)),
+                                               out.alpha, packed1);
           release_columns(leader_acc_empty0 + 8u, lane);
           ++sub1_tiles;
         }
-        store_columns<128, kTmaStore>(packed0, sbuf, out, row0, tile_col0 + group * 128, lane);
-        if (has_sub1) store_columns<64, kTmaStore>(packed1, sbuf, out, row0, tile_col0 + W0 + group * 64, lane);
+        const int out_col0 = (tile_col0 + group * 128) / (kSwiglu ? 2 : 1);
+        const int out_col1 = kSwiglu ? (tile_col0 + W0) / 2 : tile_col0 + W0 + group * 64;
+        store_columns<kOut0, kTmaStore>(packed0, sbuf, out, row0, out_col0, lane);
+        if (has_sub1 && reads_sub1) store_columns<kOut1, kTmaStore>(packed1, sbuf, out, row0, out_col1, lane);
       } else {
         const long long w0 = prof ? clock64() : 0;
         if (!mbar_wait(acc_full_bar(bank), use_parity)) {
@@ -660,6 +700,7 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   p.prefetch = L.prefetch;
   p.l2_a = L.l2_a;
   p.l2_b = L.l2_b;
+  p.handover = L.handover ? 1 : 0;
   const long long tiles = static_cast<long long>(p.tiles_m) * (p.tiles_n + p.narrow_tiles_n);
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (L.max_clusters > 0 && clusters > L.max_clusters) clusters = L.max_clusters;
@@ -697,10 +738,10 @@ int launch_fp4_store(const Fp4Launch& L, cudaStream_t stream) {
     }
   }
   if (L.swiglu) {
-    if constexpr (W0 == 256 && W1 == 0) {
+    if constexpr (W0 == 256) {
       return launch_fp4<W0, W1, fp4k::kStoreSwiglu>(L, stream);
     } else {
-      return set_error(SMB_ERR_UNSUPPORTED, "nvfp4: the gated epilogue needs 256-wide tiles");
+      return set_error(SMB_ERR_UNSUPPORTED, "nvfp4: the gated epilogue needs tiles of 256 or 384 columns");
     }
   }
   if constexpr (W0 == 128 && W1 == 0) {

@@ -612,6 +612,9 @@ struct DualParams {
   // (the buffers tmap_x / tmap_sfx read) and meet on act_counter before any of them loads
   // activations; see the comment at the top of decode_dual_body.
   int act_spread;
+  // Gated epilogue (the tiled kernels' kSwiglu store mode): weight rows are interleaved, row 2n =
+  // up projection n, row 2n + 1 = gate projection n; D is [M, N / 2] = silu(gate) * up.
+  int swiglu;
   uint8_t* act_codes;                 // [M, K/2] E2M1 codes
   uint8_t* act_sf;                    // packed UE8M0 scales of X
   unsigned long long* act_counter;    // arrivals of all launches so far (never reset)
@@ -960,6 +963,28 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
     bool store_pending = false;
     bool waited_for_previous_grid = false;
     int seg = 0;
+    // Gated epilogue in the swapped forms: a thread holds one weight row, so the (up, gate) pair
+    // of an output sits in two neighbouring lanes; the even lane gets the gate from its
+    // neighbour, applies the activation and stores output column row / 2 of the tile's 64.
+    const bool gated = p.swiglu != 0;
+    const bool writer = !gated || (lane & 1) == 0;
+    const int out_row = gated ? (row >> 1) : row;                 // column inside the tile's output block
+    const uint32_t out_pitch = gated ? 128u : 256u;               // bytes per activation row in the staging block
+    const int out_tile_cols = gated ? 64 : 128;
+    const int n_out = gated ? p.N / 2 : p.N;
+    auto finish = [&](float (&v)[16]) {
+      if (V4) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
+      }
+      if (gated) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+          v[j] = swiglu_f32(other, v[j]);     // meaningful in even lanes: own = up, neighbour = gate
+        }
+      }
+    };
     if (p.act_spread) {
       // This CTA's share of the activation quantiser (see the top of this function); the four
       // warps 8-11 take part even where they have no accumulator columns to drain.
@@ -1000,13 +1025,18 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
         out.d_ptr = p.d;
         out.ldd = p.ldd;
         out.M = p.M;
-        out.N = p.N;
+        out.N = p.swiglu ? p.N / 2 : p.N;
         out.peers = &none;
         out.alpha = p.alpha;
         const uint32_t sbuf = ring_base + static_cast<uint32_t>((warp - 4) * kStoreBufBytes);
         const uint32_t release = mapa_u32(acc_empty_bar(bank), 0);
         const int col0 = (2 * q + group) * 128;
-        if (p.d_tma) {
+        if (p.d_tma && p.swiglu) {
+          // 128 accumulator columns = one weight tile = 64 gated outputs = one store box.
+          drain_and_store<128, true, true, V4>(tbase + static_cast<uint32_t>(group * 128), sbuf, out,
+                                               quarter * 32, col0, release, lane);
+          drain_store_groups<true>(lane);
+        } else if (p.d_tma) {
           drain_and_store<128, true, false, V4>(tbase + static_cast<uint32_t>(group * 128), sbuf, out,
                                                 quarter * 32, col0, release, lane);
           drain_store_groups<true>(lane);
@@ -1025,14 +1055,14 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
           for (int c = col_begin; c < col_end; c += 16) {
             float v[16];
             ld16(tbase + static_cast<uint32_t>(sub * p.m_pad + c), v);
-            if (V4) {
+            finish(v);
+            if (writer) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const uint32_t dst = ring_base + static_cast<uint32_t>((sub * p.m_pad + c + j) * 256 + row * 2);
-              asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst), "h"(to_bf16(v[j])) : "memory");
+              for (int j = 0; j < 16; ++j) {
+                const uint32_t dst = ring_base + static_cast<uint32_t>((sub * p.m_pad + c + j)) * out_pitch +
+                                     static_cast<uint32_t>(out_row * 2);
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst), "h"(to_bf16(v[j])) : "memory");
+              }
             }
           }
         }
@@ -1043,7 +1073,8 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
             const int tile = 2 * q + sub;
             if (tile >= tiles) break;
             for (int c0 = 0; c0 < p.m_pad; c0 += chunk_rows) {
-              tma_store_2d(&tmap_d, ring_base + static_cast<uint32_t>((sub * p.m_pad + c0) * 256), tile * 128, c0);
+              tma_store_2d(&tmap_d, ring_base + static_cast<uint32_t>(sub * p.m_pad + c0) * out_pitch,
+                           tile * out_tile_cols, c0);
             }
           }
           bulk_commit_group();
@@ -1064,20 +1095,20 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
               for (int c = lo; c < hi; c += 16) {
                 float v[16];
                 ld16(taddr + c, v);
-                if (V4) {
+                finish(v);
+                if (writer) {
 #pragma unroll
-                  for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  const uint32_t dst = stage_base + static_cast<uint32_t>((c - c0 + j) * 256 + row * 2);
-                  asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst), "h"(to_bf16(v[j])) : "memory");
+                  for (int j = 0; j < 16; ++j) {
+                    const uint32_t dst = stage_base + static_cast<uint32_t>(c - c0 + j) * out_pitch +
+                                         static_cast<uint32_t>(out_row * 2);
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst), "h"(to_bf16(v[j])) : "memory");
+                  }
                 }
               }
               fence_proxy_async_smem();
               asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
               if (first_thread) {
-                tma_store_2d(&tmap_d, stage_base, tile * 128, c0);
+                tma_store_2d(&tmap_d, stage_base, tile * out_tile_cols, c0);
                 bulk_commit_group();
                 store_pending = true;
               }
@@ -1086,14 +1117,12 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
             for (int c = col_begin; c < col_end; c += 16) {
               float v[16];
               ld16(taddr + c, v);
-              if (V4) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
-              }
-              if (n < p.N) {
+              finish(v);
+              const int n_store = gated ? tile * 64 + out_row : n;
+              if (writer && n_store < n_out) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                  if (c + j < p.M) p.d[static_cast<size_t>(c + j) * p.ldd + n] = to_bf16(v[j]);
+                  if (c + j < p.M) p.d[static_cast<size_t>(c + j) * p.ldd + n_store] = to_bf16(v[j]);
                 }
               }
             }
@@ -1249,6 +1278,7 @@ int fp4_decode_dual_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
   p.alpha = L.alpha;
   p.x_src = static_cast<const uint16_t*>(L.act_src);
   p.ldx = L.act_ld;
+  p.swiglu = L.swiglu ? 1 : 0;
   p.act_spread = (!kFused && fp4_decode_spreads_activations(L)) ? 1 : 0;
   p.act_codes = static_cast<uint8_t*>(L.act_codes);
   p.act_sf = static_cast<uint8_t*>(L.act_sf);
@@ -1321,6 +1351,10 @@ int fp4_decode_launch(const Fp4DecodeLaunch& L, cudaStream_t stream) {
     return wide ? fp4_decode_dual_launch<true, true>(L, stream) : fp4_decode_dual_launch<true, false>(L, stream);
   if (L.dual && L.max_ctas == 0)
     return wide ? fp4_decode_dual_launch<false, true>(L, stream) : fp4_decode_dual_launch<false, false>(L, stream);
+  if (L.swiglu)
+    return set_error(SMB_ERR_UNSUPPORTED,
+                     "decode: the gated epilogue exists for the tile-pair forms (no forced CTA count, not the "
+                     "single-tile form)");
   static thread_local int configured_device = -1;
   static thread_local int sm_count = 0;
   constexpr int kSmemBudget = 227 * 1024;
@@ -1406,10 +1440,12 @@ int fp4_decode_bind_output(Fp4DecodeLaunch* L, void* d, int M, int N, long long 
   L->ldd = static_cast<int>(ldd);
   L->d_tma = allow_tma && (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0);
   if (L->d_tma) {
-    int rc = encode_tmap_2d(&L->tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldd * 2,
-                            fp4_decode_box_rows(M), 128, false);
+    // Gated epilogue: D is [M, N / 2] and a weight tile of 128 rows yields 64 output columns.
+    const int n_out = L->swiglu ? N / 2 : N;
+    int rc = encode_tmap_2d(&L->tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, n_out, ldd * 2,
+                            fp4_decode_box_rows(M), L->swiglu ? 64 : 128, false);
     if (rc == SMB_OK)
-      rc = encode_tmap_2d(&L->tmap_d_rows, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldd * 2, 32, 64, true);
+      rc = encode_tmap_2d(&L->tmap_d_rows, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, n_out, ldd * 2, 32, 64, true);
     return rc;
   }
   L->tmap_d = L->tmap_w;   // never dereferenced
@@ -1540,6 +1576,10 @@ extern "C" int smb_dense_gemm_nvfp4_decode_noalloc(const void* a, const void* sf
   L.act_ld = 0;
   L.block16 = false;
   L.alpha = 1.0f;
+  L.swiglu = false;
+  L.act_mode = 0;
+  L.act_codes = L.act_sf = nullptr;
+  L.act_counter = nullptr;
   L.no_overlap = true;   // the clears below must be ordered before every access of this launch
   L.scratch = static_cast<float*>(base);
   L.scratch_ctas = ctas;

@@ -755,8 +755,14 @@ def test_gated_epilogue_is_refused_where_it_cannot_work(smb, cuda_device):
     xa, xsfa, _ = _fp4_operand(smb, 16, 256, 6, 0)
     w, wsf, _ = _fp4_operand(smb, 256, 256, 5, 1)
     dd = torch.zeros(16, 128, device=cuda_device, dtype=torch.bfloat16)
-    with pytest.raises(capi.SmbError):       # decode shapes have no gated epilogue
-        smb.gemm.Fp4Plan(xa, xsfa, w, wsf, dd, 16, 256, 256, ldd=128, flags=capi.FLAG_EPILOGUE_SWIGLU)
+    with pytest.raises(capi.SmbError):       # the decode kernel's single-tile form has no gated epilogue
+        smb.gemm.Fp4Plan(xa, xsfa, w, wsf, dd, 16, 256, 256, ldd=128,
+                         flags=capi.FLAG_EPILOGUE_SWIGLU | capi.FLAG_DECODE_SINGLE)
+    plan = smb.gemm.Fp4Plan(xa, xsfa, w, wsf, dd, 16, 256, 256, ldd=128, flags=capi.FLAG_EPILOGUE_SWIGLU)
+    plan.tune(0, 4, -1)                      # ... nor do its stream-K ranges (a forced CTA count)
+    with pytest.raises(capi.SmbError):
+        plan.run()
+    plan.close()
 
 
 @pytest.mark.parametrize("form", ["FLAG_DECODE_DUAL", "FLAG_DECODE_SINGLE"])
@@ -1056,3 +1062,61 @@ def test_fp4_configurations_under_the_reference_verifier_rule(smb, golden, cuda_
     cols = torch.from_numpy(golden[f"cfg_{name}_cols"]).to(d.device)
     atol, rtol = golden["cfg_tolerances"][2:]
     assert _verifier_mismatches(_bits(d[rows, cols]), golden[f"cfg_{name}_ref_m2"], atol, rtol) == 0
+
+
+# ------------------------------------------------------------------------------- gated epilogue, wider coverage
+def _check_swiglu_torch(acc64, d, k):
+    """silu(gate) * up in float64 on the exact accumulators, with the bound of the tiled kernels'
+    gated-epilogue test: the north-star bound on each accumulator carried through the activation."""
+    torch = _torch()
+    up, gate = acc64[:, 0::2], acc64[:, 1::2]
+    want = gate / (1.0 + torch.exp(-gate)) * up
+    rms = float(acc64.pow(2).mean().sqrt())
+    eps_acc = 2.0 ** -7 * acc64.abs() + 2.0 ** -10 * (k ** 0.5) * rms
+    eps_up, eps_gate = eps_acc[:, 0::2], eps_acc[:, 1::2] + 2.0 ** -10 * gate.abs() + 2.0 ** -9
+    silu = gate / (1.0 + torch.exp(-gate))
+    bound = 2.0 ** -7 * want.abs() + 1.1 * up.abs() * eps_gate + silu.abs() * eps_up + 1e-6
+    got = d.double()
+    bad = ~torch.isfinite(got) | ((got - want).abs() > bound)
+    assert int(bad.sum()) == 0, f"{int(bad.sum())} gated outputs outside the bound"
+
+
+@pytest.mark.parametrize("shape", [(16, 1024, 1024), (64, 4096, 512), (100, 1000, 1056), (128, 28672, 1024),
+                                   (1, 256, 256), (33, 130 * 2, 96)])
+def test_fp4_decode_gated_epilogue(smb, cuda_device, shape):
+    """SMB_FLAG_EPILOGUE_SWIGLU on the decode kernel (an MLP up/gate projection at decode): weight
+    rows interleaved (2n = up, 2n + 1 = gate), D = [M, N / 2], in the swapped forms (neighbouring
+    lanes exchange their accumulators) and the wide form (M > 64)."""
+    torch = _torch()
+    m, n, k = shape
+    a, sfa, sfar = _fp4_operand(smb, m, k, 6, 0)
+    b, sfb, sfbr = _fp4_operand(smb, n, k, 5, 1)
+    ldd = n // 2 + 8
+    d = torch.full((m, ldd), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k, ldd=ldd, flags=smb.capi.FLAG_EPILOGUE_SWIGLU)
+    assert plan.describe().startswith("fp4 decode")
+    plan.run()
+    plan.check()
+    plan.close()
+    assert bool(torch.isnan(d[:, n // 2:].float()).all()), "padding columns were written"
+    acc = _dequant(a, sfar) @ _dequant(b, sfbr).t()
+    _check_swiglu_torch(acc, d[:, :n // 2], k)
+
+
+def test_fp4_gated_epilogue_on_the_384_tile(smb, cuda_device):
+    torch = _torch()
+    m, n, k = 768, 2432, 512
+    a, sfa, sfar = _fp4_operand(smb, m, k, 5, 0)
+    b, sfb, sfbr = _fp4_operand(smb, n, k, 5, 1)
+    d = torch.full((m, n // 2), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k, ldd=n // 2,
+                            flags=smb.capi.FLAG_EPILOGUE_SWIGLU | smb.capi.FLAG_TILE_N_384)
+    assert "256x384" in plan.describe() and "swiglu" in plan.describe()
+    for clusters in (0, 5):
+        d.fill_(float("nan"))
+        plan.tune(0, clusters, -1)
+        plan.run()
+        plan.check()
+        acc = _dequant(a, sfar) @ _dequant(b, sfbr).t()
+        _check_swiglu_torch(acc, d, k)
+    plan.close()
