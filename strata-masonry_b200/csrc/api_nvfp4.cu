@@ -92,8 +92,6 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
     }
   }
   if (getenv("SMB_TUNE_FP4_UNIFORM")) L.uniform_tiles = true;
-  L.handover = true;
-  if (const char* env = getenv("SMB_TUNE_FP4_HANDOVER")) L.handover = env[0] != '0';
   L.dynamic = (flags & SMB_FLAG_DYNAMIC_TILES) != 0;
   L.operands_static = (flags & (SMB_FLAG_OPERANDS_STATIC | SMB_FLAG_LAUNCH_INDEPENDENT)) != 0;
   L.output_independent = (flags & SMB_FLAG_LAUNCH_INDEPENDENT) != 0;

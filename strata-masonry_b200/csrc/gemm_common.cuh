@@ -155,7 +155,6 @@ struct Fp4Launch {
   float alpha;       // factor on every accumulator (block16 only; 1 otherwise)
   bool uniform_tiles;  // true: full-width tiles only (no narrower tiles at the end of the tile list)
   int l2_a, l2_b;    // L2 eviction hints of the A / B loads: 0 none, 1 evict-last, 2 evict-first
-  bool handover;     // 256 + 128 tile: accumulator handed over per sub-block (default) or as a whole
 };
 void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1);
 void fp4_split_phases(int M, int N, int K, int w0, int w1, int clusters, int* wide_tiles_n, int* narrow_tiles_n);

@@ -111,7 +111,6 @@ struct Params {
   float alpha;          // factor on every accumulator (block-16 variant: 1 / (global scale A x B))
   int operands_static;  // 1: operands and scales are not written by the previous kernel on the stream
   int l2_a, l2_b;       // L2 eviction hint of the A / B loads: 0 none, 1 evict-last, 2 evict-first
-  int handover;         // two-sub-block tiles: 1 = accumulator handed over sub-block by sub-block
 };
 
 enum { kProfLoadWait = 0, kProfLoadTotal, kProfMmaWaitFull, kProfMmaWaitAcc, kProfMmaTotal,
@@ -380,9 +379,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (V4) mma_nvf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc, sfa_t, sfb_t, accum);
             else mma_mxf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc, sfa_t, sfb_t, accum);
           };
-          if (C::kSubs == 2 && p.handover == 0 && (kb == 0 || kb == num_kb - 1)) {
-            // Both sub-blocks taken over before the first instruction and handed back after the last.
+          if (C::kSubs == 2 && (kb == 0 || kb == num_kb - 1)) {
+            // Two sub-blocks have a barrier pair each (a narrow tile uses only the first): both are
+            // taken over from the epilogue before the tile's first instruction and handed back
+            // after its last.  (Handing them over one by one, sub-block 0 multiplied again while
+            // sub-block 1 is still being read out, measured no faster: 6068 against 6082 TFLOP/s at
+            // 8192^3, 4396 against 4413 at 14080 x 5120 x 2048.)
             if (kb == 0) {
+              const long long a0 = prof ? clock64() : 0;
               for (int h = 0; h < 2 && ok; ++h) {
                 if (h == 1 && !has_sub1) break;
                 const uint32_t use = static_cast<uint32_t>(h == 0 ? local : sub1_tiles) & 1u;
@@ -392,6 +396,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
               }
               if (!ok) break;
+              if (prof) wait_acc += clock64() - a0;
               tc_fence_after_sync();
             }
             if (elect_one()) {
@@ -408,35 +413,6 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (has_sub1) mma_commit_pair(acc_full_bar(1), 0x3);
               }
             }
-          } else if (C::kSubs == 2 && (kb == 0 || kb == num_kb - 1)) {
-            // First and last K block of a two-sub-block tile: sub-block by sub-block, so that each
-            // is taken over from the epilogue (first block) and handed to it (last block) on its
-            // own.  The epilogue drains sub-block 0 first; its columns are multiplied again while
-            // sub-block 1 is still being read out, and sub-block 0 of the finished tile is on its
-            // way out while the last instructions of sub-block 1 run.
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              if (h == 1 && !has_sub1) break;
-              if (kb == 0) {
-                const uint32_t use = static_cast<uint32_t>(h == 0 ? local : sub1_tiles) & 1u;
-                const long long a0 = prof ? clock64() : 0;
-                if (!mbar_wait(acc_empty_bar(h), use ^ 1u)) {
-                  report_status(p.status, kDevTimeoutMmaAcc);
-                  ok = false;
-                  break;
-                }
-                if (prof) wait_acc += clock64() - a0;
-                tc_fence_after_sync();
-              }
-              if (elect_one()) {
-#pragma unroll
-                for (int ki = 0; ki < 4; ++ki) issue(h, ki);
-                if (kb == num_kb - 1) mma_commit_pair(acc_full_bar(h), 0x3);
-              }
-              __syncwarp();
-            }
-            if (!ok) break;
-            if (elect_one()) mma_commit_pair(empty_bar(s), 0x3);
           } else if (elect_one()) {
 #pragma unroll
             for (int ki = 0; ki < 4; ++ki) {
@@ -562,8 +538,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row0 = tm * 256 + static_cast<int>(rank) * kBlockM + quarter * 32;
       const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
       if constexpr (C::kSubs == 2) {
-        // Sub-block by sub-block (see the MMA role): both warp groups read their half of
-        // sub-block 0 and hand it back, then their half of sub-block 1, and only then store.
+        // Both warp groups read their half of sub-block 0 and hand it back, then their share of
+        // sub-block 1 (if the tile has one), and only then store.
         static_assert(W0 == 256 && W1 == 128, "two sub-blocks: the 256 + 128 tile");
         const bool has_sub1 = full_width && (tile_col0 + W0 < p.N);
         // Plain: group g takes 128 columns of sub-block 0 and 64 of sub-block 1.  Gated: four
@@ -700,7 +676,6 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   p.prefetch = L.prefetch;
   p.l2_a = L.l2_a;
   p.l2_b = L.l2_b;
-  p.handover = L.handover ? 1 : 0;
   const long long tiles = static_cast<long long>(p.tiles_m) * (p.tiles_n + p.narrow_tiles_n);
   int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (L.max_clusters > 0 && clusters > L.max_clusters) clusters = L.max_clusters;

@@ -1091,7 +1091,7 @@ def test_fp4_decode_gated_epilogue(smb, cuda_device, shape):
     m, n, k = shape
     a, sfa, sfar = _fp4_operand(smb, m, k, 6, 0)
     b, sfb, sfbr = _fp4_operand(smb, n, k, 5, 1)
-    ldd = n // 2 + 8
+    ldd = (n // 2 + 7) // 8 * 8 + 8
     d = torch.full((m, ldd), float("nan"), device=cuda_device, dtype=torch.bfloat16)
     plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k, ldd=ldd, flags=smb.capi.FLAG_EPILOGUE_SWIGLU)
     assert plan.describe().startswith("fp4 decode")
