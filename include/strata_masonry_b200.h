@@ -171,6 +171,14 @@ int smb_bf16_plan_wait_probe(smb_bf16_plan* plan, long long budget_cycles, void*
 int smb_bf16_grouped_plan_create(smb_bf16_plan** plan, const void* a, const void* bt_stacked, void* d,
                                  int M_total, int N, int K, int groups, const int* mtile_group_dev,
                                  unsigned flags);
+/* The same for groups of ANY row count, the layout a token permutation yields without padding
+ * (the tile map the reference describes, composites/83_grouped_gemm_tile_map.cuh:71-101, cuts
+ * every group into tiles of its own): group g owns rows [group_offsets[g], group_offsets[g + 1]) of
+ * A and D (host array of groups + 1 ints, offsets[0] = 0, M_total = offsets[groups]; empty groups
+ * allowed).  The plan builds the row-tile table itself; the last tile of a group stores only the
+ * group's own rows.  Contiguous operands (lda = ldb = K, ldd = N, or N / 2 with the gated epilogue). */
+int smb_bf16_grouped_plan_create_offsets(smb_bf16_plan** plan, const void* a, const void* bt_stacked, void* d,
+                                         int N, int K, int groups, const int* group_offsets, unsigned flags);
 /* Tuning knobs (tests and sweeps): raster group height in tiles (0 = default), cap on
  * clusters (0 = all that fit). */
 int smb_bf16_plan_tune(smb_bf16_plan* plan, int group_m, int max_clusters);
@@ -241,6 +249,12 @@ int smb_fp4_plan_set_alpha(smb_fp4_plan* plan, float alpha);
 int smb_fp4_grouped_plan_create(smb_fp4_plan** plan, const void* a, const void* sfa, const void* b_stacked,
                                 const void* sfb_stacked, void* d, int M_total, int N, int K, int groups,
                                 const int* mtile_group_dev, unsigned flags);
+/* Groups of any row count for the FP4 GEMM, with one restriction: every group starts on a multiple
+ * of 128 rows (the packed scales of A come in bands of 128 rows), i.e. groups are padded to 128, not
+ * to 256, and the last tile of a group stores only the group's own rows. */
+int smb_fp4_grouped_plan_create_offsets(smb_fp4_plan** plan, const void* a, const void* sfa, const void* b_stacked,
+                                        const void* sfb_stacked, void* d, int N, int K, int groups,
+                                        const int* group_offsets, unsigned flags);
 int smb_fp4_plan_run(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_check(smb_fp4_plan* plan, void* stream);
 int smb_fp4_plan_destroy(smb_fp4_plan* plan);

@@ -69,6 +69,9 @@ DECLARED = [
     ("smb_debug_fp4_tile", None, [_i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     ("smb_bf16_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, C.c_uint]),
     ("smb_bf16_grouped_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, _i, _vp, C.c_uint]),
+    ("smb_bf16_grouped_plan_create_offsets", _i, [C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, C.POINTER(_i), C.c_uint]),
+    ("smb_fp4_grouped_plan_create_offsets", _i,
+     [C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i, _i, _i, C.POINTER(_i), C.c_uint]),
     ("smb_bf16_plan_run", _i, [_vp, _vp]),
     ("smb_bf16_plan_check", _i, [_vp, _vp]),
     ("smb_bf16_plan_destroy", _i, [_vp]),

@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <new>
+#include <vector>
 
 #include "gemm_common.cuh"
 
@@ -19,6 +20,7 @@ struct smb_bf16_plan {
   Bf16Launch launch;
   int* status_dev;
   bool owns_status;
+  int* tile_table_dev;   // ragged grouped plans: [3][tiles] = first row, end of group, group id
   int device;   // the device that was current at creation: pointers and status word live there
 };
 
@@ -102,6 +104,9 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
   L.peers.route_rows = 0;
   L.peers.first_block = 0;
   L.mtile_group = mtile_group;
+  L.tile_row0 = L.tile_row_end = nullptr;
+  L.tile_rows = 0;
+  p->tile_table_dev = nullptr;
   L.d = d;
   L.ldd = static_cast<int>(ldd);
   L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
@@ -166,6 +171,71 @@ extern "C" int smb_bf16_grouped_plan_create(smb_bf16_plan** out, const void* a, 
     return set_error(SMB_ERR_UNSUPPORTED, "grouped plan: groups * N too large");
   return bf16_plan_create_impl(out, a, bt_stacked, d, M_total, N, K, K, K, N, flags, nullptr, groups,
                                mtile_group_dev);
+}
+
+namespace smb {
+// Row tiles of a grouped problem whose groups have any number of rows: group g owns rows
+// [offsets[g], offsets[g + 1]) and is cut into tiles of 256 rows from its own first row; the last
+// tile of a group reads on into the next group's rows (or past the end of A, where the loads
+// return zeros) and stores only its own.  Builds [first row | end of group | group id] for every
+// tile on the host and copies it to the device.  `align`: required multiple of every offset.
+int build_group_tiles(const int* offsets, int groups, int align, int** table_dev, int* tiles_out, int* m_total) {
+  if (offsets == nullptr || groups < 1) return set_error(SMB_ERR_INVALID, "grouped plan: null offsets or no group");
+  if (offsets[0] != 0) return set_error(SMB_ERR_INVALID, "grouped plan: offsets must start at 0");
+  std::vector<int> row0, row_end, group;
+  for (int g = 0; g < groups; ++g) {
+    const int lo = offsets[g], hi = offsets[g + 1];
+    if (hi < lo) return set_error(SMB_ERR_INVALID, "grouped plan: offsets must not decrease (group %d)", g);
+    if (lo % align != 0)
+      return set_error(SMB_ERR_UNSUPPORTED, "grouped plan: group %d starts at row %d, not a multiple of %d", g, lo, align);
+    for (int r = lo; r < hi; r += 256) {
+      row0.push_back(r);
+      row_end.push_back(hi);
+      group.push_back(g);
+    }
+  }
+  const int tiles = static_cast<int>(row0.size());
+  if (tiles == 0) return set_error(SMB_ERR_INVALID, "grouped plan: every group is empty");
+  std::vector<int> table;
+  table.insert(table.end(), row0.begin(), row0.end());
+  table.insert(table.end(), row_end.begin(), row_end.end());
+  table.insert(table.end(), group.begin(), group.end());
+  int* dev = nullptr;
+  cudaError_t e = cudaMalloc(&dev, table.size() * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemcpy(dev, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    if (dev) cudaFree(dev);
+    return set_cuda_error(e, "grouped plan: tile table");
+  }
+  *table_dev = dev;
+  *tiles_out = tiles;
+  *m_total = offsets[groups];
+  return SMB_OK;
+}
+}  // namespace smb
+
+extern "C" int smb_bf16_grouped_plan_create_offsets(smb_bf16_plan** out, const void* a, const void* bt_stacked,
+                                                    void* d, int N, int K, int groups, const int* group_offsets,
+                                                    unsigned flags) {
+  if (out == nullptr) return set_error(SMB_ERR_INVALID, "grouped plan: null output handle");
+  *out = nullptr;
+  if (static_cast<long long>(groups) * N > 0x7FFFFFFFLL)
+    return set_error(SMB_ERR_UNSUPPORTED, "grouped plan: groups * N too large");
+  int* table = nullptr;
+  int tiles = 0, m_total = 0;
+  int rc = build_group_tiles(group_offsets, groups, 1, &table, &tiles, &m_total);
+  if (rc != SMB_OK) return rc;
+  rc = bf16_plan_create_impl(out, a, bt_stacked, d, m_total, N, K, K, K,
+                             (flags & SMB_FLAG_EPILOGUE_SWIGLU) ? N / 2 : N, flags, nullptr, groups, table + 2 * tiles);
+  if (rc != SMB_OK) {
+    cudaFree(table);
+    return rc;
+  }
+  (*out)->tile_table_dev = table;
+  (*out)->launch.tile_row0 = table;
+  (*out)->launch.tile_row_end = table + tiles;
+  (*out)->launch.tile_rows = tiles;
+  return SMB_OK;
 }
 
 extern "C" int smb_bf16_plan_tune(smb_bf16_plan* plan, int group_m, int max_clusters) {
@@ -238,6 +308,7 @@ extern "C" int smb_bf16_plan_wait_probe(smb_bf16_plan* plan, long long budget_cy
 extern "C" int smb_bf16_plan_destroy(smb_bf16_plan* plan) {
   if (plan == nullptr) return SMB_OK;
   if (plan->status_dev && plan->owns_status) cudaFree(plan->status_dev);
+  if (plan->tile_table_dev) cudaFree(plan->tile_table_dev);
   delete plan;
   return SMB_OK;
 }

@@ -11,6 +11,7 @@
 
 namespace smb {
 const char* device_status_name(int code);
+int build_group_tiles(const int* offsets, int groups, int align, int** table_dev, int* tiles_out, int* m_total);
 }
 
 using namespace smb;
@@ -32,6 +33,7 @@ struct smb_fp4_plan {
   void* act_codes;
   void* act_sf;
   void* act_counter;   // 8 bytes: CTAs counted in by the in-kernel quantiser
+  int* tile_table_dev; // ragged grouped plans: [3][tiles] = first row, end of group, group id
 };
 
 namespace {
@@ -99,6 +101,9 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
   L.peers.route_rows = 0;
   L.peers.first_block = 0;
   L.mtile_group = mtile_group;
+  L.tile_row0 = L.tile_row_end = nullptr;
+  L.tile_rows = 0;
+  p->tile_table_dev = nullptr;
   L.d = d;
   L.ldd = static_cast<int>(ldd);
   L.tma_store = (ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) &&
@@ -253,6 +258,35 @@ extern "C" int smb_fp4_grouped_plan_create(smb_fp4_plan** out, const void* a, co
     return set_error(SMB_ERR_UNSUPPORTED, "grouped fp4 plan: groups * N too large");
   return fp4_plan_create_impl(out, a, sfa, b_stacked, sfb_stacked, d, M_total, N, K, K / 2, K / 2, N, flags,
                               groups, mtile_group_dev);
+}
+
+extern "C" int smb_fp4_grouped_plan_create_offsets(smb_fp4_plan** out, const void* a, const void* sfa,
+                                                   const void* b_stacked, const void* sfb_stacked, void* d, int N,
+                                                   int K, int groups, const int* group_offsets, unsigned flags) {
+  if (out == nullptr) return set_error(SMB_ERR_INVALID, "grouped fp4 plan: null output handle");
+  *out = nullptr;
+  if (N % 128 != 0)
+    return set_error(SMB_ERR_UNSUPPORTED,
+                     "grouped fp4 plan: N=%d must be a multiple of 128 (scale bands of the stacked B)", N);
+  if (static_cast<long long>(groups) * N > 0x7FFFFFFFLL)
+    return set_error(SMB_ERR_UNSUPPORTED, "grouped fp4 plan: groups * N too large");
+  int* table = nullptr;
+  int tiles = 0, m_total = 0;
+  // The packed scales of A come in bands of 128 rows: a group has to start on a band.
+  int rc = build_group_tiles(group_offsets, groups, 128, &table, &tiles, &m_total);
+  if (rc != SMB_OK) return rc;
+  rc = fp4_plan_create_impl(out, a, sfa, b_stacked, sfb_stacked, d, m_total, N, K, K / 2, K / 2,
+                            (flags & SMB_FLAG_EPILOGUE_SWIGLU) ? N / 2 : N, flags | SMB_FLAG_NO_DECODE, groups,
+                            table + 2 * tiles);
+  if (rc != SMB_OK) {
+    cudaFree(table);
+    return rc;
+  }
+  (*out)->tile_table_dev = table;
+  (*out)->launch.tile_row0 = table;
+  (*out)->launch.tile_row_end = table + tiles;
+  (*out)->launch.tile_rows = tiles;
+  return SMB_OK;
 }
 
 extern "C" int smb_fp4_plan_tune(smb_fp4_plan* plan, int group_m, int max_clusters, int prefetch) {
@@ -419,6 +453,7 @@ extern "C" int smb_fp4_plan_destroy(smb_fp4_plan* plan) {
   if (plan->act_codes) cudaFree(plan->act_codes);
   if (plan->act_sf) cudaFree(plan->act_sf);
   if (plan->act_counter) cudaFree(plan->act_counter);
+  if (plan->tile_table_dev) cudaFree(plan->tile_table_dev);
   delete plan;
   return SMB_OK;
 }

@@ -26,6 +26,8 @@ struct StoreTarget {
   int M, N;
   const PeerCopies* peers;     // kernel parameter, TMA path only (N % 8 == 0 there)
   float alpha;                 // factor on every accumulator (kScaled instantiations only)
+  int row_end;                 // rows >= row_end are not written (a tile's share of a ragged group;
+                               // M where tiles own whole boxes)
 };
 
 // One warp drains kCols fp32 columns of its 32 TMEM lanes starting at `taddr`, then writes them
@@ -105,9 +107,26 @@ __device__ __forceinline__ void store_columns(const uint32_t (&packed)[kOutCols 
       __syncwarp();
       const int n_peers = out.peers->count;
       const int route_rows = out.peers->route_rows;   // > 0: rows are routed, D itself is not written
+      const bool whole_box = row0 + 32 <= out.row_end || out.row_end >= out.M;
       if (lane == 0) {
-        if (route_rows == 0 && row0 < out.M && gcol0 < out.N) tma_store_2d(out.tmap_d, sbuf, gcol0, row0);
+        if (whole_box && route_rows == 0 && row0 < out.M && gcol0 < out.N) tma_store_2d(out.tmap_d, sbuf, gcol0, row0);
         bulk_commit_group();
+      }
+      if (!whole_box && route_rows == 0 && row0 < out.row_end) {
+        // The tile's rows end inside this box (last tile of a group whose row count is not a
+        // multiple of 32): the rows that belong to it go out with 16-byte stores, lane l chunk
+        // l % 8 of rows l / 8 + 4 i, read back from the swizzled staging box.
+        const int chunk = lane & 7;
+        const int gcol = gcol0 + chunk * 8;
+#pragma unroll 1
+        for (int i = 0; i < 8; ++i) {
+          const int r = i * 4 + (lane >> 3);
+          uint32_t x0, x1, x2, x3;
+          ld_shared_v4(sbuf + r * 128 + ((chunk ^ (r & 7)) << 4), x0, x1, x2, x3);
+          const int grow = row0 + r;
+          if (grow < out.row_end && gcol < out.N)
+            st_global_v4(out.d_ptr + static_cast<long long>(grow) * out.ldd + gcol, x0, x1, x2, x3);
+        }
       }
       if (n_peers > 0) {
         // Lane l copies 16-byte chunk (l % 8) of rows (l / 8) + 4 i: a warp instruction covers
@@ -120,7 +139,7 @@ __device__ __forceinline__ void store_columns(const uint32_t (&packed)[kOutCols 
           uint32_t x0, x1, x2, x3;
           ld_shared_v4(sbuf + r * 128 + ((chunk ^ (r & 7)) << 4), x0, x1, x2, x3);
           const int grow = row0 + r;
-          if (grow < out.M && gcol < out.N) {
+          if (grow < out.M && grow < out.row_end && gcol < out.N) {
             if (route_rows > 0) {
               // Row block b (route_rows rows, a multiple of the tile height, so a warp's 32 rows
               // share it) goes to destination b, at its row inside the block.
@@ -140,7 +159,7 @@ __device__ __forceinline__ void store_columns(const uint32_t (&packed)[kOutCols 
       __syncwarp();
       for (int r = 0; r < 32; ++r) {
         const int grow = row0 + r;
-        if (grow >= out.M) break;
+        if (grow >= out.M || grow >= out.row_end) break;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int cc = h * 32 + lane;

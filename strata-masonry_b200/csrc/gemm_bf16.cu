@@ -86,6 +86,8 @@ struct Params {
   PeerCopies peers;     // extra destinations of every stored box (count 0: none)
   int m_rotate;         // the tile walk starts at this 256-row tile (0 unless rows are routed)
   const int* mtile_group;  // grouped GEMM: group of every 256-row tile of A (device), or null
+  const int* tile_row0;    // ragged groups: first row of every row tile (device), or null: tile t starts at 256 t
+  const int* tile_row_end; // ... and the row where the tile's group ends
   int operands_static;  // 1: A and BT are not written by the previous kernel on the stream
   int l2_a, l2_b;       // L2 eviction hint of the A / BT loads: 0 none, 1 evict-last, 2 evict-first
 };
@@ -191,9 +193,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         tm = (tm + p.m_rotate) % p.tiles_m;   // routed stores: ranks start at different row blocks
-        const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
-        // Grouped GEMM: BT is [groups * N, K]; the rows of this 256-row tile of A belong to one
-        // group (every group's row count is a multiple of 256) and meet that group's N rows.
+        const int row_a = (p.tile_row0 != nullptr ? __ldg(p.tile_row0 + tm) : tm * 256) + static_cast<int>(rank) * kBlockM;
+        // Grouped GEMM: BT is [groups * N, K]; the rows of this row tile of A belong to one group
+        // (rows it reads beyond the end of its group are never stored) and meet that group's N rows.
         const int group_row = p.mtile_group != nullptr ? __ldg(p.mtile_group + tm) * p.N : 0;
         const int row_b = group_row + tn * C::kTileN + static_cast<int>(rank) * (TN / 2);
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -326,6 +328,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       out.N = kSwiglu ? p.N / 2 : p.N;
       out.peers = &p.peers;
       out.alpha = 1.0f;
+      out.row_end = p.M;
       int local = 0;
       bool ok = true;
       if (p.operands_static == 1) griddep_wait();   // 2: D is independent too, no wait at all
@@ -350,7 +353,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         if (prof) waited += clock64() - w0;
         tc_fence_after_sync();
-        const int row0 = tm * 256 + static_cast<int>(rank) * kBlockM + quarter * 32;
+        const int row0 = (p.tile_row0 != nullptr ? __ldg(p.tile_row0 + tm) : tm * 256) +
+                         static_cast<int>(rank) * kBlockM + quarter * 32;
+        out.row_end = p.tile_row_end != nullptr ? __ldg(p.tile_row_end + tm) : p.M;
         // First column (in the tile and in tensor memory) this warp is responsible for.
         const int tile_col = (NB == 1) ? group * C::kColsPerWarp : group * TN;
         const int col0 = tn * C::kTileN + tile_col;
@@ -421,8 +426,10 @@ int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
   p.M = L.M;
   p.N = L.N;
   p.K = L.K;
-  p.tiles_m = (L.M + 255) / 256;
+  p.tiles_m = L.tile_row0 != nullptr ? L.tile_rows : (L.M + 255) / 256;
   p.tiles_n = (L.N + C::kTileN - 1) / C::kTileN;
+  p.tile_row0 = L.tile_row0;
+  p.tile_row_end = L.tile_row_end;
   p.group_m = L.group_m > 0 ? L.group_m : raster_group_rows(p.tiles_m, static_cast<long long>(L.K) * 2);
   p.ldd = L.ldd;
   p.d_ptr = static_cast<uint16_t*>(L.d);

@@ -125,6 +125,11 @@ struct Bf16Launch {
   bool output_independent;  // with operands_static: stores need not wait either
   PeerCopies peers;
   const int* mtile_group;  // grouped GEMM (device array, one group id per 256-row tile of A), or null
+  // Grouped GEMM over groups of any row count (device arrays, one entry per row tile, or null):
+  // first row of the tile and the row where its group ends.  tiles_m then comes from tile_rows.
+  const int* tile_row0;
+  const int* tile_row_end;
+  int tile_rows;
   int l2_a, l2_b;    // L2 eviction hints of the A / BT loads: 0 none, 1 evict-last, 2 evict-first
 };
 void bf16_pick_tile(int M, int N, int K, int clusters, int* tile_n, int* sub_blocks);
@@ -151,6 +156,9 @@ struct Fp4Launch {
   bool output_independent;  // with operands_static: stores need not wait either
   PeerCopies peers;
   const int* mtile_group;  // grouped GEMM (device array, one group id per 256-row tile of A), or null
+  const int* tile_row0;    // as in Bf16Launch; group sizes multiples of 128 (scale bands)
+  const int* tile_row_end;
+  int tile_rows;
   bool block16;      // NVFP4 proper: UE4M3 scales per 16 K (256-wide tiles only)
   float alpha;       // factor on every accumulator (block16 only; 1 otherwise)
   bool uniform_tiles;  // true: full-width tiles only (no narrower tiles at the end of the tile list)

@@ -108,6 +108,8 @@ struct Params {
   PeerCopies peers;     // extra destinations of every stored box (count 0: none)
   int m_rotate;         // the tile walk starts at this 256-row tile (0 unless rows are routed)
   const int* mtile_group;  // grouped GEMM: group of every 256-row tile of A (device), or null
+  const int* tile_row0;    // ragged groups (multiples of 128 rows): first row of every row tile (device), or null
+  const int* tile_row_end; // ... and the row where the tile's group ends
   float alpha;          // factor on every accumulator (block-16 variant: 1 / (global scale A x B))
   int operands_static;  // 1: operands and scales are not written by the previous kernel on the stream
   int l2_a, l2_b;       // L2 eviction hint of the A / B loads: 0 none, 1 evict-last, 2 evict-first
@@ -252,8 +254,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
         fp4_tile<C::kTileN, W0>(t, p.tiles_m, p.tiles_n, p.narrow_tiles_n, p.narrow_col0, p.group_m, tm, col0,
                                 full_width);
         tm = (tm + p.m_rotate) % p.tiles_m;   // routed stores: ranks start at different row blocks
-        const int row_a = tm * 256 + static_cast<int>(rank) * kBlockM;
-        const int band_a = tm * 2 + static_cast<int>(rank);     // 128-row band of SFA
+        const int row_a = (p.tile_row0 != nullptr ? __ldg(p.tile_row0 + tm) : tm * 256) + static_cast<int>(rank) * kBlockM;
+        const int band_a = row_a / 128;                         // 128-row band of SFA
         // Grouped GEMM: B and its scales are stacked [groups * N, ...] (N % 128 == 0); this tile of
         // A belongs to one group and meets that group's N rows.
         const int group_row = p.mtile_group != nullptr ? __ldg(p.mtile_group + tm) * p.N : 0;
@@ -512,6 +514,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
     out.N = n_out;
     out.peers = &p.peers;
     out.alpha = p.alpha;
+    out.row_end = p.M;
     int local = 0;
     int sub1_tiles = 0;   // tiles so far that had a second sub-block
     bool ok = true;
@@ -535,7 +538,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       const int bank = C::kTwoBanks ? (local & 1) : 0;
       const uint32_t use_parity = static_cast<uint32_t>(C::kTwoBanks ? (local >> 1) : local) & 1u;
-      const int row0 = tm * 256 + static_cast<int>(rank) * kBlockM + quarter * 32;
+      const int row0 = (p.tile_row0 != nullptr ? __ldg(p.tile_row0 + tm) : tm * 256) +
+                       static_cast<int>(rank) * kBlockM + quarter * 32;
+      out.row_end = p.tile_row_end != nullptr ? __ldg(p.tile_row_end + tm) : p.M;
       const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
       if constexpr (C::kSubs == 2) {
         // Both warp groups read their half of sub-block 0 and hand it back, then their share of
@@ -653,8 +658,10 @@ int launch_fp4(const Fp4Launch& L, cudaStream_t stream) {
   p.M = L.M;
   p.N = L.N;
   p.K = L.K;
-  p.tiles_m = (L.M + 255) / 256;
+  p.tiles_m = L.tile_row0 != nullptr ? L.tile_rows : (L.M + 255) / 256;
   p.tiles_n = (L.N + C::kTileN - 1) / C::kTileN;
+  p.tile_row0 = L.tile_row0;
+  p.tile_row_end = L.tile_row_end;
   p.narrow_tiles_n = 0;
   p.narrow_col0 = 0;
   if (C::kSubs == 2 && !L.uniform_tiles) {

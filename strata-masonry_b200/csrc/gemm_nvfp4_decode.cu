@@ -1028,6 +1028,7 @@ __device__ __forceinline__ void decode_dual_body(const CUtensorMap& tmap_w, cons
         out.N = p.swiglu ? p.N / 2 : p.N;
         out.peers = &none;
         out.alpha = p.alpha;
+        out.row_end = p.M;
         const uint32_t sbuf = ring_base + static_cast<uint32_t>((warp - 4) * kStoreBufBytes);
         const uint32_t release = mapa_u32(acc_empty_bar(bank), 0);
         const int col0 = (2 * q + group) * 128;

@@ -83,6 +83,20 @@ class Bf16Plan:
             C.byref(self._h), _ptr(a), _ptr(bt_stacked), _ptr(d), m_total, n, k, groups, _ptr(mtile_group), flags))
         return self
 
+    @classmethod
+    def grouped_offsets(cls, a, bt_stacked, d, n: int, k: int, offsets, flags: int = 0):
+        """Grouped GEMM over groups of any row count: `offsets` = groups + 1 row offsets into A / D."""
+        self = cls.__new__(cls)
+        self._lib = capi.lib()
+        self._h = C.c_void_p()
+        offs = [int(x) for x in offsets]
+        self.shape = (offs[-1], n, k)
+        self._keep = (a, bt_stacked, d)
+        arr = (C.c_int * len(offs))(*offs)
+        capi.check(self._lib.smb_bf16_grouped_plan_create_offsets(
+            C.byref(self._h), _ptr(a), _ptr(bt_stacked), _ptr(d), n, k, len(offs) - 1, arr, flags))
+        return self
+
     def tune(self, group_m: int = 0, max_clusters: int = 0) -> None:
         capi.check(self._lib.smb_bf16_plan_tune(self._h, group_m, max_clusters))
 
@@ -267,6 +281,21 @@ class Fp4Plan:
         capi.check(self._lib.smb_fp4_grouped_plan_create(
             C.byref(self._h), _ptr(a), _ptr(sfa), _ptr(b_stacked), _ptr(sfb_stacked), _ptr(d), m_total, n, k,
             groups, _ptr(mtile_group), flags))
+        return self
+
+    @classmethod
+    def grouped_offsets(cls, a, sfa, b_stacked, sfb_stacked, d, n: int, k: int, offsets, flags: int = 0):
+        """Grouped FP4 GEMM over groups that start on multiples of 128 rows; see Bf16Plan.grouped_offsets."""
+        self = cls.__new__(cls)
+        self._lib = capi.lib()
+        self._h = C.c_void_p()
+        offs = [int(x) for x in offsets]
+        self.shape = (offs[-1], n, k)
+        self._keep = (a, sfa, b_stacked, sfb_stacked, d)
+        arr = (C.c_int * len(offs))(*offs)
+        capi.check(self._lib.smb_fp4_grouped_plan_create_offsets(
+            C.byref(self._h), _ptr(a), _ptr(sfa), _ptr(b_stacked), _ptr(sfb_stacked), _ptr(d), n, k,
+            len(offs) - 1, arr, flags))
         return self
 
     @classmethod
