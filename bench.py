@@ -67,10 +67,10 @@ DECODE_WEIGHT_SETS = 4   # rotate weight buffers so that every step streams from
 # reports at run time (smb_*_plan_describe), so that a changed tile choice reads as "no capture"
 # (null) instead of a stale figure; each entry names the summary under profiles/ that holds it.
 NCU_TRAFFIC = {
-    ("bf16_8192", "bf16 tile 256x512 store=tma resident=1"): (970_156_544, "profiles/bf16_gemm_8192.md"),
-    ("nvfp4_8192", "fp4 tile 256x256 store=tma"): (255_423_744, "profiles/nvfp4_gemm_8192.md"),
-    ("decode_m16", "fp4 decode m_pad=16 tile-pairs"): (128_138_240, "profiles/nvfp4_decode_m16.md"),
-    ("decode_m128", "fp4 decode m_pad=128 tile-pairs"): (128_483_072, "profiles/nvfp4_decode_m16.md"),
+    ("bf16_8192", "bf16 tile 256x512 store=tma resident=1"): (1_042_412_800, "profiles/bf16_gemm_8192.md"),
+    ("nvfp4_8192", "fp4 tile 256x384 store=tma"): (214_964_224, "profiles/nvfp4_gemm_8192.md"),
+    ("decode_m16", "fp4 decode m_pad=16 tile-pairs"): (128_733_440, "profiles/nvfp4_decode_m16.md"),
+    ("decode_m128", "fp4 decode m_pad=128 tile-pairs"): (129_742_080, "profiles/nvfp4_decode_m16.md"),
 }
 
 MIN_WARM_S = 0.3
@@ -614,6 +614,10 @@ def time_workload(env: Env, wl: Workload, steps: int | None, warmup: int, extra_
            "value": wl.flops_step / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
            "clocks": sampler.summary(), "kernel": wl.kernel_config}
     rec["roofline"] = roofline_for(env, wl, ms_local / steps, ms_total * 1e-3, burst, steps)
+    if rec["clocks"] and rec["clocks"].get("sm_mhz"):
+        # Launch time in SM clocks at the clock sampled under load: what to compare when two runs
+        # (or two kernels) were held at different clocks by the power cap.
+        rec["roofline"]["mcycles_per_launch_at_sampled_clock"] = (ms_local / steps) * rec["clocks"]["sm_mhz"] * 1e-3
     return rec
 
 

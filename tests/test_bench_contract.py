@@ -110,8 +110,7 @@ def test_traffic_table_points_at_committed_profiles():
         assert workload in bench.WORKLOADS and kernel
         text = (ROOT / source).read_text()
         mb = nbytes / 1e6
-        assert any(f"{mb:.{d}f}" in text for d in (0, 1)) or f"{nbytes:,}".replace(",", " ") in text or str(nbytes) in text, \
-            (workload, source, mb)
+        assert f"{nbytes:,}".replace(",", " ") in text or str(nbytes) in text, (workload, source, mb)
         kind, m, n, k, fill, _ = bench.WORKLOADS[workload]
         algo = (m * k + n * k + m * n) * 2 if kind == "bf16" else n * k // 2 + n * k // 32 + m * k // 2 + m * k // 32 + 2 * m * n
         assert 0.9 <= nbytes / algo <= 3.0, (workload, nbytes / algo)   # re-reads at most triple the minimum
