@@ -743,12 +743,15 @@ int launch_fp4_store(const Fp4Launch& L, cudaStream_t stream) {
 // the round-robin walk of `clusters` clusters over the tile list end soonest.  Cost of a tile in
 // SM cycles, fitted to measurements (8192^3, 14080 x 5120 x 2048, 14080 x 2048 x 4096 at the
 // ~1.57 GHz the kernels run at): a 256-wide K block costs 811 cycles on a 384-wide tile and 556
-// on a 256-wide one (768 and 512 would be the tensor pipe's own time), and every tile pays about
-// 3100-3200 cycles between its last instruction and the first of the next tile (accumulator
-// drain, barrier round trips).
+// on a 256-wide one (768 and 512 would be the tensor pipe's own time).  Between a tile's last
+// instruction and the first of the next the 384-wide kernel (one accumulator set) idles for the
+// tail of the tensor pipe, the accumulator drain and the barrier round trips: 1450 cycles after a
+// full tile (two sub-blocks to read out), 1950 after a 256-wide one (fitted before and after the
+// accumulator hand-over lost its cluster-scope release, which had cost 1750 and 1150 of the
+// former 3200 and 3100).  The 256-wide kernel (two accumulator sets) fits 3100 per tile.
 constexpr double kFp4CyclesPerColumnAndKBlock384 = 811.0 / 384.0;
 constexpr double kFp4CyclesPerColumnAndKBlock256 = 556.0 / 256.0;
-constexpr double kFp4TileOverhead384 = 3200.0, kFp4TileOverhead256 = 3100.0;
+constexpr double kFp4TileOverhead384 = 1450.0, kFp4TileOverheadNarrowIn384 = 1950.0, kFp4TileOverhead256 = 3100.0;
 namespace {
 thread_local double g_last_phase_cost = 0.0;   // written by fp4_split_phases for fp4_pick_tile (same thread, same call)
 }
@@ -762,7 +765,7 @@ void fp4_split_phases(int M, int N, int K, int w0, int w1, int clusters, int* wi
   if (w1 == 0 || clusters < 1) return;
   const double kb = (K + 255) / 256;
   const double cost_wide = kb * kFp4CyclesPerColumnAndKBlock384 * tile_n + kFp4TileOverhead384;
-  const double cost_narrow = kb * kFp4CyclesPerColumnAndKBlock256 * w0 + kFp4TileOverhead256;
+  const double cost_narrow = kb * kFp4CyclesPerColumnAndKBlock256 * w0 + kFp4TileOverheadNarrowIn384;
   double best = -1.0;
   // Only the last few wide tiles of a row are worth trading: beyond that the narrow tiles'
   // extra drains and operand traffic outweigh any balance gained.
@@ -780,7 +783,7 @@ void fp4_split_phases(int M, int N, int K, int w0, int w1, int clusters, int* wi
     const double work = wide * cost_wide + narrow * cost_narrow;
     const double quantum = narrow > 0 ? cost_narrow : cost_wide;
     const double worst = work / clusters + 0.5 * quantum;
-    if (best < 0.0 || worst < best * 0.995) {   // a change of plan must buy at least half a percent
+    if (best < 0.0 || worst < best * 0.998) {   // a change of plan must buy at least a fifth of a percent
       best = worst;
       *wide_tiles_n = a;
       *narrow_tiles_n = b;
@@ -819,6 +822,9 @@ void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1) {
   if (clusters < 1) clusters = 74;
   const long long tiles_m = (M + 255) / 256;
   const long long kb = (K + 255) / 256;
+  // A tile of one K block is all read-out: the two accumulator sets of the 256-wide kernel hide
+  // it behind the next tile (8192 x 8192 x 256: 26.5 against 28.3 us).
+  if (kb <= 1) return;
   const long long waves256 = (tiles_m * ((N + 255) / 256) + clusters - 1) / clusters;
   const long long waves384 = (tiles_m * ((N + 383) / 384) + clusters - 1) / clusters;
   const double cost256 = static_cast<double>(waves256) * (kb * 556.0 + kFp4TileOverhead256);
