@@ -382,39 +382,34 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a,
             else mma_mxf4_ss<2>(acc_base + acc_col, desc_a + 2u * ki, desc_b + 2u * ki, idesc, sfa_t, sfb_t, accum);
           };
           if (C::kSubs == 2 && (kb == 0 || kb == num_kb - 1)) {
-            // Two sub-blocks have a barrier pair each (a narrow tile uses only the first): both are
-            // taken over from the epilogue before the tile's first instruction and handed back
-            // after its last.  (Handing them over one by one, sub-block 0 multiplied again while
-            // sub-block 1 is still being read out, measured no faster: 6068 against 6082 TFLOP/s at
-            // 8192^3, 4396 against 4413 at 14080 x 5120 x 2048.)
-            if (kb == 0) {
-              const long long a0 = prof ? clock64() : 0;
-              for (int h = 0; h < 2 && ok; ++h) {
-                if (h == 1 && !has_sub1) break;
+            // Two sub-blocks have a barrier pair each (a narrow tile uses only the first).  In the
+            // tile's first and last K block the instructions go sub-block by sub-block: the first
+            // K block multiplies into sub-block 0 as soon as the epilogue has read it out, while
+            // sub-block 1 is still being read; the last hands sub-block 0 to the epilogue while
+            // sub-block 1 still multiplies.
+            const bool first = kb == 0, last = kb == num_kb - 1;
+            for (int h = 0; h < 2 && ok; ++h) {
+              if (h == 1 && !has_sub1) break;
+              if (first) {
+                const long long a0 = prof ? clock64() : 0;
                 const uint32_t use = static_cast<uint32_t>(h == 0 ? local : sub1_tiles) & 1u;
                 if (!mbar_wait(acc_empty_bar(h), use ^ 1u)) {
                   report_status(p.status, kDevTimeoutMmaAcc);
                   ok = false;
+                  break;
                 }
+                if (prof) wait_acc += clock64() - a0;
+                tc_fence_after_sync();
               }
-              if (!ok) break;
-              if (prof) wait_acc += clock64() - a0;
-              tc_fence_after_sync();
-            }
-            if (elect_one()) {
+              if (elect_one()) {
 #pragma unroll
-              for (int ki = 0; ki < 4; ++ki) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                  if (h == 0 || has_sub1) issue(h, ki);
-                }
+                for (int ki = 0; ki < 4; ++ki) issue(h, ki);
+                if (last) mma_commit_pair(acc_full_bar(h), 0x3);
               }
-              mma_commit_pair(empty_bar(s), 0x3);
-              if (kb == num_kb - 1) {
-                mma_commit_pair(acc_full_bar(0), 0x3);
-                if (has_sub1) mma_commit_pair(acc_full_bar(1), 0x3);
-              }
+              __syncwarp();
             }
+            if (!ok) break;
+            if (elect_one()) mma_commit_pair(empty_bar(s), 0x3);
           } else if (elect_one()) {
 #pragma unroll
             for (int ki = 0; ki < 4; ++ki) {

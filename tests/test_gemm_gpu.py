@@ -1054,7 +1054,8 @@ def test_fp4_host_context(smb, cuda_device, shape):
 
 
 # ------------------------------------------------------------------------------- mixed tile widths
-@pytest.mark.parametrize("shape", [(1024, 1920, 512), (2048, 2432, 256), (512, 1000, 288), (8192, 8192, 256)])
+@pytest.mark.parametrize("shape", [(1024, 1280, 1024), (2048, 2432, 1024), (1024, 2304, 1024), (512, 1000, 288),
+                                   (8192, 8192, 256)])
 @pytest.mark.parametrize("clusters", [0, 7, 3])
 def test_fp4_full_and_narrow_tiles_in_one_launch(smb, cuda_device, shape, clusters):
     """The 256 x 384 kernel ends its tile list with 256-wide tiles where that evens the clusters
@@ -1087,8 +1088,10 @@ def test_fp4_full_and_narrow_tiles_in_one_launch(smb, cuda_device, shape, cluste
             nn = torch.arange(n, device=d.device).view(1, -1)
             exact = (k * torch.exp2((mm % 5) - 2.0) * torch.exp2((nn % 3) - 1.0)).to(torch.bfloat16)
             assert torch.equal(d[:, :n], exact)
-    if shape == (2048, 2432, 256):
-        assert narrow.value > 0       # this shape does get narrow tiles
+    if shape in ((1024, 1280, 1024), (2048, 2432, 1024)):
+        assert narrow.value == 2      # these shapes do get narrow tiles (2 or 5 full ones before them)
+    if shape == (1024, 2304, 1024):
+        assert (wide.value, narrow.value) == ((4, 3) if clusters == 0 else (6, 0))
 
 
 # ------------------------------------------------------------------------------- every configuration under the verifiers' rule
