@@ -81,6 +81,15 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
   if (flags & SMB_FLAG_TILE_N_128) { L.w0 = 128; L.w1 = 0; }
   if (flags & SMB_FLAG_TILE_N_256) { L.w0 = 256; L.w1 = 0; }
   if (flags & SMB_FLAG_TILE_N_384) { L.w0 = 256; L.w1 = 128; }
+  if (flags & SMB_FLAG_TILE_N_192) {
+    if (!fp4_arun_supports(M, N, K) || block16 || swiglu || mtile_group != nullptr || (flags & SMB_FLAG_DYNAMIC_TILES)) {
+      delete p;
+      return set_error(SMB_ERR_UNSUPPORTED,
+                       "fp4 plan: the A-resident schedule needs K <= 2048, N >= 384 and the plain UE8M0 GEMM");
+    }
+    L.w0 = 192;
+    L.w1 = 0;
+  }
   L.group_m = 0;
   L.max_clusters = 0;
   L.prof = nullptr;
@@ -156,7 +165,7 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
                         kchunks * 512, 1, sf_box, false);
   if (rc == SMB_OK)
     rc = encode_tmap_2d(&L.tmap_sfb, sfb, CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, bands_b, kchunks * 64,
-                        kchunks * 512, tile_n / 128, sf_box, false);
+                        kchunks * 512, (tile_n + 127) / 128, sf_box, false);
   if (rc == SMB_OK) {
     if (L.tma_store)
       rc = encode_tmap_2d(&L.tmap_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, n_out, ldd * 2, 32, 64, true);
@@ -435,8 +444,9 @@ extern "C" int smb_fp4_plan_describe(smb_fp4_plan* plan, char* out, size_t capac
              D.act_src != nullptr ? " bf16-activations" : "");
   } else {
     const Fp4Launch& L = plan->launch;
-    snprintf(out, capacity, "fp4 tile 256x%d store=%s%s", L.w0 + L.w1,
-             L.swiglu ? "swiglu" : (L.tma_store ? "tma" : "plain"), L.block16 ? " block16" : "");
+    snprintf(out, capacity, "fp4 tile 256x%d store=%s%s%s", L.w0 + L.w1,
+             L.swiglu ? "swiglu" : (L.tma_store ? "tma" : "plain"), L.block16 ? " block16" : "",
+             L.w0 == 192 ? " a-resident" : "");
   }
   return SMB_OK;
 }

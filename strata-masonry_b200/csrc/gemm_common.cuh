@@ -167,6 +167,11 @@ struct Fp4Launch {
 void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1);
 void fp4_split_phases(int M, int N, int K, int w0, int w1, int clusters, int* wide_tiles_n, int* narrow_tiles_n);
 int fp4_launch(const Fp4Launch& L, cudaStream_t stream);
+// The A-resident schedule for short K (gemm_nvfp4_arun.cu; L.w0 == 192): whether a shape has it,
+// how a tile row is cut into runs for `clusters` clusters (returns the estimated cycles), launch.
+bool fp4_arun_supports(int M, int N, int K);
+double fp4_arun_split(int M, int N, int K, int clusters, int* chunks, int* run_len);
+int fp4_arun_launch(const Fp4Launch& L, cudaStream_t stream);
 
 // --------------------------------------------------------------------------- nvfp4 decode launch
 struct Fp4DecodeLaunch {

@@ -832,6 +832,7 @@ void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1) {
 }
 
 int fp4_launch(const Fp4Launch& L, cudaStream_t stream) {
+  if (L.w0 == 192 && L.w1 == 0) return fp4_arun_launch(L, stream);
   if (L.w0 == 128 && L.w1 == 0) return launch_fp4_store<128, 0>(L, stream);
   if (L.w0 == 256 && L.w1 == 0) return launch_fp4_store<256, 0>(L, stream);
   if (L.w0 == 256 && L.w1 == 128) return launch_fp4_store<256, 128>(L, stream);

@@ -1053,6 +1053,59 @@ def test_fp4_host_context(smb, cuda_device, shape):
     _check_fp4_full(A, B, d, k)
 
 
+# ------------------------------------------------------------------------------- A-resident schedule
+@pytest.mark.parametrize("shape", [(512, 768, 512), (300, 400, 96), (1000, 1000, 1056), (2048, 2304, 2048),
+                                   (4096, 5120, 2048), (256, 1920, 256)])
+@pytest.mark.parametrize("clusters", [0, 3])
+@pytest.mark.parametrize("store", ["FLAG_NONE", "FLAG_FORCE_PLAIN_STORE"])
+def test_fp4_a_resident_schedule(smb, cuda_device, shape, clusters, store):
+    """The short-K kernel (A panel loaded once per run of 192-column tiles, two accumulator sets):
+    ragged M, N and K, odd tiles (whose B scales start half a band in), several runs per cluster
+    (the A slots are handed over between runs), more and fewer runs than clusters, both store
+    paths; full fp64 check, exact constant fill, padding columns of D untouched, and the same
+    bits as the general kernel."""
+    torch = _torch()
+    m, n, k = shape
+    ldd = n + (24 if store == "FLAG_NONE" else 3)
+    flags = smb.capi.FLAG_TILE_N_192 | smb.capi.FLAG_NO_DECODE | getattr(smb.capi, store)
+    for fill in (5, 3):
+        a, sfa, sfar = _fp4_operand(smb, m, k, fill, 0)
+        b, sfb, sfbr = _fp4_operand(smb, n, k, fill, 1)
+        d = torch.full((m, ldd), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+        plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k, ldd=ldd, flags=flags)
+        if clusters:
+            plan.tune(0, clusters, -1)
+        assert plan.describe().endswith("a-resident")
+        plan.run()
+        plan.run()
+        plan.check()
+        plan.close()
+        assert bool(torch.isnan(d[:, n:].float()).all()), "padding columns were written"
+        if fill == 5:
+            _check_fp4_full((a, sfar), (b, sfbr), d[:, :n].contiguous(), k)
+            d2 = torch.empty((m, n), device=cuda_device, dtype=torch.bfloat16)
+            other = smb.gemm.Fp4Plan(a, sfa, b, sfb, d2, m, n, k, flags=smb.capi.FLAG_TILE_N_256 | smb.capi.FLAG_NO_DECODE)
+            other.run()
+            other.check()
+            other.close()
+            assert torch.equal(d[:, :n], d2)
+        else:
+            mm = torch.arange(m, device=d.device).view(-1, 1)
+            nn = torch.arange(n, device=d.device).view(1, -1)
+            exact = (k * torch.exp2((mm % 5) - 2.0) * torch.exp2((nn % 3) - 1.0)).to(torch.bfloat16)
+            assert torch.equal(d[:, :n], exact)
+
+
+def test_fp4_a_resident_schedule_refuses_what_it_has_no_form_for(smb, cuda_device):
+    torch = _torch()
+    for (m, n, k), extra in (((512, 768, 4096), 0), ((512, 256, 512), 0), ((512, 768, 512), smb.capi.FLAG_SCALE_BLOCK16)):
+        a, sfa, _ = _fp4_operand(smb, m, k, 5, 0)
+        b, sfb, _ = _fp4_operand(smb, n, k, 5, 1)
+        d = torch.empty((m, n), device=cuda_device, dtype=torch.bfloat16)
+        with pytest.raises(smb.capi.SmbError):
+            smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k, flags=smb.capi.FLAG_TILE_N_192 | smb.capi.FLAG_NO_DECODE | extra)
+
+
 # ------------------------------------------------------------------------------- mixed tile widths
 @pytest.mark.parametrize("shape", [(1024, 1280, 1024), (2048, 2432, 1024), (1024, 2304, 1024), (512, 1000, 288),
                                    (8192, 8192, 256)])
