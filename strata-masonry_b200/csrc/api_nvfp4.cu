@@ -123,6 +123,12 @@ int fp4_plan_create_impl(smb_fp4_plan** out, const void* a, const void* sfa, con
     L.w0 = 256;
     L.w1 = 0;
   }
+  // The A-resident schedule has no grouped or queued form (and no block-16 or gated one: those
+  // choose their tile above and below).
+  if (L.w0 == 192 && !(flags & SMB_FLAG_TILE_N_192) && (mtile_group != nullptr || L.dynamic)) {
+    L.w0 = 256;
+    L.w1 = 0;
+  }
   L.swiglu = swiglu;
   if (swiglu) {
     if (!L.tma_store) {

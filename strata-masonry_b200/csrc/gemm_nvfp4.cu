@@ -817,9 +817,14 @@ void fp4_pick_tile(int M, int N, int K, int clusters, int* w0, int* w1) {
   if (clusters < 1) clusters = 74;
   const long long tiles_m = (M + 255) / 256;
   const long long kb = (K + 255) / 256;
-  // A tile of one K block is all read-out: the two accumulator sets of the 256-wide kernel hide
-  // it behind the next tile (8192 x 8192 x 256: 26.5 against 28.3 us).
-  if (kb <= 1) return;
+  // One or two K blocks per tile are all read-out: the A-resident schedule (two accumulator sets,
+  // 192-column tiles) hides it behind the next tile.  8192 x 8192 x 512: 2590-2600 TFLOP/s against
+  // 2410 (256-wide) and 2226 (384-wide); K = 256: 1402-1410 against 1280-1297 and 1223-1231.
+  if (kb <= 2 && fp4_arun_supports(M, N, K)) {
+    *w0 = 192;
+    return;
+  }
+  if (kb <= 1) return;   // ... and where that schedule has no form, the 256-wide tile (26.5 against 28.3 us)
   const long long waves256 = (tiles_m * ((N + 255) / 256) + clusters - 1) / clusters;
   const long long waves384 = (tiles_m * ((N + 383) / 384) + clusters - 1) / clusters;
   const double cost256 = static_cast<double>(waves256) * (kb * 556.0 + kFp4TileOverhead256);
