@@ -125,6 +125,12 @@ uint64_t smb_debug_sf_offset(uint32_t row, uint32_t kblock, uint32_t kblocks);
 void smb_debug_fp4_phases(int M, int N, int K, int clusters, int* wide_tiles_n, int* narrow_tiles_n);
 void smb_debug_fp4_tile(int t, int tiles_m, int wide_tiles_n, int narrow_tiles_n, int group_m, int* tm,
                         int* col0, int* full_width);
+/* The run split of the A-resident FP4 schedule (SMB_FLAG_TILE_N_192): every 256-row tile row is cut
+ * into `chunks` runs of `run_len` tiles of 192 columns (the last run may be shorter); a cluster
+ * loads the row's A panel once per run.  Returns 1 if the shape has that schedule (K <= 2048,
+ * N >= 384), else 0 and leaves the outputs alone.  Counterpart of the reference's same-row runs
+ * (nvfp4/dense_gemm_nvfp4.cu:372-434). */
+int smb_debug_fp4_arun_split(int M, int N, int K, int clusters, int* chunks, int* run_len);
 
 /* ------------------------------------------------------------------------------------
  * Dense BF16 GEMM:  D[M,N] = bf16_rne( sum_k A[M,K] * BT[N,K] ), FP32 accumulate.

@@ -440,6 +440,17 @@ double fp4_arun_split(int M, int N, int K, int clusters, int* chunks, int* run_l
   return best;
 }
 
+}  // namespace smb
+
+// Host-side view of the run split, for known-answer tests (no device needed).
+extern "C" int smb_debug_fp4_arun_split(int M, int N, int K, int clusters, int* chunks, int* run_len) {
+  if (!smb::fp4_arun_supports(M, N, K)) return 0;
+  smb::fp4_arun_split(M, N, K, clusters, chunks, run_len);
+  return 1;
+}
+
+namespace smb {
+
 namespace {
 
 template <bool kTmaStore>

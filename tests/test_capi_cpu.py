@@ -273,3 +273,25 @@ def test_fp4_tile_list_covers_every_column_once(smb, shape):
     wide, narrow = C.c_int(), C.c_int()
     lib.smb_debug_fp4_phases(8192, 8192, 8192, 74, C.byref(wide), C.byref(narrow))
     assert narrow.value >= 2 and wide.value * 384 + narrow.value * 256 == 8192
+
+
+def test_fp4_a_resident_run_split_covers_every_tile_once(smb):
+    """Runs of the A-resident schedule: chunks x run_len covers the tile row, no run is empty, and
+    the shapes outside its range are refused (K > 2048, N < 384)."""
+    lib = smb.capi.lib()
+    for (m, n, k) in [(512, 768, 512), (14080, 5120, 2048), (30720, 5120, 2048), (8192, 8192, 256), (300, 400, 96),
+                      (256, 100000, 1024)]:
+        for clusters in (74, 7, 1):
+            chunks, run_len = C.c_int(-1), C.c_int(-1)
+            assert lib.smb_debug_fp4_arun_split(m, n, k, clusters, C.byref(chunks), C.byref(run_len)) == 1
+            tiles_n = (n + 191) // 192
+            assert chunks.value >= 1 and run_len.value >= 1
+            assert chunks.value * run_len.value >= tiles_n
+            assert (chunks.value - 1) * run_len.value < tiles_n
+    chunks, run_len = C.c_int(-1), C.c_int(-1)
+    assert lib.smb_debug_fp4_arun_split(512, 768, 4096, 74, C.byref(chunks), C.byref(run_len)) == 0
+    assert lib.smb_debug_fp4_arun_split(512, 256, 512, 74, C.byref(chunks), C.byref(run_len)) == 0
+    assert chunks.value == -1
+    # One cluster: nothing to balance, one run per tile row.
+    assert lib.smb_debug_fp4_arun_split(2048, 3840, 2048, 1, C.byref(chunks), C.byref(run_len)) == 1
+    assert (chunks.value, run_len.value) == (1, 20)
