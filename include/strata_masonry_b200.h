@@ -429,6 +429,9 @@ int smb_fp4_host_ctx_create_sharded(smb_fp4_host_ctx** ctx, int M, int n_local, 
 #define SMB_FLAG_TILE_N_256 8u        /* force 256 x 256 tiles, two accumulator banks */
 #define SMB_FLAG_TILE_N_512 16u       /* force 256 x 512 tiles, one accumulator set */
 #define SMB_FLAG_TILE_N_384 32u       /* FP4 only: force 256 x 384 tiles */
+#define SMB_FLAG_STREAM_K 524288u     /* BF16 only: 256 x 512 tiles with their K loops cut where the clusters' shares
+                                         end, partial sums through a workspace the plan owns (chosen by itself where
+                                         whole tiles would leave much of the last wave idle) */
 #define SMB_FLAG_TILE_N_192 262144u   /* FP4 only: force the A-resident schedule (256 x 192 tiles, two accumulator
                                          sets, K <= 2048, N >= 384); SMB_ERR_UNSUPPORTED where it has no form */
  /* Hand tiles out through the hardware work queue (clusterlaunchcontrol.try_cancel, the

@@ -29,7 +29,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
           "--expt-relaxed-constexpr"]
 
-LIB_SOURCES = ["runtime.cu", "fills.cu", "gemm_bf16.cu", "api_bf16.cu", "gemm_nvfp4.cu",
+LIB_SOURCES = ["runtime.cu", "fills.cu", "gemm_bf16.cu", "gemm_bf16_streamk.cu", "api_bf16.cu", "gemm_nvfp4.cu",
                "gemm_nvfp4_arun.cu", "gemm_nvfp4_decode.cu", "api_nvfp4.cu", "peer.cu", "gather.cu", "selftest.cu"]
 DRIVERS = {"kernel_sm100a_dense_gemm_bf16": "driver_bf16.cu",
            "kernel_sm100a_dense_gemm_nvfp4": "driver_nvfp4.cu"}

@@ -40,6 +40,7 @@ FLAG_ACT_QUANT_PER_CTA = 32768
 FLAG_ACT_QUANT_CHAINED = 65536
 FLAG_ACT_QUANT_SHARED = 131072
 FLAG_TILE_N_192 = 262144
+FLAG_STREAM_K = 524288
 
 _vp = C.c_void_p
 _i = C.c_int

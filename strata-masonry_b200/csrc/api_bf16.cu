@@ -21,6 +21,7 @@ struct smb_bf16_plan {
   int* status_dev;
   bool owns_status;
   int* tile_table_dev;   // ragged grouped plans: [3][tiles] = first row, end of group, group id
+  unsigned launches;     // stream-K plans: launches so far (the flags carry the launch number)
   int device;   // the device that was current at creation: pointers and status word live there
 };
 
@@ -121,6 +122,27 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
     L.tile_n = 256;   // 64 output columns per store box = 128 accumulator columns per warp
   }
   p->status_dev = nullptr;
+  p->launches = 0;
+  L.streamk_partial = nullptr;
+  L.streamk_flags = nullptr;
+  L.streamk_clusters = 0;
+  L.streamk_epoch = 0;
+  // Whole tiles, or K loops cut where the clusters' shares end: the second where the tiles leave
+  // much of the last wave idle (or on request), for the plain GEMM with 256 x 512 tiles.
+  bool streamk = (flags & SMB_FLAG_STREAM_K) != 0;
+  const bool streamk_possible = L.tile_n == 256 && L.tma_store && !swiglu && mtile_group == nullptr &&
+                                !L.dynamic && N > 256;
+  if (streamk && !streamk_possible) {
+    delete p;
+    return set_error(SMB_ERR_UNSUPPORTED,
+                     "plan: the stream-K walk needs N > 256, an aligned D and the plain, ungrouped GEMM");
+  }
+  if (!streamk && streamk_possible && L.sub_blocks == 2 && !(flags & SMB_FLAG_TILE_N_512))
+    streamk = bf16_streamk_pays(M, N, K, device_cluster_slots());
+  if (const char* env = getenv("SMB_TUNE_BF16_STREAMK")) {   // tuning sweeps: 0 = never
+    if (env[0] == '0' && !(flags & SMB_FLAG_STREAM_K)) streamk = false;
+  }
+  if (streamk) L.sub_blocks = 2;
 
   int rc = encode_tmap_2d(&L.tmap_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda * 2, 128, 64, true);
   if (rc == SMB_OK)
@@ -141,8 +163,18 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
   } else if (rc == SMB_OK) {
     p->status_dev = shared_status;
   }
+  if (rc == SMB_OK && streamk) {
+    const int slots = device_cluster_slots() > 0 ? device_cluster_slots() : 74;
+    cudaError_t e = cudaMalloc(&L.streamk_partial, bf16_streamk_workspace_bytes(slots));
+    if (e == cudaSuccess) e = cudaMalloc(&L.streamk_flags, bf16_streamk_flag_bytes(slots));
+    if (e == cudaSuccess) e = cudaMemset(L.streamk_flags, 0, bf16_streamk_flag_bytes(slots));
+    if (e != cudaSuccess) rc = set_cuda_error(e, "plan: stream-K workspace allocation");
+    L.streamk_clusters = slots;
+  }
   if (rc != SMB_OK) {
     if (p->status_dev && p->owns_status) cudaFree(p->status_dev);
+    if (L.streamk_partial) cudaFree(L.streamk_partial);
+    if (L.streamk_flags) cudaFree(L.streamk_flags);
     delete p;
     return rc;
   }
@@ -272,7 +304,14 @@ extern "C" int smb_bf16_plan_run(smb_bf16_plan* plan, void* stream) {
   if (cudaGetDevice(&device) != cudaSuccess || device != plan->device)
     return set_error(SMB_ERR_INVALID, "plan: created on device %d, run with device %d current", plan->device,
                      device);
-  return bf16_launch(plan->launch, static_cast<cudaStream_t>(stream));
+  Bf16Launch& L = plan->launch;
+  // Peer copies and row routes belong to the whole-tile kernel's epilogue.
+  if (L.streamk_partial != nullptr && L.peers.count == 0 && L.peers.route_rows == 0) {
+    if (++plan->launches == 0) ++plan->launches;   // 0 is what the cleared flags hold
+    L.streamk_epoch = plan->launches;
+    return bf16_streamk_launch(L, static_cast<cudaStream_t>(stream));
+  }
+  return bf16_launch(L, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int smb_bf16_plan_check(smb_bf16_plan* plan, void* stream) {
@@ -295,8 +334,9 @@ extern "C" int smb_bf16_plan_describe(smb_bf16_plan* plan, char* out, size_t cap
     return set_error(SMB_ERR_INVALID, "plan describe: null argument");
   const Bf16Launch& L = plan->launch;
   const bool narrow_pair = L.tile_n <= 128 && L.operands_static && !L.swiglu;
-  snprintf(out, capacity, "bf16 tile 256x%d store=%s resident=%d", L.tile_n * L.sub_blocks,
-           L.swiglu ? "swiglu" : (L.tma_store ? "tma" : "plain"), narrow_pair ? 2 : 1);
+  const bool streamk = L.streamk_partial != nullptr && L.peers.count == 0 && L.peers.route_rows == 0;
+  snprintf(out, capacity, "bf16 tile 256x%d store=%s resident=%d%s", L.tile_n * L.sub_blocks,
+           L.swiglu ? "swiglu" : (L.tma_store ? "tma" : "plain"), narrow_pair ? 2 : 1, streamk ? " stream-k" : "");
   return SMB_OK;
 }
 
@@ -309,6 +349,8 @@ extern "C" int smb_bf16_plan_destroy(smb_bf16_plan* plan) {
   if (plan == nullptr) return SMB_OK;
   if (plan->status_dev && plan->owns_status) cudaFree(plan->status_dev);
   if (plan->tile_table_dev) cudaFree(plan->tile_table_dev);
+  if (plan->launch.streamk_partial) cudaFree(plan->launch.streamk_partial);
+  if (plan->launch.streamk_flags) cudaFree(plan->launch.streamk_flags);
   delete plan;
   return SMB_OK;
 }

@@ -131,11 +131,30 @@ struct Bf16Launch {
   const int* tile_row_end;
   int tile_rows;
   int l2_a, l2_b;    // L2 eviction hints of the A / BT loads: 0 none, 1 evict-last, 2 evict-first
+  // Stream-K walk (gemm_bf16_streamk.cu): workspace for partial sums and flags (device, owned by
+  // the plan), the number of clusters they have slots for, and this launch's number.  Null: whole tiles.
+  float* streamk_partial;
+  unsigned* streamk_flags;
+  int streamk_clusters;
+  unsigned streamk_epoch;
 };
 void bf16_pick_tile(int M, int N, int K, int clusters, int* tile_n, int* sub_blocks);
 // Number of 2-CTA clusters that can run at once on the current device (SM count / 2), 0 if unknown.
 int device_cluster_slots();
 int bf16_launch(const Bf16Launch& L, cudaStream_t stream);
+// The same GEMM with the tiles' K loops cut where the clusters' shares end (256 x 512 tiles, aligned
+// plain store): whether it pays for a shape, what it needs, launch.
+// The cut of the last wave: `full_waves` waves of whole tiles, then `rem_tiles` tiles whose K
+// blocks [0, cut) go to one cluster each and [cut, end) to the spare clusters, `tails_per_cluster`
+// tiles each (parts == 0), or which are cut into parts + 1 equal slices (parts > 0).
+struct StreamKWalk {
+  int full_waves, rem_tiles, cut, tails_per_cluster, parts;
+};
+double bf16_streamk_plan(long long tiles, int kb, int clusters, StreamKWalk* w);
+bool bf16_streamk_pays(int M, int N, int K, int clusters);
+size_t bf16_streamk_workspace_bytes(int clusters);
+size_t bf16_streamk_flag_bytes(int clusters);
+int bf16_streamk_launch(const Bf16Launch& L, cudaStream_t stream);
 
 // --------------------------------------------------------------------------- nvfp4 launch
 struct Fp4Launch {

@@ -1053,6 +1053,59 @@ def test_fp4_host_context(smb, cuda_device, shape):
     _check_fp4_full(A, B, d, k)
 
 
+# ------------------------------------------------------------------------------- stream-K walk (BF16)
+@pytest.mark.parametrize("case", [((512, 1024, 4096), 3), ((256, 512, 8192), 5), ((1000, 1104, 2080), 7),
+                                   ((2048, 2048, 1024), 0), ((8192, 1024, 8192), 0), ((300, 600, 1024), 74)])
+def test_bf16_stream_k_walk(smb, oracle, cuda_device, case):
+    """K loops of the 256 x 512 tiles cut where the clusters' shares end: tiles split over two
+    clusters, a tile split over five, whole tiles in between, ragged edges, more clusters than
+    tiles; three launches in a row on one plan (the flags carry the launch number); full fp64
+    check, within bf16 rounding of the whole-tile kernel, padding columns untouched."""
+    torch = _torch()
+    (m, n, k), clusters = case
+    ldd = n + 24
+    a = torch.empty(m, k, device=cuda_device, dtype=torch.bfloat16)
+    bt = torch.empty(n, k, device=cuda_device, dtype=torch.bfloat16)
+    smb.gemm.bf16_operands_device(a, bt, m, n, k, 5)
+    d = torch.full((m, ldd), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    plan = smb.gemm.Bf16Plan(a, bt, d, m, n, k, ldd=ldd, flags=smb.capi.FLAG_STREAM_K)
+    plan.tune(0, clusters)
+    assert plan.describe().endswith("stream-k")
+    for _ in range(3):
+        d[:, :n] = float("nan")
+        plan.run()
+        plan.check()
+        assert bool(torch.isnan(d[:, n:].float()).all()), "padding columns were written"
+        _check_bf16_full(oracle, a, bt, d, n, k)
+    plan.close()
+    d2 = torch.empty((m, n), device=cuda_device, dtype=torch.bfloat16)
+    whole = smb.gemm.Bf16Plan(a, bt, d2, m, n, k, flags=smb.capi.FLAG_TILE_N_512)
+    whole.run()
+    whole.check()
+    assert not whole.describe().endswith("stream-k")
+    whole.close()
+    diff = (d[:, :n].float() - d2.float()).abs()
+    assert float((diff / d2.float().abs().clamp_min(1e-3)).max()) <= 2.0 ** -6   # a bf16 rounding step or two
+
+
+def test_bf16_stream_k_is_refused_where_it_has_no_form(smb, cuda_device):
+    torch = _torch()
+    a = torch.empty(1024, 4096, device=cuda_device, dtype=torch.bfloat16)
+    bt = torch.empty(256, 4096, device=cuda_device, dtype=torch.bfloat16)
+    d = torch.empty(1024, 256, device=cuda_device, dtype=torch.bfloat16)
+    with pytest.raises(smb.capi.SmbError):
+        smb.gemm.Bf16Plan(a, bt, d, 1024, 256, 4096, flags=smb.capi.FLAG_STREAM_K)
+    bt = torch.empty(1024, 4096, device=cuda_device, dtype=torch.bfloat16)
+    d = torch.empty(1024, 1024 + 3, device=cuda_device, dtype=torch.bfloat16)
+    with pytest.raises(smb.capi.SmbError):
+        smb.gemm.Bf16Plan(a, bt, d, 1024, 1024, 4096, ldd=1027, flags=smb.capi.FLAG_STREAM_K)
+    # Left to itself the plan keeps whole tiles for the column shards of 8192^3.
+    d = torch.empty(1024, 1024, device=cuda_device, dtype=torch.bfloat16)
+    plan = smb.gemm.Bf16Plan(a, bt, d, 1024, 1024, 4096)
+    assert not plan.describe().endswith("stream-k")
+    plan.close()
+
+
 # ------------------------------------------------------------------------------- A-resident schedule
 @pytest.mark.parametrize("shape", [(512, 768, 512), (300, 400, 96), (1000, 1000, 1056), (2048, 2304, 2048),
                                    (4096, 5120, 2048), (256, 1920, 256)])
