@@ -69,6 +69,7 @@ DECODE_WEIGHT_SETS = 4   # rotate weight buffers so that every step streams from
 NCU_TRAFFIC = {
     ("bf16_8192", "bf16 tile 256x512 store=tma resident=1"): (1_067_447_040, "profiles/bf16_gemm_8192.md"),
     ("nvfp4_8192", "fp4 tile 256x384 store=tma"): (205_597_184, "profiles/nvfp4_gemm_8192.md"),
+    ("bf16_large", "bf16 tile 256x512 store=tma resident=1"): (42_861_576_960, "profiles/bf16_gemm_32768x57344x8192.md"),
     ("decode_m16", "fp4 decode m_pad=16 tile-pairs"): (128_733_440, "profiles/nvfp4_decode_m16.md"),
     ("decode_m64", "fp4 decode m_pad=64 tile-pairs"): (128_104_704, "profiles/nvfp4_decode_m16.md"),
     ("decode_m128", "fp4 decode m_pad=128 tile-pairs"): (129_742_080, "profiles/nvfp4_decode_m16.md"),

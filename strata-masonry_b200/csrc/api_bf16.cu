@@ -90,7 +90,11 @@ int bf16_plan_create_impl(smb_bf16_plan** out, const void* a, const void* bt, vo
   if (flags & SMB_FLAG_TILE_N_64) { L.tile_n = 64; L.sub_blocks = 1; }
   L.group_m = 0;
   L.max_clusters = 0;
-  L.l2_a = L.l2_b = 1;   // evict-last on both operands: +1-2 % sustained on 8192^3 over no hint
+  // Evict-last on both operands: +1-2 % sustained on 8192^3 over no hint.  A BT too large to stay
+  // in L2 between raster groups (above 256 MB) gets no hint: marked evict-last it pushes the A
+  // panel of the group out (32768 x 57344 x 8192: 1344 with, 1382-1417 without, TFLOP/s sustained).
+  L.l2_a = 1;
+  L.l2_b = (static_cast<long long>(groups) * N * K * 2 > (256ll << 20)) ? 0 : 1;
   if (const char* env = getenv("SMB_TUNE_BF16_L2")) {   // tuning sweeps: "<a><b>", digits 0..2
     if (env[0] >= '0' && env[0] <= '2' && env[1] >= '0' && env[1] <= '2') {
       L.l2_a = env[0] - '0';

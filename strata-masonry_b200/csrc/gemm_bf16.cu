@@ -430,7 +430,9 @@ int launch_bf16(const Bf16Launch& L, cudaStream_t stream) {
   p.tiles_n = (L.N + C::kTileN - 1) / C::kTileN;
   p.tile_row0 = L.tile_row0;
   p.tile_row_end = L.tile_row_end;
-  p.group_m = L.group_m > 0 ? L.group_m : raster_group_rows(p.tiles_m, static_cast<long long>(L.K) * 2);
+  p.group_m = L.group_m > 0 ? L.group_m
+                            : raster_group_rows(p.tiles_m, static_cast<long long>(L.K) * 2,
+                                                static_cast<long long>(L.N) * L.K * 2);
   p.ldd = L.ldd;
   p.d_ptr = static_cast<uint16_t*>(L.d);
   p.status = L.status;

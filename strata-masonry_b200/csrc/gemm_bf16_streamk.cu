@@ -511,7 +511,9 @@ int bf16_streamk_launch(const Bf16Launch& L, cudaStream_t stream) {
   p.K = L.K;
   p.tiles_m = (L.M + 255) / 256;
   p.tiles_n = (L.N + bf16s::kTileN - 1) / bf16s::kTileN;
-  p.group_m = L.group_m > 0 ? L.group_m : raster_group_rows(p.tiles_m, static_cast<long long>(L.K) * 2);
+  p.group_m = L.group_m > 0 ? L.group_m
+                            : raster_group_rows(p.tiles_m, static_cast<long long>(L.K) * 2,
+                                                static_cast<long long>(L.N) * L.K * 2);
   p.ldd = L.ldd;
   p.d_ptr = static_cast<uint16_t*>(L.d);
   p.status = L.status;

@@ -57,8 +57,14 @@ __host__ __device__ inline void tile_coords(int t, int tiles_m, int tiles_n, int
 //   BF16 8192 x 8192 x 4096: 8 1600, 16 1614, 32 1572;  30720 x 2048 x 4096 (256 x 256 tiles): 8 1565,
 //   16 1557, 32 1390;  14080 x 5120 x 2048: 8 1552, 16 1542, 32 1537.
 // `row_bytes` = bytes of one row of A.  BF16: 32 MB of A per group, kept between 8 and 16 rows.
-inline int raster_group_rows(int tiles_m, long long row_bytes) {
+// `b_bytes` = size of the other operand: one that cannot stay in L2 between groups anyway (above
+// 256 MB) is read from DRAM once per group, so the groups are made as tall as L2 has room for the
+// A panel (16 rows at K = 8192: 64 MB).  32768 x 57344 x 8192, groups of 8 / 16 / 24 rows, sustained
+// TFLOP/s: 1383-1392 / 1397-1417 / 1348-1349 (DRAM reads per launch at 8 rows with both operands
+// marked evict-last: 58.5 GB, eleven times the operands).
+inline int raster_group_rows(int tiles_m, long long row_bytes, long long b_bytes = 0) {
   long long rows = (32ll << 20) / (256 * (row_bytes > 0 ? row_bytes : 1));
+  if (b_bytes > (256ll << 20)) rows = (64ll << 20) / (256 * (row_bytes > 0 ? row_bytes : 1));
   if (rows < 8) rows = 8;
   if (rows > 16) rows = 16;
   if (rows > tiles_m) rows = tiles_m;
