@@ -131,6 +131,12 @@ void smb_debug_fp4_tile(int t, int tiles_m, int wide_tiles_n, int narrow_tiles_n
  * N >= 384), else 0 and leaves the outputs alone.  Counterpart of the reference's same-row runs
  * (nvfp4/dense_gemm_nvfp4.cu:372-434). */
 int smb_debug_fp4_arun_split(int M, int N, int K, int clusters, int* chunks, int* run_len);
+/* The cut of the last wave of the BF16 walk of SMB_FLAG_STREAM_K for `tiles` tiles of `kb` K blocks
+ * on `clusters` clusters: out[0] whole-tile waves, out[1] tiles of the last wave, out[2] first K
+ * block of the spare clusters' parts, out[3] such parts per spare cluster, out[4] equal K slices
+ * per tile beyond the first (0: the form of out[2], out[3]).  Returns 1 if bf16_streamk_pays would
+ * choose the walk for an M x N x K with that many tiles, else 0. */
+int smb_debug_bf16_streamk_plan(long long tiles, int kb, int clusters, int* out);
 
 /* ------------------------------------------------------------------------------------
  * Dense BF16 GEMM:  D[M,N] = bf16_rne( sum_k A[M,K] * BT[N,K] ), FP32 accumulate.

@@ -70,6 +70,7 @@ DECLARED = [
     ("smb_debug_fp4_phases", None, [_i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
     ("smb_debug_fp4_tile", None, [_i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     ("smb_debug_fp4_arun_split", _i, [_i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
+    ("smb_debug_bf16_streamk_plan", _i, [C.c_longlong, _i, _i, C.POINTER(_i)]),
     ("smb_bf16_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, C.c_uint]),
     ("smb_bf16_grouped_plan_create", _i, [C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, _i, _vp, C.c_uint]),
     ("smb_bf16_grouped_plan_create_offsets", _i, [C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, C.POINTER(_i), C.c_uint]),

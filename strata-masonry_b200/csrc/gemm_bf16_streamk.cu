@@ -475,6 +475,24 @@ bool bf16_streamk_pays(int M, int N, int K, int clusters) {
   return (w.parts > 0 || w.cut < kb) && cut < whole * 0.97;
 }
 
+}  // namespace smb
+
+// Host-side view of the cut, for known-answer tests (no device needed).
+extern "C" int smb_debug_bf16_streamk_plan(long long tiles, int kb, int clusters, int* out) {
+  if (out == nullptr || tiles < 1 || kb < 1 || clusters < 1) return 0;
+  smb::StreamKWalk w;
+  const double cut = smb::bf16_streamk_plan(tiles, kb, clusters, &w);
+  out[0] = w.full_waves;
+  out[1] = w.rem_tiles;
+  out[2] = w.cut;
+  out[3] = w.tails_per_cluster;
+  out[4] = w.parts;
+  const double whole = static_cast<double>((tiles + clusters - 1) / clusters) * kb;
+  return ((w.parts > 0 || w.cut < kb) && kb >= 16 && cut < whole * 0.97) ? 1 : 0;
+}
+
+namespace smb {
+
 int bf16_streamk_launch(const Bf16Launch& L, cudaStream_t stream) {
   auto kernel = bf16s::gemm_bf16_streamk_kernel;
   static thread_local int configured_device = -1;

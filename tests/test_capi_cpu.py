@@ -295,3 +295,36 @@ def test_fp4_a_resident_run_split_covers_every_tile_once(smb):
     # One cluster: nothing to balance, one run per tile row.
     assert lib.smb_debug_fp4_arun_split(2048, 3840, 2048, 1, C.byref(chunks), C.byref(run_len)) == 1
     assert (chunks.value, run_len.value) == (1, 20)
+
+
+def test_bf16_last_wave_cut_covers_every_k_block_once(smb):
+    """The walk of SMB_FLAG_STREAM_K: whole-tile waves, then the last wave either as [0, cut) on one
+    cluster per tile plus [cut, end) on the spare clusters, or as equal K slices.  Every K block of
+    every tile is covered exactly once, no cluster gets more than one owner part, and the choice
+    for the column shards of 8192^3 is what was measured to pay (2 GPUs) or not (4, 8 GPUs, 1 GPU)."""
+    lib = smb.capi.lib()
+    out = (C.c_int * 5)()
+    for tiles, kb, clusters in [(64, 128, 74), (128, 128, 74), (256, 128, 74), (512, 128, 74), (1792, 128, 74),
+                                (4, 64, 3), (1, 128, 5), (12, 33, 7), (32, 16, 74), (4, 16, 74), (74, 128, 74), (75, 128, 74)]:
+        lib.smb_debug_bf16_streamk_plan(tiles, kb, clusters, out)
+        full, rem, cut, tails, parts = list(out)
+        assert full == tiles // clusters and rem == tiles % clusters
+        spare = clusters - rem
+        covered = 0
+        if rem:
+            if parts > 0:
+                assert spare >= rem * parts and parts <= 7
+                bounds = [kb * i // (parts + 1) for i in range(parts + 2)]
+                assert bounds[0] == 0 and bounds[-1] == kb and all(b1 > b0 for b0, b1 in zip(bounds, bounds[1:]))
+                covered = rem * kb
+            elif cut < kb:
+                assert 1 <= cut and tails >= 1 and spare * tails >= rem      # every tile's tail has a cluster
+                covered = rem * cut + rem * (kb - cut)
+            else:
+                covered = rem * kb                                             # left whole
+        assert covered == rem * kb
+    assert lib.smb_debug_bf16_streamk_plan(256, 128, 74, out) == 1    # 8192 x 4096 x 8192: one long slice per spare cluster
+    assert list(out) == [3, 34, 128, 0, 1]
+    assert lib.smb_debug_bf16_streamk_plan(64, 128, 74, out) == 0     # 8192 x 1024 x 8192: seven tails per spare cluster
+    assert lib.smb_debug_bf16_streamk_plan(128, 128, 74, out) == 0
+    assert lib.smb_debug_bf16_streamk_plan(512, 128, 74, out) == 0
