@@ -1295,3 +1295,68 @@ def test_fp4_gated_epilogue_on_the_384_tile(smb, cuda_device):
         acc = _dequant(a, sfar) @ _dequant(b, sfbr).t()
         _check_swiglu_torch(acc, d, k)
     plan.close()
+
+
+# ------------------------------------------------------------------------------- seeded random shapes
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_fp4_schedules_agree_bit_for_bit_on_random_shapes(smb, cuda_device, seed):
+    """The three FP4 schedules (256-wide tiles, the 384-wide tile list, the A-resident runs where K
+    allows) accumulate every output element over K in the same order: on seeded random shapes,
+    cluster counts and store paths their outputs are the same bits, and padding columns stay
+    untouched."""
+    import random
+    torch = _torch()
+    capi = smb.capi
+    rng = random.Random(seed)
+    for _ in range(25):
+        m = rng.choice([1, 17, 129, 256, 257, 300, 512, 1000, 2048, 3000])
+        n = rng.choice([384, 385, 400, 577, 768, 1000, 1152, 2048, 2432])
+        k = 32 * rng.randint(1, 96)
+        clusters = rng.choice([0, 0, 1, 3, 7, 20, 74])
+        store = rng.choice([0, capi.FLAG_FORCE_PLAIN_STORE])
+        ldd = n + (rng.choice([0, 8, 24]) if store == 0 else rng.choice([0, 1, 3]))
+        a, sfa, _ = _fp4_operand(smb, m, k, 5, 0)
+        b, sfb, _ = _fp4_operand(smb, n, k, 5, 1)
+        base = torch.empty((m, n), device=cuda_device, dtype=torch.bfloat16)
+        plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, base, m, n, k, flags=capi.FLAG_TILE_N_256 | capi.FLAG_NO_DECODE)
+        plan.run()
+        plan.check()
+        plan.close()
+        variants = [capi.FLAG_TILE_N_384] + ([capi.FLAG_TILE_N_192] if k <= 2048 else [])
+        for tile in variants:
+            d = torch.full((m, ldd), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+            plan = smb.gemm.Fp4Plan(a, sfa, b, sfb, d, m, n, k, ldd=ldd, flags=tile | capi.FLAG_NO_DECODE | store)
+            plan.tune(0, clusters, -1)
+            plan.run()
+            plan.run()
+            plan.check()
+            plan.close()
+            assert torch.equal(d[:, :n], base), (m, n, k, clusters, store, ldd, tile)
+            assert ldd == n or bool(torch.isnan(d[:, n:].float()).all()), (m, n, k, ldd, tile)
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_bf16_last_wave_cut_on_random_shapes(smb, oracle, cuda_device, seed):
+    """SMB_FLAG_STREAM_K on seeded random shapes and cluster counts, three launches per plan: full
+    fp64 check each time."""
+    import random
+    torch = _torch()
+    rng = random.Random(seed)
+    for _ in range(12):
+        m = rng.choice([256, 300, 512, 1000, 2048])
+        n = rng.choice([264, 512, 520, 1024, 1104, 2048, 3000])
+        k = 64 * rng.randint(1, 64) + rng.choice([0, 0, 8, 32])
+        clusters = rng.choice([0, 0, 1, 2, 3, 5, 7, 20, 37, 74])
+        ldd = (n + rng.choice([0, 8, 24]) + 7) // 8 * 8
+        a = torch.empty(m, k, device=cuda_device, dtype=torch.bfloat16)
+        bt = torch.empty(n, k, device=cuda_device, dtype=torch.bfloat16)
+        smb.gemm.bf16_operands_device(a, bt, m, n, k, 5)
+        d = torch.full((m, ldd), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+        plan = smb.gemm.Bf16Plan(a, bt, d, m, n, k, ldd=ldd, flags=smb.capi.FLAG_STREAM_K)
+        plan.tune(0, clusters)
+        for _ in range(3):
+            plan.run()
+        plan.check()
+        plan.close()
+        assert ldd == n or bool(torch.isnan(d[:, n:].float()).all()), (m, n, k, clusters, ldd)
+        _check_bf16_full(oracle, a, bt, d, n, k)
